@@ -1,0 +1,282 @@
+/* C ABI of the B200 (sm_100a) Qwen4 mixture-of-experts layer.
+ *
+ * libqwen4_moe_b200.so exports two groups of symbols:
+ *
+ *  1. The entry points of picoforge's MoE operator (picoforge src/qwen4_moe.h:13-27 and
+ *     the two private helpers its tests and GPU glue link, src/qwen4_moe_internal.h:15,94),
+ *     byte-compatible: same names, same by-value view structs, same status codes, same
+ *     "outputs untouched on error" behaviour.  picoforge's forward graph
+ *     (src/qwen4_forward.c:174-187, :365) links against them unchanged.
+ *
+ *  2. Additive `qw4cu_*` entry points that the reference does not have: device-pointer
+ *     forward (inputs already in HBM), bit-exact weight decode and grouping probes for
+ *     parity tests, and timing / memory plumbing for the benchmark.
+ *
+ * Plain C11; no CUDA or C++ types cross this boundary.  All strides and capacities are
+ * BYTES, all dimensions are element counts, the last axis is contiguous.
+ */
+#ifndef QWEN4_MOE_B200_H
+#define QWEN4_MOE_B200_H
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------
+ * Types shared with the engine.  Layouts follow picoforge src/qwen4_types.h:14-46,75-80,
+ * src/qwen4_packed.h:6-11 and src/qwen4_moe.h:7-11.  When this header is included after
+ * picoforge's own headers, define QWEN4_MOE_B200_NO_TYPES to skip them.
+ * ---------------------------------------------------------------------------------- */
+#ifndef QWEN4_MOE_B200_NO_TYPES
+#define QWEN4_MAX_RANK 4u
+
+typedef enum {
+    QW4_OK = 0,
+    QW4_INVALID_ARGUMENT = 1,
+    QW4_MISSING = 2,
+    QW4_TYPE = 3,
+    QW4_RANGE = 4,
+    QW4_SHAPE = 5,
+    QW4_STRIDE = 6,
+    QW4_FORMAT = 7,
+    QW4_UNSUPPORTED = 8,
+    QW4_OVERFLOW = 9,
+    QW4_CAPACITY = 10,
+    QW4_OOM = 11,
+    QW4_OWNER = 12,
+    QW4_BUSY = 13,
+    QW4_STALE = 14,
+    QW4_BAD_STATE = 15,
+    QW4_NONFINITE = 16,
+    QW4_IO = 17,
+    QW4_EOF = 18,
+    QW4_CANCELLED = 19,
+    QW4_GPU_ERROR = 20
+} Qwen4Status;
+
+typedef struct {
+    Qwen4Status code;
+    int os_errno;
+    uint64_t file_offset;
+    uint64_t row;                 /* token row of a nonfinite router logit */
+    size_t requested_bytes;
+    size_t completed_bytes;
+    char subject[128];
+    char detail[256];
+} Qwen4Error;
+
+typedef struct {
+    const unsigned char *data;
+    size_t bytes;
+} Qwen4CpuSpan;
+
+/* Read-only and mutable FP32 views of rank <= 4. */
+typedef struct {
+    const float *data;
+    size_t capacity_bytes;
+    size_t rank;
+    size_t dim[QWEN4_MAX_RANK];
+    size_t stride_bytes[QWEN4_MAX_RANK];
+} Qwen4F32;
+
+typedef struct {
+    float *data;
+    size_t capacity_bytes;
+    size_t rank;
+    size_t dim[QWEN4_MAX_RANK];
+    size_t stride_bytes[QWEN4_MAX_RANK];
+} Qwen4F32Mut;
+
+typedef struct {
+    uint32_t *data;
+    size_t capacity_bytes;
+    size_t rows;
+    size_t cols;
+    size_t row_stride_bytes;
+} Qwen4U32Mut;
+
+typedef struct {
+    uint32_t hidden_size;
+    uint32_t experts;
+    uint32_t top_k;
+    uint32_t intermediate;
+    uint32_t shared_intermediate;
+    uint32_t down_physical;       /* stored K of the routed down projection, >= intermediate */
+    bool norm_topk_prob;
+    uint32_t trunk_type[3];
+} Qwen4MoeConfig;
+
+/* One weight tensor [expert][row][packed K], K contiguous.  gguf_type is the GGUF tensor
+ * type id: 0 F32, 1 F16, 8 Q8_0, 10 Q2_K, 12 Q4_K, 16 IQ2_XXS, 30 BF16, 39 MXFP4. */
+typedef struct {
+    uint32_t gguf_type;
+    size_t k_storage;
+    size_t k_logical;
+    size_t n_out;
+    size_t n_experts;
+    size_t row_bytes;
+    size_t expert_bytes;
+    size_t tensor_bytes;
+} QW4PackedLayout;
+
+typedef struct {
+    Qwen4CpuSpan span;
+    QW4PackedLayout layout;
+} QW4PackedCpuView;
+
+typedef struct Qwen4Moe Qwen4Moe;
+typedef struct Qwen4MoeWork Qwen4MoeWork;
+
+typedef struct {
+    QW4PackedCpuView router;
+    QW4PackedCpuView gate;
+    QW4PackedCpuView up;
+    QW4PackedCpuView down;
+    QW4PackedCpuView shared_gate;
+    QW4PackedCpuView shared_up;
+    QW4PackedCpuView shared_down;
+    QW4PackedCpuView shared_router;
+} Qwen4MoeWeights;
+
+typedef struct {
+    Qwen4U32Mut ids;
+    Qwen4F32Mut weights;
+} Qwen4MoeRoutes;
+
+typedef void (*QW4MoeObserver)(void *ctx, size_t stage, size_t expert, size_t token,
+                               Qwen4F32 input, Qwen4F32 output);
+
+typedef struct {
+    size_t *offsets;              /* [experts + 1] */
+    size_t offsets_capacity_bytes;
+    size_t *cursors;              /* [experts], scratch; ends equal to offsets[e + 1] */
+    size_t cursors_capacity_bytes;
+    size_t *pair_to_row;          /* [T * K] */
+    size_t *row_to_pair;          /* [T * K] */
+    size_t pair_to_row_capacity_bytes;
+    size_t row_to_pair_capacity_bytes;
+} QW4MoeGrouping;
+#endif /* QWEN4_MOE_B200_NO_TYPES */
+
+/* ------------------------------------------------------------------------------------
+ * Group 1: the reference operator's entry points.
+ * ---------------------------------------------------------------------------------- */
+
+/* Replaces qwen4_moe_create (picoforge src/qwen4_moe.h:13-14, src/qwen4_moe.c:47-74).
+ * Validates the eight layouts against the config with the reference's status codes, then
+ * UPLOADS every weight tensor into HBM (all experts resident; no SSD pool).  The host
+ * bytes are read during this call only: later changes to them are not seen by forward. */
+Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *config, const Qwen4MoeWeights *weights,
+                             Qwen4Moe **out, Qwen4Error *err);
+
+/* Replaces qwen4_moe_destroy (src/qwen4_moe.h:15, src/qwen4_moe.c:76).  Workspaces keep
+ * the device image alive until the last of them is destroyed. */
+void qwen4_moe_destroy(Qwen4Moe *moe);
+
+/* Replaces qwen4_moe_work_size (src/qwen4_moe.h:16-17, src/qwen4_moe.c:106-111).
+ * Reports the HOST bytes of a workspace (metadata plus pinned staging for routes); the
+ * device scratch it also owns is reported by qw4cu_moe_work_device_bytes. */
+Qwen4Status qwen4_moe_work_size(const Qwen4Moe *moe, size_t token_cap, size_t *bytes,
+                                Qwen4Error *err);
+
+/* Replaces qwen4_moe_work_create (src/qwen4_moe.h:18-19, src/qwen4_moe.c:112-124). */
+Qwen4Status qwen4_moe_work_create(const Qwen4Moe *moe, size_t token_cap, size_t byte_budget,
+                                  Qwen4MoeWork **out, Qwen4Error *err);
+
+/* Replaces qwen4_moe_work_reset (src/qwen4_moe.h:20, src/qwen4_moe.c:125-130): clears the
+ * failure latch set by a forward that returned an error. */
+Qwen4Status qwen4_moe_work_reset(Qwen4MoeWork *work, Qwen4Error *err);
+
+/* Replaces qwen4_moe_work_destroy (src/qwen4_moe.h:21, src/qwen4_moe.c:131-133). */
+void qwen4_moe_work_destroy(Qwen4MoeWork *work);
+
+/* Replaces qwen4_moe_route (src/qwen4_moe.h:24-25, src/qwen4_moe.c:188-249): softmax over
+ * experts, top-k with ties to the lower id, optional renormalisation.  Host views in and
+ * out; the arithmetic runs on the GPU in the reference's order (serial exp-sum). */
+Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *config, Qwen4F32 logits,
+                            Qwen4MoeRoutes routes, Qwen4F32Mut probabilities, Qwen4Error *err);
+
+/* Replaces qwen4_moe_forward (src/qwen4_moe.h:26-27, src/qwen4_moe.c:384-431).  x and y are
+ * HOST views; the call copies x to HBM, runs the layer, copies y (and routes) back and is
+ * synchronous.  y is written only when the status is QW4_OK. */
+Qwen4Status qwen4_moe_forward(const Qwen4Moe *moe, Qwen4F32 x, Qwen4F32Mut y,
+                              Qwen4MoeRoutes *optional_routes, Qwen4MoeWork *work,
+                              Qwen4Error *err);
+
+/* Replaces qw4_moe_group_pairs (src/qwen4_moe_internal.h:78-95, src/qwen4_moe.c:251-303):
+ * stable counting sort of (token, slot) pairs by expert, computed by the dispatch kernels. */
+Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *config, Qwen4U32Mut ids,
+                                QW4MoeGrouping grouping, Qwen4Error *err);
+
+/* Replaces qw4_moe_observe (src/qwen4_moe_internal.h:9-15, src/qwen4_moe.c:134-136).  When
+ * set, forward copies stage buffers back and calls the observer for stage 0 (router
+ * logits), 11 (routed sum) and 12 (y); the per-expert stages 1-10 are not materialised by
+ * the fused kernels and are not reported. */
+void qw4_moe_observe(Qwen4MoeWork *work, QW4MoeObserver observer, void *ctx);
+
+/* ------------------------------------------------------------------------------------
+ * Group 2: additions (no counterpart in the reference).
+ * ---------------------------------------------------------------------------------- */
+
+/* Number of CUDA devices, or -1 when the runtime cannot be initialised. */
+int qw4cu_device_count(void);
+/* Selects the device used by every later call on this thread.  Returns 0 on success. */
+int qw4cu_set_device(int device);
+/* Text of the last CUDA error seen by this library on this thread ("" if none). */
+const char *qw4cu_last_error(void);
+
+/* Router arithmetic.  0 "exact": logits summed serially over k without FMA, bit-identical
+ * to the reference CPU path (ids always match).  1 "fast": warp-tree sums; ids can differ
+ * only where two probabilities are within rounding of each other.  Default 0.  The
+ * environment variable QW4CU_ROUTER=exact|fast sets the initial value. */
+void qw4cu_set_router_mode(int mode);
+int qw4cu_get_router_mode(void);
+
+/* Device bytes held by the resident weight image of one MoE, and by one workspace. */
+size_t qw4cu_moe_device_bytes(const Qwen4Moe *moe);
+size_t qw4cu_moe_work_device_bytes(const Qwen4MoeWork *work);
+
+/* Forward on device pointers: x_dev [tokens, hidden] and y_dev [tokens, hidden] are dense
+ * FP32 in HBM; ids_dev [tokens, k] and weights_dev [tokens, k] may be NULL.  Enqueues on
+ * the workspace's stream and returns without waiting; errors found by the kernels are
+ * reported by qw4cu_moe_work_sync. */
+Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *moe, const float *x_dev, float *y_dev,
+                                     size_t tokens, uint32_t *ids_dev, float *weights_dev,
+                                     Qwen4MoeWork *work, Qwen4Error *err);
+/* Waits for the workspace's stream, converts the device error word (bit 1 nonfinite, bit 2
+ * bounds, bit 4 state) into a status and latches the workspace on failure. */
+Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
+
+/* Timing on the workspace's stream with CUDA events.  begin/end record events; elapsed
+ * waits for the end event and returns milliseconds (negative on error). */
+int qw4cu_moe_work_timer_begin(Qwen4MoeWork *work);
+int qw4cu_moe_work_timer_end(Qwen4MoeWork *work);
+float qw4cu_moe_work_timer_elapsed_ms(Qwen4MoeWork *work);
+/* Kernels launched by this library in this process so far. */
+uint64_t qw4cu_launch_count(void);
+
+/* Decodes rows [row0, row0 + rows) of one expert of a resident tensor (index 0-7 in
+ * Qwen4MoeWeights order) FROM THE DEVICE IMAGE into host floats [rows, k_storage].  Used to
+ * prove that the resident (repacked) image decodes to the reference's bits. */
+Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *moe, uint32_t tensor, size_t expert,
+                                  size_t row0, size_t rows, float *out, size_t out_elements,
+                                  Qwen4Error *err);
+
+/* Raw device memory and transfers for callers that keep activations in HBM. */
+void *qw4cu_malloc(size_t bytes);
+void qw4cu_free(void *device_pointer);
+void *qw4cu_host_alloc(size_t bytes);            /* pinned host memory */
+void qw4cu_host_free(void *host_pointer);
+int qw4cu_upload(void *device_dst, const void *host_src, size_t bytes);
+int qw4cu_download(void *host_dst, const void *device_src, size_t bytes);
+/* Writes `bytes` of a scratch buffer larger than L2 so that the next kernel starts cold. */
+int qw4cu_flush_l2(void);
+int qw4cu_device_synchronize(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWEN4_MOE_B200_H */

@@ -1,0 +1,100 @@
+/* Internal C boundary between the C11 host (moe_host.c) and the CUDA translation units.
+ * Plain C types only.  Every function returns 0 on success or a nonzero CUDA error code,
+ * whose text is kept for qw4cu_last_error(). */
+#ifndef QW4_CUDA_SHIM_H
+#define QW4_CUDA_SHIM_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Mirror of qw4::DevTensor (formats.cuh). */
+typedef struct {
+    const uint8_t *data;
+    uint32_t type;
+    uint32_t k_storage, k_logical, n_out, n_experts;
+    uint32_t row_bytes;
+    uint64_t expert_bytes;
+} QW4ShTensor;
+
+typedef struct {
+    uint32_t hidden, experts, top_k, inter, shared_inter, down_physical;
+    int norm;
+    QW4ShTensor w[8];             /* router, gate, up, down, sgate, sup, sdown, srouter */
+} QW4ShLayer;
+
+/* Device scratch of one workspace, sized for `cap` tokens. */
+typedef struct {
+    size_t cap;
+    float *x, *y;                 /* [cap, hidden] staging for the host-pointer forward */
+    float *logits, *probs;        /* [cap, experts] */
+    float *shared_logit;          /* [cap] */
+    uint32_t *ids;                /* [cap, k] */
+    float *weights;               /* [cap, k] */
+    uint32_t *offsets;            /* [experts + 1] */
+    uint32_t *pair_to_row, *row_to_pair;  /* [cap * k] */
+    uint32_t *active;             /* [experts + 1]: active[0] = count, then expert ids */
+    float *act;                   /* [cap * k, inter] in pair order */
+    float *shared_act;            /* [cap, shared_inter] */
+    float *routed;                /* [cap, hidden], only when an observer is set */
+    uint32_t *status;             /* [4]: error bits, first bad row, spare */
+    void *stream;                 /* cudaStream_t */
+    void *timer[2];               /* cudaEvent_t */
+} QW4ShWork;
+
+enum { QW4SH_ERR_NONFINITE = 1u, QW4SH_ERR_BOUNDS = 2u, QW4SH_ERR_STATE = 4u };
+
+int qw4sh_device_count(void);
+int qw4sh_set_device(int device);
+const char *qw4sh_last_error(void);
+uint64_t qw4sh_launch_count(void);
+
+void *qw4sh_malloc(size_t bytes);
+void qw4sh_free(void *p);
+void *qw4sh_host_alloc(size_t bytes);
+void qw4sh_host_free(void *p);
+int qw4sh_memcpy(void *dst, const void *src, size_t bytes, int to_device);
+int qw4sh_memcpy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
+                         size_t width_bytes, size_t rows, int to_device, void *stream);
+int qw4sh_memset_async(void *dst, int value, size_t bytes, void *stream);
+int qw4sh_stream_create(void **stream);
+void qw4sh_stream_destroy(void *stream);
+int qw4sh_stream_sync(void *stream);
+int qw4sh_device_sync(void);
+int qw4sh_event_create(void **event);
+void qw4sh_event_destroy(void *event);
+int qw4sh_event_record(void *event, void *stream);
+float qw4sh_event_elapsed_ms(void *begin, void *end);
+int qw4sh_flush_l2(void);
+
+/* Uploads one tensor (natural GGUF layout on the host) and regroups it into the resident
+ * layout described in formats.cuh.  *device receives a cudaMalloc'ed image. */
+int qw4sh_upload_tensor(const void *host, size_t bytes, uint32_t type, size_t k_storage,
+                        size_t n_out, size_t n_experts, void **device);
+
+/* out[rows, k_storage] (device) = exact decode of rows [row0, row0+rows) of one expert. */
+int qw4sh_decode_rows(const QW4ShTensor *t, size_t expert, size_t row0, size_t rows, float *out,
+                      void *stream);
+
+/* Router arithmetic on logits [tokens, experts] with `pitch` floats per row.  status[0]
+ * gets QW4SH_ERR_NONFINITE and status[1] the lowest bad row if a logit is not finite. */
+int qw4sh_route(uint32_t experts, uint32_t k, int norm, const float *logits, size_t pitch,
+                size_t tokens, float *probs, uint32_t *ids, float *weights, uint32_t *status,
+                void *stream);
+
+/* Stable per-expert lists of pair = token * k + slot. */
+int qw4sh_group(uint32_t experts, uint32_t k, size_t tokens, const uint32_t *ids, uint32_t *offsets,
+                uint32_t *pair_to_row, uint32_t *row_to_pair, uint32_t *active, uint32_t *status,
+                void *stream);
+
+/* The whole layer on device pointers: x, y dense [tokens, hidden].  router_mode 0 exact,
+ * 1 fast.  ids_out / weights_out may be NULL. */
+int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y,
+                        size_t tokens, uint32_t *ids_out, float *weights_out, int router_mode);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,863 @@
+// CUDA kernels of the Qwen4 MoE layer for sm_100a, and the C shim that launches them.
+//
+// Path (one launch each; picoforge src/qwen4_moe.c:334-382 is the CPU statement of the
+// same sequence):
+//   router_logits  x -> logits [T,E] and the shared-expert gate logit [T]
+//   route          softmax, top-k, renormalise -> ids, weights [T,k]
+//   group          stable per-expert pair lists (dispatch)
+//   gate_up        act[pair] = silu(gate_e x) * (up_e x), weights dequantised in registers
+//   down_reduce    y[t] = sum_s w[t,s] (down_e act[pair]) + sigmoid(slogit[t]) (sdown sact[t])
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "cuda_shim.h"
+#include "formats.cuh"
+
+using namespace qw4;
+
+// ------------------------------------------------------------------------------------
+// Bookkeeping
+// ------------------------------------------------------------------------------------
+static thread_local char g_error[256] = "";
+static unsigned long long g_launches = 0;
+
+static int fail(cudaError_t e, const char *where) {
+    snprintf(g_error, sizeof g_error, "%s: %s", where, cudaGetErrorString(e));
+    return (int)e ? (int)e : -1;
+}
+#define CU(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(e_, #call); } while (0)
+#define LAUNCHED(name) do { __sync_fetch_and_add(&g_launches, 1ull); cudaError_t e_ = cudaGetLastError(); \
+    if (e_ != cudaSuccess) return fail(e_, name); } while (0)
+
+static bool g_constants_ready[64] = {false};
+static int ensure_constants() {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    if (!g_constants_ready[device]) {
+        CU(cudaMemcpyToSymbol(c_iq2_levels, QW4_IQ2XXS_LEVELS, sizeof QW4_IQ2XXS_LEVELS));
+        g_constants_ready[device] = true;
+    }
+    return 0;
+}
+
+extern "C" int qw4sh_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { fail(cudaGetLastError(), "cudaGetDeviceCount"); return -1; }
+    return n;
+}
+extern "C" int qw4sh_set_device(int device) { CU(cudaSetDevice(device)); return ensure_constants(); }
+extern "C" const char *qw4sh_last_error(void) { return g_error; }
+extern "C" uint64_t qw4sh_launch_count(void) { return g_launches; }
+
+extern "C" void *qw4sh_malloc(size_t bytes) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 1) != cudaSuccess) { fail(cudaGetLastError(), "cudaMalloc"); return nullptr; }
+    return p;
+}
+extern "C" void qw4sh_free(void *p) { if (p) cudaFree(p); }
+extern "C" void *qw4sh_host_alloc(size_t bytes) {
+    void *p = nullptr;
+    if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) { fail(cudaGetLastError(), "cudaHostAlloc"); return nullptr; }
+    return p;
+}
+extern "C" void qw4sh_host_free(void *p) { if (p) cudaFreeHost(p); }
+extern "C" int qw4sh_memcpy(void *dst, const void *src, size_t bytes, int to_device) {
+    if (bytes) CU(cudaMemcpy(dst, src, bytes, to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost));
+    return 0;
+}
+extern "C" int qw4sh_memcpy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
+                                    size_t width, size_t rows, int to_device, void *stream) {
+    if (width && rows)
+        CU(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, rows,
+                             to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qw4sh_memset_async(void *dst, int value, size_t bytes, void *stream) {
+    if (bytes) CU(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
+    return 0;
+}
+extern "C" int qw4sh_stream_create(void **stream) {
+    cudaStream_t s;
+    CU(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = s;
+    return ensure_constants();
+}
+extern "C" void qw4sh_stream_destroy(void *stream) { if (stream) cudaStreamDestroy((cudaStream_t)stream); }
+extern "C" int qw4sh_stream_sync(void *stream) { CU(cudaStreamSynchronize((cudaStream_t)stream)); return 0; }
+extern "C" int qw4sh_device_sync(void) { CU(cudaDeviceSynchronize()); return 0; }
+extern "C" int qw4sh_event_create(void **event) { cudaEvent_t e; CU(cudaEventCreate(&e)); *event = e; return 0; }
+extern "C" void qw4sh_event_destroy(void *event) { if (event) cudaEventDestroy((cudaEvent_t)event); }
+extern "C" int qw4sh_event_record(void *event, void *stream) { CU(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream)); return 0; }
+extern "C" float qw4sh_event_elapsed_ms(void *begin, void *end) {
+    float ms = -1.0f;
+    if (cudaEventSynchronize((cudaEvent_t)end) != cudaSuccess ||
+        cudaEventElapsedTime(&ms, (cudaEvent_t)begin, (cudaEvent_t)end) != cudaSuccess) { fail(cudaGetLastError(), "event elapsed"); return -1.0f; }
+    return ms;
+}
+
+// Writes a buffer larger than the 126 MB L2 so that the next kernel reads HBM.
+static void *g_flush[64] = {nullptr};
+static const size_t FLUSH_BYTES = 256u << 20;
+extern "C" int qw4sh_flush_l2(void) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (!g_flush[device]) CU(cudaMalloc(&g_flush[device], FLUSH_BYTES));
+    CU(cudaMemsetAsync(g_flush[device], 0x5a, FLUSH_BYTES, 0));
+    CU(cudaDeviceSynchronize());
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------
+// Upload + regroup into the resident layout (formats.cuh)
+// ------------------------------------------------------------------------------------
+__global__ void regroup_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, uint32_t type,
+                               uint64_t blocks_per_matrix, uint64_t matrices) {
+    const uint64_t total = blocks_per_matrix * matrices;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t matrix = i / blocks_per_matrix, block = i % blocks_per_matrix;
+        if (type == T_Q2_K) {
+            const uint8_t *b = src + i * 84u;
+            uint8_t *base = dst + matrix * blocks_per_matrix * 84u;
+            for (int j = 0; j < 64; j++) base[block * 64u + j] = b[16 + j];
+            for (int j = 0; j < 16; j++) base[blocks_per_matrix * 64u + block * 16u + j] = b[j];
+            for (int j = 0; j < 4; j++) base[blocks_per_matrix * 80u + block * 4u + j] = b[80 + j];
+        } else {                                               // IQ2_XXS
+            const uint8_t *b = src + i * 66u;
+            uint8_t *base = dst + matrix * blocks_per_matrix * 66u;
+            for (int j = 0; j < 64; j++) base[block * 64u + j] = b[2 + j];
+            base[blocks_per_matrix * 64u + block * 2u] = b[0];
+            base[blocks_per_matrix * 64u + block * 2u + 1] = b[1];
+        }
+    }
+}
+
+extern "C" int qw4sh_upload_tensor(const void *host, size_t bytes, uint32_t type, size_t k_storage,
+                                   size_t n_out, size_t n_experts, void **device) {
+    *device = nullptr;
+    if (ensure_constants()) return -1;
+    void *image = nullptr;
+    CU(cudaMalloc(&image, bytes ? bytes : 16));
+    if (type == T_Q2_K || type == T_IQ2_XXS) {
+        void *staging = nullptr;
+        cudaError_t e = cudaMalloc(&staging, bytes ? bytes : 16);
+        if (e != cudaSuccess) { cudaFree(image); return fail(e, "cudaMalloc staging"); }
+        e = cudaMemcpy(staging, host, bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) {
+            const uint64_t per_matrix = (uint64_t)n_out * (k_storage / 256);
+            regroup_kernel<<<1184, 256>>>((const uint8_t *)staging, (uint8_t *)image, type, per_matrix, n_experts);
+            __sync_fetch_and_add(&g_launches, 1ull);
+            e = cudaGetLastError();
+            if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        }
+        cudaFree(staging);
+        if (e != cudaSuccess) { cudaFree(image); return fail(e, "regroup"); }
+    } else if (bytes) {
+        cudaError_t e = cudaMemcpy(image, host, bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { cudaFree(image); return fail(e, "cudaMemcpy weights"); }
+    }
+    *device = image;
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------
+// Exact decode probe
+// ------------------------------------------------------------------------------------
+__global__ void decode_rows_kernel(DevTensor t, uint32_t expert, uint32_t row0, uint32_t rows, float *out) {
+    const uint64_t total = (uint64_t)rows * t.k_storage;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = decode_value(t, expert, row0 + (uint32_t)(i / t.k_storage), (uint32_t)(i % t.k_storage));
+}
+static DevTensor as_dev(const QW4ShTensor &s) {
+    DevTensor t;
+    t.data = s.data; t.type = s.type; t.k_storage = s.k_storage; t.k_logical = s.k_logical;
+    t.n_out = s.n_out; t.n_experts = s.n_experts; t.row_bytes = s.row_bytes; t.expert_bytes = s.expert_bytes;
+    return t;
+}
+extern "C" int qw4sh_decode_rows(const QW4ShTensor *t, size_t expert, size_t row0, size_t rows, float *out, void *stream) {
+    if (!rows) return 0;
+    decode_rows_kernel<<<592, 256, 0, (cudaStream_t)stream>>>(as_dev(*t), (uint32_t)expert, (uint32_t)row0, (uint32_t)rows, out);
+    LAUNCHED("decode_rows_kernel");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------
+// expf with glibc's bits.
+//
+// The reference computes softmax and sigmoid with libm expf (picoforge src/qwen4_moe.c:228,
+// src/qwen4_cpu_internal.h:103-106).  glibc's expf is the table-driven double-precision
+// algorithm published in ARM's optimized routines (N = 32 table, cubic polynomial); on x86-64
+// machines with FMA its products and sums are fused.  Restating it with explicit fma() gives
+// the same binary32 result as glibc 2.39 for every input <= 0 (1 120 927 745 values checked
+// on the CPU), which is the whole domain used here: z - max <= 0 and -|x|.
+// ------------------------------------------------------------------------------------
+__device__ __constant__ unsigned long long c_exp2_table[32] = {
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
+};
+__device__ __forceinline__ float expf_libm(float x) {          // x <= 0 (or +0)
+    if (x < -0x1.9fe368p6f) return 0.0f;
+    const double inv_ln2_n = 0x1.71547652b82fep+0 * 32.0, shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / 32 / 32 / 32, c1 = 0x1.ebfce50fac4f3p-3 / 32 / 32, c2 = 0x1.62e42ff0c52d6p-1 / 32;
+    const double xd = (double)x;
+    double kd = fma(inv_ln2_n, xd, shift);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, shift);
+    const double r = fma(inv_ln2_n, xd, -kd);
+    unsigned long long t = c_exp2_table[ki & 31u];
+    t += ki << 47;
+    const double s = __longlong_as_double((long long)t);
+    const double z = fma(c0, r, c1), r2 = __dmul_rn(r, r);
+    double y = fma(c2, r, 1.0);
+    y = fma(z, r2, y);
+    return __double2float_rn(__dmul_rn(y, s));
+}
+__device__ __forceinline__ float sigmoid_libm(float x) {      // src/qwen4_cpu_internal.h:103-106
+    if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-x)));
+    const float z = expf_libm(x);
+    return __fdiv_rn(z, __fadd_rn(1.0f, z));
+}
+__device__ __forceinline__ bool finite_f32(float v) { return (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u; }
+
+// ------------------------------------------------------------------------------------
+// Router logits.
+// Exact: one thread per (token, expert) walks k = 0..K-1 with separately rounded product and
+// sum, the reference's order (src/qwen4_packed.c:164-173), so logits carry the CPU path's
+// bits.  The weight tile goes through shared memory so that global reads stay coalesced.
+// Row `experts` of the grid is the shared expert's gate (a [1, K] F32 tensor).
+// ------------------------------------------------------------------------------------
+template <int TT>
+__global__ void __launch_bounds__(32 * TT) router_exact_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x,
+                                                               uint32_t tokens, float *__restrict__ logits,
+                                                               float *__restrict__ shared_logit, uint32_t *status) {
+    constexpr int KC = 128;
+    __shared__ float ws[32][KC + 1];
+    __shared__ float xs[TT][KC];
+    const uint32_t experts = router.n_out, k_total = router.k_logical;
+    const uint32_t e = blockIdx.x * 32 + threadIdx.x, t = blockIdx.y * TT + threadIdx.y;
+    const uint32_t tid = threadIdx.y * 32 + threadIdx.x, nthreads = 32 * TT;
+    float sum = 0.0f;
+    for (uint32_t k0 = 0; k0 < k_total; k0 += KC) {
+        const uint32_t kc = min((uint32_t)KC, k_total - k0);
+        for (uint32_t i = tid; i < 32 * KC; i += nthreads) {
+            const uint32_t row = i / KC, col = i % KC, ge = blockIdx.x * 32 + row;
+            float v = 0.0f;
+            if (col < kc && ge <= experts) {
+                const float *src = ge < experts ? (const float *)(router.data + (uint64_t)ge * router.row_bytes)
+                                                : (const float *)srouter.data;
+                v = src[k0 + col];
+            }
+            ws[row][col] = v;
+        }
+        for (uint32_t i = tid; i < TT * KC; i += nthreads) {
+            const uint32_t row = i / KC, col = i % KC, gt = blockIdx.y * TT + row;
+            xs[row][col] = (col < kc && gt < tokens) ? x[(uint64_t)gt * k_total + k0 + col] : 0.0f;
+        }
+        __syncthreads();
+        if (kc == KC) {
+#pragma unroll 16
+            for (int kk = 0; kk < KC; kk++) sum = __fadd_rn(sum, __fmul_rn(ws[threadIdx.x][kk], xs[threadIdx.y][kk]));
+        } else {
+            for (uint32_t kk = 0; kk < kc; kk++) sum = __fadd_rn(sum, __fmul_rn(ws[threadIdx.x][kk], xs[threadIdx.y][kk]));
+        }
+        __syncthreads();
+    }
+    if (t < tokens && e <= experts) {
+        if (!finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
+        if (e < experts) logits[(uint64_t)t * experts + e] = sum;
+        else shared_logit[t] = sum;
+    }
+}
+
+// Fast: one warp per router row, lanes stride K with 128-bit loads, tree sum.  Up to 8 tokens
+// per pass share the weight reads.
+__global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x,
+                                                          uint32_t tokens, float *__restrict__ logits,
+                                                          float *__restrict__ shared_logit, uint32_t *status) {
+    const uint32_t experts = router.n_out, k_total = router.k_logical;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t e = blockIdx.x * 8 + warp;
+    if (e > experts) return;
+    const float *w = e < experts ? (const float *)(router.data + (uint64_t)e * router.row_bytes) : (const float *)srouter.data;
+    for (uint32_t t0 = blockIdx.y * 8; t0 < tokens; t0 += gridDim.y * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const uint32_t nt = min(8u, tokens - t0);
+        if ((k_total & 3u) == 0) {
+            for (uint32_t k = lane * 4; k < k_total; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4 *>(w + k);
+#pragma unroll
+                for (int r = 0; r < 8; r++) if ((uint32_t)r < nt) {
+                    const float4 xv = *reinterpret_cast<const float4 *>(x + (uint64_t)(t0 + r) * k_total + k);
+                    acc[r] = fmaf(wv.x, xv.x, fmaf(wv.y, xv.y, fmaf(wv.z, xv.z, fmaf(wv.w, xv.w, acc[r]))));
+                }
+            }
+        } else {
+            for (uint32_t k = lane; k < k_total; k += 32)
+#pragma unroll
+                for (int r = 0; r < 8; r++) if ((uint32_t)r < nt) acc[r] = fmaf(w[k], x[(uint64_t)(t0 + r) * k_total + k], acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            float v = acc[r];
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && (uint32_t)r < nt) {
+                if (!finite_f32(v)) atomicOr(status, QW4SH_ERR_NONFINITE);
+                if (e < experts) logits[(uint64_t)(t0 + r) * experts + e] = v;
+                else shared_logit[t0 + r] = v;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Route: one warp per token (src/qwen4_moe.c:209-247).  The exp-sum runs serially over
+// e = 0..E-1 on one lane, the reference's order, so probabilities and weights carry its bits;
+// the k argmax rounds are warp-parallel with ties to the lower id (strict > in ascending e).
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) route_kernel(uint32_t experts, uint32_t k, int norm, const float *__restrict__ logits,
+                                                    uint64_t pitch, uint32_t tokens, float *__restrict__ probs,
+                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status) {
+    extern __shared__ float route_smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    const uint32_t t = blockIdx.x * warps + warp;
+    if (t >= tokens) return;
+    float *p = route_smem + (uint64_t)warp * experts;
+    const float *z = logits + (uint64_t)t * pitch;
+    bool bad = false;
+    float maximum = -CUDART_INF_F;
+    for (uint32_t e = lane; e < experts; e += 32) {
+        const float v = z[e];
+        bad |= !finite_f32(v);
+        maximum = fmaxf(maximum, v);
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (bad) {
+        if (lane == 0) { atomicOr(status, QW4SH_ERR_NONFINITE); atomicMin(status + 1, t); }
+        return;
+    }
+    for (int o = 16; o; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+    for (uint32_t e = lane; e < experts; e += 32) p[e] = expf_libm(__fsub_rn(z[e], maximum));
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0) {
+        uint32_t e = 0;
+        for (; e + 8 <= experts; e += 8) {
+            const float a0 = p[e], a1 = p[e + 1], a2 = p[e + 2], a3 = p[e + 3], a4 = p[e + 4], a5 = p[e + 5], a6 = p[e + 6], a7 = p[e + 7];
+            sum = __fadd_rn(sum, a0); sum = __fadd_rn(sum, a1); sum = __fadd_rn(sum, a2); sum = __fadd_rn(sum, a3);
+            sum = __fadd_rn(sum, a4); sum = __fadd_rn(sum, a5); sum = __fadd_rn(sum, a6); sum = __fadd_rn(sum, a7);
+        }
+        for (; e < experts; e++) sum = __fadd_rn(sum, p[e]);
+    }
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (uint32_t e = lane; e < experts; e += 32) {
+        const float v = __fdiv_rn(p[e], sum);
+        p[e] = v;
+        probs[(uint64_t)t * experts + e] = v;
+    }
+    __syncwarp();
+    float selected = 0.0f;
+    for (uint32_t slot = 0; slot < k; slot++) {
+        float best = -1.0f;
+        uint32_t best_e = 0xffffffffu;
+        for (uint32_t e = lane; e < experts; e += 32) {
+            const float v = p[e];
+            if (v > best) { best = v; best_e = e; }
+        }
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (lane == 0) { ids[(uint64_t)t * k + slot] = best_e; weights[(uint64_t)t * k + slot] = best; }
+        if ((best_e & 31u) == lane) p[best_e] = -1.0f;         // probabilities are >= 0: never chosen again
+        selected = __fadd_rn(selected, best);
+        __syncwarp();
+    }
+    // Lane 0 stored the raw weights above and is the only reader here.
+    if (norm && lane == 0)
+        for (uint32_t slot = 0; slot < k; slot++)
+            weights[(uint64_t)t * k + slot] = __fdiv_rn(weights[(uint64_t)t * k + slot], selected);
+}
+
+// ------------------------------------------------------------------------------------
+// Dispatch: stable counting sort of pair = t*k + slot by expert (src/qwen4_moe.c:285-301),
+// one CTA.  Order inside an expert is by ascending pair, so the lists equal the CPU path's.
+// Thread e owns expert e: it counts, then walks the pairs in order and places its own.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) group_kernel(uint32_t experts, uint32_t pairs, const uint32_t *__restrict__ ids,
+                                                     uint32_t *__restrict__ offsets, uint32_t *__restrict__ pair_to_row,
+                                                     uint32_t *__restrict__ row_to_pair, uint32_t *__restrict__ active, uint32_t *status) {
+    extern __shared__ uint32_t group_smem[];                   // counts[experts + 1]
+    uint32_t *counts = group_smem;
+    for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    bool bounds = false;
+    for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const uint32_t e = ids[p];
+        if (e < experts) atomicAdd(&counts[e], 1u); else bounds = true;
+    }
+    if (bounds) atomicOr(status, QW4SH_ERR_BOUNDS);
+    __syncthreads();
+    if (threadIdx.x == 0) {                                    // exclusive prefix; E is small
+        uint32_t running = 0, n_active = 0;
+        for (uint32_t e = 0; e < experts; e++) {
+            const uint32_t c = counts[e];
+            counts[e] = running;
+            offsets[e] = running;
+            if (c) active[1 + n_active++] = e;
+            running += c;
+        }
+        counts[experts] = running;
+        offsets[experts] = running;
+        active[0] = n_active;
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
+        uint32_t cursor = counts[e];
+        const uint32_t end = counts[e + 1];
+        for (uint32_t p = 0; p < pairs && cursor < end; p++)
+            if (ids[p] == e) { pair_to_row[p] = cursor; row_to_pair[cursor] = p; cursor++; }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Expert products.  Weights are read as 32-weight units (one unit per lane per step):
+//   Q4_K     16 B of nibbles: 16 low-nibble weights at col0.. and 16 high-nibble at col0+32..
+//   Q2_K      8 B of 2-bit codes: 4 runs of 8 weights, 32 columns apart
+//   IQ2_XXS   8 B group: 4 codebook vectors of 8 weights, 32 contiguous columns
+// decode_unit writes the 32 decoded weights and the column of each run of 8.
+// Activations sit in shared memory with 4 floats of padding after every 32 (index
+// k + 4*(k/32)) so that 128-bit reads by consecutive lanes fall in distinct banks.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t xs_index(uint32_t k) { return k + ((k >> 5) << 2); }
+
+template <uint32_t TYPE> struct Unit;
+
+template <> struct Unit<T_Q4_K> {
+    __device__ static __forceinline__ void decode(const uint8_t *mat, uint32_t rows, uint32_t nb, uint32_t row, uint32_t unit,
+                                                  const uint16_t *, float (&w)[32], uint32_t (&col)[4]) {
+        (void)rows;
+        const uint32_t b = unit >> 3, i = unit & 7u, cc = i >> 1, h = i & 1u;
+        const uint8_t *blk = mat + ((uint64_t)row * nb + b) * 144u;
+        const uint4 head = *reinterpret_cast<const uint4 *>(blk);
+        const uint4 q = *reinterpret_cast<const uint4 *>(blk + 16 + i * 16);
+        const float d = __half2float(__ushort_as_half((uint16_t)(head.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((uint16_t)(head.x >> 16)));
+        const uint8_t sc[12] = {(uint8_t)head.y, (uint8_t)(head.y >> 8), (uint8_t)(head.y >> 16), (uint8_t)(head.y >> 24),
+                                (uint8_t)head.z, (uint8_t)(head.z >> 8), (uint8_t)(head.z >> 16), (uint8_t)(head.z >> 24),
+                                (uint8_t)head.w, (uint8_t)(head.w >> 8), (uint8_t)(head.w >> 16), (uint8_t)(head.w >> 24)};
+        uint32_t s0, m0, s1, m1;
+        q4k_scale_min(sc, 2 * cc, s0, m0);
+        q4k_scale_min(sc, 2 * cc + 1, s1, m1);
+        const float dl0 = d * (float)s0, ml0 = dmin * (float)m0, dl1 = d * (float)s1, ml1 = dmin * (float)m1;
+        const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint32_t byte = (words[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+            w[j] = fmaf(dl0, (float)(byte & 15u), -ml0);
+            w[16 + j] = fmaf(dl1, (float)(byte >> 4), -ml1);
+        }
+        const uint32_t col0 = b * 256 + cc * 64 + h * 16;
+        col[0] = col0; col[1] = col0 + 8; col[2] = col0 + 32; col[3] = col0 + 40;
+    }
+};
+
+template <> struct Unit<T_Q2_K> {
+    __device__ static __forceinline__ void decode(const uint8_t *mat, uint32_t rows, uint32_t nb, uint32_t row, uint32_t unit,
+                                                  const uint16_t *, float (&w)[32], uint32_t (&col)[4]) {
+        const uint32_t b = unit >> 3, i = unit & 7u, hh = i >> 2, ii = i & 3u;
+        const uint64_t blocks = (uint64_t)rows * nb, block = (uint64_t)row * nb + b;
+        const uint2 codes = *reinterpret_cast<const uint2 *>(mat + block * 64u + hh * 32 + ii * 8);
+        const uint8_t *scales = mat + blocks * 64u + block * 16u;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(mat + blocks * 80u + block * 4u);
+        const float d = __half2float(__ushort_as_half((uint16_t)(dd & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((uint16_t)(dd >> 16)));
+        const uint32_t words[2] = {codes.x, codes.y};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t column = hh * 128 + q * 32 + ii * 8;       // within the block
+            const uint32_t s = scales[column >> 4];
+            const float dl = d * (float)(s & 15u), ml = dmin * (float)(s >> 4);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint32_t byte = (words[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+                w[q * 8 + j] = fmaf(dl, (float)((byte >> (2 * q)) & 3u), -ml);
+            }
+            col[q] = b * 256 + column;
+        }
+    }
+};
+
+template <> struct Unit<T_IQ2_XXS> {
+    __device__ static __forceinline__ void decode(const uint8_t *mat, uint32_t rows, uint32_t nb, uint32_t row, uint32_t unit,
+                                                  const uint16_t *levels_lut, float (&w)[32], uint32_t (&col)[4]) {
+        const uint32_t b = unit >> 3, g = unit & 7u;
+        const uint64_t blocks = (uint64_t)rows * nb, block = (uint64_t)row * nb + b;
+        const uint2 group = *reinterpret_cast<const uint2 *>(mat + block * 64u + g * 8u);
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(mat + blocks * 64u + block * 2u)));
+        const float scale = d * (float)(2u * (group.y >> 28) + 1u) * 0.125f;
+#pragma unroll
+        for (int slot = 0; slot < 4; slot++) {
+            const uint32_t levels = levels_lut[(group.x >> (8 * slot)) & 0xffu];
+            const uint32_t signs = iq2_signs8((group.y >> (7 * slot)) & 127u);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint32_t level = (levels >> (2 * j)) & 3u;
+                const float value = scale * (float)iq2_magnitude(level);
+                w[slot * 8 + j] = __uint_as_float(__float_as_uint(value) ^ (((signs >> j) & 1u) << 31));
+            }
+            col[slot] = b * 256 + g * 32 + slot * 8;
+        }
+    }
+};
+
+// acc[r] += sum over the unit's 32 weights of w * x_r, x rows in padded shared memory.
+template <int NR>
+__device__ __forceinline__ void unit_fma(const float (&w)[32], const uint32_t (&col)[4], const float *xs, uint32_t x_pitch,
+                                         uint32_t k_logical, float (&acc)[NR]) {
+#pragma unroll
+    for (int run = 0; run < 4; run++) {
+        if (col[run] >= k_logical) continue;                   // stored padding columns are never read
+        const uint32_t at = xs_index(col[run]);
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            const float4 a = *reinterpret_cast<const float4 *>(xs + r * x_pitch + at);
+            const float4 b = *reinterpret_cast<const float4 *>(xs + r * x_pitch + at + 4);
+            float s = acc[r];
+            s = fmaf(w[run * 8 + 0], a.x, s); s = fmaf(w[run * 8 + 1], a.y, s);
+            s = fmaf(w[run * 8 + 2], a.z, s); s = fmaf(w[run * 8 + 3], a.w, s);
+            s = fmaf(w[run * 8 + 4], b.x, s); s = fmaf(w[run * 8 + 5], b.y, s);
+            s = fmaf(w[run * 8 + 6], b.z, s); s = fmaf(w[run * 8 + 7], b.w, s);
+            acc[r] = s;
+        }
+    }
+}
+
+// Any-format fallback: the unit is 32 consecutive columns decoded one by one.
+template <> struct Unit<0xffffffffu> {};
+
+constexpr int GU_ROWS = 4;            // token rows per pass in gate_up
+constexpr int GU_WARPS = 8;
+constexpr int GU_TILE = 16;           // output rows per CTA
+
+// act[pair, n] = silu(gate_e[n] . x) * (up_e[n] . x) for every pair routed to expert e.
+// grid = (ceil(inter / GU_TILE), groups); group g of the grid is expert active[1 + g].
+// row_to_pair == nullptr means one group holding rows 0..tokens-1 of x (the shared expert).
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(GU_WARPS * 32) gate_up_kernel(DevTensor gate, DevTensor up, const float *__restrict__ x,
+                                                                uint32_t hidden, const uint32_t *__restrict__ offsets,
+                                                                const uint32_t *__restrict__ row_to_pair,
+                                                                const uint32_t *__restrict__ active, uint32_t k_div, uint32_t tokens,
+                                                                float *__restrict__ act, uint32_t *status) {
+    extern __shared__ __align__(16) float gu_smem[];
+    __shared__ uint16_t levels_lut[256];
+    const uint32_t inter = gate.n_out, nb = gate.k_storage >> 8, units = gate.k_storage >> 5;
+    const uint32_t x_pitch = xs_index(hidden) + 4;
+    uint32_t expert = 0, first = 0, count = tokens;
+    if (row_to_pair) {
+        if (blockIdx.y >= active[0]) return;
+        expert = active[1 + blockIdx.y];
+        first = offsets[expert];
+        count = offsets[expert + 1] - first;
+    }
+    if (TYPE == T_IQ2_XXS) for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) levels_lut[i] = c_iq2_levels[i];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint8_t *gmat = gate.data + (uint64_t)expert * gate.expert_bytes, *umat = up.data + (uint64_t)expert * up.expert_bytes;
+    for (uint32_t r0 = 0; r0 < count; r0 += GU_ROWS) {
+        const uint32_t nr = min((uint32_t)GU_ROWS, count - r0);
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < GU_ROWS * (hidden >> 2); i += blockDim.x) {
+            const uint32_t r = i / (hidden >> 2), c4 = i % (hidden >> 2);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < nr) {
+                const uint32_t src_row = row_to_pair ? row_to_pair[first + r0 + r] / k_div : r0 + r;
+                v = *reinterpret_cast<const float4 *>(x + (uint64_t)src_row * hidden + c4 * 4);
+            }
+            *reinterpret_cast<float4 *>(gu_smem + r * x_pitch + xs_index(c4 * 4)) = v;
+        }
+        __syncthreads();
+        for (uint32_t j = warp; j < GU_TILE; j += GU_WARPS) {
+            const uint32_t n = blockIdx.x * GU_TILE + j;
+            if (n >= inter) break;
+            float ag[GU_ROWS] = {0, 0, 0, 0}, au[GU_ROWS] = {0, 0, 0, 0};
+            for (uint32_t u = lane; u < units; u += 32) {
+                float w[32];
+                uint32_t col[4];
+                Unit<TYPE>::decode(gmat, inter, nb, n, u, levels_lut, w, col);
+                unit_fma<GU_ROWS>(w, col, gu_smem, x_pitch, gate.k_logical, ag);
+                Unit<TYPE>::decode(umat, inter, nb, n, u, levels_lut, w, col);
+                unit_fma<GU_ROWS>(w, col, gu_smem, x_pitch, gate.k_logical, au);
+            }
+#pragma unroll
+            for (int r = 0; r < GU_ROWS; r++) {
+                float g = ag[r], v = au[r];
+                for (int o = 16; o; o >>= 1) { g += __shfl_xor_sync(0xffffffffu, g, o); v += __shfl_xor_sync(0xffffffffu, v, o); }
+                if (lane == 0 && (uint32_t)r < nr) {
+                    const float a = __fmul_rn(__fmul_rn(g, sigmoid_libm(g)), v);
+                    if (!finite_f32(a)) atomicOr(status, QW4SH_ERR_NONFINITE);
+                    const uint32_t dst = row_to_pair ? row_to_pair[first + r0 + r] : r0 + r;
+                    act[(uint64_t)dst * inter + n] = a;
+                }
+            }
+        }
+    }
+}
+
+// Any-format version (one lane per column, exact decode_value): covers F32/F16/BF16/Q8_0/
+// MXFP4 tensors and shapes whose K is not a multiple of 256.
+__global__ void __launch_bounds__(256) gate_up_generic_kernel(DevTensor gate, DevTensor up, const float *__restrict__ x,
+                                                              uint32_t hidden, const uint32_t *__restrict__ offsets,
+                                                              const uint32_t *__restrict__ row_to_pair,
+                                                              const uint32_t *__restrict__ active, uint32_t k_div, uint32_t tokens,
+                                                              float *__restrict__ act, uint32_t *status) {
+    const uint32_t inter = gate.n_out;
+    uint32_t expert = 0, first = 0, count = tokens;
+    if (row_to_pair) {
+        if (blockIdx.y >= active[0]) return;
+        expert = active[1 + blockIdx.y];
+        first = offsets[expert];
+        count = offsets[expert + 1] - first;
+    }
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t n = blockIdx.x * 8 + warp; n < inter; n += gridDim.x * 8)
+        for (uint32_t r = 0; r < count; r++) {
+            const uint32_t pair = row_to_pair ? row_to_pair[first + r] : r;
+            const float *xr = x + (uint64_t)(row_to_pair ? pair / k_div : pair) * hidden;
+            float g = 0.f, v = 0.f;
+            for (uint32_t c = lane; c < gate.k_logical; c += 32) {
+                g = fmaf(decode_value(gate, expert, n, c), xr[c], g);
+                v = fmaf(decode_value(up, expert, n, c), xr[c], v);
+            }
+            for (int o = 16; o; o >>= 1) { g += __shfl_xor_sync(0xffffffffu, g, o); v += __shfl_xor_sync(0xffffffffu, v, o); }
+            if (lane == 0) {
+                const float a = __fmul_rn(__fmul_rn(g, sigmoid_libm(g)), v);
+                if (!finite_f32(a)) atomicOr(status, QW4SH_ERR_NONFINITE);
+                act[(uint64_t)pair * inter + n] = a;
+            }
+        }
+}
+
+// y[t, c] = sum over slots (in slot order) of weight[t,s] * (down_e[c] . act[t*k+s])
+//           + sigmoid(shared_logit[t]) * (shared_down[c] . shared_act[t])
+// (src/qwen4_moe.c:362-380).  grid = (ceil(hidden / DR_TILE), tokens).
+constexpr int DR_WARPS = 8;
+constexpr int DR_TILE = 64;
+
+template <uint32_t TYPE>
+__device__ __forceinline__ float row_dot(const DevTensor &t, const uint8_t *mat, uint32_t row, const float *xs,
+                                         const uint16_t *levels_lut, uint32_t lane) {
+    float acc[1] = {0.f};
+    const uint32_t nb = t.k_storage >> 8, units = t.k_storage >> 5;
+    for (uint32_t u = lane; u < units; u += 32) {
+        float w[32];
+        uint32_t col[4];
+        Unit<TYPE>::decode(mat, t.n_out, nb, row, u, levels_lut, w, col);
+        unit_fma<1>(w, col, xs, 0, t.k_logical, acc);
+    }
+    float v = acc[0];
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+template <>
+__device__ __forceinline__ float row_dot<0xffffffffu>(const DevTensor &t, const uint8_t *mat, uint32_t row, const float *xs,
+                                                       const uint16_t *, uint32_t lane) {
+    float v = 0.f;
+    const uint32_t expert = (uint32_t)((mat - t.data) / (t.expert_bytes ? t.expert_bytes : 1));
+    for (uint32_t c = lane; c < t.k_logical; c += 32) v = fmaf(decode_value(t, expert, row, c), xs[xs_index(c)], v);
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <uint32_t RT, uint32_t ST>
+__global__ void __launch_bounds__(DR_WARPS * 32) down_reduce_kernel(DevTensor down, DevTensor sdown, const float *__restrict__ act,
+                                                                    const float *__restrict__ shared_act,
+                                                                    const uint32_t *__restrict__ ids, const float *__restrict__ weights,
+                                                                    const float *__restrict__ shared_logit, uint32_t k,
+                                                                    float *__restrict__ y, float *__restrict__ routed, uint32_t *status) {
+    extern __shared__ __align__(16) float dr_smem[];
+    __shared__ uint16_t levels_lut[256];
+    const uint32_t t = blockIdx.y, hidden = down.n_out, inter = down.k_logical, sinter = sdown.k_logical;
+    const uint32_t a_pitch = xs_index(inter) + 4;
+    float *sa = dr_smem + (uint64_t)k * a_pitch;
+    if (RT == T_IQ2_XXS || ST == T_IQ2_XXS) for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) levels_lut[i] = c_iq2_levels[i];
+    for (uint32_t i = threadIdx.x; i < k * inter; i += blockDim.x) {
+        const uint32_t s = i / inter, c = i % inter;
+        dr_smem[s * a_pitch + xs_index(c)] = act[((uint64_t)t * k + s) * inter + c];
+    }
+    for (uint32_t i = threadIdx.x; i < sinter; i += blockDim.x) sa[xs_index(i)] = shared_act[(uint64_t)t * sinter + i];
+    __syncthreads();
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const float gate = sigmoid_libm(shared_logit[t]);
+    for (uint32_t j = warp; j < DR_TILE; j += DR_WARPS) {
+        const uint32_t c = blockIdx.x * DR_TILE + j;
+        if (c >= hidden) break;
+        float sum = 0.f;
+        bool bad = false;
+        for (uint32_t s = 0; s < k; s++) {
+            const uint32_t e = ids[(uint64_t)t * k + s];
+            if (e >= down.n_experts) { bad = true; continue; }
+            const float dot = row_dot<RT>(down, down.data + (uint64_t)e * down.expert_bytes, c, dr_smem + s * a_pitch, levels_lut, lane);
+            sum = __fadd_rn(sum, __fmul_rn(weights[(uint64_t)t * k + s], dot));
+        }
+        const float sdot = row_dot<ST>(sdown, sdown.data, c, sa, levels_lut, lane);
+        const float out = __fadd_rn(sum, __fmul_rn(gate, sdot));
+        if (lane == 0) {
+            if (bad) atomicOr(status, QW4SH_ERR_BOUNDS);
+            if (!finite_f32(out) || !finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
+            if (routed) routed[(uint64_t)t * hidden + c] = sum;
+            y[(uint64_t)t * hidden + c] = out;
+        }
+    }
+}
+
+
+// ------------------------------------------------------------------------------------
+// Launch helpers
+// ------------------------------------------------------------------------------------
+static const uint32_t GENERIC = 0xffffffffu;
+static uint32_t kernel_type(uint32_t type, uint32_t k_storage) {
+    return ((type == T_Q4_K || type == T_Q2_K || type == T_IQ2_XXS) && k_storage % 256 == 0) ? type : GENERIC;
+}
+static size_t xs_floats(size_t k) { return k + ((k >> 5) << 2) + 4; }
+
+template <typename Kernel>
+static int allow_smem(Kernel kernel, size_t smem) {
+    if (smem > 200u * 1024u) return fail(cudaErrorInvalidValue, "shape needs more shared memory than one CTA has");
+    if (smem > 48u * 1024u) CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    return 0;
+}
+
+extern "C" int qw4sh_route(uint32_t experts, uint32_t k, int norm, const float *logits, size_t pitch, size_t tokens,
+                           float *probs, uint32_t *ids, float *weights, uint32_t *status, void *stream) {
+    if (!tokens) return 0;
+    if (ensure_constants()) return -1;
+    const size_t per_warp = (size_t)experts * sizeof(float);
+    int warps = 4;
+    while (warps > 1 && per_warp * warps > 96u * 1024u) warps >>= 1;
+    const size_t smem = per_warp * warps;
+    if (allow_smem(route_kernel, smem)) return -1;
+    const unsigned blocks = (unsigned)((tokens + warps - 1) / warps);
+    route_kernel<<<blocks, warps * 32, smem, (cudaStream_t)stream>>>(experts, k, norm, logits, pitch, (uint32_t)tokens, probs, ids, weights, status);
+    LAUNCHED("route_kernel");
+    return 0;
+}
+
+extern "C" int qw4sh_group(uint32_t experts, uint32_t k, size_t tokens, const uint32_t *ids, uint32_t *offsets,
+                           uint32_t *pair_to_row, uint32_t *row_to_pair, uint32_t *active, uint32_t *status, void *stream) {
+    const size_t smem = ((size_t)experts + 1) * sizeof(uint32_t);
+    if (allow_smem(group_kernel, smem)) return -1;
+    group_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(experts, (uint32_t)(tokens * k), ids, offsets, pair_to_row, row_to_pair, active, status);
+    LAUNCHED("group_kernel");
+    return 0;
+}
+
+static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens, float *logits, float *shared_logit,
+                         uint32_t *status, int mode, cudaStream_t stream) {
+    const DevTensor router = as_dev(layer->w[0]), srouter = as_dev(layer->w[7]);
+    const uint32_t rows = layer->experts + 1;
+    if (mode == 0) {
+        if (tokens <= 1) {
+            router_exact_kernel<1><<<dim3((rows + 31) / 32, (unsigned)tokens), dim3(32, 1), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        } else if (tokens <= 4) {
+            router_exact_kernel<4><<<dim3((rows + 31) / 32, (unsigned)((tokens + 3) / 4)), dim3(32, 4), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        } else {
+            router_exact_kernel<8><<<dim3((rows + 31) / 32, (unsigned)((tokens + 7) / 8)), dim3(32, 8), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        }
+        LAUNCHED("router_exact_kernel");
+    } else {
+        const unsigned ty = (unsigned)((tokens + 7) / 8);
+        router_fast_kernel<<<dim3((rows + 7) / 8, ty > 64 ? 64 : ty), 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        LAUNCHED("router_fast_kernel");
+    }
+    return 0;
+}
+
+static int launch_gate_up(const DevTensor &gate, const DevTensor &up, const float *x, uint32_t hidden, const uint32_t *offsets,
+                          const uint32_t *row_to_pair, const uint32_t *active, uint32_t k_div, uint32_t tokens, uint32_t groups,
+                          float *act, uint32_t *status, cudaStream_t stream) {
+    uint32_t type = kernel_type(gate.type, gate.k_storage);
+    if (up.type != gate.type || hidden % 4) type = GENERIC;
+    const size_t smem = (size_t)GU_ROWS * xs_floats(hidden) * sizeof(float);
+    const dim3 grid((gate.n_out + GU_TILE - 1) / GU_TILE, groups);
+#define GU_CASE(T) case T: if (allow_smem(gate_up_kernel<T>, smem)) return -1; \
+    gate_up_kernel<T><<<grid, GU_WARPS * 32, smem, stream>>>(gate, up, x, hidden, offsets, row_to_pair, active, k_div, tokens, act, status); break;
+    switch (type) {
+        GU_CASE(T_Q4_K) GU_CASE(T_Q2_K) GU_CASE(T_IQ2_XXS)
+    default: {
+        const unsigned gx = (gate.n_out + 7) / 8;
+        gate_up_generic_kernel<<<dim3(gx > 256 ? 256 : gx, groups), 256, 0, stream>>>(gate, up, x, hidden, offsets, row_to_pair, active, k_div, tokens, act, status);
+    }
+    }
+#undef GU_CASE
+    LAUNCHED("gate_up_kernel");
+    return 0;
+}
+
+template <uint32_t RT>
+static int launch_down_st(uint32_t st, const DevTensor &down, const DevTensor &sdown, const float *act, const float *shared_act,
+                          const uint32_t *ids, const float *weights, const float *shared_logit, uint32_t k, uint32_t tokens,
+                          float *y, float *routed, uint32_t *status, cudaStream_t stream) {
+    const size_t smem = ((size_t)k * xs_floats(down.k_logical) + xs_floats(sdown.k_logical)) * sizeof(float);
+    const dim3 grid((down.n_out + DR_TILE - 1) / DR_TILE, tokens);
+#define DR_CASE(S) case S: if (allow_smem(down_reduce_kernel<RT, S>, smem)) return -1; \
+    down_reduce_kernel<RT, S><<<grid, DR_WARPS * 32, smem, stream>>>(down, sdown, act, shared_act, ids, weights, shared_logit, k, y, routed, status); break;
+    switch (st) {
+        DR_CASE(T_Q4_K) DR_CASE(T_Q2_K) DR_CASE(T_IQ2_XXS)
+    default:
+        if (allow_smem(down_reduce_kernel<RT, GENERIC>, smem)) return -1;
+        down_reduce_kernel<RT, GENERIC><<<grid, DR_WARPS * 32, smem, stream>>>(down, sdown, act, shared_act, ids, weights, shared_logit, k, y, routed, status);
+    }
+#undef DR_CASE
+    LAUNCHED("down_reduce_kernel");
+    return 0;
+}
+
+static int launch_down(const DevTensor &down, const DevTensor &sdown, const float *act, const float *shared_act,
+                       const uint32_t *ids, const float *weights, const float *shared_logit, uint32_t k, uint32_t tokens,
+                       float *y, float *routed, uint32_t *status, cudaStream_t stream) {
+    const uint32_t rt = kernel_type(down.type, down.k_storage), st = kernel_type(sdown.type, sdown.k_storage);
+    switch (rt) {
+    case T_Q4_K: return launch_down_st<T_Q4_K>(st, down, sdown, act, shared_act, ids, weights, shared_logit, k, tokens, y, routed, status, stream);
+    case T_Q2_K: return launch_down_st<T_Q2_K>(st, down, sdown, act, shared_act, ids, weights, shared_logit, k, tokens, y, routed, status, stream);
+    case T_IQ2_XXS: return launch_down_st<T_IQ2_XXS>(st, down, sdown, act, shared_act, ids, weights, shared_logit, k, tokens, y, routed, status, stream);
+    default: return launch_down_st<GENERIC>(st, down, sdown, act, shared_act, ids, weights, shared_logit, k, tokens, y, routed, status, stream);
+    }
+}
+
+__global__ void copy_routes_kernel(const uint32_t *ids, const float *weights, uint32_t n, uint32_t *ids_out, float *weights_out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { if (ids_out) ids_out[i] = ids[i]; if (weights_out) weights_out[i] = weights[i]; }
+}
+
+extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
+                                   uint32_t *ids_out, float *weights_out, int router_mode) {
+    if (!tokens) return 0;
+    if (ensure_constants()) return -1;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
+    int rc;
+    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
+    if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
+    if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
+    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), x, H, work->offsets, work->row_to_pair, work->active, k, T,
+                             groups, work->act, work->status, stream))) return rc;
+    if ((rc = launch_gate_up(as_dev(layer->w[4]), as_dev(layer->w[5]), x, H, nullptr, nullptr, nullptr, 1, T, 1,
+                             work->shared_act, work->status, stream))) return rc;
+    if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
+                          work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
+    if (ids_out || weights_out) {
+        copy_routes_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(work->ids, work->weights, T * k, ids_out, weights_out);
+        LAUNCHED("copy_routes_kernel");
+    }
+    return 0;
+}

@@ -1,0 +1,591 @@
+/* C11 host side of the B200 Qwen4 MoE operator: handles, argument checking with the
+ * reference's status codes, residency of the weights in HBM, host<->device staging.  All
+ * arithmetic is in the CUDA translation units behind cuda_shim.h; there is no CPU path.
+ *
+ * The entry points mirror picoforge src/qwen4_moe.h:13-27 (see include/qwen4_moe_b200.h).
+ */
+#include "../../include/qwen4_moe_b200.h"
+#include "cuda_shim.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+_Static_assert(sizeof(float) == 4 && sizeof(uint32_t) == 4, "32-bit elements");
+_Static_assert(sizeof(Qwen4F32) == 88 && sizeof(QW4PackedLayout) == 64, "ABI layout");
+
+enum { CHUNK_TOKENS = 2048, PIN_BYTES = 256 * 1024 };
+
+struct Qwen4Moe {
+    Qwen4MoeConfig c;
+    QW4PackedCpuView host[8];     /* spans kept for the alias checks of forward */
+    QW4ShLayer layer;             /* resident image */
+    void *image[8];
+    size_t device_bytes;
+    size_t refs;
+    bool alive;
+};
+
+struct Qwen4MoeWork {
+    Qwen4Moe *owner;
+    size_t cap, chunk, host_bytes, device_bytes;
+    bool busy, failed;
+    QW4ShWork d;
+    void *device_block;           /* one allocation carved into d.* */
+    uint32_t *status_host;        /* pinned [4] */
+    unsigned char *pin;           /* pinned staging: x | y | ids | weights for small batches */
+    QW4MoeObserver observer;
+    void *observer_ctx;
+};
+
+typedef struct { uintptr_t first, end; } Span;
+
+/* ---- errors --------------------------------------------------------------------------- */
+static Qwen4Status report(Qwen4Error *err, Qwen4Status code, const char *detail) {
+    if (err) {
+        memset(err, 0, sizeof *err);
+        err->code = code;
+        if (code != QW4_OK) {
+            snprintf(err->subject, sizeof err->subject, "qwen4_moe");
+            snprintf(err->detail, sizeof err->detail, "%s", detail);
+        }
+    }
+    return code;
+}
+static Qwen4Status cuda_failure(Qwen4Error *err, const char *what) {
+    char text[256];
+    snprintf(text, sizeof text, "%s: %s", what, qw4sh_last_error());
+    return report(err, QW4_GPU_ERROR, text);
+}
+#define TRY(call) do { Qwen4Status st_ = (call); if (st_ != QW4_OK) return st_; } while (0)
+
+static int router_mode = -1;
+static int current_router_mode(void) {
+    if (router_mode < 0) {
+        const char *env = getenv("QW4CU_ROUTER");
+        router_mode = env && strcmp(env, "fast") == 0 ? 1 : 0;
+    }
+    return router_mode;
+}
+void qw4cu_set_router_mode(int mode) { router_mode = mode ? 1 : 0; }
+int qw4cu_get_router_mode(void) { return current_router_mode(); }
+
+/* ---- view checks (status codes as picoforge src/qwen4_moe.c:138-186) ------------------ */
+static Qwen4Status check_config(const Qwen4MoeConfig *c, Qwen4Error *err) {
+    if (!c) return report(err, QW4_INVALID_ARGUMENT, "null config");
+    if (!c->hidden_size || !c->experts || !c->top_k || c->top_k > c->experts || !c->intermediate ||
+        !c->shared_intermediate || c->down_physical < c->intermediate)
+        return report(err, QW4_RANGE, "invalid MoE dimensions");
+    return QW4_OK;
+}
+static Qwen4Status check_memory(const void *data, size_t cap, size_t bytes, size_t alignment, Span *span, Qwen4Error *err) {
+    span->first = span->end = 0;
+    if (!bytes) return QW4_OK;
+    if (cap < bytes) return report(err, QW4_CAPACITY, "view capacity too small");
+    if (!data) return report(err, QW4_INVALID_ARGUMENT, "null nonempty view");
+    const uintptr_t first = (uintptr_t)data;
+    if (first % alignment) return report(err, QW4_STRIDE, "unaligned view");
+    if (bytes > UINTPTR_MAX - first) return report(err, QW4_OVERFLOW, "address extent overflow");
+    span->first = first; span->end = first + bytes;
+    return QW4_OK;
+}
+static Qwen4Status check_rows(const void *data, size_t cap, size_t rows, size_t cols, size_t pitch, Span *span, Qwen4Error *err) {
+    span->first = span->end = 0;
+    if (cols > SIZE_MAX / 4) return report(err, QW4_OVERFLOW, "row bytes overflow");
+    const size_t row_bytes = cols * 4;
+    if (pitch % 4 || pitch < row_bytes) return report(err, QW4_STRIDE, "row stride must cover contiguous features");
+    if (!rows) return QW4_OK;
+    if (rows - 1 > (SIZE_MAX - row_bytes) / pitch) return report(err, QW4_OVERFLOW, "view extent overflow");
+    return check_memory(data, cap, (rows - 1) * pitch + row_bytes, 4, span, err);
+}
+static Qwen4Status check_f32(const float *data, size_t cap, size_t rank, const size_t *dim, const size_t *stride,
+                             size_t rows, size_t cols, Span *span, Qwen4Error *err) {
+    if (rank != 2 || dim[0] != rows || dim[1] != cols) return report(err, QW4_SHAPE, "expected rank-2 token-major view");
+    if (stride[1] != sizeof(float)) return report(err, QW4_STRIDE, "features must be contiguous");
+    return check_rows(data, cap, rows, cols, stride[0], span, err);
+}
+static Qwen4Status check_disjoint(const Span *spans, size_t n, Qwen4Error *err) {
+    for (size_t i = 0; i < n; i++)
+        for (size_t j = 0; j < i; j++)
+            if (spans[i].first < spans[j].end && spans[j].first < spans[i].end)
+                return report(err, QW4_INVALID_ARGUMENT, "overlapping views");
+    return QW4_OK;
+}
+
+/* ---- packed layouts (status codes as picoforge src/qwen4_packed.c:8-50) --------------- */
+static bool format_of(uint32_t type, size_t *block, size_t *bytes) {
+    static const struct { uint32_t id; size_t block, bytes; } table[] = {
+        {0, 1, 4}, {1, 1, 2}, {8, 32, 34}, {10, 256, 84}, {12, 256, 144}, {16, 256, 66}, {30, 1, 2}, {39, 32, 17}};
+    for (size_t i = 0; i < sizeof table / sizeof *table; i++)
+        if (table[i].id == type) { *block = table[i].block; *bytes = table[i].bytes; return true; }
+    return false;
+}
+static bool mul_ok(size_t a, size_t b, size_t *out) {
+    if (a && b > SIZE_MAX / a) return false;
+    *out = a * b;
+    return true;
+}
+static Qwen4Status check_packed(const QW4PackedCpuView *v, Qwen4Error *err) {
+    const QW4PackedLayout *l = &v->layout;
+    size_t block, bytes, row, expert, tensor;
+    if (!format_of(l->gguf_type, &block, &bytes)) return report(err, QW4_FORMAT, "invalid weight view: format not executable");
+    if (!l->k_logical || l->k_logical > l->k_storage || !l->n_out || !l->n_experts)
+        return report(err, QW4_SHAPE, "invalid weight view: empty or incompatible dimensions");
+    if (l->k_storage % block) return report(err, QW4_FORMAT, "invalid weight view: incomplete physical block");
+    if (!mul_ok(l->k_storage / block, bytes, &row) || !mul_ok(row, l->n_out, &expert) || !mul_ok(expert, l->n_experts, &tensor))
+        return report(err, QW4_OVERFLOW, "invalid weight view: tensor extent overflow");
+    if (l->row_bytes != row || l->expert_bytes != expert || l->tensor_bytes != tensor)
+        return report(err, QW4_FORMAT, "invalid weight view: layout bytes differ from physical shape");
+    if (v->span.bytes < tensor) return report(err, QW4_CAPACITY, "invalid weight view: span shorter than tensor");
+    if (!v->span.data || tensor > UINTPTR_MAX - (uintptr_t)v->span.data)
+        return report(err, QW4_INVALID_ARGUMENT, "invalid weight view: bad address");
+    if (l->k_storage > UINT32_MAX || l->n_out > UINT32_MAX || l->n_experts > UINT32_MAX || row > UINT32_MAX)
+        return report(err, QW4_OVERFLOW, "invalid weight view: dimension exceeds 32 bits");
+    return QW4_OK;
+}
+
+/* ---- create / destroy ------------------------------------------------------------------ */
+static void release(Qwen4Moe *m) {
+    if (m && --m->refs == 0) {
+        for (int a = 0; a < 8; a++) qw4sh_free(m->image[a]);
+        free(m);
+    }
+}
+
+Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, Qwen4Moe **out, Qwen4Error *err) {
+    if (out) *out = NULL;
+    if (!out || !weights) return report(err, QW4_INVALID_ARGUMENT, "null create argument");
+    TRY(check_config(c, err));
+    const QW4PackedCpuView w[8] = {weights->router, weights->gate, weights->up, weights->down,
+        weights->shared_gate, weights->shared_up, weights->shared_down, weights->shared_router};
+    const size_t h = c->hidden_size, i = c->intermediate, s = c->shared_intermediate;
+    const size_t in[8] = {h, h, h, i, h, h, s, h}, n[8] = {c->experts, i, i, h, s, s, h, 1};
+    for (size_t a = 0; a < 8; a++) {
+        const QW4PackedLayout *l = &w[a].layout;
+        const size_t experts = (a >= 1 && a <= 3) ? c->experts : 1;
+        if (l->k_logical != in[a] || l->n_out != n[a] || l->n_experts != experts ||
+            l->k_storage != (a == 3 ? c->down_physical : in[a]))
+            return report(err, QW4_SHAPE, "MoE weight shape mismatch");
+        if ((a == 0 || a == 7) && l->gguf_type != 0) return report(err, QW4_FORMAT, "router must be F32");
+        TRY(check_packed(&w[a], err));
+    }
+    if (qw4sh_device_count() <= 0) return cuda_failure(err, "no CUDA device");
+    Qwen4Moe *m = calloc(1, sizeof *m);
+    if (!m) return report(err, QW4_OOM, "MoE allocation");
+    m->c = *c; memcpy(m->host, w, sizeof w); m->refs = 1; m->alive = true;
+    m->layer.hidden = c->hidden_size; m->layer.experts = c->experts; m->layer.top_k = c->top_k;
+    m->layer.inter = c->intermediate; m->layer.shared_inter = c->shared_intermediate;
+    m->layer.down_physical = c->down_physical; m->layer.norm = c->norm_topk_prob ? 1 : 0;
+    for (size_t a = 0; a < 8; a++) {
+        const QW4PackedLayout *l = &w[a].layout;
+        if (qw4sh_upload_tensor(w[a].span.data, l->tensor_bytes, l->gguf_type, l->k_storage, l->n_out, l->n_experts, &m->image[a])) {
+            release(m);
+            return cuda_failure(err, "weight upload");
+        }
+        m->device_bytes += l->tensor_bytes;
+        m->layer.w[a] = (QW4ShTensor){.data = m->image[a], .type = l->gguf_type, .k_storage = (uint32_t)l->k_storage,
+            .k_logical = (uint32_t)l->k_logical, .n_out = (uint32_t)l->n_out, .n_experts = (uint32_t)l->n_experts,
+            .row_bytes = (uint32_t)l->row_bytes, .expert_bytes = l->expert_bytes};
+    }
+    *out = m;
+    return report(err, QW4_OK, "");
+}
+
+void qwen4_moe_destroy(Qwen4Moe *m) {
+    if (m && m->alive) { m->alive = false; release(m); }
+}
+size_t qw4cu_moe_device_bytes(const Qwen4Moe *m) { return m ? m->device_bytes : 0; }
+
+/* ---- workspace ------------------------------------------------------------------------- */
+static void *status_start(Qwen4MoeWork *w) {
+    w->status_host[0] = 0; w->status_host[1] = UINT32_MAX; w->status_host[2] = 0; w->status_host[3] = 0;
+    return w->status_host;
+}
+/* Clears the device error word, ahead of a batch of launches. */
+static int status_clear(Qwen4MoeWork *w) {
+    status_start(w);
+    return qw4sh_memcpy2d_async(w->d.status, 16, w->status_host, 16, 16, 1, 1, w->d.stream);
+}
+typedef struct { size_t offset[16], total; } Plan;
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan *plan, Qwen4Error *err) {
+    if (!m || !m->alive) return report(err, QW4_BAD_STATE, "inactive MoE");
+    const size_t t = cap < CHUNK_TOKENS ? cap : CHUNK_TOKENS, k = m->c.top_k, e = m->c.experts, h = m->c.hidden_size;
+    if (k && t > SIZE_MAX / k) return report(err, QW4_OVERFLOW, "pair count overflow");
+    const size_t pairs = t * k;
+    const size_t count[15] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
+        pairs * m->c.intermediate, t * m->c.shared_intermediate, t * h, 4};
+    size_t at = 0;
+    for (int j = 0; j < 15; j++) {
+        if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
+        plan->offset[j] = at;
+        at += align256(count[j] * 4 + 4);
+    }
+    plan->total = at;
+    *chunk = t;
+    return QW4_OK;
+}
+
+Qwen4Status qwen4_moe_work_size(const Qwen4Moe *m, size_t cap, size_t *bytes, Qwen4Error *err) {
+    if (!bytes) return report(err, QW4_INVALID_ARGUMENT, "null size output");
+    *bytes = 0;
+    Plan plan; size_t chunk;
+    TRY(plan_work(m, cap, &chunk, &plan, err));
+    *bytes = sizeof(Qwen4MoeWork) + PIN_BYTES + 64;
+    return report(err, QW4_OK, "");
+}
+
+void qwen4_moe_work_destroy(Qwen4MoeWork *w) {
+    if (!w || w->busy) return;
+    if (w->d.stream) qw4sh_stream_sync(w->d.stream);
+    qw4sh_event_destroy(w->d.timer[0]); qw4sh_event_destroy(w->d.timer[1]);
+    qw4sh_stream_destroy(w->d.stream);
+    qw4sh_free(w->device_block);
+    qw4sh_host_free(w->status_host);
+    qw4sh_host_free(w->pin);
+    release(w->owner);
+    free(w);
+}
+
+Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, Qwen4MoeWork **out, Qwen4Error *err) {
+    if (out) *out = NULL;
+    if (!out) return report(err, QW4_INVALID_ARGUMENT, "null workspace output");
+    Plan plan; size_t chunk;
+    TRY(plan_work(m, cap, &chunk, &plan, err));
+    const size_t host_bytes = sizeof(Qwen4MoeWork) + PIN_BYTES + 64;
+    if (budget < host_bytes) return report(err, QW4_CAPACITY, "workspace budget too small");
+    Qwen4MoeWork *w = calloc(1, sizeof *w);
+    if (!w) return report(err, QW4_OOM, "workspace metadata");
+    w->owner = (Qwen4Moe *)m; w->owner->refs++;
+    w->cap = cap; w->chunk = chunk; w->host_bytes = host_bytes; w->device_bytes = plan.total;
+    w->device_block = qw4sh_malloc(plan.total);
+    w->status_host = qw4sh_host_alloc(64);
+    w->pin = qw4sh_host_alloc(PIN_BYTES);
+    if (!w->device_block || !w->status_host || !w->pin || qw4sh_stream_create(&w->d.stream) ||
+        qw4sh_event_create(&w->d.timer[0]) || qw4sh_event_create(&w->d.timer[1])) {
+        Qwen4Status st = cuda_failure(err, "workspace allocation");
+        qwen4_moe_work_destroy(w);
+        return st;
+    }
+    char *base = w->device_block;
+    w->d.cap = chunk;
+    w->d.x = (float *)(base + plan.offset[0]); w->d.y = (float *)(base + plan.offset[1]);
+    w->d.logits = (float *)(base + plan.offset[2]); w->d.probs = (float *)(base + plan.offset[3]);
+    w->d.shared_logit = (float *)(base + plan.offset[4]);
+    w->d.ids = (uint32_t *)(base + plan.offset[5]); w->d.weights = (float *)(base + plan.offset[6]);
+    w->d.offsets = (uint32_t *)(base + plan.offset[7]);
+    w->d.pair_to_row = (uint32_t *)(base + plan.offset[8]); w->d.row_to_pair = (uint32_t *)(base + plan.offset[9]);
+    w->d.active = (uint32_t *)(base + plan.offset[10]);
+    w->d.act = (float *)(base + plan.offset[11]); w->d.shared_act = (float *)(base + plan.offset[12]);
+    w->d.routed = NULL;
+    w->d.status = (uint32_t *)(base + plan.offset[14]);
+    if (qw4sh_memset_async(w->device_block, 0, plan.total, w->d.stream) || status_clear(w) || qw4sh_stream_sync(w->d.stream)) {
+        Qwen4Status st = cuda_failure(err, "workspace clear");
+        qwen4_moe_work_destroy(w);
+        return st;
+    }
+    *out = w;
+    return report(err, QW4_OK, "");
+}
+
+Qwen4Status qwen4_moe_work_reset(Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!w) return report(err, QW4_INVALID_ARGUMENT, "null workspace");
+    if (w->busy) return report(err, QW4_BUSY, "workspace executing");
+    if (!w->owner->alive) return report(err, QW4_BAD_STATE, "destroyed owner");
+    if (qw4sh_memset_async(w->device_block, 0, w->device_bytes, w->d.stream) || status_clear(w) || qw4sh_stream_sync(w->d.stream))
+        return cuda_failure(err, "workspace clear");
+    w->failed = false;
+    return report(err, QW4_OK, "");
+}
+size_t qw4cu_moe_work_device_bytes(const Qwen4MoeWork *w) { return w ? w->device_bytes : 0; }
+
+void qw4_moe_observe(Qwen4MoeWork *w, QW4MoeObserver fn, void *ctx) {
+    if (w && !w->busy) { w->observer = fn; w->observer_ctx = ctx; }
+}
+
+/* ---- forward ---------------------------------------------------------------------------- */
+static Qwen4Status status_result(Qwen4MoeWork *w, Qwen4Error *err) {
+    const uint32_t bits = w->status_host[0];
+    if (bits & QW4SH_ERR_BOUNDS) return report(err, QW4_GPU_ERROR, "expert id outside the tensor");
+    if (bits & QW4SH_ERR_STATE) return report(err, QW4_GPU_ERROR, "device state error");
+    if (bits & QW4SH_ERR_NONFINITE) {
+        Qwen4Status st = report(err, QW4_NONFINITE, "nonfinite input or arithmetic");
+        if (err && w->status_host[1] != UINT32_MAX) err->row = w->status_host[1];
+        return st;
+    }
+    return QW4_OK;
+}
+
+Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *m, const float *x_dev, float *y_dev, size_t tokens,
+                                     uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
+    if (w->owner != m) return report(err, QW4_OWNER, "workspace belongs to another MoE");
+    if (!m->alive || w->failed) return report(err, QW4_BAD_STATE, "inactive MoE/workspace; reset required");
+    if (w->busy) return report(err, QW4_BUSY, "workspace executing");
+    if (tokens > w->cap) return report(err, QW4_CAPACITY, "batch exceeds token capacity");
+    if (tokens && (!x_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    const size_t h = m->c.hidden_size, k = m->c.top_k;
+    for (size_t start = 0; start < tokens; start += w->chunk) {
+        const size_t n = tokens - start < w->chunk ? tokens - start : w->chunk;
+        if (qw4sh_layer_forward(&m->layer, &w->d, x_dev + start * h, y_dev + start * h, n,
+                                ids_dev ? ids_dev + start * k : NULL, weights_dev ? weights_dev + start * k : NULL,
+                                current_router_mode()))
+            return cuda_failure(err, "layer launch");
+    }
+    return report(err, QW4_OK, "");
+}
+
+Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!w) return report(err, QW4_INVALID_ARGUMENT, "null workspace");
+    if (qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream) || qw4sh_stream_sync(w->d.stream)) {
+        w->failed = true;
+        return cuda_failure(err, "stream synchronize");
+    }
+    Qwen4Status st = status_result(w, err);
+    if (st != QW4_OK) { w->failed = true; status_clear(w); qw4sh_stream_sync(w->d.stream); return st; }
+    return report(err, QW4_OK, "");
+}
+
+Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen4MoeRoutes *routes,
+                              Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
+    if (w->owner != m) return report(err, QW4_OWNER, "workspace belongs to another MoE");
+    if (!m->alive || w->failed) return report(err, QW4_BAD_STATE, "inactive MoE/workspace; reset required");
+    if (w->busy) return report(err, QW4_BUSY, "workspace executing");
+    const size_t t = x.dim[0], h = m->c.hidden_size, k = m->c.top_k;
+    if (t > w->cap) return report(err, QW4_CAPACITY, "batch exceeds token capacity");
+    Span spans[4]; size_t ns = 2;
+    TRY(check_f32(x.data, x.capacity_bytes, x.rank, x.dim, x.stride_bytes, t, h, &spans[0], err));
+    TRY(check_f32(y.data, y.capacity_bytes, y.rank, y.dim, y.stride_bytes, t, h, &spans[1], err));
+    if (routes) {
+        TRY(check_f32(routes->weights.data, routes->weights.capacity_bytes, routes->weights.rank, routes->weights.dim,
+                      routes->weights.stride_bytes, t, k, &spans[2], err));
+        if (routes->ids.rows != t || routes->ids.cols != k) return report(err, QW4_SHAPE, "optional route shape mismatch");
+        TRY(check_rows(routes->ids.data, routes->ids.capacity_bytes, t, k, routes->ids.row_stride_bytes, &spans[3], err));
+        ns = 4;
+    }
+    TRY(check_disjoint(spans, ns, err));
+    for (size_t a = 0; a < 8; a++) {
+        const Span weights = {(uintptr_t)m->host[a].span.data, (uintptr_t)m->host[a].span.data + m->host[a].layout.tensor_bytes};
+        for (size_t b = 0; b < ns; b++) {
+            const Span both[2] = {spans[b], weights};
+            TRY(check_disjoint(both, 2, err));
+        }
+    }
+    /* Nonfinite input is rejected before any state is touched (src/qwen4_moe.c:411-413). */
+    for (size_t row = 0; row < t; row++) {
+        const float *p = x.data + row * (x.stride_bytes[0] / 4);
+        for (size_t col = 0; col < h; col++)
+            if (!isfinite(p[col])) return report(err, QW4_NONFINITE, "nonfinite input");
+    }
+    if (!t) return report(err, QW4_OK, "");
+    w->busy = true;
+    Qwen4Status st = QW4_OK;
+    const bool observe = w->observer != NULL;
+    for (size_t start = 0; start < t && st == QW4_OK; start += w->chunk) {
+        const size_t n = t - start < w->chunk ? t - start : w->chunk;
+        const float *xs = x.data + start * (x.stride_bytes[0] / 4);
+        float *ys = y.data + start * (y.stride_bytes[0] / 4);
+        const size_t x_bytes = n * h * 4, r_bytes = n * k * 4;
+        const bool small = 2 * x_bytes + 2 * r_bytes <= PIN_BYTES;
+        float *pin_x = (float *)w->pin, *pin_y = (float *)(w->pin + x_bytes);
+        uint32_t *pin_ids = (uint32_t *)(w->pin + 2 * x_bytes);
+        float *pin_w = (float *)(w->pin + 2 * x_bytes + r_bytes);
+        int rc = status_clear(w);
+        if (small) {
+            for (size_t row = 0; row < n; row++) memcpy(pin_x + row * h, xs + row * (x.stride_bytes[0] / 4), h * 4);
+            rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, pin_x, h * 4, h * 4, n, 1, w->d.stream);
+        } else rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, xs, x.stride_bytes[0], h * 4, n, 1, w->d.stream);
+        if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, w->d.y, n, NULL, NULL, current_router_mode());
+        if (!rc) rc = qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream);
+        if (!rc && small) {
+            rc = qw4sh_memcpy2d_async(pin_y, h * 4, w->d.y, h * 4, h * 4, n, 0, w->d.stream);
+            if (routes) {
+                rc |= qw4sh_memcpy2d_async(pin_ids, k * 4, w->d.ids, k * 4, k * 4, n, 0, w->d.stream);
+                rc |= qw4sh_memcpy2d_async(pin_w, k * 4, w->d.weights, k * 4, k * 4, n, 0, w->d.stream);
+            }
+        }
+        if (!rc) rc = qw4sh_stream_sync(w->d.stream);
+        if (rc) { st = cuda_failure(err, "layer execution"); break; }
+        if ((st = status_result(w, err)) != QW4_OK) break;
+        if (small) {
+            for (size_t row = 0; row < n; row++) {
+                memcpy(ys + row * (y.stride_bytes[0] / 4), pin_y + row * h, h * 4);
+                if (routes) {
+                    memcpy(routes->ids.data + (start + row) * (routes->ids.row_stride_bytes / 4), pin_ids + row * k, k * 4);
+                    memcpy(routes->weights.data + (start + row) * (routes->weights.stride_bytes[0] / 4), pin_w + row * k, k * 4);
+                }
+            }
+        } else {
+            rc = qw4sh_memcpy2d_async(ys, y.stride_bytes[0], w->d.y, h * 4, h * 4, n, 0, w->d.stream);
+            if (routes) {
+                rc |= qw4sh_memcpy2d_async(routes->ids.data + start * (routes->ids.row_stride_bytes / 4), routes->ids.row_stride_bytes,
+                                           w->d.ids, k * 4, k * 4, n, 0, w->d.stream);
+                rc |= qw4sh_memcpy2d_async(routes->weights.data + start * (routes->weights.stride_bytes[0] / 4),
+                                           routes->weights.stride_bytes[0], w->d.weights, k * 4, k * 4, n, 0, w->d.stream);
+            }
+            if (!rc) rc = qw4sh_stream_sync(w->d.stream);
+            if (rc) { st = cuda_failure(err, "result copy"); break; }
+        }
+        if (observe) {                         /* stage 0: router logits; stage 12: y */
+            float *logits = malloc(n * m->c.experts * 4);
+            if (logits && !qw4sh_memcpy(logits, w->d.logits, n * m->c.experts * 4, 0)) {
+                Qwen4F32 in = x; in.data = xs; in.dim[0] = n;
+                Qwen4F32 lo = {.data = logits, .capacity_bytes = n * m->c.experts * 4, .rank = 2,
+                    .dim = {n, m->c.experts, 1, 1}, .stride_bytes = {m->c.experts * 4, 4, 0, 0}};
+                w->observer(w->observer_ctx, 0, 0, start, in, lo);
+                Qwen4F32 yo = {.data = ys, .capacity_bytes = y.capacity_bytes, .rank = 2, .dim = {n, h, 1, 1},
+                    .stride_bytes = {y.stride_bytes[0], 4, 0, 0}};
+                w->observer(w->observer_ctx, 12, SIZE_MAX, start, in, yo);
+            }
+            free(logits);
+        }
+    }
+    w->busy = false;
+    if (st != QW4_OK) { w->failed = true; return st; }
+    return report(err, QW4_OK, "");
+}
+
+/* ---- pure routing ---------------------------------------------------------------------- */
+Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *c, Qwen4F32 logits, Qwen4MoeRoutes routes, Qwen4F32Mut probabilities,
+                            Qwen4Error *err) {
+    TRY(check_config(c, err));
+    const size_t t = logits.dim[0], e = c->experts, k = c->top_k;
+    Span spans[4];
+    TRY(check_f32(logits.data, logits.capacity_bytes, logits.rank, logits.dim, logits.stride_bytes, t, e, &spans[0], err));
+    TRY(check_f32(probabilities.data, probabilities.capacity_bytes, probabilities.rank, probabilities.dim,
+                  probabilities.stride_bytes, t, e, &spans[1], err));
+    TRY(check_f32(routes.weights.data, routes.weights.capacity_bytes, routes.weights.rank, routes.weights.dim,
+                  routes.weights.stride_bytes, t, k, &spans[2], err));
+    if (routes.ids.rows != t || routes.ids.cols != k) return report(err, QW4_SHAPE, "route ID shape mismatch");
+    TRY(check_rows(routes.ids.data, routes.ids.capacity_bytes, t, k, routes.ids.row_stride_bytes, &spans[3], err));
+    TRY(check_disjoint(spans, 4, err));
+    if (!t) return report(err, QW4_OK, "");
+    if (t > UINT32_MAX / 2) return report(err, QW4_OVERFLOW, "too many rows");
+    const size_t ze = t * e * 4, zk = t * k * 4;
+    char *dev = qw4sh_malloc(2 * ze + 2 * zk + 64);
+    char *host = malloc(ze + 2 * zk + 64);
+    Qwen4Status st = QW4_OK;
+    if (!dev || !host) { st = dev ? report(err, QW4_OOM, "route scratch") : cuda_failure(err, "route scratch"); goto done; }
+    float *d_logits = (float *)dev, *d_probs = (float *)(dev + ze), *d_w = (float *)(dev + 2 * ze + zk);
+    uint32_t *d_ids = (uint32_t *)(dev + 2 * ze), *d_status = (uint32_t *)(dev + 2 * ze + 2 * zk);
+    uint32_t status[4] = {0, UINT32_MAX, 0, 0};
+    int rc = qw4sh_memcpy(d_status, status, 16, 1);
+    rc |= qw4sh_memcpy2d_async(d_logits, e * 4, logits.data, logits.stride_bytes[0], e * 4, t, 1, NULL);
+    if (!rc) rc = qw4sh_route(c->experts, c->top_k, c->norm_topk_prob, d_logits, e, t, d_probs, d_ids, d_w, d_status, NULL);
+    if (!rc) rc = qw4sh_stream_sync(NULL);
+    if (!rc) rc = qw4sh_memcpy(status, d_status, 16, 0);
+    if (rc) { st = cuda_failure(err, "route"); goto done; }
+    if (status[0] & QW4SH_ERR_NONFINITE) {
+        st = report(err, QW4_NONFINITE, "nonfinite router logit");
+        if (err) err->row = status[1];
+        goto done;
+    }
+    float *h_probs = (float *)host, *h_w = (float *)(host + ze + zk);
+    uint32_t *h_ids = (uint32_t *)(host + ze);
+    if (qw4sh_memcpy(h_probs, d_probs, ze, 0) || qw4sh_memcpy(h_ids, d_ids, zk, 0) || qw4sh_memcpy(h_w, d_w, zk, 0)) {
+        st = cuda_failure(err, "route readback"); goto done;
+    }
+    for (size_t row = 0; row < t; row++) {
+        memcpy(probabilities.data + row * (probabilities.stride_bytes[0] / 4), h_probs + row * e, e * 4);
+        memcpy(routes.ids.data + row * (routes.ids.row_stride_bytes / 4), h_ids + row * k, k * 4);
+        memcpy(routes.weights.data + row * (routes.weights.stride_bytes[0] / 4), h_w + row * k, k * 4);
+    }
+    st = report(err, QW4_OK, "");
+done:
+    qw4sh_free(dev); free(host);
+    return st;
+}
+
+/* ---- dispatch lists --------------------------------------------------------------------- */
+Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *c, Qwen4U32Mut ids, QW4MoeGrouping g, Qwen4Error *err) {
+    TRY(check_config(c, err));
+    if (ids.cols != c->top_k) return report(err, QW4_SHAPE, "group ID shape mismatch");
+    const size_t e = c->experts, k = c->top_k;
+    if (ids.rows > SIZE_MAX / k || e == SIZE_MAX) return report(err, QW4_OVERFLOW, "group count overflow");
+    const size_t pairs = ids.rows * k;
+    Span spans[5];
+    TRY(check_rows(ids.data, ids.capacity_bytes, ids.rows, ids.cols, ids.row_stride_bytes, &spans[0], err));
+    const void *data[4] = {g.offsets, g.cursors, g.pair_to_row, g.row_to_pair};
+    const size_t counts[4] = {e + 1, e, pairs, pairs};
+    const size_t caps[4] = {g.offsets_capacity_bytes, g.cursors_capacity_bytes, g.pair_to_row_capacity_bytes,
+                            g.row_to_pair_capacity_bytes};
+    for (size_t a = 0; a < 4; a++) {
+        if (counts[a] > SIZE_MAX / sizeof(size_t)) return report(err, QW4_OVERFLOW, "group array bytes overflow");
+        TRY(check_memory(data[a], caps[a], counts[a] * sizeof(size_t), _Alignof(size_t), &spans[a + 1], err));
+    }
+    TRY(check_disjoint(spans, 5, err));
+    for (size_t t = 0; t < ids.rows; t++) {
+        const uint32_t *row = ids.data + t * (ids.row_stride_bytes / 4);
+        for (size_t s = 0; s < k; s++) {
+            if (row[s] >= e) return report(err, QW4_RANGE, "expert ID out of range");
+            for (size_t j = 0; j < s; j++)
+                if (row[j] == row[s]) return report(err, QW4_INVALID_ARGUMENT, "duplicate expert ID");
+        }
+    }
+    if (pairs > UINT32_MAX / 2) return report(err, QW4_OVERFLOW, "too many pairs");
+    const size_t zp = pairs * 4, ze = (e + 1) * 4;
+    char *dev = qw4sh_malloc(3 * zp + 2 * ze + 64 + 16);
+    uint32_t *host = malloc(3 * zp + ze + 64);
+    Qwen4Status st = QW4_OK;
+    if (!dev || !host) { st = dev ? report(err, QW4_OOM, "group scratch") : cuda_failure(err, "group scratch"); goto done; }
+    uint32_t *d_ids = (uint32_t *)dev, *d_p2r = (uint32_t *)(dev + zp), *d_r2p = (uint32_t *)(dev + 2 * zp);
+    uint32_t *d_off = (uint32_t *)(dev + 3 * zp), *d_active = (uint32_t *)(dev + 3 * zp + ze);
+    uint32_t *d_status = (uint32_t *)(dev + 3 * zp + 2 * ze + 16);
+    uint32_t status[4] = {0, 0, 0, 0};
+    int rc = qw4sh_memcpy(d_status, status, 16, 1);
+    if (pairs) rc |= qw4sh_memcpy2d_async(d_ids, k * 4, ids.data, ids.row_stride_bytes, k * 4, ids.rows, 1, NULL);
+    if (!rc) rc = qw4sh_group(c->experts, c->top_k, ids.rows, d_ids, d_off, d_p2r, d_r2p, d_active, d_status, NULL);
+    if (!rc) rc = qw4sh_stream_sync(NULL);
+    uint32_t *h_off = host, *h_p2r = host + (e + 1), *h_r2p = host + (e + 1) + pairs;
+    if (!rc) rc = qw4sh_memcpy(h_off, d_off, ze, 0);
+    if (!rc && pairs) rc = qw4sh_memcpy(h_p2r, d_p2r, zp, 0) | qw4sh_memcpy(h_r2p, d_r2p, zp, 0);
+    if (rc) { st = cuda_failure(err, "group"); goto done; }
+    for (size_t j = 0; j <= e; j++) g.offsets[j] = h_off[j];
+    for (size_t j = 0; j < e; j++) g.cursors[j] = h_off[j + 1];
+    for (size_t j = 0; j < pairs; j++) { g.pair_to_row[j] = h_p2r[j]; g.row_to_pair[j] = h_r2p[j]; }
+    st = report(err, QW4_OK, "");
+done:
+    qw4sh_free(dev); free(host);
+    return st;
+}
+
+/* ---- probes and plumbing ---------------------------------------------------------------- */
+Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *m, uint32_t tensor, size_t expert, size_t row0, size_t rows, float *out,
+                                  size_t out_elements, Qwen4Error *err) {
+    if (!m || !m->alive) return report(err, QW4_BAD_STATE, "inactive MoE");
+    if (tensor >= 8 || !out) return report(err, QW4_INVALID_ARGUMENT, "bad tensor index or output");
+    const QW4ShTensor *t = &m->layer.w[tensor];
+    if (expert >= t->n_experts || row0 > t->n_out || rows > t->n_out - row0) return report(err, QW4_RANGE, "row outside tensor");
+    if (out_elements / t->k_storage < rows) return report(err, QW4_CAPACITY, "short output");
+    if (!rows) return report(err, QW4_OK, "");
+    const size_t bytes = rows * (size_t)t->k_storage * 4;
+    float *dev = qw4sh_malloc(bytes);
+    if (!dev) return cuda_failure(err, "decode scratch");
+    int rc = qw4sh_decode_rows(t, expert, row0, rows, dev, NULL);
+    if (!rc) rc = qw4sh_stream_sync(NULL);
+    if (!rc) rc = qw4sh_memcpy(out, dev, bytes, 0);
+    qw4sh_free(dev);
+    if (rc) return cuda_failure(err, "decode");
+    for (size_t i = 0; i < rows * (size_t)t->k_storage; i++)
+        if (!isfinite(out[i])) return report(err, QW4_NONFINITE, "nonfinite packed value");
+    return report(err, QW4_OK, "");
+}
+
+int qw4cu_device_count(void) { return qw4sh_device_count(); }
+int qw4cu_set_device(int device) { return qw4sh_set_device(device); }
+const char *qw4cu_last_error(void) { return qw4sh_last_error(); }
+uint64_t qw4cu_launch_count(void) { return qw4sh_launch_count(); }
+void *qw4cu_malloc(size_t bytes) { return qw4sh_malloc(bytes); }
+void qw4cu_free(void *p) { qw4sh_free(p); }
+void *qw4cu_host_alloc(size_t bytes) { return qw4sh_host_alloc(bytes); }
+void qw4cu_host_free(void *p) { qw4sh_host_free(p); }
+int qw4cu_upload(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy(dst, src, bytes, 1); }
+int qw4cu_download(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy(dst, src, bytes, 0); }
+int qw4cu_flush_l2(void) { return qw4sh_flush_l2(); }
+int qw4cu_device_synchronize(void) { return qw4sh_device_sync(); }
+int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
+int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }
+float qw4cu_moe_work_timer_elapsed_ms(Qwen4MoeWork *w) { return w ? qw4sh_event_elapsed_ms(w->d.timer[0], w->d.timer[1]) : -1.0f; }
