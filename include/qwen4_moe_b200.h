@@ -241,7 +241,7 @@ size_t qw4cu_moe_work_device_bytes(const Qwen4MoeWork *work);
 
 /* Forward on device pointers: x_dev [tokens, hidden] and y_dev [tokens, hidden] are dense
  * FP32 in HBM; ids_dev [tokens, k] and weights_dev [tokens, k] may be NULL.  Enqueues on
- * the workspace's stream and returns without waiting; errors found by the kernels are
+ * the library's stream (one per device, shared by all workspaces) and returns without waiting; errors found by the kernels are
  * reported by qw4cu_moe_work_sync. */
 Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *moe, const float *x_dev, float *y_dev,
                                      size_t tokens, uint32_t *ids_dev, float *weights_dev,
@@ -255,6 +255,17 @@ Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *work);
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *work);
 float qw4cu_moe_work_timer_elapsed_ms(Qwen4MoeWork *work);
+/* Launch strategy of qw4cu_moe_forward_device.  0 (default): kernels are launched one by
+ * one.  1: the second identical call on a workspace (same layer, pointers, token count) is
+ * captured into a CUDA graph and later identical calls replay it. */
+void qw4cu_set_graph_mode(int on);
+int qw4cu_get_graph_mode(void);
+/* Profiling aid: while on, every layer forward records a CUDA event between its kernels
+ * (router logits, route, group, routed gate+up, shared gate+up, down+reduce) and graphs are
+ * not replayed.  qw4cu_stage_times copies the accumulated milliseconds of the six stages
+ * into ms[6] and the number of forwards into *forwards, then clears both. */
+void qw4cu_set_stage_timing(int on);
+int qw4cu_stage_times(double *ms, uint64_t *forwards);
 /* Kernels launched by this library in this process so far. */
 uint64_t qw4cu_launch_count(void);
 

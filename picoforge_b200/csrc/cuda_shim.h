@@ -40,8 +40,9 @@ typedef struct {
     float *shared_act;            /* [cap, shared_inter] */
     float *routed;                /* [cap, hidden], only when an observer is set */
     uint32_t *status;             /* [4]: error bits, first bad row, spare */
-    void *stream;                 /* cudaStream_t */
+    void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
+    void *graph_cache;            /* replay cache of the launch sequence (qw4sh_graph_cache_create) */
 } QW4ShWork;
 
 enum { QW4SH_ERR_NONFINITE = 1u, QW4SH_ERR_BOUNDS = 2u, QW4SH_ERR_STATE = 4u };
@@ -59,8 +60,21 @@ int qw4sh_memcpy(void *dst, const void *src, size_t bytes, int to_device);
 int qw4sh_memcpy2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch,
                          size_t width_bytes, size_t rows, int to_device, void *stream);
 int qw4sh_memset_async(void *dst, int value, size_t bytes, void *stream);
-int qw4sh_stream_create(void **stream);
-void qw4sh_stream_destroy(void *stream);
+/* The one non-blocking stream this library uses on the current device (created on first use,
+ * never destroyed): layers run one after another, as the engine calls them. */
+int qw4sh_shared_stream(void **stream);
+void *qw4sh_graph_cache_create(void);
+void qw4sh_graph_cache_destroy(void *cache);
+/* 0: launch kernels directly.  1: the second identical forward (same layer, pointers, token
+ * count) is captured into a CUDA graph and later ones replay it. */
+void qw4sh_set_graph_mode(int on);
+int qw4sh_get_graph_mode(void);
+/* Per-kernel timing for profiles: when on, layer forwards record an event between stages
+ * (and never replay graphs).  stage_times returns accumulated milliseconds for the
+ * QW4SH_STAGES stages and the number of forwards accumulated, then clears them. */
+enum { QW4SH_STAGES = 6 };
+void qw4sh_set_stage_timing(int on);
+int qw4sh_stage_times(double *ms, uint64_t *forwards);
 int qw4sh_stream_sync(void *stream);
 int qw4sh_device_sync(void);
 int qw4sh_event_create(void **event);

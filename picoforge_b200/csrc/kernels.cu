@@ -80,13 +80,15 @@ extern "C" int qw4sh_memset_async(void *dst, int value, size_t bytes, void *stre
     if (bytes) CU(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
     return 0;
 }
-extern "C" int qw4sh_stream_create(void **stream) {
-    cudaStream_t s;
-    CU(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-    *stream = s;
+static cudaStream_t g_stream[64] = {nullptr};
+extern "C" int qw4sh_shared_stream(void **stream) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    if (!g_stream[device]) CU(cudaStreamCreateWithFlags(&g_stream[device], cudaStreamNonBlocking));
+    *stream = g_stream[device];
     return ensure_constants();
 }
-extern "C" void qw4sh_stream_destroy(void *stream) { if (stream) cudaStreamDestroy((cudaStream_t)stream); }
 extern "C" int qw4sh_stream_sync(void *stream) { CU(cudaStreamSynchronize((cudaStream_t)stream)); return 0; }
 extern "C" int qw4sh_device_sync(void) { CU(cudaDeviceSynchronize()); return 0; }
 extern "C" int qw4sh_event_create(void **event) { cudaEvent_t e; CU(cudaEventCreate(&e)); *event = e; return 0; }
@@ -838,26 +840,121 @@ __global__ void copy_routes_kernel(const uint32_t *ids, const float *weights, ui
     if (i < n) { if (ids_out) ids_out[i] = ids[i]; if (weights_out) weights_out[i] = weights[i]; }
 }
 
+// ------------------------------------------------------------------------------------
+// Layer forward: direct launches, CUDA-graph replay, or per-stage timing
+// ------------------------------------------------------------------------------------
+struct GraphCache {
+    cudaGraphExec_t exec = nullptr;
+    const void *layer = nullptr, *x = nullptr, *y = nullptr, *ids = nullptr, *weights = nullptr;
+    size_t tokens = 0;
+    int mode = -1, seen = 0;
+};
+extern "C" void *qw4sh_graph_cache_create(void) { return new GraphCache(); }
+extern "C" void qw4sh_graph_cache_destroy(void *cache) {
+    GraphCache *c = (GraphCache *)cache;
+    if (!c) return;
+    if (c->exec) cudaGraphExecDestroy(c->exec);
+    delete c;
+}
+static int g_graph_mode = 0, g_stage_timing = 0;
+extern "C" void qw4sh_set_graph_mode(int on) { g_graph_mode = on ? 1 : 0; }
+extern "C" int qw4sh_get_graph_mode(void) { return g_graph_mode; }
+
+static cudaEvent_t g_stage_event[QW4SH_STAGES + 1] = {nullptr};
+static bool g_stage_pending = false;
+static double g_stage_ms[QW4SH_STAGES] = {0};
+static uint64_t g_stage_forwards = 0;
+static int stage_collect() {
+    if (!g_stage_pending) return 0;
+    CU(cudaEventSynchronize(g_stage_event[QW4SH_STAGES]));
+    for (int i = 0; i < QW4SH_STAGES; i++) {
+        float ms = 0;
+        CU(cudaEventElapsedTime(&ms, g_stage_event[i], g_stage_event[i + 1]));
+        g_stage_ms[i] += ms;
+    }
+    g_stage_forwards++;
+    g_stage_pending = false;
+    return 0;
+}
+extern "C" void qw4sh_set_stage_timing(int on) { g_stage_timing = on ? 1 : 0; }
+extern "C" int qw4sh_stage_times(double *ms, uint64_t *forwards) {
+    if (stage_collect()) return -1;
+    for (int i = 0; i < QW4SH_STAGES; i++) { ms[i] = g_stage_ms[i]; g_stage_ms[i] = 0; }
+    *forwards = g_stage_forwards;
+    g_stage_forwards = 0;
+    return 0;
+}
+
+static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
+                          uint32_t *ids_out, float *weights_out, int router_mode, bool timed) {
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
+    int rc, stage = 0;
+#define STAGE_MARK() do { if (timed) CU(cudaEventRecord(g_stage_event[stage++], stream)); } while (0)
+    STAGE_MARK();
+    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
+    STAGE_MARK();
+    if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
+    STAGE_MARK();
+    if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    STAGE_MARK();
+    const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
+    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), x, H, work->offsets, work->row_to_pair, work->active, k, T,
+                             groups, work->act, work->status, stream))) return rc;
+    STAGE_MARK();
+    if ((rc = launch_gate_up(as_dev(layer->w[4]), as_dev(layer->w[5]), x, H, nullptr, nullptr, nullptr, 1, T, 1,
+                             work->shared_act, work->status, stream))) return rc;
+    STAGE_MARK();
+    if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
+                          work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
+    STAGE_MARK();
+#undef STAGE_MARK
+    if (ids_out || weights_out) {
+        copy_routes_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(work->ids, work->weights, T * k, ids_out, weights_out);
+        LAUNCHED("copy_routes_kernel");
+    }
+    return 0;
+}
+
 extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                                    uint32_t *ids_out, float *weights_out, int router_mode) {
     if (!tokens) return 0;
     if (ensure_constants()) return -1;
     cudaStream_t stream = (cudaStream_t)work->stream;
-    const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
-    int rc;
-    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
-    if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
-    if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
-    const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
-    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), x, H, work->offsets, work->row_to_pair, work->active, k, T,
-                             groups, work->act, work->status, stream))) return rc;
-    if ((rc = launch_gate_up(as_dev(layer->w[4]), as_dev(layer->w[5]), x, H, nullptr, nullptr, nullptr, 1, T, 1,
-                             work->shared_act, work->status, stream))) return rc;
-    if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
-                          work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
-    if (ids_out || weights_out) {
-        copy_routes_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(work->ids, work->weights, T * k, ids_out, weights_out);
-        LAUNCHED("copy_routes_kernel");
+    if (g_stage_timing) {
+        if (stage_collect()) return -1;
+        for (int i = 0; i <= QW4SH_STAGES; i++) if (!g_stage_event[i]) CU(cudaEventCreate(&g_stage_event[i]));
+        const int rc = layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, true);
+        g_stage_pending = rc == 0;
+        return rc;
     }
+    GraphCache *cache = (GraphCache *)work->graph_cache;
+    if (!g_graph_mode || !cache) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
+    const bool same = cache->layer == layer && cache->x == x && cache->y == y && cache->ids == ids_out &&
+                      cache->weights == weights_out && cache->tokens == tokens && cache->mode == router_mode;
+    if (same && cache->exec) {
+        CU(cudaGraphLaunch(cache->exec, stream));
+        __sync_fetch_and_add(&g_launches, (unsigned long long)cache->seen);
+        return 0;
+    }
+    if (!same) {                                      // first sight: run directly (also sets kernel attributes)
+        if (cache->exec) { cudaGraphExecDestroy(cache->exec); cache->exec = nullptr; }
+        cache->layer = layer; cache->x = x; cache->y = y; cache->ids = ids_out; cache->weights = weights_out;
+        cache->tokens = tokens; cache->mode = router_mode;
+        return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
+    }
+    cudaGraph_t graph = nullptr;                      // second sight: capture, then replay
+    const unsigned long long before = g_launches;
+    CU(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
+    cudaError_t e = cudaStreamEndCapture(stream, &graph);
+    cache->seen = (int)(g_launches - before);
+    g_launches = before;
+    if (rc || e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); return rc ? rc : fail(e, "graph capture"); }
+    e = cudaGraphInstantiate(&cache->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { cache->exec = nullptr; return fail(e, "graph instantiate"); }
+    CU(cudaGraphLaunch(cache->exec, stream));
+    __sync_fetch_and_add(&g_launches, (unsigned long long)cache->seen);
     return 0;
 }

@@ -241,7 +241,7 @@ void qwen4_moe_work_destroy(Qwen4MoeWork *w) {
     if (!w || w->busy) return;
     if (w->d.stream) qw4sh_stream_sync(w->d.stream);
     qw4sh_event_destroy(w->d.timer[0]); qw4sh_event_destroy(w->d.timer[1]);
-    qw4sh_stream_destroy(w->d.stream);
+    qw4sh_graph_cache_destroy(w->d.graph_cache);
     qw4sh_free(w->device_block);
     qw4sh_host_free(w->status_host);
     qw4sh_host_free(w->pin);
@@ -263,7 +263,8 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->device_block = qw4sh_malloc(plan.total);
     w->status_host = qw4sh_host_alloc(64);
     w->pin = qw4sh_host_alloc(PIN_BYTES);
-    if (!w->device_block || !w->status_host || !w->pin || qw4sh_stream_create(&w->d.stream) ||
+    w->d.graph_cache = qw4sh_graph_cache_create();
+    if (!w->device_block || !w->status_host || !w->pin || !w->d.graph_cache || qw4sh_shared_stream(&w->d.stream) ||
         qw4sh_event_create(&w->d.timer[0]) || qw4sh_event_create(&w->d.timer[1])) {
         Qwen4Status st = cuda_failure(err, "workspace allocation");
         qwen4_moe_work_destroy(w);
@@ -586,6 +587,10 @@ int qw4cu_upload(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy
 int qw4cu_download(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy(dst, src, bytes, 0); }
 int qw4cu_flush_l2(void) { return qw4sh_flush_l2(); }
 int qw4cu_device_synchronize(void) { return qw4sh_device_sync(); }
+void qw4cu_set_graph_mode(int on) { qw4sh_set_graph_mode(on); }
+int qw4cu_get_graph_mode(void) { return qw4sh_get_graph_mode(); }
+void qw4cu_set_stage_timing(int on) { qw4sh_set_stage_timing(on); }
+int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }
 float qw4cu_moe_work_timer_elapsed_ms(Qwen4MoeWork *w) { return w ? qw4sh_event_elapsed_ms(w->d.timer[0], w->d.timer[1]) : -1.0f; }
