@@ -36,7 +36,7 @@ sys.path.insert(0, str(ROOT))
 from picoforge_b200 import abi, synth  # noqa: E402
 from picoforge_b200.layer import MoeLayer  # noqa: E402
 
-STAGES = ("router_logits", "route", "group", "gate_up_routed", "gate_up_shared", "down_reduce")
+STAGES = ("router_logits", "route", "group", "gate_up_routed", "gate_up_shared", "down_routed", "down_shared", "combine")
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
 
@@ -84,7 +84,7 @@ def stage_bytes(spec, ids):
         "route": 0, "group": 0,
         "gate_up_routed": distinct * (per_expert[1] + per_expert[2]),
         "gate_up_shared": layouts[4].tensor_bytes + layouts[5].tensor_bytes,
-        "down_reduce": distinct * per_expert[3] + layouts[6].tensor_bytes,
+        "down_routed": distinct * per_expert[3], "down_shared": layouts[6].tensor_bytes, "combine": 0,
     }, distinct
 
 
@@ -187,6 +187,7 @@ def main():
     parser.add_argument("--layers", type=int, default=8, help="rotating weight sets (L2 hygiene)")
     parser.add_argument("--router", default="exact", choices=["exact", "fast"])
     parser.add_argument("--no-graph", action="store_true")
+    parser.add_argument("--expert-path", type=int, default=-1, help="-1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--profile", action="store_true",
                         help="only W + K directly launched steps (the command to run under ncu); prints no bench line")
@@ -232,6 +233,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
+    lib.qw4cu_set_expert_path(args.expert_path)
     desc, tokens, specs, x = workload(args.workload, args.layers)
     layers = [MoeLayer(api, spec, tokens) for spec in specs]
     err = abi.Qwen4Error()
@@ -276,7 +278,7 @@ def main():
     for i in range(3 * len(layers)):
         device_step(i)
     sync_all()
-    stage_ms = (C.c_double * 6)()
+    stage_ms = (C.c_double * len(STAGES))()
     forwards = C.c_uint64()
     lib.qw4cu_stage_times(stage_ms, C.byref(forwards))           # discard the warm-up passes
     profile_steps = max(len(layers) * 4, min(args.steps, 200))

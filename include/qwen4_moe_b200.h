@@ -260,10 +260,16 @@ float qw4cu_moe_work_timer_elapsed_ms(Qwen4MoeWork *work);
  * captured into a CUDA graph and later identical calls replay it. */
 void qw4cu_set_graph_mode(int on);
 int qw4cu_get_graph_mode(void);
-/* Profiling aid: while on, every layer forward records a CUDA event between its kernels
- * (router logits, route, group, routed gate+up, shared gate+up, down+reduce) and graphs are
- * not replayed.  qw4cu_stage_times copies the accumulated milliseconds of the six stages
- * into ms[6] and the number of forwards into *forwards, then clears both. */
+/* Which expert kernels run.  -1 (default): batches of up to 64 tokens use the tensor-core
+ * grouped kernels (groups of <= 4 rows, int8 MMA on the raw codes) when every expert tensor is
+ * Q4_K or IQ2_XXS, everything else the CUDA-core kernels.  0: CUDA-core kernels only.  1:
+ * tensor-core grouped kernels for any batch size the formats allow. */
+void qw4cu_set_expert_path(int path);
+/* Profiling aid: while on, every layer forward records a CUDA event between its stages
+ * (router logits + activation quantisation, route, dispatch, routed gate+up, shared gate+up,
+ * routed down, shared down, combine) and graphs are not replayed.  qw4cu_stage_times copies
+ * the accumulated milliseconds of the eight stages into ms[8] and the number of forwards into
+ * *forwards, then clears both. */
 void qw4cu_set_stage_timing(int on);
 int qw4cu_stage_times(double *ms, uint64_t *forwards);
 /* Kernels launched by this library in this process so far. */

@@ -39,6 +39,13 @@ typedef struct {
     float *act;                   /* [cap * k, inter] in pair order */
     float *shared_act;            /* [cap, shared_inter] */
     float *routed;                /* [cap, hidden], only when an observer is set */
+    float *out;                   /* [cap * k, hidden] per-pair down outputs (tensor-core path) */
+    float *shared_out;            /* [cap, hidden] */
+    int8_t *xq;                   /* [cap, 2, hidden] int8 digits of x */
+    int *xsum;                    /* [cap, hidden / 32, 2] digit sums per 32-column chunk */
+    float *xscale;                /* [cap] */
+    void *groups, *shared_groups; /* [cap * k], [cap / 4 + 1] groups of <= 4 rows (16 bytes each) */
+    uint32_t *n_groups;           /* [2]: routed, shared */
     uint32_t *status;             /* [4]: error bits, first bad row, spare */
     void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
@@ -72,8 +79,11 @@ int qw4sh_get_graph_mode(void);
 /* Per-kernel timing for profiles: when on, layer forwards record an event between stages
  * (and never replay graphs).  stage_times returns accumulated milliseconds for the
  * QW4SH_STAGES stages and the number of forwards accumulated, then clears them. */
-enum { QW4SH_STAGES = 6 };
+enum { QW4SH_STAGES = 8 };
 void qw4sh_set_stage_timing(int on);
+/* -1 automatic (tensor-core grouped kernels for small batches), 0 CUDA-core kernels only,
+ * 1 tensor-core grouped kernels whenever the formats allow. */
+void qw4sh_set_expert_path(int path);
 int qw4sh_stage_times(double *ms, uint64_t *forwards);
 int qw4sh_stream_sync(void *stream);
 int qw4sh_device_sync(void);

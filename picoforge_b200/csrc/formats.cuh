@@ -33,7 +33,8 @@ struct DevTensor {
     uint64_t expert_bytes;
 };
 
-__device__ __constant__ uint16_t c_iq2_levels[256];
+// Statically initialised per translation unit: no runtime copy is needed.
+static __device__ __constant__ uint16_t c_iq2_levels[256] = { QW4_IQ2XXS_LEVEL_LIST };
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) {
     return __half2float(__ushort_as_half(h));          // exact, subnormals included

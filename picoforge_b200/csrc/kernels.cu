@@ -32,15 +32,18 @@ static int fail(cudaError_t e, const char *where) {
 #define LAUNCHED(name) do { __sync_fetch_and_add(&g_launches, 1ull); cudaError_t e_ = cudaGetLastError(); \
     if (e_ != cudaSuccess) return fail(e_, name); } while (0)
 
+extern "C" int qw4sh_note_launch(const char *name) {
+    __sync_fetch_and_add(&g_launches, 1ull);
+    cudaError_t e = cudaGetLastError();
+    return e != cudaSuccess ? fail(e, name) : 0;
+}
+
 static bool g_constants_ready[64] = {false};
 static int ensure_constants() {
     int device = 0;
     CU(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
-    if (!g_constants_ready[device]) {
-        CU(cudaMemcpyToSymbol(c_iq2_levels, QW4_IQ2XXS_LEVELS, sizeof QW4_IQ2XXS_LEVELS));
-        g_constants_ready[device] = true;
-    }
+    g_constants_ready[device] = true;
     return 0;
 }
 
@@ -885,29 +888,85 @@ extern "C" int qw4sh_stage_times(double *ms, uint64_t *forwards) {
     return 0;
 }
 
+extern "C" int qw4sh_mma_supported(const QW4ShTensor *w, int mode);
+extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
+                                 const uint32_t *row_to_pair, uint32_t k_div, const int8_t *xq, const int *xsum, const float *xscale,
+                                 const float *act_in, float *out, uint32_t *status, int ctas, void *stream);
+extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int *xsum, float *xscale, void *stream);
+extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,
+                             uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, void *stream);
+extern "C" int qw4sh_build_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream);
+extern "C" int qw4sh_build_dense_groups(uint32_t tokens, void *groups, uint32_t *n_groups, void *stream);
+
+static int g_sm_count[64] = {0};
+static int sm_count() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (!g_sm_count[device] && cudaDeviceGetAttribute(&g_sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        g_sm_count[device] = 148;
+    return g_sm_count[device];
+}
+static int g_expert_path = -1;                     // -1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels
+extern "C" void qw4sh_set_expert_path(int path) { g_expert_path = path; }
+
+// Token batches up to this size take the decode path (groups of <= 4 rows on int8 MMA).
+static const size_t MMA_MAX_TOKENS = 64;
+
+static bool mma_path(const QW4ShLayer *layer, size_t tokens) {
+    if (g_expert_path == 0) return false;
+    if (g_expert_path < 0 && tokens > MMA_MAX_TOKENS) return false;
+    return layer->w[1].type == layer->w[2].type && layer->w[4].type == layer->w[5].type &&
+           qw4sh_mma_supported(&layer->w[1], 0) && qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) &&
+           qw4sh_mma_supported(&layer->w[4], 0) && qw4sh_mma_supported(&layer->w[5], 0) && qw4sh_mma_supported(&layer->w[6], 1);
+}
+
 static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                           uint32_t *ids_out, float *weights_out, int router_mode, bool timed) {
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
+    const bool mma = mma_path(layer, tokens);
     int rc, stage = 0;
 #define STAGE_MARK() do { if (timed) CU(cudaEventRecord(g_stage_event[stage++], stream)); } while (0)
     STAGE_MARK();
     if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
+    if (mma && (rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xsum, work->xscale, stream))) return rc;
     STAGE_MARK();
     if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
     STAGE_MARK();
     if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    if (mma) {
+        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_build_dense_groups(T, work->shared_groups, work->n_groups + 1, stream))) return rc;
+    }
     STAGE_MARK();
-    const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
-    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), x, H, work->offsets, work->row_to_pair, work->active, k, T,
-                             groups, work->act, work->status, stream))) return rc;
-    STAGE_MARK();
-    if ((rc = launch_gate_up(as_dev(layer->w[4]), as_dev(layer->w[5]), x, H, nullptr, nullptr, nullptr, 1, T, 1,
-                             work->shared_act, work->status, stream))) return rc;
-    STAGE_MARK();
-    if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
-                          work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
-    STAGE_MARK();
+    if (mma) {
+        const int ctas = sm_count();
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq,
+                                    work->xsum, work->xscale, nullptr, work->act, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 1, nullptr, 1, work->xq,
+                                    work->xsum, work->xscale, nullptr, work->shared_act, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, k, nullptr, nullptr,
+                                    nullptr, work->act, work->out, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 1, nullptr, 1, nullptr, nullptr,
+                                    nullptr, work->shared_act, work->shared_out, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
+        STAGE_MARK();
+    } else {
+        const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
+        if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), x, H, work->offsets, work->row_to_pair, work->active, k, T,
+                                 groups, work->act, work->status, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = launch_gate_up(as_dev(layer->w[4]), as_dev(layer->w[5]), x, H, nullptr, nullptr, nullptr, 1, T, 1,
+                                 work->shared_act, work->status, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
+                              work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
+        STAGE_MARK(); STAGE_MARK(); STAGE_MARK();
+    }
 #undef STAGE_MARK
     if (ids_out || weights_out) {
         copy_routes_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(work->ids, work->weights, T * k, ids_out, weights_out);

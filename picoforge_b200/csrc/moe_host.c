@@ -207,7 +207,7 @@ static int status_clear(Qwen4MoeWork *w) {
     status_start(w);
     return qw4sh_memcpy2d_async(w->d.status, 16, w->status_host, 16, 16, 1, 1, w->d.stream);
 }
-typedef struct { size_t offset[16], total; } Plan;
+typedef struct { size_t offset[24], total; } Plan;
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan *plan, Qwen4Error *err) {
@@ -215,10 +215,11 @@ static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan 
     const size_t t = cap < CHUNK_TOKENS ? cap : CHUNK_TOKENS, k = m->c.top_k, e = m->c.experts, h = m->c.hidden_size;
     if (k && t > SIZE_MAX / k) return report(err, QW4_OVERFLOW, "pair count overflow");
     const size_t pairs = t * k;
-    const size_t count[15] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
-        pairs * m->c.intermediate, t * m->c.shared_intermediate, t * h, 4};
+    const size_t count[23] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
+        pairs * m->c.intermediate, t * m->c.shared_intermediate, t * h, 4,
+        pairs * h, t * h, t * h / 2 + 8, t * (h / 32 + 1) * 2, t, pairs * 4 + 4, t + 8, 2};
     size_t at = 0;
-    for (int j = 0; j < 15; j++) {
+    for (int j = 0; j < 23; j++) {
         if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
         plan->offset[j] = at;
         at += align256(count[j] * 4 + 4);
@@ -282,6 +283,11 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->d.act = (float *)(base + plan.offset[11]); w->d.shared_act = (float *)(base + plan.offset[12]);
     w->d.routed = NULL;
     w->d.status = (uint32_t *)(base + plan.offset[14]);
+    w->d.out = (float *)(base + plan.offset[15]); w->d.shared_out = (float *)(base + plan.offset[16]);
+    w->d.xq = (int8_t *)(base + plan.offset[17]); w->d.xsum = (int *)(base + plan.offset[18]);
+    w->d.xscale = (float *)(base + plan.offset[19]);
+    w->d.groups = base + plan.offset[20]; w->d.shared_groups = base + plan.offset[21];
+    w->d.n_groups = (uint32_t *)(base + plan.offset[22]);
     if (qw4sh_memset_async(w->device_block, 0, plan.total, w->d.stream) || status_clear(w) || qw4sh_stream_sync(w->d.stream)) {
         Qwen4Status st = cuda_failure(err, "workspace clear");
         qwen4_moe_work_destroy(w);
@@ -590,6 +596,7 @@ int qw4cu_device_synchronize(void) { return qw4sh_device_sync(); }
 void qw4cu_set_graph_mode(int on) { qw4sh_set_graph_mode(on); }
 int qw4cu_get_graph_mode(void) { return qw4sh_get_graph_mode(); }
 void qw4cu_set_stage_timing(int on) { qw4sh_set_stage_timing(on); }
+void qw4cu_set_expert_path(int path) { qw4sh_set_expert_path(path); }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }

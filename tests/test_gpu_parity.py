@@ -229,6 +229,24 @@ def test_config2_prefill_chunk_zipf(gpu):
         np.testing.assert_array_equal(a, b)
 
 
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("routed,shared,tokens", [(abi.Q4_K, abi.Q4_K, 1), (abi.IQ2_XXS, abi.Q4_K, 4), (abi.Q4_K, abi.IQ2_XXS, 23),
+                                                  (abi.IQ2_XXS, abi.IQ2_XXS, 70)])
+def test_both_expert_paths(gpu, path, routed, shared, tokens):
+    """The CUDA-core kernels (path 0) and the tensor-core grouped kernels (path 1) both hold the
+    tolerance; 23 and 70 tokens over 16 experts give groups of more than four rows."""
+    spec = synth.make_layer(60 + routed + tokens, routed_type=routed, shared_type=shared, experts=16, top_k=4)
+    x = synth.activations(60 + tokens, tokens)
+    out = oracle.forward(spec, x, threads=synth.threads())
+    gpu.lib.qw4cu_set_expert_path(path)
+    try:
+        with MoeLayer(gpu, spec, tokens) as layer:
+            y, ids, weights = layer.forward(x)
+    finally:
+        gpu.lib.qw4cu_set_expert_path(-1)
+    check_layer(out, y, ids, weights)
+
+
 @pytest.mark.parametrize("routed,shared", [(abi.Q2_K, abi.Q4_K), (abi.Q4_K, abi.Q2_K), (abi.IQ2_XXS, abi.IQ2_XXS)])
 def test_mixed_formats_small(gpu, routed, shared):
     spec = cases.small_layer(90 + routed, routed, shared, experts=32, top_k=6)

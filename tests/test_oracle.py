@@ -26,7 +26,7 @@ def bits(a):
 
 def test_iq2xxs_codebook_is_the_published_table():
     text = (Path(__file__).parents[1] / "picoforge_b200/csrc/iq2xxs_codebook.h").read_text()
-    body = text[text.index("QW4_IQ2XXS_LEVELS[256]"):]
+    body = text[text.index("#define QW4_IQ2XXS_LEVEL_LIST"):]
     words = [int(w, 16) for w in __import__("re").findall(r"0x([0-9a-f]{4})", body)]
     assert len(words) == 256
     raw = bytearray()
