@@ -282,6 +282,28 @@ Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *moe, uint32_t tensor, size_t e
                                   size_t row0, size_t rows, float *out, size_t out_elements,
                                   Qwen4Error *err);
 
+/* Dispatch lists for ids that are already in device memory, computed WITHOUT allocating
+ * anything.  This entry point has no counterpart in the reference.  It is for callers that
+ * must not allocate while they run: a decode loop that has given all spare HBM to weights and
+ * caches (where cudaMalloc can fail and in any case stalls the device), or host code that is
+ * inside a stream capture, where cudaMalloc is not allowed.  The caller passes inputs and
+ * outputs, all device pointers: ids_dev [tokens, top_k] dense uint32; offsets_dev
+ * [experts + 1], pair_to_row_dev and row_to_pair_dev [tokens * top_k] uint32.  The kernel's own
+ * working memory is a fixed array built into the library (about 33 KB of every GPU that loads
+ * it, until exit), which limits a call to QW4CU_NOALLOC_MAX_EXPERTS experts and
+ * QW4CU_NOALLOC_MAX_PAIRS pairs; more returns QW4_CAPACITY with the limit in the message.
+ * The first call on each device looks up the array's device address, so make that call before
+ * any stream capture begins.  All calls share the array: calls that overlap on the GPU race,
+ * so serialise them.  Runs on the default stream and returns when the lists are complete.
+ * Ids are taken to be distinct within a token (routing produces them so); an id >= experts
+ * returns QW4_RANGE and leaves the outputs unspecified. */
+#define QW4CU_NOALLOC_MAX_EXPERTS 4096
+#define QW4CU_NOALLOC_MAX_PAIRS (1 << 22)
+Qwen4Status qw4cu_group_pairs_device_noalloc(uint32_t experts, uint32_t top_k, size_t tokens,
+                                             const uint32_t *ids_dev, uint32_t *offsets_dev,
+                                             uint32_t *pair_to_row_dev, uint32_t *row_to_pair_dev,
+                                             Qwen4Error *err);
+
 /* Raw device memory and transfers for callers that keep activations in HBM. */
 void *qw4cu_malloc(size_t bytes);
 void qw4cu_free(void *device_pointer);
