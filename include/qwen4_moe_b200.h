@@ -265,6 +265,12 @@ int qw4cu_get_graph_mode(void);
  * Q4_K or IQ2_XXS, everything else the CUDA-core kernels.  0: CUDA-core kernels only.  1:
  * tensor-core grouped kernels for any batch size the formats allow. */
 void qw4cu_set_expert_path(int path);
+/* Profiling aid: launch only one step of the small-batch sequence on later forwards, so that a
+ * kernel can be timed back to back in isolation (the workspace keeps the results of an
+ * earlier complete forward).  Steps: 0 router logits, 1 quantise x, 2 route + dispatch, 3 routed
+ * gate+up, 4 shared gate+up, 5 quantise act, 6 routed down, 7 quantise shared act, 8 shared
+ * down, 9 combine; -1 (default) runs the whole layer. */
+void qw4cu_set_only_step(int step);
 /* Profiling aid: while on, every layer forward records a CUDA event between its stages
  * (router logits + activation quantisation, route, dispatch, routed gate+up, shared gate+up,
  * routed down, shared down, combine) and graphs are not replayed.  qw4cu_stage_times copies

@@ -41,9 +41,11 @@ typedef struct {
     float *routed;                /* [cap, hidden], only when an observer is set */
     float *out;                   /* [cap * k, hidden] per-pair down outputs (tensor-core path) */
     float *shared_out;            /* [cap, hidden] */
-    int8_t *xq;                   /* [cap, 2, hidden] int8 digits of x */
-    int *xsum;                    /* [cap, hidden / 32, 2] digit sums per 32-column chunk */
-    float *xscale;                /* [cap] */
+    /* int8 digit images of the three activation matrices (quantize_rows): x [cap rows of
+     * hidden], act [cap*k rows of inter], shared_act [cap rows of shared_inter] */
+    int8_t *xq, *xneg, *aq, *aneg, *sq, *sneg;   /* [rows, 2, K] digits and negated digits */
+    int *xsum, *asum, *ssum;      /* [rows, K / 32, 2] digit sums per 32-column chunk */
+    float *xscale, *ascale, *sscale;  /* [rows] */
     void *groups, *shared_groups; /* [cap * k], [cap / 4 + 1] groups of <= 4 rows (16 bytes each) */
     uint32_t *n_groups;           /* [2]: routed, shared */
     uint32_t *status;             /* [4]: error bits, first bad row, spare */
@@ -84,6 +86,10 @@ void qw4sh_set_stage_timing(int on);
 /* -1 automatic (tensor-core grouped kernels for small batches), 0 CUDA-core kernels only,
  * 1 tensor-core grouped kernels whenever the formats allow. */
 void qw4sh_set_expert_path(int path);
+/* Profiling: launch only step `step` of the tensor-core decode sequence (-1: all). */
+void qw4sh_set_only_step(int step);
+/* Builds per-device tables of the tensor-core path (allocates: call outside stream capture). */
+int qw4sh_prepare_mma(void);
 int qw4sh_stage_times(double *ms, uint64_t *forwards);
 int qw4sh_stream_sync(void *stream);
 int qw4sh_device_sync(void);

@@ -2,20 +2,23 @@
 //
 // Work is cut into (group, row-tile) units.  A group is up to four token rows routed to one
 // expert (larger per-expert lists are split into several groups by the dispatch kernel).
-// Packed weights of a unit are staged into shared memory by TMA bulk copies
-// (cp.async.bulk + mbarrier, a ring of stages fed by one producer warp), and sixteen consumer
-// warps turn them into int8 MMA operands in registers:
+// One producer warp feeds two rings of shared-memory stages with TMA bulk copies
+// (cp.async.bulk + mbarrier): packed weight rows of the next units, and the activation digits
+// of the next group.  Sixteen consumer warps turn the packed bytes into int8 MMA operands in
+// registers:
 //
 //   Q4_K      the 4-bit codes ARE the A operand (nibbles masked out of the packed bytes);
 //             sum(code * x) comes from mma.m16n8k32.s8, and the 6-bit sub-block scale and min
 //             are applied to the int32 sums with integer multiply-adds
-//   IQ2_XXS   the codebook vector (eight int8 magnitudes) comes from a bank-conflict-free
-//             shared-memory table, signs are applied with one XOR per four weights and a
-//             second MMA on the sign masks; the 4-bit group scale multiplies the int32 sums
+//   IQ2_XXS   the codebook vector (eight int8 magnitudes) and the byte masks of its sign word
+//             come from bank-conflict-free shared-memory tables; a negative weight is
+//             (v ^ 0xff) + 1 per byte, two integer operations per four weights; the 4-bit
+//             group scale multiplies the int32 sums
 //
 // Activations enter as two int8 digits per value (x ~ dx * (q1 + q2 / 254), |error| <= dx/508
-// with dx = max|x| / 127 per token), so four tokens fill the eight MMA columns and products
-// are exact integers.  The fp16 super-scales are applied in FP32 once per half block.
+// with dx = max|x| / 127 per row; quantize_rows_kernel), so four tokens fill the eight MMA
+// columns and products are exact integers.  The fp16 super-scales are applied in FP32 once per
+// half block.
 //
 // MMA k-slots are permuted so that each lane's eight k-slots of a 32-column chunk are eight
 // CONSECUTIVE columns: lane (g, t) holds columns 8t..8t+7 of rows g and g+8, which is one
@@ -37,6 +40,7 @@ constexpr int CT = CW * 32;                     // consumer threads
 constexpr int NT = CT + 32;                     // + one producer warp
 constexpr int TOK = 4;                          // token rows per group
 constexpr uint32_t KMAX = 4096;                 // largest K held in shared memory
+constexpr uint32_t LUT_GRID_BYTES = 256 * 128, LUT_SIGN_BYTES = 128 * 128, LUT_BYTES = LUT_GRID_BYTES + LUT_SIGN_BYTES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -74,74 +78,83 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator on input (no registers to clear).
+__device__ __forceinline__ void mma_s8_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // One group of the dispatch: rows [first, first + count) of the expert-sorted pair list.
 struct VGroup { uint32_t expert, first, count, pad; };
+
+// Quantised activation rows in global memory (quantize_rows_kernel).
+struct QuantRows {
+    const int8_t *digits;              // [rows][2][K]
+    const int8_t *negated;             // [rows][2][K]
+    const int *sums;                   // [rows][K/32][2]
+    const float *scale;                // [rows]
+};
 
 struct GroupedArgs {
     DevTensor w0, w1;                  // gate and up, or down (w1 unused)
     const VGroup *groups;              // device list; n_groups[0] entries
     const uint32_t *n_groups;
     const uint32_t *row_to_pair;       // nullptr: pair = row (shared expert)
-    uint32_t k_div;                    // token = pair / k_div for the gate/up input
-    // gate_up input: activations prequantised per token by quantize_rows_kernel
-    const int8_t *xq;                  // [tokens][2][K]
-    const int *xsum;                   // [tokens][K/32][2] digit sums per 32-column chunk
-    const float *xscale;               // [tokens] dx
-    // down input: FP32 activations [pairs][K], quantised per group inside the CTA
-    const float *act_in;
-    float *out;                        // gate_up: act [pairs][n_out]; down: out [pairs][n_out]
+    uint32_t k_div;                    // input row = pair / k_div
+    QuantRows in;
+    const uint8_t *lut;                // IQ2_XXS tables image, LUT_BYTES
+    float *out;                        // [pairs][n_out]
     uint32_t *status;
 };
 
 template <uint32_t TYPE> struct Fmt;
 template <> struct Fmt<T_Q4_K> {
     static constexpr uint32_t BLOCK_BYTES = 144;
-    __host__ __device__ static uint32_t pitch(uint32_t nb) {           // row pitch = 8 words mod 32
+    static constexpr bool NEEDS_LUT = false;
+    __host__ __device__ static uint32_t pitch(uint32_t nb) {           // row pitch = 8 words mod 32: no bank conflicts
         uint32_t p = nb * 144;
         while ((p / 4) % 32 != 8) p += 16;
         return p;
     }
-    static constexpr bool NEEDS_LUT = false;
 };
 template <> struct Fmt<T_IQ2_XXS> {
     static constexpr uint32_t BLOCK_BYTES = 64;                          // payload; fp16 d kept apart
-    __host__ __device__ static uint32_t pitch(uint32_t nb) {
-        uint32_t p = nb * 64;
-        while ((p / 4) % 32 != 8) p += 16;
-        return p;
-    }
     static constexpr bool NEEDS_LUT = true;
+    __host__ __device__ static uint32_t pitch(uint32_t nb) { return nb * 64; }   // rows are swizzled in the image
 };
 
 // Shared-memory plan (byte offsets), the same on host and device.
 struct Plan {
-    uint32_t bars, lut_grid, lut_sign, xq, xneg, xsum, tokmeta, partial, stages, stage_bytes, total;
-    uint32_t n_stages, kp, pitch, unit_rows, matrices, dsec;
+    uint32_t bars, lut, bslot, bslot_bytes, xq, xneg, xsum, meta, partial, stages, stage_bytes, total;
+    uint32_t n_stages, kp, pitch, unit_rows, matrices, dsec, per_matrix;
 };
 template <uint32_t TYPE, int MODE>
 __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
     Plan p;
     const uint32_t nb = k_storage / 256;
-    p.unit_rows = MODE == 0 ? 16 : 64;
+    p.unit_rows = MODE == 0 ? 16 : 128;
     p.matrices = MODE == 0 ? 2 : 1;
     p.kp = k_storage + 32;
     p.pitch = Fmt<TYPE>::pitch(nb);
     uint32_t at = 0;
-    p.bars = at; at += 256;
-    p.lut_grid = at; if (Fmt<TYPE>::NEEDS_LUT) at += 256 * 128;
-    p.lut_sign = at; if (Fmt<TYPE>::NEEDS_LUT) at += 128 * 128;
-    p.xq = at; at += 8 * p.kp;
-    p.xneg = at; if (Fmt<TYPE>::NEEDS_LUT) at += 8 * p.kp;
-    p.xsum = at; at += TOK * (k_storage / 32) * 8;
-    p.tokmeta = at; at += 64;
-    p.partial = at; at += 2 * CW * 32 * 2 * 4;                           // [parity][warp][64 floats]
+    p.bars = at; at += 512;
+    p.lut = at; if (Fmt<TYPE>::NEEDS_LUT) at += LUT_BYTES;
+    // one activation slot: digits [8][kp], chunk sums [TOK][K/32] int2, metadata
+    uint32_t b = 0;
+    p.xq = b; b += 8 * p.kp;
+    p.xneg = b;
+    p.xsum = b; b += TOK * (k_storage / 32) * 8;
+    p.meta = b; b += 64;                                                 // [0..3] pair, [4] count, [8..11] float scale
+    p.bslot_bytes = (b + 127) & ~127u;
+    p.bslot = at; at += 2 * p.bslot_bytes;
+    p.partial = at; at += 2 * CW * 64 * 4;                               // [parity][warp][64 floats]
     at = (at + 127) & ~127u;
     p.dsec = p.unit_rows * p.pitch;                                      // IQ2_XXS: fp16 d after the payload rows
     uint32_t per_matrix = p.unit_rows * p.pitch + (TYPE == T_IQ2_XXS ? ((p.unit_rows * nb * 2 + 15) & ~15u) : 0);
-    per_matrix = (per_matrix + 127) & ~127u;
-    p.stage_bytes = per_matrix * p.matrices;
+    p.per_matrix = (per_matrix + 127) & ~127u;
+    p.stage_bytes = p.per_matrix * p.matrices;
     p.stages = at;
-    const uint32_t budget = 200u * 1024u;
+    const uint32_t budget = 220u * 1024u;
     uint32_t n = at < budget ? (budget - at) / p.stage_bytes : 0;
     p.n_stages = n > 8 ? 8 : n;
     p.total = at + p.n_stages * p.stage_bytes;
@@ -151,12 +164,13 @@ __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
 // ------------------------------------------------------------------------------------
 // Per-format consumption of one half block (128 columns = 4 chunks) for rows g and g+8.
 // facc[0] += row g . x[token t], facc[1] += row g+8 . x[token t] (both still to be scaled by dx).
+// `act` points at the activation slot in use.
 // ------------------------------------------------------------------------------------
 template <uint32_t TYPE> struct Consume;
 
 template <> struct Consume<T_Q4_K> {
-    __device__ static __forceinline__ void half_block(const uint8_t *stage, const Plan &p, const uint8_t *smem, uint32_t nb,
-                                                      uint32_t row0, uint32_t half, uint32_t g, uint32_t t, float (&facc)[2]) {
+    __device__ static __forceinline__ void half_block(const uint8_t *stage, const Plan &p, const uint8_t *, const uint8_t *act,
+                                                      uint32_t nb, uint32_t row0, uint32_t half, uint32_t g, uint32_t t, float (&facc)[2]) {
         const uint32_t b = half >> 1, hb = half & 1u;
         const uint8_t *r0 = stage + (row0 + g) * p.pitch + b * 144u, *r1 = r0 + 8 * p.pitch;
         const uint4 h0 = *reinterpret_cast<const uint4 *>(r0), h1 = *reinterpret_cast<const uint4 *>(r1);
@@ -166,8 +180,8 @@ template <> struct Consume<T_Q4_K> {
             sc0 = (h0.w & 0x0f0f0f0fu) | ((h0.y >> 2) & 0x30303030u); mn0 = ((h0.w >> 4) & 0x0f0f0f0fu) | ((h0.z >> 2) & 0x30303030u);
             sc1 = (h1.w & 0x0f0f0f0fu) | ((h1.y >> 2) & 0x30303030u); mn1 = ((h1.w >> 4) & 0x0f0f0f0fu) | ((h1.z >> 2) & 0x30303030u);
         }
-        const uint8_t *xq = smem + p.xq + g * p.kp + (half * 4u) * 32u + 8u * t;
-        const int2 *xsum = reinterpret_cast<const int2 *>(smem + p.xsum) + t * (nb * 8u) + half * 4u;
+        const uint8_t *xq = act + p.xq + g * p.kp + (half * 4u) * 32u + 8u * t;
+        const int2 *xsum = reinterpret_cast<const int2 *>(act + p.xsum) + t * (nb * 8u) + half * 4u;
         int qacc[4] = {0, 0, 0, 0}, macc[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int cc = 0; cc < 2; cc++) {                                 // sub-block pair: low and high nibbles
@@ -177,8 +191,8 @@ template <> struct Consume<T_Q4_K> {
             for (int nib = 0; nib < 2; nib++) {
                 const int j = cc * 2 + nib;                              // chunk within the half block
                 const uint2 bq = *reinterpret_cast<const uint2 *>(xq + j * 32);
-                int c[4] = {0, 0, 0, 0};
-                mma_s8(c, (q0.x >> (4 * nib)) & 0x0f0f0f0fu, (q1.x >> (4 * nib)) & 0x0f0f0f0fu,
+                int c[4];
+                mma_s8_zero(c, (q0.x >> (4 * nib)) & 0x0f0f0f0fu, (q1.x >> (4 * nib)) & 0x0f0f0f0fu,
                        (q0.y >> (4 * nib)) & 0x0f0f0f0fu, (q1.y >> (4 * nib)) & 0x0f0f0f0fu, bq.x, bq.y);
                 const int s0 = (int)((sc0 >> (8 * j)) & 0xffu), s1 = (int)((sc1 >> (8 * j)) & 0xffu);
                 const int m0 = (int)((mn0 >> (8 * j)) & 0xffu), m1 = (int)((mn1 >> (8 * j)) & 0xffu);
@@ -196,25 +210,29 @@ template <> struct Consume<T_Q4_K> {
 };
 
 template <> struct Consume<T_IQ2_XXS> {
-    __device__ static __forceinline__ void half_block(const uint8_t *stage, const Plan &p, const uint8_t *smem, uint32_t nb,
-                                                      uint32_t row0, uint32_t half, uint32_t g, uint32_t t, float (&facc)[2]) {
-        const uint32_t b = half >> 1, lane16 = (threadIdx.x & 15u) * 8u;
-        const uint8_t *r0 = stage + (row0 + g) * p.pitch + half * 32u, *r1 = r0 + 8 * p.pitch;
-        const uint8_t *grid = smem + p.lut_grid + lane16, *sign = smem + p.lut_sign + lane16;
-        const uint8_t *xq = smem + p.xq + g * p.kp + (half * 4u) * 32u + 8u * t;
-        const uint8_t *xn = smem + p.xneg + g * p.kp + (half * 4u) * 32u + 8u * t;
+    __device__ static __forceinline__ void half_block(const uint8_t *stage, const Plan &p, const uint8_t *lut, const uint8_t *act,
+                                                      uint32_t nb, uint32_t row0, uint32_t half, uint32_t g, uint32_t t, float (&facc)[2]) {
+        const uint32_t b = half >> 1;
+        // groups 4*half .. 4*half+3 of the row sit at ((4*half) ^ swizzle) + j: the swizzle only
+        // touches bits 2-3 of the group index
+        const uint8_t *r0 = stage + (row0 + g) * p.pitch + (((half * 4u) ^ iq2_swizzle(g, nb)) * 8u), *r1 = r0 + 8 * p.pitch;
+        const uint8_t *grid = lut + (threadIdx.x & 15u) * 8u;            // 64-bit reads: 16 copies
+        const uint8_t *sign = lut + LUT_GRID_BYTES + (threadIdx.x & 7u) * 16u;   // 128-bit reads: 8 copies
+        const uint8_t *xq = act + p.xq + g * p.kp + (half * 4u) * 32u + 8u * t;
+        const uint32_t pick = 0x4440u + t, shift_s = 7 * t;              // byte t of the index word; 7-bit sign field t
         int iacc[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint2 g0 = *reinterpret_cast<const uint2 *>(r0 + 8 * j), g1 = *reinterpret_cast<const uint2 *>(r1 + 8 * j);
-            const uint32_t i0 = (g0.x >> (8 * t)) & 0xffu, i1 = (g1.x >> (8 * t)) & 0xffu;
-            const uint32_t s0 = (g0.y >> (7 * t)) & 127u, s1 = (g1.y >> (7 * t)) & 127u;
+            const uint32_t i0 = __byte_perm(g0.x, 0u, pick), i1 = __byte_perm(g1.x, 0u, pick);
+            const uint32_t s0 = (g0.y >> shift_s) & 127u, s1 = (g1.y >> shift_s) & 127u;
             const uint2 v0 = *reinterpret_cast<const uint2 *>(grid + i0 * 128u), v1 = *reinterpret_cast<const uint2 *>(grid + i1 * 128u);
-            const uint2 m0 = *reinterpret_cast<const uint2 *>(sign + s0 * 128u), m1 = *reinterpret_cast<const uint2 *>(sign + s1 * 128u);
-            const uint2 bq = *reinterpret_cast<const uint2 *>(xq + j * 32), bn = *reinterpret_cast<const uint2 *>(xn + j * 32);
-            int c[4] = {0, 0, 0, 0};
-            mma_s8(c, v0.x ^ m0.x, v1.x ^ m1.x, v0.y ^ m0.y, v1.y ^ m1.y, bq.x, bq.y);   // +v, or -v-1 where negative
-            mma_s8(c, m0.x, m1.x, m0.y, m1.y, bn.x, bn.y);                                   // (-1) * (-x) adds the missing x
+            const uint4 m0 = *reinterpret_cast<const uint4 *>(sign + s0 * 128u), m1 = *reinterpret_cast<const uint4 *>(sign + s1 * 128u);
+            const uint2 bq = *reinterpret_cast<const uint2 *>(xq + j * 32);
+            int c[4];
+            // m.x/m.y: 0xff where the weight is negative; m.z/m.w: 0x01 there.  Magnitudes are
+            // never zero, so (v ^ 0xff) + 1 = -v stays inside its byte.
+            mma_s8_zero(c, (v0.x ^ m0.x) + m0.z, (v1.x ^ m1.x) + m1.z, (v0.y ^ m0.y) + m0.w, (v1.y ^ m1.y) + m1.w, bq.x, bq.y);
             const int w0 = (int)((g0.y >> 27) | 1u), w1 = (int)((g1.y >> 27) | 1u);         // 2 * scale + 1
             iacc[0] += c[0] * w0; iacc[1] += c[1] * w0; iacc[2] += c[2] * w1; iacc[3] += c[3] * w1;
         }
@@ -227,74 +245,97 @@ template <> struct Consume<T_IQ2_XXS> {
     }
 };
 
-// Producer: stage one unit (unit_rows rows of each matrix) with bulk copies.
+// Producer: stage one unit (unit_rows rows of each matrix).
 template <uint32_t TYPE>
 __device__ __forceinline__ void produce_unit(const GroupedArgs &a, const Plan &p, uint8_t *stage, uint64_t *full, uint32_t expert,
                                              uint32_t row0, uint32_t lane) {
     const uint32_t nb = a.w0.k_storage >> 8, rows = p.unit_rows;
     const uint32_t row_bytes = nb * Fmt<TYPE>::BLOCK_BYTES;
-    const uint32_t dbytes = (rows * nb * 2 + 15) & ~15u;
-    const uint32_t per_matrix = (rows * p.pitch + (TYPE == T_IQ2_XXS ? dbytes : 0) + 127) & ~127u;
+    const bool contiguous = p.pitch == row_bytes;
     if (lane == 0) mbar_expect_tx(full, p.matrices * (rows * row_bytes + (TYPE == T_IQ2_XXS ? rows * nb * 2 : 0)));
     __syncwarp();
     for (uint32_t m = 0; m < p.matrices; m++) {
         const DevTensor &w = m == 0 ? a.w0 : a.w1;
         const uint8_t *mat = w.data + (uint64_t)expert * w.expert_bytes;
-        uint8_t *dst = stage + m * per_matrix;
-        for (uint32_t r = lane; r < rows; r += 32)
-            bulk_copy(dst + r * p.pitch, mat + (uint64_t)(row0 + r) * row_bytes, row_bytes, full);
-        if (TYPE == T_IQ2_XXS && lane == 0)
+        uint8_t *dst = stage + m * p.per_matrix;
+        if (contiguous) {
+            if (lane == 0) bulk_copy(dst, mat + (uint64_t)row0 * row_bytes, rows * row_bytes, full);
+        } else {
+            for (uint32_t r = lane; r < rows; r += 32) bulk_copy(dst + r * p.pitch, mat + (uint64_t)(row0 + r) * row_bytes, row_bytes, full);
+        }
+        if (TYPE == T_IQ2_XXS && lane == 1)
             bulk_copy(dst + p.dsec, mat + (uint64_t)w.n_out * nb * 64u + (uint64_t)row0 * nb * 2u, rows * nb * 2, full);
     }
 }
 
-// MODE 0: gate + up + SwiGLU -> act.  MODE 1: down -> out (one row per pair).
+// Producer: stage one group's activation digits, chunk sums and metadata.
+template <uint32_t TYPE>
+__device__ __forceinline__ void produce_group(const GroupedArgs &a, const Plan &p, uint8_t *slot, uint64_t *full, const VGroup grp,
+                                              uint32_t lane) {
+    const uint32_t K = a.w0.k_storage, sums_bytes = (K >> 5) * 8;
+    const uint32_t per_token = 2 * K + sums_bytes;
+    uint32_t row = 0;
+    if (lane < grp.count) {
+        const uint32_t pair = a.row_to_pair ? a.row_to_pair[grp.first + lane] : grp.first + lane;
+        row = pair / a.k_div;
+        reinterpret_cast<uint32_t *>(slot + p.meta)[lane] = pair;
+        reinterpret_cast<float *>(slot + p.meta)[8 + lane] = a.in.scale[row];
+    }
+    if (lane == 4) reinterpret_cast<uint32_t *>(slot + p.meta)[4] = grp.count;
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(full, grp.count * per_token);
+    __syncwarp();
+    for (uint32_t tok = 0; tok < grp.count; tok++) {
+        const uint32_t src_row = __shfl_sync(0xffffffffu, row, tok);
+        if (lane < 2) bulk_copy(slot + p.xq + (2 * tok + lane) * p.kp, a.in.digits + ((uint64_t)src_row * 2 + lane) * K, K, full);
+        else if (lane == 4) bulk_copy(slot + p.xsum + tok * sums_bytes, a.in.sums + (uint64_t)src_row * (K >> 5) * 2, sums_bytes, full);
+    }
+}
+
+// MODE 0: gate + up + SwiGLU -> out = act.  MODE 1: down -> out (one row per pair).
 template <uint32_t TYPE, int MODE>
 __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t K = a.w0.k_storage, nb = K >> 8, halves = K >> 7;
     const Plan p = make_plan<TYPE, MODE>(K);
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + p.bars), *empty = full + 8;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + p.bars), *empty = full + 8, *bfull = full + 16, *bempty = full + 18, *lutbar = full + 20;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t n_groups = *a.n_groups;
     const uint32_t units_per_group = a.w0.n_out / p.unit_rows;
     const uint64_t total = (uint64_t)n_groups * units_per_group;
     const uint32_t u_begin = (uint32_t)(total * blockIdx.x / gridDim.x), u_end = (uint32_t)(total * (blockIdx.x + 1) / gridDim.x);
+    if (u_begin == u_end) return;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < p.n_stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+        for (uint32_t s = 0; s < 2; s++) { mbar_init(&bfull[s], 1); mbar_init(&bempty[s], CW); }
+        mbar_init(lutbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (Fmt<TYPE>::NEEDS_LUT) {                                          // conflict-free tables: 16 copies, 8 B apart
-        for (uint32_t i = tid; i < 256 * 16; i += NT) {
-            const uint32_t entry = i >> 4, levels = c_iq2_levels[entry];
-            uint32_t lo = 0, hi = 0;
-            for (int j = 0; j < 4; j++) {
-                lo |= iq2_magnitude((levels >> (2 * j)) & 3u) << (8 * j);
-                hi |= iq2_magnitude((levels >> (2 * j + 8)) & 3u) << (8 * j);
-            }
-            *reinterpret_cast<uint2 *>(smem + p.lut_grid + entry * 128u + (i & 15u) * 8u) = make_uint2(lo, hi);
-        }
-        for (uint32_t i = tid; i < 128 * 16; i += NT) {
-            const uint32_t signs = iq2_signs8(i >> 4);
-            uint32_t lo = 0, hi = 0;
-            for (int j = 0; j < 4; j++) {
-                if ((signs >> j) & 1u) lo |= 0xffu << (8 * j);
-                if ((signs >> (j + 4)) & 1u) hi |= 0xffu << (8 * j);
-            }
-            *reinterpret_cast<uint2 *>(smem + p.lut_sign + (i >> 4) * 128u + (i & 15u) * 8u) = make_uint2(lo, hi);
-        }
     }
     __syncthreads();
 
     if (warp == CW) {                                                    // ---- producer warp ----
-        uint32_t stage = 0, phase = 0;
+        if (Fmt<TYPE>::NEEDS_LUT && lane == 0) {
+            mbar_expect_tx(lutbar, LUT_BYTES);
+            bulk_copy(smem + p.lut, a.lut, LUT_BYTES, lutbar);
+        }
+        uint32_t stage = 0, phase = 0, bslot = 0, bphase = 0, staged = 0, current = 0xffffffffu;
         bool alive = true;
         for (uint32_t u = u_begin; u < u_end && alive; u++) {
+            const uint32_t gi = u / units_per_group;
+            const VGroup grp = a.groups[gi];
+            if (gi != current) {                                         // next group's activations, one slot ahead
+                if (lane == 0 && staged >= 2) alive = mbar_wait(&bempty[bslot], bphase ^ 1u, a.status);
+                alive = __shfl_sync(0xffffffffu, alive, 0);
+                if (!alive) break;
+                produce_group<TYPE>(a, p, smem + p.bslot + bslot * p.bslot_bytes, &bfull[bslot], grp, lane);
+                staged++;
+                if (++bslot == 2) { bslot = 0; bphase ^= 1u; }
+                current = gi;
+            }
             if (lane == 0 && u - u_begin >= p.n_stages) alive = mbar_wait(&empty[stage], phase ^ 1u, a.status);
             alive = __shfl_sync(0xffffffffu, alive, 0);
             if (!alive) break;
-            const VGroup grp = a.groups[u / units_per_group];
             produce_unit<TYPE>(a, p, smem + p.stages + stage * p.stage_bytes, &full[stage], grp.expert,
                                (u % units_per_group) * p.unit_rows, lane);
             if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
@@ -304,122 +345,51 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
 
     // ---- consumer warps ----
     const uint32_t g = lane >> 2, t = lane & 3u;
-    uint32_t *tokmeta = reinterpret_cast<uint32_t *>(smem + p.tokmeta);  // [0..3] pair of token column, [4] count
-    float *tokscale = reinterpret_cast<float *>(smem + p.tokmeta + 32);
     float *partial = reinterpret_cast<float *>(smem + p.partial);
-    const uint32_t per_matrix = p.stage_bytes / p.matrices;
-    uint32_t stage = 0, phase = 0, parity = 0, current = 0xffffffffu;
+    uint32_t stage = 0, phase = 0, parity = 0, current = 0xffffffffu, bslot = 1, bphase = 1;
     bool alive = true;
+    if (Fmt<TYPE>::NEEDS_LUT) {
+        if (lane == 0) alive = mbar_wait(lutbar, 0, a.status);
+        alive = __shfl_sync(0xffffffffu, alive, 0);
+    }
+    const uint8_t *act = smem + p.bslot;
     for (uint32_t u = u_begin; u < u_end; u++) {
         const uint32_t gi = u / units_per_group, row_tile = (u % units_per_group) * p.unit_rows;
-        if (gi != current) {                                             // ---- stage this group's activations ----
-            consumer_sync();
-            const VGroup grp = a.groups[gi];
-            if (tid < 8) {
-                uint32_t pair = 0;
-                if (tid < grp.count) pair = a.row_to_pair ? a.row_to_pair[grp.first + tid] : grp.first + tid;
-                if (tid < TOK) tokmeta[tid] = pair;
-                if (tid == 4) tokmeta[4] = grp.count;
+        if (gi != current) {                                             // switch to the next activation slot
+            if (current != 0xffffffffu) {
+                consumer_sync();                                         // epilogues of the old group have read its metadata
+                if (lane == 0) mbar_arrive(&bempty[bslot]);
             }
-            if (MODE == 0) {
-                for (uint32_t i = tid; i < TOK * 2 * (K >> 4); i += CT) {        // 16-byte pieces of the digit rows
-                    const uint32_t col = i / (K >> 4), piece = i % (K >> 4), tok = col >> 1;
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (tok < grp.count) {
-                        const uint32_t pair = a.row_to_pair ? a.row_to_pair[grp.first + tok] : grp.first + tok;
-                        v = *reinterpret_cast<const uint4 *>(a.xq + ((uint64_t)(pair / a.k_div) * 2 + (col & 1u)) * K + piece * 16);
-                    }
-                    *reinterpret_cast<uint4 *>(smem + p.xq + col * p.kp + piece * 16) = v;
-                    if (Fmt<TYPE>::NEEDS_LUT)
-                        *reinterpret_cast<uint4 *>(smem + p.xneg + col * p.kp + piece * 16) =
-                            make_uint4(__vneg4(v.x), __vneg4(v.y), __vneg4(v.z), __vneg4(v.w));
-                }
-                for (uint32_t i = tid; i < TOK * (K >> 5); i += CT) {
-                    const uint32_t tok = i / (K >> 5), chunk = i % (K >> 5);
-                    int2 s = make_int2(0, 0);
-                    if (tok < grp.count) {
-                        const uint32_t pair = a.row_to_pair ? a.row_to_pair[grp.first + tok] : grp.first + tok;
-                        s = *reinterpret_cast<const int2 *>(a.xsum + ((uint64_t)(pair / a.k_div) * (K >> 5) + chunk) * 2);
-                    }
-                    reinterpret_cast<int2 *>(smem + p.xsum)[i] = s;
-                }
-                if (tid < TOK) {
-                    const uint32_t pair = tid < grp.count ? (a.row_to_pair ? a.row_to_pair[grp.first + tid] : grp.first + tid) : 0;
-                    tokscale[tid] = tid < grp.count ? a.xscale[pair / a.k_div] : 0.0f;
-                }
-            } else {                                                     // quantise FP32 rows here (K <= 16 * CT)
-                float *red = reinterpret_cast<float *>(smem + p.partial);      // reuse: [CW][TOK]
-                float v[TOK][4];
-                float amax[TOK];
-#pragma unroll
-                for (int r = 0; r < TOK; r++) {
-                    amax[r] = 0.0f;
-                    uint32_t pair = 0;
-                    if ((uint32_t)r < grp.count) pair = a.row_to_pair ? a.row_to_pair[grp.first + r] : grp.first + r;
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const uint32_t col = tid + q * CT;
-                        v[r][q] = ((uint32_t)r < grp.count && col < a.w0.k_logical) ? a.act_in[(uint64_t)pair * a.w0.k_logical + col] : 0.0f;
-                        amax[r] = fmaxf(amax[r], fabsf(v[r][q]));
-                    }
-                    for (int o = 16; o; o >>= 1) amax[r] = fmaxf(amax[r], __shfl_xor_sync(0xffffffffu, amax[r], o));
-                    if (lane == 0) red[warp * TOK + r] = amax[r];
-                }
-                consumer_sync();
-#pragma unroll
-                for (int r = 0; r < TOK; r++) {
-                    float m = 0.0f;
-                    for (int w = 0; w < CW; w++) m = fmaxf(m, red[w * TOK + r]);
-                    const float dx = m > 0.0f ? m / 127.0f : 1.0f, inv = 1.0f / dx, inv2 = 254.0f / dx;
-                    if (tid == 0) tokscale[r] = m > 0.0f ? dx : 0.0f;
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const uint32_t col = tid + q * CT;
-                        if (col >= K) continue;
-                        const float q1 = rintf(v[r][q] * inv);
-                        const float q2 = fminf(fmaxf(rintf((v[r][q] - q1 * dx) * inv2), -127.0f), 127.0f);
-                        const int i1 = (int)q1, i2 = (int)q2;
-                        smem[p.xq + (2 * r) * p.kp + col] = (uint8_t)(int8_t)i1;
-                        smem[p.xq + (2 * r + 1) * p.kp + col] = (uint8_t)(int8_t)i2;
-                        if (Fmt<TYPE>::NEEDS_LUT) {
-                            smem[p.xneg + (2 * r) * p.kp + col] = (uint8_t)(int8_t)(-i1);
-                            smem[p.xneg + (2 * r + 1) * p.kp + col] = (uint8_t)(int8_t)(-i2);
-                        }
-                        int s1 = i1, s2 = i2;                            // warp = one 32-column chunk
-                        for (int o = 16; o; o >>= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
-                        if (lane == 0) reinterpret_cast<int2 *>(smem + p.xsum)[r * (K >> 5) + (col >> 5)] = make_int2(s1, s2);
-                    }
-                }
-                consumer_sync();                                         // red[] is reused as partials below
-            }
-            consumer_sync();
+            if (++bslot == 2) { bslot = 0; bphase ^= 1u; }
+            if (alive && lane == 0) alive = mbar_wait(&bfull[bslot], bphase, a.status);
+            alive = __shfl_sync(0xffffffffu, alive, 0);
+            act = smem + p.bslot + bslot * p.bslot_bytes;
             current = gi;
         }
         if (alive && lane == 0) alive = mbar_wait(&full[stage], phase, a.status);
         alive = __shfl_sync(0xffffffffu, alive, 0);
         const uint8_t *st = smem + p.stages + stage * p.stage_bytes;
         float facc[2] = {0.0f, 0.0f};
-        uint32_t out_slot;
         if (MODE == 0) {                                                 // warp = (matrix, k-slice of 8)
             const uint32_t m = warp & 1u, ks = warp >> 1;
             if (alive)
-                for (uint32_t h = ks; h < halves; h += 8) Consume<TYPE>::half_block(st + m * per_matrix, p, smem, nb, 0, h, g, t, facc);
-            out_slot = warp;
-        } else {                                                         // warp = (row tile of 4, k-slice of 4)
-            const uint32_t rt = warp & 3u, ks = warp >> 2;
+                for (uint32_t h = ks; h < halves; h += 8) Consume<TYPE>::half_block(st + m * p.per_matrix, p, smem + p.lut, act, nb, 0, h, g, t, facc);
+        } else {                                                         // warp = (row tile of 8, k-slice of 2)
+            const uint32_t rt = warp & 7u, ks = warp >> 3;
             if (alive)
-                for (uint32_t h = ks; h < halves; h += 4) Consume<TYPE>::half_block(st, p, smem, nb, rt * 16, h, g, t, facc);
-            out_slot = warp;
+                for (uint32_t h = ks; h < halves; h += 2) Consume<TYPE>::half_block(st, p, smem + p.lut, act, nb, rt * 16, h, g, t, facc);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);
         if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
-        float *mine = partial + (parity * CW + out_slot) * 64;
+        float *mine = partial + (parity * CW + warp) * 64;
         mine[lane] = facc[0];                                            // (row g, token t) at 4g + t
         mine[32 + lane] = facc[1];                                       // (row g + 8, token t)
         consumer_sync();
         const float *part = partial + parity * CW * 64;
-        const uint32_t count = tokmeta[4];
+        const uint32_t *meta = reinterpret_cast<const uint32_t *>(act + p.meta);
+        const float *tokscale = reinterpret_cast<const float *>(act + p.meta) + 8;
+        const uint32_t count = meta[4];
         if (MODE == 0) {
             if (tid < 64) {                                              // 16 rows x 4 tokens
                 const uint32_t row = tid >> 2, tok = tid & 3u;
@@ -433,30 +403,27 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
                     const float sig = gsum >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
                     const float v = gsum * sig * usum;
                     if ((__float_as_uint(v) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
-                    a.out[(uint64_t)tokmeta[tok] * a.w0.n_out + row_tile + row] = v;
+                    a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + row] = v;
                 }
             }
-        } else {
-            if (tid < 256) {                                             // 64 rows x 4 tokens
-                const uint32_t rt = tid >> 6, within = tid & 63u, tok = within & 3u;
-                float sum = 0.0f;
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) sum += part[(ks * 4 + rt) * 64 + within];
-                if (tok < count) {
-                    sum *= tokscale[tok];
-                    if ((__float_as_uint(sum) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
-                    a.out[(uint64_t)tokmeta[tok] * a.w0.n_out + row_tile + rt * 16 + (within >> 2)] = sum;
-                }
+        } else {                                                         // 128 rows x 4 tokens: every consumer thread
+            const uint32_t rt = tid >> 6, within = tid & 63u, tok = within & 3u;
+            const float sum = (part[rt * 64 + within] + part[(8 + rt) * 64 + within]) * tokscale[tok];
+            if (tok < count) {
+                if ((__float_as_uint(sum) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
+                a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + rt * 16 + (within >> 2)] = sum;
             }
         }
         parity ^= 1u;
     }
+    if (current != 0xffffffffu) { consumer_sync(); if (lane == 0) mbar_arrive(&bempty[bslot]); }
 }
 
-// Two int8 digits per activation: x ~ dx * (q1 + q2 / 254), dx = max|x| / 127 per token.
-// One CTA per token row.  Also writes the per-chunk digit sums Q4_K's min term needs.
+// Two int8 digits per activation: x ~ dx * (q1 + q2 / 254), dx = max|x| / 127 per row.
+// One CTA per row.  Also writes the negated digits (IQ2_XXS sign correction) and the per-chunk
+// digit sums (Q4_K min term).  k is a multiple of 32.
 __global__ void __launch_bounds__(512) quantize_rows_kernel(const float *__restrict__ x, uint32_t k, int8_t *__restrict__ xq,
-                                                            int *__restrict__ xsum, float *__restrict__ xscale) {
+                                                            int8_t *__restrict__ xneg, int *__restrict__ xsum, float *__restrict__ xscale) {
     __shared__ float red[16];
     const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float *src = x + (uint64_t)row * k;
@@ -469,14 +436,43 @@ __global__ void __launch_bounds__(512) quantize_rows_kernel(const float *__restr
     for (int w = 0; w < 16; w++) amax = fmaxf(amax, red[w]);
     const float dx = amax > 0.0f ? amax / 127.0f : 1.0f, inv = 1.0f / dx, inv2 = 254.0f / dx;
     if (tid == 0) xscale[row] = amax > 0.0f ? dx : 0.0f;
-    for (uint32_t c = tid; c < k; c += 512) {                            // k is a multiple of 32: whole warps per chunk
+    for (uint32_t c = tid; c < k; c += 512) {                            // whole warps per 32-column chunk
         const float v = src[c], q1 = rintf(v * inv);
         const float q2 = fminf(fmaxf(rintf((v - q1 * dx) * inv2), -127.0f), 127.0f);
         int s1 = (int)q1, s2 = (int)q2;
         xq[((uint64_t)row * 2) * k + c] = (int8_t)s1;
         xq[((uint64_t)row * 2 + 1) * k + c] = (int8_t)s2;
+        xneg[((uint64_t)row * 2) * k + c] = (int8_t)(-s1);
+        xneg[((uint64_t)row * 2 + 1) * k + c] = (int8_t)(-s2);
         for (int o = 16; o; o >>= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
         if (lane == 0) { xsum[((uint64_t)row * (k >> 5) + (c >> 5)) * 2] = s1; xsum[((uint64_t)row * (k >> 5) + (c >> 5)) * 2 + 1] = s2; }
+    }
+}
+
+// IQ2_XXS tables as the kernels want them in shared memory.  256 codebook vectors of 8 bytes,
+// each 16 times (8 bytes apart, 128 bytes per entry): lane L reads copy L % 16 with a 64-bit
+// load.  128 sign words of 16 bytes {mask lo, mask hi, ones lo, ones hi}, each 8 times (128
+// bytes per entry): lane L reads copy L % 8 with a 128-bit load.  Neither has bank conflicts.
+__global__ void build_lut_kernel(uint8_t *lut) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < 256 * 16 + 128 * 8; i += gridDim.x * blockDim.x) {
+        if (i < 256 * 16) {
+            const uint32_t entry = i >> 4, levels = c_iq2_levels[entry];
+            uint32_t lo = 0, hi = 0;
+            for (int j = 0; j < 4; j++) {
+                lo |= iq2_magnitude((levels >> (2 * j)) & 3u) << (8 * j);
+                hi |= iq2_magnitude((levels >> (2 * j + 8)) & 3u) << (8 * j);
+            }
+            *reinterpret_cast<uint2 *>(lut + entry * 128u + (i & 15u) * 8u) = make_uint2(lo, hi);
+        } else {
+            const uint32_t k = i - 256 * 16, entry = k >> 3, signs = iq2_signs8(entry);
+            uint32_t lo = 0, hi = 0;
+            for (int j = 0; j < 4; j++) {
+                if ((signs >> j) & 1u) lo |= 0xffu << (8 * j);
+                if ((signs >> (j + 4)) & 1u) hi |= 0xffu << (8 * j);
+            }
+            *reinterpret_cast<uint4 *>(lut + LUT_GRID_BYTES + entry * 128u + (k & 7u) * 16u) =
+                make_uint4(lo, hi, lo & 0x01010101u, hi & 0x01010101u);
+        }
     }
 }
 
@@ -530,11 +526,24 @@ static DevTensor dev(const QW4ShTensor &s) {
     return t;
 }
 
+static uint8_t *g_lut[64] = {nullptr};
+static const uint8_t *lut_image() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    if (!g_lut[device]) {
+        uint8_t *p = nullptr;
+        if (cudaMalloc(&p, LUT_BYTES) != cudaSuccess) return nullptr;
+        build_lut_kernel<<<24, 256>>>(p);
+        if (qw4sh_note_launch("build_lut_kernel") || cudaDeviceSynchronize() != cudaSuccess) { cudaFree(p); return nullptr; }
+        g_lut[device] = p;
+    }
+    return g_lut[device];
+}
+
 extern "C" int qw4sh_mma_supported(const QW4ShTensor *w, int mode) {
     if (w->type != T_Q4_K && w->type != T_IQ2_XXS) return 0;
     if (w->k_storage % 256 || w->k_storage > KMAX || w->k_logical != w->k_storage) return 0;
-    if (w->n_out % (mode == 0 ? 16 : 64)) return 0;
-    if (mode == 1 && w->k_storage > 4 * CT) return 0;
+    if (w->n_out % (mode == 0 ? 16 : 128)) return 0;
     return 1;
 }
 
@@ -549,20 +558,26 @@ static int launch_grouped(const GroupedArgs &a, int ctas, cudaStream_t stream) {
 }
 
 // mode 0: gate+up (w0, w1) -> out = act [pairs][n_out]; mode 1: down (w0) -> out [pairs][n_out].
+// Input rows are the quantised rows of quantize_rows (row = pair / k_div).
 extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
-                                 const uint32_t *row_to_pair, uint32_t k_div, const int8_t *xq, const int *xsum, const float *xscale,
-                                 const float *act_in, float *out, uint32_t *status, int ctas, void *stream) {
+                                 const uint32_t *row_to_pair, uint32_t k_div, const int8_t *digits, const int8_t *negated,
+                                 const int *sums, const float *scale, float *out, uint32_t *status, int ctas, void *stream) {
     GroupedArgs a;
     a.w0 = dev(*w0); a.w1 = dev(w1 ? *w1 : *w0);
     a.groups = (const VGroup *)groups; a.n_groups = n_groups; a.row_to_pair = row_to_pair; a.k_div = k_div;
-    a.xq = xq; a.xsum = xsum; a.xscale = xscale; a.act_in = act_in; a.out = out; a.status = status;
+    a.in.digits = digits; a.in.negated = negated; a.in.sums = sums; a.in.scale = scale;
+    a.lut = nullptr; a.out = out; a.status = status;
+    if (w0->type == T_IQ2_XXS && !(a.lut = lut_image())) return -3;
     cudaStream_t s = (cudaStream_t)stream;
     if (w0->type == T_Q4_K) return mode == 0 ? launch_grouped<T_Q4_K, 0>(a, ctas, s) : launch_grouped<T_Q4_K, 1>(a, ctas, s);
     return mode == 0 ? launch_grouped<T_IQ2_XXS, 0>(a, ctas, s) : launch_grouped<T_IQ2_XXS, 1>(a, ctas, s);
 }
 
-extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int *xsum, float *xscale, void *stream) {
-    quantize_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(x, k, xq, xsum, xscale);
+extern "C" int qw4sh_prepare_mma(void) { return lut_image() ? 0 : -1; }
+
+extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {
+    if (!rows) return 0;
+    quantize_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(x, k, xq, xneg, xsum, xscale);
     return qw4sh_note_launch("quantize_rows_kernel");
 }
 extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,

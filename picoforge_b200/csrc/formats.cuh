@@ -10,7 +10,10 @@
 //
 //   Q4_K     unchanged: block b of row n at (n * nb + b) * 144; 144 = 9 * 16 bytes.
 //   Q2_K     [rows*nb][64 B codes] | [rows*nb][16 B scale/min bytes] | [rows*nb][d, dmin f16]
-//   IQ2_XXS  [rows*nb][8 groups x 8 B] | [rows*nb][d f16]
+//   IQ2_XXS  [rows][nb*8 groups x 8 B] | [rows*nb][d f16]; inside a row, 8-byte group c is
+//            stored at position c ^ ((row & 3) << 2) (rows of two or more blocks), so that the
+//            four rows a half-warp reads together fall in different shared-memory banks when
+//            whole row tiles are copied to shared memory unchanged
 //   others   unchanged (F32, F16, BF16, Q8_0, MXFP4).
 //
 // nb = k_storage / 256.  The regrouping is a permutation of bytes done once at upload.
@@ -43,6 +46,9 @@ __device__ __forceinline__ uint32_t load_u16(const uint8_t *p) { return *reinter
 __device__ __forceinline__ uint32_t load_u32(const uint8_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
 
 __device__ __forceinline__ uint32_t iq2_magnitude(uint32_t level) { return 8u + 17u * level + (level >> 1); }
+
+// Position swizzle of IQ2_XXS groups inside a row of the resident image.
+__host__ __device__ __forceinline__ uint32_t iq2_swizzle(uint32_t row, uint32_t nb) { return nb >= 2 ? (row & 3u) << 2 : 0u; }
 
 // 8th sign of an IQ2_XXS vector: parity of the seven stored ones.
 __device__ __forceinline__ uint32_t iq2_signs8(uint32_t seven) { return seven | ((__popc(seven) & 1u) << 7); }
@@ -100,7 +106,7 @@ __device__ inline float decode_value(const DevTensor &t, uint32_t expert, uint32
     case T_IQ2_XXS: {
         const uint64_t blocks = (uint64_t)t.n_out * nb, block = (uint64_t)row * nb + (column >> 8);
         const uint32_t lane = column & 255u, slot = (lane & 31u) >> 3;
-        const uint8_t *group = mat + block * 64u + (lane >> 5) * 8u;
+        const uint8_t *group = mat + ((uint64_t)row * nb * 8u + ((((column >> 8) * 8u) + (lane >> 5)) ^ iq2_swizzle(row, nb))) * 8u;
         const uint32_t bits = load_u32(group + 4);
         const uint32_t signs = iq2_signs8((bits >> (7 * slot)) & 127u);
         const uint32_t level = (c_iq2_levels[group[slot]] >> (2 * (lane & 7u))) & 3u;

@@ -120,7 +120,7 @@ extern "C" int qw4sh_flush_l2(void) {
 // Upload + regroup into the resident layout (formats.cuh)
 // ------------------------------------------------------------------------------------
 __global__ void regroup_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, uint32_t type,
-                               uint64_t blocks_per_matrix, uint64_t matrices) {
+                               uint64_t blocks_per_matrix, uint64_t matrices, uint64_t nb) {
     const uint64_t total = blocks_per_matrix * matrices;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t matrix = i / blocks_per_matrix, block = i % blocks_per_matrix;
@@ -133,7 +133,9 @@ __global__ void regroup_kernel(const uint8_t *__restrict__ src, uint8_t *__restr
         } else {                                               // IQ2_XXS
             const uint8_t *b = src + i * 66u;
             uint8_t *base = dst + matrix * blocks_per_matrix * 66u;
-            for (int j = 0; j < 64; j++) base[block * 64u + j] = b[2 + j];
+            const uint64_t row = block / nb, first = row * nb * 8u, swz = iq2_swizzle((uint32_t)row, (uint32_t)nb);
+            for (int j = 0; j < 64; j++)                       // group c of the row goes to position c ^ swizzle
+                base[(first + ((((block % nb) * 8u + (j >> 3))) ^ swz)) * 8u + (j & 7)] = b[2 + j];
             base[blocks_per_matrix * 64u + block * 2u] = b[0];
             base[blocks_per_matrix * 64u + block * 2u + 1] = b[1];
         }
@@ -153,7 +155,7 @@ extern "C" int qw4sh_upload_tensor(const void *host, size_t bytes, uint32_t type
         e = cudaMemcpy(staging, host, bytes, cudaMemcpyHostToDevice);
         if (e == cudaSuccess) {
             const uint64_t per_matrix = (uint64_t)n_out * (k_storage / 256);
-            regroup_kernel<<<1184, 256>>>((const uint8_t *)staging, (uint8_t *)image, type, per_matrix, n_experts);
+            regroup_kernel<<<1184, 256>>>((const uint8_t *)staging, (uint8_t *)image, type, per_matrix, n_experts, k_storage / 256);
             __sync_fetch_and_add(&g_launches, 1ull);
             e = cudaGetLastError();
             if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -199,7 +201,9 @@ extern "C" int qw4sh_decode_rows(const QW4ShTensor *t, size_t expert, size_t row
 // the same binary32 result as glibc 2.39 for every input <= 0 (1 120 927 745 values checked
 // on the CPU), which is the whole domain used here: z - max <= 0 and -|x|.
 // ------------------------------------------------------------------------------------
-__device__ __constant__ unsigned long long c_exp2_table[32] = {
+// In global (not constant) memory: lanes index it with different k, which the constant cache
+// would serialise; the 256 bytes stay in L1.
+__device__ const unsigned long long c_exp2_table[32] = {
     0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
     0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
     0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
@@ -218,7 +222,7 @@ __device__ __forceinline__ float expf_libm(float x) {          // x <= 0 (or +0)
     const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
     kd = __dsub_rn(kd, shift);
     const double r = fma(inv_ln2_n, xd, -kd);
-    unsigned long long t = c_exp2_table[ki & 31u];
+    unsigned long long t = __ldg(&c_exp2_table[ki & 31u]);
     t += ki << 47;
     const double s = __longlong_as_double((long long)t);
     const double z = fma(c0, r, c1), r2 = __dmul_rn(r, r);
@@ -283,6 +287,74 @@ __global__ void __launch_bounds__(32 * TT) router_exact_kernel(DevTensor router,
     }
 }
 
+// Exact, few tokens: one warp per (32 router rows, token).  The serial chain of separately
+// rounded multiply-adds (the reference's order) is the critical path: K dependent additions.
+// To keep operands ahead of the chain, the 32 rows are staged through shared memory by bulk
+// copies (one per lane and chunk of 512 columns, three chunks in flight); rows are padded by
+// 16 bytes so that the lanes' 128-bit reads fall in different banks.
+__device__ __forceinline__ uint32_t rsm_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+constexpr uint32_t RS_CHUNK = 512, RS_PITCH = RS_CHUNK * 4 + 16, RS_STAGES = 3;
+__global__ void __launch_bounds__(32) router_exact_small_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x,
+                                                                float *__restrict__ logits, float *__restrict__ shared_logit,
+                                                                uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t rs_smem[];       // [STAGES][32][PITCH] | x [K] floats | barriers
+    const uint32_t experts = router.n_out, K = router.k_logical, lane = threadIdx.x;
+    const uint32_t e = blockIdx.x * 32 + lane, t = blockIdx.y;
+    const uint8_t *row = e < experts ? router.data + (uint64_t)e * router.row_bytes : (e == experts ? srouter.data : router.data);
+    float *xs = reinterpret_cast<float *>(rs_smem + RS_STAGES * 32 * RS_PITCH);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(rs_smem + RS_STAGES * 32 * RS_PITCH + ((K * 4 + 15) & ~15u));
+    const uint32_t chunks = (K + RS_CHUNK - 1) / RS_CHUNK;
+    if (lane == 0) {
+        for (uint32_t s = 0; s < RS_STAGES; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rsm_u32(&bar[s])), "r"(1u) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    auto issue = [&](uint32_t c) {
+        const uint32_t s = c % RS_STAGES, bytes = min(RS_CHUNK, K - c * RS_CHUNK) * 4;
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(rsm_u32(&bar[s])), "r"(bytes * 32) : "memory");
+        __syncwarp();
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(rsm_u32(rs_smem + (s * 32 + lane) * RS_PITCH)), "l"(row + (uint64_t)c * RS_CHUNK * 4), "r"(bytes), "r"(rsm_u32(&bar[s])) : "memory");
+    };
+    for (uint32_t c = 0; c < RS_STAGES && c < chunks; c++) issue(c);
+    for (uint32_t k = lane * 4; k < K; k += 128) *reinterpret_cast<float4 *>(xs + k) = *reinterpret_cast<const float4 *>(x + (uint64_t)t * K + k);
+    __syncwarp();
+    float sum = 0.0f;
+    bool alive = true;
+    for (uint32_t c = 0; c < chunks; c++) {
+        const uint32_t s = c % RS_STAGES, parity = (c / RS_STAGES) & 1u, cols = min(RS_CHUNK, K - c * RS_CHUNK);
+        if (alive) {                                           // bounded wait (~1 s), then give up with an error bit
+            const long long start = clock64();
+            uint32_t ok = 0;
+            while (!ok) {
+                asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                             : "=r"(ok) : "r"(rsm_u32(&bar[s])), "r"(parity) : "memory");
+                if (!ok && clock64() - start > (1ll << 31)) { atomicOr(status, QW4SH_ERR_STATE); alive = false; break; }
+            }
+        }
+        alive = __all_sync(0xffffffffu, alive);
+        if (alive) {
+            const float4 *w = reinterpret_cast<const float4 *>(rs_smem + (s * 32 + lane) * RS_PITCH);
+            const float4 *xv = reinterpret_cast<const float4 *>(xs + c * RS_CHUNK);
+#pragma unroll 8
+            for (uint32_t i = 0; i < cols / 4; i++) {
+                const float4 a = w[i], b = xv[i];
+                sum = __fadd_rn(sum, __fmul_rn(a.x, b.x)); sum = __fadd_rn(sum, __fmul_rn(a.y, b.y));
+                sum = __fadd_rn(sum, __fmul_rn(a.z, b.z)); sum = __fadd_rn(sum, __fmul_rn(a.w, b.w));
+            }
+        }
+        __syncwarp();
+        if (alive && c + RS_STAGES < chunks) issue(c + RS_STAGES);
+    }
+    if (e <= experts && alive) {
+        if (!finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
+        if (e < experts) logits[(uint64_t)t * experts + e] = sum;
+        else shared_logit[t] = sum;
+    }
+}
+
 // Fast: one warp per router row, lanes stride K with 128-bit loads, tree sum.  Up to 8 tokens
 // per pass share the weight reads.
 __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x,
@@ -328,15 +400,10 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
 // e = 0..E-1 on one lane, the reference's order, so probabilities and weights carry its bits;
 // the k argmax rounds are warp-parallel with ties to the lower id (strict > in ascending e).
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) route_kernel(uint32_t experts, uint32_t k, int norm, const float *__restrict__ logits,
-                                                    uint64_t pitch, uint32_t tokens, float *__restrict__ probs,
-                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status) {
-    extern __shared__ float route_smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
-    const uint32_t t = blockIdx.x * warps + warp;
-    if (t >= tokens) return;
-    float *p = route_smem + (uint64_t)warp * experts;
-    const float *z = logits + (uint64_t)t * pitch;
+// One token: warp-wide.  p is this warp's shared-memory row of `experts` floats.
+__device__ __forceinline__ void route_token(uint32_t experts, uint32_t k, int norm, const float *__restrict__ z, uint32_t t,
+                                            float *p, float *__restrict__ probs, uint32_t *__restrict__ ids,
+                                            float *__restrict__ weights, uint32_t *status, uint32_t lane) {
     bool bad = false;
     float maximum = -CUDART_INF_F;
     for (uint32_t e = lane; e < experts; e += 32) {
@@ -391,6 +458,204 @@ __global__ void __launch_bounds__(128) route_kernel(uint32_t experts, uint32_t k
     if (norm && lane == 0)
         for (uint32_t slot = 0; slot < k; slot++)
             weights[(uint64_t)t * k + slot] = __fdiv_rn(weights[(uint64_t)t * k + slot], selected);
+}
+
+// The same, for experts <= 32 * PL, with the token's probabilities in registers: lane L holds
+// experts L, L + 32, ...  The exp-sum still runs in expert order (e = 0, 1, 2, ...): every lane
+// fetches the values one by one with shuffles and adds them in that order.
+template <int PL>
+__device__ __forceinline__ void route_token_regs(uint32_t experts, uint32_t k, int norm, const float *__restrict__ z, uint32_t t,
+                                                 float *__restrict__ probs, uint32_t *__restrict__ ids, float *__restrict__ weights,
+                                                 uint32_t *status, uint32_t lane) {
+    float p[PL];
+    bool bad = false;
+    float maximum = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < PL; i++) {
+        const uint32_t e = lane + 32 * i;
+        p[i] = e < experts ? z[e] : -CUDART_INF_F;
+        if (e < experts) { bad |= !finite_f32(p[i]); maximum = fmaxf(maximum, p[i]); }
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (bad) {
+        if (lane == 0) { atomicOr(status, QW4SH_ERR_NONFINITE); atomicMin(status + 1, t); }
+        return;
+    }
+    for (int o = 16; o; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+#pragma unroll
+    for (int i = 0; i < PL; i++) p[i] = lane + 32 * i < experts ? expf_libm(__fsub_rn(p[i], maximum)) : 0.0f;
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PL; i++) {
+        if (32u * i >= experts) break;
+        const uint32_t n = min(32u, experts - 32u * i);
+        if (n == 32) {
+#pragma unroll
+            for (int l = 0; l < 32; l++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, p[i], l));
+        } else {
+            for (uint32_t l = 0; l < n; l++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, p[i], l));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < PL; i++) {
+        const uint32_t e = lane + 32 * i;
+        if (e < experts) { p[i] = __fdiv_rn(p[i], sum); probs[(uint64_t)t * experts + e] = p[i]; }
+        else p[i] = -1.0f;
+    }
+    float selected = 0.0f, mine = 0.0f;                        // lane s keeps the weight of slot s
+    for (uint32_t slot = 0; slot < k; slot++) {
+        float best = -1.0f;
+        uint32_t best_e = 0xffffffffu;
+#pragma unroll
+        for (int i = 0; i < PL; i++) if (p[i] > best) { best = p[i]; best_e = lane + 32 * i; }
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (lane == 0) ids[(uint64_t)t * k + slot] = best_e;
+        if ((slot & 31u) == lane) mine = best;                 // k <= 32 on this path
+        if ((best_e & 31u) == lane) {
+#pragma unroll
+            for (int i = 0; i < PL; i++) if ((uint32_t)i == (best_e >> 5)) p[i] = -1.0f;
+        }
+        selected = __fadd_rn(selected, best);
+    }
+    if (lane < k) weights[(uint64_t)t * k + lane] = norm ? __fdiv_rn(mine, selected) : mine;
+}
+
+__global__ void __launch_bounds__(128) route_kernel(uint32_t experts, uint32_t k, int norm, const float *__restrict__ logits,
+                                                    uint64_t pitch, uint32_t tokens, float *__restrict__ probs,
+                                                    uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status) {
+    extern __shared__ float route_smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    const uint32_t t = blockIdx.x * warps + warp;
+    if (t >= tokens) return;
+    if (experts <= 512 && k <= 32) route_token_regs<16>(experts, k, norm, logits + (uint64_t)t * pitch, t, probs, ids, weights, status, lane);
+    else route_token(experts, k, norm, logits + (uint64_t)t * pitch, t, route_smem + (uint64_t)warp * experts, probs, ids, weights, status, lane);
+}
+
+// Few tokens: one CTA of 512 threads per token routes it (thread e owns expert e, experts <=
+// 512), and the CTA that finishes last builds the stable per-expert lists and the groups of
+// <= 4 rows for all tokens (no CTA waits for another: the last one to arrive is found with an
+// atomic counter).  One lone warp per token would be bound by its own instruction latency;
+// spreading exp, division and the k arg-max rounds over 16 warps leaves only the exp-sum serial
+// (512 dependent additions in expert order, the reference's order).
+struct Group4 { uint32_t expert, first, count, pad; };
+__global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts, uint32_t k, int norm, const float *__restrict__ logits,
+                                                                uint32_t tokens, float *__restrict__ probs, uint32_t *__restrict__ ids,
+                                                                float *__restrict__ weights, uint32_t *__restrict__ offsets,
+                                                                uint32_t *__restrict__ pair_to_row, uint32_t *__restrict__ row_to_pair,
+                                                                uint32_t *__restrict__ active, Group4 *__restrict__ groups,
+                                                                uint32_t *__restrict__ n_groups, uint32_t *status) {
+    __shared__ __align__(16) float p[512];
+    __shared__ float wred[16];
+    __shared__ float2 wbest[2][16];
+    __shared__ float s_sum;
+    __shared__ uint32_t s_bad, s_last, wsum[16];
+    extern __shared__ uint32_t sids[];                         // [tokens * k] for the dispatch step
+    const uint32_t t = blockIdx.x, e = threadIdx.x, lane = e & 31u, warp = e >> 5;
+    if (e == 0) s_bad = 0;
+    __syncthreads();
+    float z = e < experts ? logits[(uint64_t)t * experts + e] : -CUDART_INF_F;
+    if (e < experts && !finite_f32(z)) s_bad = 1;
+    float m = z;
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) wred[warp] = m;
+    __syncthreads();
+    const bool bad = s_bad != 0;
+    if (bad && e == 0) { atomicOr(status, QW4SH_ERR_NONFINITE); atomicMin(status + 1, t); }
+    float value = -1.0f;
+    if (!bad) {
+        float maximum = wred[0];
+        for (int w = 1; w < 16; w++) maximum = fmaxf(maximum, wred[w]);
+        p[e] = e < experts ? expf_libm(__fsub_rn(z, maximum)) : 0.0f;
+        __syncthreads();
+        if (e == 0) {                                          // the reference's serial sum, e = 0, 1, 2, ...
+            float sum = 0.0f;
+            uint32_t i = 0;
+            for (; i + 16 <= experts; i += 16) {
+                const float4 a = *reinterpret_cast<const float4 *>(p + i), b = *reinterpret_cast<const float4 *>(p + i + 4);
+                const float4 c = *reinterpret_cast<const float4 *>(p + i + 8), d = *reinterpret_cast<const float4 *>(p + i + 12);
+                sum = __fadd_rn(sum, a.x); sum = __fadd_rn(sum, a.y); sum = __fadd_rn(sum, a.z); sum = __fadd_rn(sum, a.w);
+                sum = __fadd_rn(sum, b.x); sum = __fadd_rn(sum, b.y); sum = __fadd_rn(sum, b.z); sum = __fadd_rn(sum, b.w);
+                sum = __fadd_rn(sum, c.x); sum = __fadd_rn(sum, c.y); sum = __fadd_rn(sum, c.z); sum = __fadd_rn(sum, c.w);
+                sum = __fadd_rn(sum, d.x); sum = __fadd_rn(sum, d.y); sum = __fadd_rn(sum, d.z); sum = __fadd_rn(sum, d.w);
+            }
+            for (; i < experts; i++) sum = __fadd_rn(sum, p[i]);
+            s_sum = sum;
+        }
+        __syncthreads();
+        if (e < experts) { value = __fdiv_rn(p[e], s_sum); probs[(uint64_t)t * experts + e] = value; }
+        float selected = 0.0f, mine = 0.0f;
+        for (uint32_t slot = 0; slot < k; slot++) {
+            float best = value;
+            uint32_t best_e = e;
+            for (int o = 16; o; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (lane == 0) wbest[slot & 1u][warp] = make_float2(best, __uint_as_float(best_e));
+            __syncthreads();
+            best = -2.0f; best_e = 0xffffffffu;
+#pragma unroll
+            for (int w = 0; w < 16; w++) {
+                const float2 c = wbest[slot & 1u][w];
+                const uint32_t ce = __float_as_uint(c.y);
+                if (c.x > best || (c.x == best && ce < best_e)) { best = c.x; best_e = ce; }
+            }
+            if (e == best_e) value = -1.0f;                    // probabilities are >= 0: never chosen again
+            if (e == 0) ids[(uint64_t)t * k + slot] = best_e;
+            if (e == slot) mine = best;                        // thread s keeps the weight of slot s (k <= 512)
+            selected = __fadd_rn(selected, best);
+        }
+        if (e < k) weights[(uint64_t)t * k + e] = norm ? __fdiv_rn(mine, selected) : mine;
+    }
+    // ---- the CTA that arrives last does the dispatch for all tokens ----
+    __threadfence();
+    __syncthreads();
+    if (e == 0) s_last = atomicAdd(n_groups + 2, 1u) == tokens - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    if (e == 0) n_groups[2] = 0;                                // ready for the next call
+    __threadfence();
+    const uint32_t pairs = tokens * k;
+    for (uint32_t q = e; q < pairs; q += blockDim.x) sids[q] = __ldcg(ids + q);
+    __syncthreads();
+    uint32_t count = 0;
+    if (e < experts) for (uint32_t q = 0; q < pairs; q++) count += sids[q] == e;
+    // packed: bits 0-11 rows, 12-21 groups of four, 22-31 non-empty flag
+    const uint32_t packed = count | (((count + 3) >> 2) << 12) | ((count ? 1u : 0u) << 22);
+    uint32_t scan = packed;
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(0xffffffffu, scan, o); if (lane >= (uint32_t)o) scan += v; }
+    if (lane == 31) wsum[warp] = scan;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t v = lane < 16 ? wsum[lane] : 0, sc = v;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, sc, o); if (lane >= (uint32_t)o) sc += u; }
+        if (lane < 16) wsum[lane] = sc - v;
+    }
+    __syncthreads();
+    const uint32_t exclusive = scan - packed + wsum[warp];
+    const uint32_t first = exclusive & 0xfffu, gfirst = (exclusive >> 12) & 0x3ffu, arank = exclusive >> 22;
+    if (e < experts) {
+        offsets[e] = first;
+        if (count) {
+            active[1 + arank] = e;
+            for (uint32_t j = 0; j < (count + 3) >> 2; j++) groups[gfirst + j] = Group4{e, first + 4 * j, min(4u, count - 4 * j), 0};
+            uint32_t cursor = first;
+            for (uint32_t q = 0; q < pairs; q++)
+                if (sids[q] == e) { pair_to_row[q] = cursor; row_to_pair[cursor] = q; cursor++; }
+        }
+    }
+    if (e == blockDim.x - 1) {                                   // inclusive total sits in the last thread
+        const uint32_t total = exclusive + packed;
+        offsets[experts] = total & 0xfffu; n_groups[0] = (total >> 12) & 0x3ffu; active[0] = total >> 22;
+    }
+    for (uint32_t j = e; j < (tokens + 3) / 4; j += blockDim.x)   // the shared expert's groups: rows four at a time
+        groups[pairs + j] = Group4{0, 4 * j, min(4u, tokens - 4 * j), 0};
+    if (e == 0) n_groups[1] = (tokens + 3) / 4;
 }
 
 // ------------------------------------------------------------------------------------
@@ -507,7 +772,7 @@ template <> struct Unit<T_IQ2_XXS> {
                                                   const uint16_t *levels_lut, float (&w)[32], uint32_t (&col)[4]) {
         const uint32_t b = unit >> 3, g = unit & 7u;
         const uint64_t blocks = (uint64_t)rows * nb, block = (uint64_t)row * nb + b;
-        const uint2 group = *reinterpret_cast<const uint2 *>(mat + block * 64u + g * 8u);
+        const uint2 group = *reinterpret_cast<const uint2 *>(mat + ((uint64_t)row * nb * 8u + ((b * 8u + g) ^ iq2_swizzle(row, nb))) * 8u);
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(mat + blocks * 64u + block * 2u)));
         const float scale = d * (float)(2u * (group.y >> 28) + 1u) * 0.125f;
 #pragma unroll
@@ -736,7 +1001,7 @@ static size_t xs_floats(size_t k) { return k + ((k >> 5) << 2) + 4; }
 
 template <typename Kernel>
 static int allow_smem(Kernel kernel, size_t smem) {
-    if (smem > 200u * 1024u) return fail(cudaErrorInvalidValue, "shape needs more shared memory than one CTA has");
+    if (smem > 227u * 1024u) return fail(cudaErrorInvalidValue, "shape needs more shared memory than one CTA has");
     if (smem > 48u * 1024u) CU(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     return 0;
 }
@@ -769,7 +1034,12 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
                          uint32_t *status, int mode, cudaStream_t stream) {
     const DevTensor router = as_dev(layer->w[0]), srouter = as_dev(layer->w[7]);
     const uint32_t rows = layer->experts + 1;
-    if (mode == 0) {
+    if (mode == 0 && tokens <= 16 && router.k_logical % 4 == 0 && router.k_logical <= 4096) {
+        const size_t smem = RS_STAGES * 32 * RS_PITCH + (((size_t)router.k_logical * 4 + 15) & ~(size_t)15) + 64;
+        if (allow_smem(router_exact_small_kernel, smem)) return -1;
+        router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
+        LAUNCHED("router_exact_small_kernel");
+    } else if (mode == 0) {
         if (tokens <= 1) {
             router_exact_kernel<1><<<dim3((rows + 31) / 32, (unsigned)tokens), dim3(32, 1), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         } else if (tokens <= 4) {
@@ -890,9 +1160,9 @@ extern "C" int qw4sh_stage_times(double *ms, uint64_t *forwards) {
 
 extern "C" int qw4sh_mma_supported(const QW4ShTensor *w, int mode);
 extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
-                                 const uint32_t *row_to_pair, uint32_t k_div, const int8_t *xq, const int *xsum, const float *xscale,
-                                 const float *act_in, float *out, uint32_t *status, int ctas, void *stream);
-extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int *xsum, float *xscale, void *stream);
+                                 const uint32_t *row_to_pair, uint32_t k_div, const int8_t *digits, const int8_t *negated,
+                                 const int *sums, const float *scale, float *out, uint32_t *status, int ctas, void *stream);
+extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream);
 extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,
                              uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, void *stream);
 extern "C" int qw4sh_build_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream);
@@ -906,6 +1176,9 @@ static int sm_count() {
         g_sm_count[device] = 148;
     return g_sm_count[device];
 }
+static int g_only_step = -1;                       // profiling: launch just one step of the layer (-1: all)
+extern "C" void qw4sh_set_only_step(int step) { g_only_step = step; }
+#define STEP(id) (g_only_step < 0 || g_only_step == (id))
 static int g_expert_path = -1;                     // -1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels
 extern "C" void qw4sh_set_expert_path(int path) { g_expert_path = path; }
 
@@ -920,40 +1193,102 @@ static bool mma_path(const QW4ShLayer *layer, size_t tokens) {
            qw4sh_mma_supported(&layer->w[4], 0) && qw4sh_mma_supported(&layer->w[5], 0) && qw4sh_mma_supported(&layer->w[6], 1);
 }
 
+static cudaStream_t g_side_stream[64] = {nullptr};
+static cudaEvent_t g_side_event[64][4] = {{nullptr}};
+static int side_stream(cudaStream_t *stream, cudaEvent_t **events) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    if (!g_side_stream[device]) {
+        CU(cudaStreamCreateWithFlags(&g_side_stream[device], cudaStreamNonBlocking));
+        for (int i = 0; i < 4; i++) CU(cudaEventCreateWithFlags(&g_side_event[device][i], cudaEventDisableTiming));
+    }
+    *stream = g_side_stream[device]; *events = g_side_event[device];
+    return 0;
+}
+
+static int launch_route_group_small(const QW4ShLayer *layer, const QW4ShWork *work, uint32_t T, cudaStream_t stream) {
+    const uint32_t E = layer->experts, k = layer->top_k;
+    route_group_small_kernel<<<T, 512, (size_t)T * k * 4, stream>>>(E, k, layer->norm, work->logits, T, work->probs, work->ids,
+                                                                    work->weights, work->offsets, work->pair_to_row, work->row_to_pair,
+                                                                    work->active, (Group4 *)work->groups, work->n_groups, work->status);
+    LAUNCHED("route_group_small_kernel");
+    return 0;
+}
+
 static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                           uint32_t *ids_out, float *weights_out, int router_mode, bool timed) {
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
     const bool mma = mma_path(layer, tokens);
+    const bool fused_route = mma && T <= 64 && E <= 512 && k <= E && T * k < 4096;
     int rc, stage = 0;
 #define STAGE_MARK() do { if (timed) CU(cudaEventRecord(g_stage_event[stage++], stream)); } while (0)
     STAGE_MARK();
-    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
-    if (mma && (rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xsum, work->xscale, stream))) return rc;
-    STAGE_MARK();
-    if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
-    STAGE_MARK();
-    if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
-    if (mma) {
-        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
-        if ((rc = qw4sh_build_dense_groups(T, work->shared_groups, work->n_groups + 1, stream))) return rc;
+    // The shared expert and the quantisation of x need only x: they run on a second stream
+    // beside router and route, and join before the routed experts / the combine.  (Serial when
+    // timing stages.)
+    cudaStream_t side = stream;
+    cudaEvent_t *ev = nullptr;                          // [0] fork, [1] x digits ready, [2] routes ready, [3] shared expert done
+    const bool overlap = mma && !timed;
+    uint8_t *shared_groups = (uint8_t *)work->groups + (size_t)T * k * 16;      // behind the routed groups
+    if (overlap) {
+        if ((rc = side_stream(&side, &ev))) return rc;
+        CU(cudaEventRecord(ev[0], stream));
+        CU(cudaStreamWaitEvent(side, ev[0], 0));
     }
-    STAGE_MARK();
     if (mma) {
-        const int ctas = sm_count();
-        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq,
-                                    work->xsum, work->xscale, nullptr, work->act, work->status, ctas, stream))) return rc;
+        if (STEP(1) && (rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xneg, work->xsum, work->xscale, side))) return rc;
+        if (overlap) CU(cudaEventRecord(ev[1], side));
+    }
+    const int ctas = sm_count();
+    auto shared_branch = [&](int which) -> int {
+        if (which == 0) {
+            if (!fused_route && (rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, side))) return rc;
+            if (!STEP(4)) return 0;
+            return qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], shared_groups, work->n_groups + 1, nullptr, 1, work->xq, work->xneg,
+                                     work->xsum, work->xscale, work->shared_act, work->status, ctas, side);
+        }
+        if (STEP(7) && (rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
+        if (!STEP(8)) return 0;
+        return qw4sh_grouped_mma(1, &layer->w[6], nullptr, shared_groups, work->n_groups + 1, nullptr, 1, work->sq, work->sneg, work->ssum,
+                                 work->sscale, work->shared_out, work->status, ctas, side);
+    };
+    if (STEP(0) && (rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
+    STAGE_MARK();
+    if (fused_route) {
+        if (STEP(2) && (rc = launch_route_group_small(layer, work, T, stream))) return rc;
+        STAGE_MARK(); STAGE_MARK();
+        if (overlap) {                                // shared groups are written by the fused kernel
+            CU(cudaEventRecord(ev[2], stream));
+            CU(cudaStreamWaitEvent(side, ev[2], 0));
+        }
+    } else {
+        if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
         STAGE_MARK();
-        if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 1, nullptr, 1, work->xq,
-                                    work->xsum, work->xscale, nullptr, work->shared_act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+        if (mma && (rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         STAGE_MARK();
-        if ((rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, k, nullptr, nullptr,
-                                    nullptr, work->act, work->out, work->status, ctas, stream))) return rc;
+    }
+    if (mma) {
+        if (overlap) {
+            if ((rc = shared_branch(0)) || (rc = shared_branch(1))) return rc;
+            CU(cudaEventRecord(ev[3], side));
+            CU(cudaStreamWaitEvent(stream, ev[1], 0));
+        }
+        if (STEP(3) && (rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq,
+                                    work->xneg, work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
         STAGE_MARK();
-        if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 1, nullptr, 1, nullptr, nullptr,
-                                    nullptr, work->shared_act, work->shared_out, work->status, ctas, stream))) return rc;
+        if (!overlap && (rc = shared_branch(0))) return rc;
         STAGE_MARK();
-        if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
+        if (STEP(5) && (rc = qw4sh_quantize_rows(work->act, T * k, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
+        if (STEP(6) && (rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
+                                    work->asum, work->ascale, work->out, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if (!overlap && (rc = shared_branch(1))) return rc;
+        STAGE_MARK();
+        if (overlap) CU(cudaStreamWaitEvent(stream, ev[3], 0));
+        if (STEP(9) && (rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
         STAGE_MARK();
     } else {
         const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);

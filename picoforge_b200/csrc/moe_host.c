@@ -207,7 +207,7 @@ static int status_clear(Qwen4MoeWork *w) {
     status_start(w);
     return qw4sh_memcpy2d_async(w->d.status, 16, w->status_host, 16, 16, 1, 1, w->d.stream);
 }
-typedef struct { size_t offset[24], total; } Plan;
+typedef struct { size_t offset[40], total; } Plan;
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan *plan, Qwen4Error *err) {
@@ -215,11 +215,17 @@ static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan 
     const size_t t = cap < CHUNK_TOKENS ? cap : CHUNK_TOKENS, k = m->c.top_k, e = m->c.experts, h = m->c.hidden_size;
     if (k && t > SIZE_MAX / k) return report(err, QW4_OVERFLOW, "pair count overflow");
     const size_t pairs = t * k;
-    const size_t count[23] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
-        pairs * m->c.intermediate, t * m->c.shared_intermediate, t * h, 4,
-        pairs * h, t * h, t * h / 2 + 8, t * (h / 32 + 1) * 2, t, pairs * 4 + 4, t + 8, 2};
+    const size_t i = m->c.intermediate, si = m->c.shared_intermediate;
+    /* sizes in 4-byte words */
+    const size_t count[34] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
+        pairs * i, t * si, t * h, 4,
+        pairs * h, t * h,                                   /* 15 out, 16 shared_out */
+        t * h / 2 + 8, t * h / 2 + 8, t * (h / 32 + 1) * 2, t,                 /* 17 xq, 18 xneg, 19 xsum, 20 xscale */
+        pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) * 2, pairs,  /* 21 aq, 22 aneg, 23 asum, 24 ascale */
+        t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) * 2, t,              /* 25 sq, 26 sneg, 27 ssum, 28 sscale */
+        pairs * 4 + t + 16, t + 8, 4, 0, 0};                                  /* 29 groups, 30 spare, 31 n_groups */
     size_t at = 0;
-    for (int j = 0; j < 23; j++) {
+    for (int j = 0; j < 34; j++) {
         if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
         plan->offset[j] = at;
         at += align256(count[j] * 4 + 4);
@@ -284,10 +290,19 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->d.routed = NULL;
     w->d.status = (uint32_t *)(base + plan.offset[14]);
     w->d.out = (float *)(base + plan.offset[15]); w->d.shared_out = (float *)(base + plan.offset[16]);
-    w->d.xq = (int8_t *)(base + plan.offset[17]); w->d.xsum = (int *)(base + plan.offset[18]);
-    w->d.xscale = (float *)(base + plan.offset[19]);
-    w->d.groups = base + plan.offset[20]; w->d.shared_groups = base + plan.offset[21];
-    w->d.n_groups = (uint32_t *)(base + plan.offset[22]);
+    w->d.xq = (int8_t *)(base + plan.offset[17]); w->d.xneg = (int8_t *)(base + plan.offset[18]);
+    w->d.xsum = (int *)(base + plan.offset[19]); w->d.xscale = (float *)(base + plan.offset[20]);
+    w->d.aq = (int8_t *)(base + plan.offset[21]); w->d.aneg = (int8_t *)(base + plan.offset[22]);
+    w->d.asum = (int *)(base + plan.offset[23]); w->d.ascale = (float *)(base + plan.offset[24]);
+    w->d.sq = (int8_t *)(base + plan.offset[25]); w->d.sneg = (int8_t *)(base + plan.offset[26]);
+    w->d.ssum = (int *)(base + plan.offset[27]); w->d.sscale = (float *)(base + plan.offset[28]);
+    w->d.groups = base + plan.offset[29]; w->d.shared_groups = base + plan.offset[30];
+    w->d.n_groups = (uint32_t *)(base + plan.offset[31]);
+    if (qw4sh_prepare_mma()) {
+        Qwen4Status st = cuda_failure(err, "tensor-core tables");
+        qwen4_moe_work_destroy(w);
+        return st;
+    }
     if (qw4sh_memset_async(w->device_block, 0, plan.total, w->d.stream) || status_clear(w) || qw4sh_stream_sync(w->d.stream)) {
         Qwen4Status st = cuda_failure(err, "workspace clear");
         qwen4_moe_work_destroy(w);
@@ -597,6 +612,7 @@ void qw4cu_set_graph_mode(int on) { qw4sh_set_graph_mode(on); }
 int qw4cu_get_graph_mode(void) { return qw4sh_get_graph_mode(); }
 void qw4cu_set_stage_timing(int on) { qw4sh_set_stage_timing(on); }
 void qw4cu_set_expert_path(int path) { qw4sh_set_expert_path(path); }
+void qw4cu_set_only_step(int step) { qw4sh_set_only_step(step); }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }
