@@ -250,6 +250,37 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *moe, const float *x_dev, fl
  * bounds, bit 4 state) into a status and latches the workspace on failure. */
 Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
 
+/* Expert parallelism (no counterpart in the reference, which is a single-device engine).
+ * A sharded handle holds experts [first_expert, first_expert + local_experts) of the layer:
+ * weights->gate/up/down carry local_experts experts, the router and the shared expert are
+ * complete.  The layer is then run in three device-pointer pieces, between which the caller
+ * exchanges rows with the other ranks (all-to-all):
+ *   route     x [tokens, hidden] -> ids, weights [tokens, k] (global expert ids), kept in the
+ *             workspace for the combine and optionally copied out;
+ *   experts   rows [rows, hidden] gathered from all ranks, local_ids [rows] = expert index
+ *             inside this shard or 0xffffffff for an unused row -> out [rows, hidden], the
+ *             expert's SwiGLU output per row (unused rows are not meaningful);
+ *   combine   pair_out [tokens * k, hidden] in pair order (token * k + slot) -> y = slot-order
+ *             weighted sum + sigmoid-gated shared expert, with the weights of the route call.
+ * All three enqueue on the stream in force and return without waiting. */
+Qwen4Status qw4cu_moe_create_sharded(const Qwen4MoeConfig *config, const Qwen4MoeWeights *weights,
+                                     uint32_t first_expert, uint32_t local_experts, Qwen4Moe **out,
+                                     Qwen4Error *err);
+Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
+                                   uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work,
+                                   Qwen4Error *err);
+Qwen4Status qw4cu_moe_experts_device(const Qwen4Moe *moe, const float *rows_dev, size_t rows,
+                                     const uint32_t *local_ids_dev, float *out_dev,
+                                     Qwen4MoeWork *work, Qwen4Error *err);
+Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
+                                     const float *pair_out_dev, float *y_dev, Qwen4MoeWork *work,
+                                     Qwen4Error *err);
+/* Makes every later call on this device enqueue on the caller's CUDA stream (a cudaStream_t
+ * passed as void *), so that the library's kernels order with the caller's own work, e.g. the
+ * NCCL all-to-all of an expert-parallel step.  NULL restores the library's own stream; the legacy
+ * default stream is named by its handle cudaStreamLegacy ((cudaStream_t)1), not by 0. */
+int qw4cu_set_stream(void *cuda_stream);
+
 /* Timing on the workspace's stream with CUDA events.  begin/end record events; elapsed
  * waits for the end event and returns milliseconds (negative on error). */
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *work);

@@ -190,6 +190,11 @@ class MoeApi:
             "qw4cu_moe_work_device_bytes": ([P], C.c_size_t),
             "qw4cu_moe_forward_device": ([P, P, P, C.c_size_t, P, P, P, E], C.c_int),
             "qw4cu_moe_work_sync": ([P, E], C.c_int),
+            "qw4cu_moe_create_sharded": ([C.POINTER(Qwen4MoeConfig), C.POINTER(Qwen4MoeWeights), C.c_uint32, C.c_uint32, C.POINTER(P), E], C.c_int),
+            "qw4cu_moe_route_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
+            "qw4cu_moe_experts_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
+            "qw4cu_moe_combine_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
+            "qw4cu_set_stream": ([P], C.c_int),
             "qw4cu_moe_work_timer_begin": ([P], C.c_int),
             "qw4cu_moe_work_timer_end": ([P], C.c_int),
             "qw4cu_moe_work_timer_elapsed_ms": ([P], C.c_float),

@@ -124,6 +124,16 @@ int qw4sh_group(uint32_t experts, uint32_t k, size_t tokens, const uint32_t *ids
 int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y,
                         size_t tokens, uint32_t *ids_out, float *weights_out, int router_mode);
 
+/* Expert-parallel pieces of the layer (see include/qwen4_moe_b200.h). */
+int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode);
+int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *rows_x, size_t rows,
+                          const uint32_t *local_ids, uint32_t local_experts, float *out);
+int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens,
+                          const float *pair_out, float *y);
+/* Caller-provided stream (NULL: back to the library's own).  current_stream returns the one in force. */
+int qw4sh_set_stream(void *stream);
+int qw4sh_current_stream(void **stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -76,7 +76,8 @@ extern "C" int qw4sh_memcpy2d_async(void *dst, size_t dst_pitch, const void *src
                                     size_t width, size_t rows, int to_device, void *stream) {
     if (width && rows)
         CU(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, rows,
-                             to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+                             to_device == 2 ? cudaMemcpyDeviceToDevice : to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                             (cudaStream_t)stream));
     return 0;
 }
 extern "C" int qw4sh_memset_async(void *dst, int value, size_t bytes, void *stream) {
@@ -673,7 +674,7 @@ __global__ void __launch_bounds__(1024) group_kernel(uint32_t experts, uint32_t 
     bool bounds = false;
     for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) {
         const uint32_t e = ids[p];
-        if (e < experts) atomicAdd(&counts[e], 1u); else bounds = true;
+        if (e < experts) atomicAdd(&counts[e], 1u); else if (e != 0xffffffffu) bounds = true;   // 0xffffffff: no expert, skipped
     }
     if (bounds) atomicOr(status, QW4SH_ERR_BOUNDS);
     __syncthreads();
@@ -963,10 +964,10 @@ __global__ void __launch_bounds__(DR_WARPS * 32) down_reduce_kernel(DevTensor do
         const uint32_t s = i / inter, c = i % inter;
         dr_smem[s * a_pitch + xs_index(c)] = act[((uint64_t)t * k + s) * inter + c];
     }
-    for (uint32_t i = threadIdx.x; i < sinter; i += blockDim.x) sa[xs_index(i)] = shared_act[(uint64_t)t * sinter + i];
+    if (shared_act) for (uint32_t i = threadIdx.x; i < sinter; i += blockDim.x) sa[xs_index(i)] = shared_act[(uint64_t)t * sinter + i];
     __syncthreads();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const float gate = sigmoid_libm(shared_logit[t]);
+    const float gate = shared_act ? sigmoid_libm(shared_logit[t]) : 0.0f;
     for (uint32_t j = warp; j < DR_TILE; j += DR_WARPS) {
         const uint32_t c = blockIdx.x * DR_TILE + j;
         if (c >= hidden) break;
@@ -974,11 +975,12 @@ __global__ void __launch_bounds__(DR_WARPS * 32) down_reduce_kernel(DevTensor do
         bool bad = false;
         for (uint32_t s = 0; s < k; s++) {
             const uint32_t e = ids[(uint64_t)t * k + s];
+            if (e == 0xffffffffu) continue;                    // no expert for this row (expert-parallel padding)
             if (e >= down.n_experts) { bad = true; continue; }
             const float dot = row_dot<RT>(down, down.data + (uint64_t)e * down.expert_bytes, c, dr_smem + s * a_pitch, levels_lut, lane);
-            sum = __fadd_rn(sum, __fmul_rn(weights[(uint64_t)t * k + s], dot));
+            sum = __fadd_rn(sum, __fmul_rn(weights ? weights[(uint64_t)t * k + s] : 1.0f, dot));
         }
-        const float sdot = row_dot<ST>(sdown, sdown.data, c, sa, levels_lut, lane);
+        const float sdot = shared_act ? row_dot<ST>(sdown, sdown.data, c, sa, levels_lut, lane) : 0.0f;
         const float out = __fadd_rn(sum, __fmul_rn(gate, sdot));
         if (lane == 0) {
             if (bad) atomicOr(status, QW4SH_ERR_BOUNDS);
@@ -1308,6 +1310,88 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         LAUNCHED("copy_routes_kernel");
     }
     return 0;
+}
+
+// ------------------------------------------------------------------------------------
+// Expert-parallel pieces: route only / experts only (rows already gathered from all ranks,
+// ids local to this rank's shard, 0xffffffff = no expert) / shared expert + combine.
+// ------------------------------------------------------------------------------------
+extern "C" int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode) {
+    if (!tokens) return 0;
+    if (ensure_constants()) return -1;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    int rc;
+    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
+    return qw4sh_route(layer->experts, layer->top_k, layer->norm, work->logits, layer->experts, tokens, work->probs, work->ids,
+                       work->weights, work->status, stream);
+}
+
+extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *rows_x, size_t rows,
+                                     const uint32_t *local_ids, uint32_t local_experts, float *out) {
+    if (!rows) return 0;
+    if (ensure_constants()) return -1;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t R = (uint32_t)rows, H = layer->hidden;
+    int rc;
+    if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
+                     qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) && (g_expert_path == 1 || rows <= 2048);
+    if (mma) {
+        const int ctas = sm_count();
+        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(rows_x, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xneg,
+                                    work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
+        return qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
+                                 work->asum, work->ascale, out, work->status, ctas, stream);
+    }
+    const uint32_t groups = R < local_experts ? R : local_experts;
+    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), rows_x, H, work->offsets, work->row_to_pair, work->active, 1, R,
+                             groups, work->act, work->status, stream))) return rc;
+    return launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, nullptr, local_ids, nullptr, nullptr, 1, R, out, nullptr,
+                       work->status, stream);
+}
+
+extern "C" int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *pair_out,
+                                     float *y) {
+    if (!tokens) return 0;
+    if (ensure_constants()) return -1;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t T = (uint32_t)tokens, H = layer->hidden;
+    if (layer->w[4].type != layer->w[5].type || !qw4sh_mma_supported(&layer->w[4], 0) || !qw4sh_mma_supported(&layer->w[5], 0) ||
+        !qw4sh_mma_supported(&layer->w[6], 1))
+        return fail(cudaErrorNotSupported, "expert-parallel combine needs a Q4_K or IQ2_XXS shared expert");
+    const int ctas = sm_count();
+    uint8_t *shared_groups = (uint8_t *)work->groups + (size_t)T * layer->top_k * 16;
+    int rc;
+    if ((rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, stream))) return rc;
+    if ((rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+    if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], shared_groups, work->n_groups + 1, nullptr, 1, work->xq, work->xneg, work->xsum,
+                                work->xscale, work->shared_act, work->status, ctas, stream))) return rc;
+    if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, stream))) return rc;
+    if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, shared_groups, work->n_groups + 1, nullptr, 1, work->sq, work->sneg, work->ssum,
+                                work->sscale, work->shared_out, work->status, ctas, stream))) return rc;
+    return qw4sh_combine(pair_out, work->shared_out, work->weights, work->shared_logit, layer->top_k, H, T, y, nullptr, work->status, stream);
+}
+
+// The stream every workspace created afterwards (and every existing one, through
+// qw4sh_current_stream) enqueues on.  nullptr: the library's own stream.
+static cudaStream_t g_user_stream[64] = {nullptr};
+static bool g_user_stream_set[64] = {false};
+extern "C" int qw4sh_set_stream(void *stream) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    g_user_stream[device] = (cudaStream_t)stream;
+    g_user_stream_set[device] = stream != nullptr;
+    return 0;
+}
+extern "C" int qw4sh_current_stream(void **stream) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device >= 0 && device < 64 && g_user_stream_set[device]) { *stream = g_user_stream[device]; return 0; }
+    return qw4sh_shared_stream(stream);
 }
 
 extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,

@@ -25,6 +25,7 @@ struct Qwen4Moe {
     size_t device_bytes;
     size_t refs;
     bool alive;
+    uint32_t first_expert, local_experts;   /* expert shard held by this handle (all of them unless sharded) */
 };
 
 struct Qwen4MoeWork {
@@ -153,17 +154,20 @@ static void release(Qwen4Moe *m) {
     }
 }
 
-Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, Qwen4Moe **out, Qwen4Error *err) {
+static Qwen4Status create_shard(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, uint32_t first_expert,
+                                uint32_t local_experts, Qwen4Moe **out, Qwen4Error *err) {
     if (out) *out = NULL;
     if (!out || !weights) return report(err, QW4_INVALID_ARGUMENT, "null create argument");
     TRY(check_config(c, err));
+    if (!local_experts || first_expert > c->experts || local_experts > c->experts - first_expert)
+        return report(err, QW4_RANGE, "expert shard outside the layer");
     const QW4PackedCpuView w[8] = {weights->router, weights->gate, weights->up, weights->down,
         weights->shared_gate, weights->shared_up, weights->shared_down, weights->shared_router};
     const size_t h = c->hidden_size, i = c->intermediate, s = c->shared_intermediate;
     const size_t in[8] = {h, h, h, i, h, h, s, h}, n[8] = {c->experts, i, i, h, s, s, h, 1};
     for (size_t a = 0; a < 8; a++) {
         const QW4PackedLayout *l = &w[a].layout;
-        const size_t experts = (a >= 1 && a <= 3) ? c->experts : 1;
+        const size_t experts = (a >= 1 && a <= 3) ? local_experts : 1;
         if (l->k_logical != in[a] || l->n_out != n[a] || l->n_experts != experts ||
             l->k_storage != (a == 3 ? c->down_physical : in[a]))
             return report(err, QW4_SHAPE, "MoE weight shape mismatch");
@@ -174,6 +178,7 @@ Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *wei
     Qwen4Moe *m = calloc(1, sizeof *m);
     if (!m) return report(err, QW4_OOM, "MoE allocation");
     m->c = *c; memcpy(m->host, w, sizeof w); m->refs = 1; m->alive = true;
+    m->first_expert = first_expert; m->local_experts = local_experts;
     m->layer.hidden = c->hidden_size; m->layer.experts = c->experts; m->layer.top_k = c->top_k;
     m->layer.inter = c->intermediate; m->layer.shared_inter = c->shared_intermediate;
     m->layer.down_physical = c->down_physical; m->layer.norm = c->norm_topk_prob ? 1 : 0;
@@ -190,6 +195,14 @@ Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *wei
     }
     *out = m;
     return report(err, QW4_OK, "");
+}
+
+Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, Qwen4Moe **out, Qwen4Error *err) {
+    return create_shard(c, weights, 0, c ? c->experts : 0, out, err);
+}
+Qwen4Status qw4cu_moe_create_sharded(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, uint32_t first_expert,
+                                     uint32_t local_experts, Qwen4Moe **out, Qwen4Error *err) {
+    return create_shard(c, weights, first_expert, local_experts, out, err);
 }
 
 void qwen4_moe_destroy(Qwen4Moe *m) {
@@ -328,6 +341,10 @@ void qw4_moe_observe(Qwen4MoeWork *w, QW4MoeObserver fn, void *ctx) {
 }
 
 /* ---- forward ---------------------------------------------------------------------------- */
+static void use_current_stream(Qwen4MoeWork *w) {
+    void *stream = NULL;
+    if (!qw4sh_current_stream(&stream)) w->d.stream = stream;
+}
 static Qwen4Status status_result(Qwen4MoeWork *w, Qwen4Error *err) {
     const uint32_t bits = w->status_host[0];
     if (bits & QW4SH_ERR_BOUNDS) return report(err, QW4_GPU_ERROR, "expert id outside the tensor");
@@ -348,6 +365,8 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *m, const float *x_dev, floa
     if (w->busy) return report(err, QW4_BUSY, "workspace executing");
     if (tokens > w->cap) return report(err, QW4_CAPACITY, "batch exceeds token capacity");
     if (tokens && (!x_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (m->local_experts != m->c.experts) return report(err, QW4_BAD_STATE, "sharded handle: use the route/experts/combine calls");
+    use_current_stream(w);
     const size_t h = m->c.hidden_size, k = m->c.top_k;
     for (size_t start = 0; start < tokens; start += w->chunk) {
         const size_t n = tokens - start < w->chunk ? tokens - start : w->chunk;
@@ -359,8 +378,45 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *m, const float *x_dev, floa
     return report(err, QW4_OK, "");
 }
 
+/* ---- expert-parallel pieces -------------------------------------------------------------- */
+static Qwen4Status piece_checks(const Qwen4Moe *m, Qwen4MoeWork *w, size_t rows, Qwen4Error *err) {
+    if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
+    if (w->owner != m) return report(err, QW4_OWNER, "workspace belongs to another MoE");
+    if (!m->alive || w->failed) return report(err, QW4_BAD_STATE, "inactive MoE/workspace; reset required");
+    if (w->busy) return report(err, QW4_BUSY, "workspace executing");
+    if (rows > w->chunk) return report(err, QW4_CAPACITY, "batch exceeds the workspace (cap and 2048-row chunk)");
+    use_current_stream(w);
+    return QW4_OK;
+}
+Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, uint32_t *ids_dev, float *weights_dev,
+                                   Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens, err));
+    if (tokens && !x_dev) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (qw4sh_route_forward(&m->layer, &w->d, x_dev, tokens, current_router_mode())) return cuda_failure(err, "route launch");
+    const size_t bytes = tokens * m->c.top_k * 4;
+    if (tokens && ids_dev && qw4sh_memcpy2d_async(ids_dev, bytes, w->d.ids, bytes, bytes, 1, 2, w->d.stream)) return cuda_failure(err, "ids copy");
+    if (tokens && weights_dev && qw4sh_memcpy2d_async(weights_dev, bytes, w->d.weights, bytes, bytes, 1, 2, w->d.stream)) return cuda_failure(err, "weights copy");
+    return report(err, QW4_OK, "");
+}
+Qwen4Status qw4cu_moe_experts_device(const Qwen4Moe *m, const float *rows_dev, size_t rows, const uint32_t *local_ids_dev,
+                                     float *out_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, rows, err));
+    if (rows && (!rows_dev || !local_ids_dev || !out_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (qw4sh_experts_forward(&m->layer, &w->d, rows_dev, rows, local_ids_dev, m->local_experts, out_dev)) return cuda_failure(err, "experts launch");
+    return report(err, QW4_OK, "");
+}
+Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, const float *pair_out_dev, float *y_dev,
+                                     Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens, err));
+    if (tokens && (!x_dev || !pair_out_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (qw4sh_combine_forward(&m->layer, &w->d, x_dev, tokens, pair_out_dev, y_dev)) return cuda_failure(err, "combine launch");
+    return report(err, QW4_OK, "");
+}
+int qw4cu_set_stream(void *cuda_stream) { return qw4sh_set_stream(cuda_stream); }
+
 Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *w, Qwen4Error *err) {
     if (!w) return report(err, QW4_INVALID_ARGUMENT, "null workspace");
+    use_current_stream(w);
     if (qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream) || qw4sh_stream_sync(w->d.stream)) {
         w->failed = true;
         return cuda_failure(err, "stream synchronize");
@@ -378,6 +434,8 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
     if (w->busy) return report(err, QW4_BUSY, "workspace executing");
     const size_t t = x.dim[0], h = m->c.hidden_size, k = m->c.top_k;
     if (t > w->cap) return report(err, QW4_CAPACITY, "batch exceeds token capacity");
+    if (m->local_experts != m->c.experts) return report(err, QW4_BAD_STATE, "sharded handle: use the route/experts/combine calls");
+    use_current_stream(w);
     Span spans[4]; size_t ns = 2;
     TRY(check_f32(x.data, x.capacity_bytes, x.rank, x.dim, x.stride_bytes, t, h, &spans[0], err));
     TRY(check_f32(y.data, y.capacity_bytes, y.rank, y.dim, y.stride_bytes, t, h, &spans[1], err));

@@ -217,7 +217,7 @@ int qw4s_encode_rows(uint32_t type, const float *src, size_t rows, size_t k, uin
 }
 
 typedef struct {
-    uint32_t type; uint64_t seed, stream; float sigma; size_t rows, k, first, last; uint8_t *out; int status;
+    uint32_t type; uint64_t seed, stream; float sigma; size_t rows, k, first, last, row0; uint8_t *out; int status;
 } Slice;
 static void *slice_worker(void *arg) {
     Slice *s = arg;
@@ -225,7 +225,7 @@ static void *slice_worker(void *arg) {
     float *row = malloc(s->k * sizeof *row);
     if (!row) { s->status = -1; return NULL; }
     for (size_t r = s->first; r < s->last; r++) {
-        normal_row(s->seed, s->stream, r, s->sigma, row, s->k);
+        normal_row(s->seed, s->stream, r + s->row0, s->sigma, row, s->k);
         if (qw4s_encode_rows(s->type, row, 1, s->k, s->out + r * bytes)) { s->status = -1; break; }
     }
     free(row);
@@ -234,8 +234,16 @@ static void *slice_worker(void *arg) {
 
 /* A whole tensor of `rows` rows (all experts stacked) of k weights ~ N(0, sigma), encoded
  * as `type`, written to out.  threads >= 1. */
+int qw4s_tensor_rows(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size_t row0, size_t rows, size_t k,
+                     uint8_t *out, int threads);
 int qw4s_tensor(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size_t rows, size_t k,
                 uint8_t *out, int threads) {
+    return qw4s_tensor_rows(type, seed, stream, sigma, 0, rows, k, out, threads);
+}
+/* Rows [row0, row0 + rows) of the same tensor (an expert shard): identical bytes to the
+ * corresponding slice of the whole tensor. */
+int qw4s_tensor_rows(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size_t row0, size_t rows, size_t k,
+                     uint8_t *out, int threads) {
     if (type != 0 && (!block_bytes(type) || k % 256)) return -1;
     if (threads < 1) threads = 1;
     if (threads > 256) threads = 256;
@@ -246,7 +254,7 @@ int qw4s_tensor(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size
     int started = 0;
     for (int i = 0; i < threads; i++) {
         const size_t first = per * (size_t)i, last = first + per < rows ? first + per : rows;
-        slice[i] = (Slice){type, seed, stream, sigma, rows, k, first < rows ? first : rows, last, out, 0};
+        slice[i] = (Slice){type, seed, stream, sigma, rows, k, first < rows ? first : rows, last, row0, out, 0};
         if (i + 1 < threads && pthread_create(&tid[started], NULL, slice_worker, &slice[i]) == 0) started++;
         else slice_worker(&slice[i]);
     }

@@ -27,15 +27,32 @@ class LayerSpec:
     norm: bool = True
     types: tuple = (abi.F32, abi.Q4_K, abi.Q4_K, abi.Q4_K, abi.Q4_K, abi.Q4_K, abi.Q4_K, abi.F32)
     tensors: list = field(default_factory=list)   # eight uint8 arrays in Qwen4MoeWeights order
+    first_expert: int = 0                         # expert shard held by the routed tensors
+    local_experts: int | None = None              # None: all of them
 
     def __post_init__(self):
         if self.down_physical is None:
             self.down_physical = self.inter
 
+    @property
+    def sharded(self) -> bool:
+        return self.local_experts is not None and self.local_experts != self.experts
+
+    def shard(self, first: int, count: int) -> "LayerSpec":
+        """A spec whose routed tensors are experts [first, first + count) of this (complete) one."""
+        assert not self.sharded
+        out = LayerSpec(self.hidden, self.experts, self.top_k, self.inter, self.shared_inter, self.down_physical, self.norm,
+                        self.types, list(self.tensors), first, count)
+        for index, layout in zip((1, 2, 3), self.layouts()[1:4]):
+            eb = layout.expert_bytes
+            out.tensors[index] = self.tensors[index][first * eb:(first + count) * eb]
+        return out
+
     def shapes(self):
         """(k_storage, k_logical, n_out, n_experts) of the eight tensors."""
-        h, i, s, e, dp = self.hidden, self.inter, self.shared_inter, self.experts, self.down_physical
-        return [(h, h, e, 1), (h, h, i, e), (h, h, i, e), (dp, i, h, e),
+        h, i, s, dp = self.hidden, self.inter, self.shared_inter, self.down_physical
+        e = self.experts if self.local_experts is None else self.local_experts
+        return [(h, h, self.experts, 1), (h, h, i, e), (h, h, i, e), (dp, i, h, e),
                 (h, h, s, 1), (h, h, s, 1), (s, s, h, 1), (h, h, 1, 1)]
 
     def layouts(self):
@@ -64,7 +81,11 @@ class MoeLayer:
         self.work = C.c_void_p()
         err = abi.Qwen4Error()
         cfg, weights = spec.config(), spec.weights()
-        st = api.lib.qwen4_moe_create(C.byref(cfg), C.byref(weights), C.byref(self.moe), C.byref(err))
+        if spec.sharded:
+            st = api.lib.qw4cu_moe_create_sharded(C.byref(cfg), C.byref(weights), spec.first_expert, spec.local_experts,
+                                                  C.byref(self.moe), C.byref(err))
+        else:
+            st = api.lib.qwen4_moe_create(C.byref(cfg), C.byref(weights), C.byref(self.moe), C.byref(err))
         if st:
             raise abi.MoeError(st, err)
         size = C.c_size_t()

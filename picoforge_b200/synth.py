@@ -28,6 +28,9 @@ def _lib():
         _LIB.qw4s_tensor.argtypes = [C.c_uint32, C.c_uint64, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t,
                                      C.c_void_p, C.c_int]
         _LIB.qw4s_tensor.restype = C.c_int
+        _LIB.qw4s_tensor_rows.argtypes = [C.c_uint32, C.c_uint64, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t, C.c_size_t,
+                                          C.c_void_p, C.c_int]
+        _LIB.qw4s_tensor_rows.restype = C.c_int
         _LIB.qw4s_encode_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
         _LIB.qw4s_encode_rows.restype = C.c_int
         _LIB.qw4s_normal.argtypes = [C.c_uint64, C.c_uint64, C.c_float, C.c_void_p, C.c_size_t, C.c_size_t]
@@ -39,10 +42,11 @@ def threads() -> int:
     return max(1, min(64, len(os.sched_getaffinity(0))))
 
 
-def tensor(gguf_type: int, seed: int, stream: int, rows: int, k: int, sigma: float = 0.02) -> np.ndarray:
-    """`rows` rows of k weights ~ N(0, sigma) encoded as gguf_type; returns the packed bytes."""
+def tensor(gguf_type: int, seed: int, stream: int, rows: int, k: int, sigma: float = 0.02, row0: int = 0) -> np.ndarray:
+    """Rows [row0, row0 + rows) of a tensor of k-weight rows ~ N(0, sigma) encoded as gguf_type;
+    returns the packed bytes (a shard has the same bytes as that slice of the whole tensor)."""
     out = np.empty(rows * abi.row_bytes(gguf_type, k), np.uint8)
-    if _lib().qw4s_tensor(gguf_type, seed, stream, sigma, rows, k, out.ctypes.data, threads()):
+    if _lib().qw4s_tensor_rows(gguf_type, seed, stream, sigma, row0, rows, k, out.ctypes.data, threads()):
         raise ValueError(f"cannot synthesise type {gguf_type} with k={k}")
     return out
 
@@ -64,14 +68,19 @@ def normal(seed: int, stream: int, rows: int, k: int, sigma: float = 1.0) -> np.
 
 def make_layer(seed: int, layer: int = 0, routed_type: int = abi.Q4_K, shared_type: int = abi.Q4_K,
                hidden: int = 2048, experts: int = 512, top_k: int = 10, inter: int = 512,
-               shared_inter: int = 512, down_type: int | None = None, norm: bool = True) -> LayerSpec:
-    """One synthetic layer.  Stream ids: layer * 8 + tensor index."""
+               shared_inter: int = 512, down_type: int | None = None, norm: bool = True,
+               shard: tuple | None = None) -> LayerSpec:
+    """One synthetic layer.  Stream ids: layer * 8 + tensor index.  shard = (first_expert,
+    local_experts) generates only that slice of the routed expert tensors."""
     down_type = routed_type if down_type is None else down_type
     types = (abi.F32, routed_type, routed_type, down_type, shared_type, shared_type, shared_type, abi.F32)
     spec = LayerSpec(hidden, experts, top_k, inter, shared_inter, inter, norm, types)
+    if shard is not None:
+        spec.first_expert, spec.local_experts = shard
     tensors = []
     for index, (gguf_type, (k_storage, _, n_out, n_experts)) in enumerate(zip(types, spec.shapes())):
-        tensors.append(tensor(gguf_type, seed, layer * 8 + index, n_out * n_experts, k_storage))
+        row0 = spec.first_expert * n_out if 1 <= index <= 3 else 0
+        tensors.append(tensor(gguf_type, seed, layer * 8 + index, n_out * n_experts, k_storage, row0=row0))
     spec.tensors = tensors
     return spec
 
