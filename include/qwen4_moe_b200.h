@@ -296,6 +296,17 @@ int qw4cu_get_graph_mode(void);
  * Q4_K or IQ2_XXS, everything else the CUDA-core kernels.  0: CUDA-core kernels only.  1:
  * tensor-core grouped kernels for any batch size the formats allow. */
 void qw4cu_set_expert_path(int path);
+/* One-kernel decode path (no counterpart in the reference): batches of up to four tokens whose
+ * expert tensors are all Q4_K or IQ2_XXS run the whole layer as one persistent cooperative kernel
+ * (router, top-k, gate/up + SwiGLU, down + combine, two grid-wide barriers).  -1 (default): used
+ * whenever the layer fits it; 0: never (the multi-kernel sequence runs instead).
+ * qw4cu_decode_phase_clocks copies the SM clock that CTA 0 of the workspace's last one-kernel
+ * launch read at its phase boundaries into clocks[0..12] (start, x staged, x digitised, router
+ * rows done, barrier 1 passed, logits loaded, routed, sources listed, gate/up slices done,
+ * units stored, barrier 2 passed, activations digitised, end); call it after
+ * qw4cu_moe_work_sync. */
+void qw4cu_set_fused_decode(int mode);
+int qw4cu_decode_phase_clocks(const Qwen4MoeWork *work, uint64_t clocks[16]);
 /* Profiling aid: launch only one step of the small-batch sequence on later forwards, so that a
  * kernel can be timed back to back in isolation (the workspace keeps the results of an
  * earlier complete forward).  Steps: 0 router logits, 1 quantise x, 2 route + dispatch, 3 routed

@@ -49,6 +49,7 @@ typedef struct {
     void *groups, *shared_groups; /* [cap * k], [cap / 4 + 1] groups of <= 4 rows (16 bytes each) */
     uint32_t *n_groups;           /* [2]: routed, shared */
     uint32_t *status;             /* [4]: error bits, first bad row, spare */
+    uint32_t *sync;               /* [256]: grid-barrier counters, phase clocks and row maxima of the one-kernel decode path */
     void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
     void *graph_cache;            /* replay cache of the launch sequence (qw4sh_graph_cache_create) */
@@ -123,6 +124,16 @@ int qw4sh_group(uint32_t experts, uint32_t k, size_t tokens, const uint32_t *ids
  * 1 fast.  ids_out / weights_out may be NULL. */
 int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y,
                         size_t tokens, uint32_t *ids_out, float *weights_out, int router_mode);
+
+/* One-kernel decode path (decode_fused.cu): up to four tokens, Q4_K / IQ2_XXS experts.
+ * supported: 1 when the layer, batch and pointers fit it.  set_fused_decode: -1 automatic
+ * (default), 0 never.  fused_decode launches it; phase_clocks copies CTA 0's SM clock at its
+ * phase boundaries of the workspace's last launch (after a synchronise). */
+int qw4sh_fused_supported(const QW4ShLayer *layer, size_t tokens, const float *x, const float *y, int sm_count);
+void qw4sh_set_fused_decode(int mode);
+int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
+                       uint32_t *ids_out, float *weights_out, int router_mode, int sm_count);
+int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]);
 
 /* Expert-parallel pieces of the layer (see include/qwen4_moe_b200.h). */
 int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode);

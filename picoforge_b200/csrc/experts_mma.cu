@@ -574,6 +574,7 @@ extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTen
 }
 
 extern "C" int qw4sh_prepare_mma(void) { return lut_image() ? 0 : -1; }
+extern "C" const uint8_t *qw4sh_lut_image(void) { return lut_image(); }
 
 extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {
     if (!rows) return 0;

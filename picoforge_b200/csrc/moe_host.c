@@ -236,7 +236,7 @@ static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan 
         t * h / 2 + 8, t * h / 2 + 8, t * (h / 32 + 1) * 2, t,                 /* 17 xq, 18 xneg, 19 xsum, 20 xscale */
         pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) * 2, pairs,  /* 21 aq, 22 aneg, 23 asum, 24 ascale */
         t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) * 2, t,              /* 25 sq, 26 sneg, 27 ssum, 28 sscale */
-        pairs * 4 + t + 16, t + 8, 4, 0, 0};                                  /* 29 groups, 30 spare, 31 n_groups */
+        pairs * 4 + t + 16, t + 8, 4, 256, 0};                                  /* 29 groups, 30 spare, 31 n_groups, 32 sync */
     size_t at = 0;
     for (int j = 0; j < 34; j++) {
         if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
@@ -311,6 +311,7 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->d.ssum = (int *)(base + plan.offset[27]); w->d.sscale = (float *)(base + plan.offset[28]);
     w->d.groups = base + plan.offset[29]; w->d.shared_groups = base + plan.offset[30];
     w->d.n_groups = (uint32_t *)(base + plan.offset[31]);
+    w->d.sync = (uint32_t *)(base + plan.offset[32]);
     if (qw4sh_prepare_mma()) {
         Qwen4Status st = cuda_failure(err, "tensor-core tables");
         qwen4_moe_work_destroy(w);
@@ -671,6 +672,8 @@ int qw4cu_get_graph_mode(void) { return qw4sh_get_graph_mode(); }
 void qw4cu_set_stage_timing(int on) { qw4sh_set_stage_timing(on); }
 void qw4cu_set_expert_path(int path) { qw4sh_set_expert_path(path); }
 void qw4cu_set_only_step(int step) { qw4sh_set_only_step(step); }
+void qw4cu_set_fused_decode(int mode) { qw4sh_set_fused_decode(mode); }
+int qw4cu_decode_phase_clocks(const Qwen4MoeWork *w, uint64_t clocks[16]) { return w ? qw4sh_fused_phase_clocks(&w->d, clocks) : -1; }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }
