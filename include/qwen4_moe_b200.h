@@ -306,6 +306,15 @@ void qw4cu_set_expert_path(int path);
  * units stored, barrier 2 passed, activations digitised, end); call it after
  * qw4cu_moe_work_sync. */
 void qw4cu_set_fused_decode(int mode);
+/* Tensor-core prefill path (no counterpart in the reference): batches of more than 64 tokens whose
+ * expert tensors are all Q4_K run gate/up and down as grouped GEMMs on tcgen05 tensor cores with
+ * TMEM accumulators (groups of <= 32 token rows per expert, exact integer codes as fp16 operands,
+ * activations split into fp16 hi + lo).  -1 (default): used whenever the layer fits; 0: never. */
+void qw4cu_set_prefill_path(int path);
+/* Profiling aid of the tensor-core prefill kernels: device_words is a device array of 64 x 8 bytes (NULL: off).
+ * CTA 0 of every later launch stores the SM cycles its roles (0 epilogue, 1 dequantise, 2 TMA, 3 MMA issue,
+ * 4 activation loader) spent waiting, at [32 * mode + 4 * role + kind]; kind 3 is the role's whole run. */
+void qw4cu_prefill_debug(void *device_words);
 int qw4cu_decode_phase_clocks(const Qwen4MoeWork *work, uint64_t clocks[16]);
 /* Profiling aid: launch only one step of the small-batch sequence on later forwards, so that a
  * kernel can be timed back to back in isolation (the workspace keeps the results of an

@@ -49,6 +49,11 @@ typedef struct {
     void *groups, *shared_groups; /* [cap * k], [cap / 4 + 1] groups of <= 4 rows (16 bytes each) */
     uint32_t *n_groups;           /* [2]: routed, shared */
     uint32_t *status;             /* [4]: error bits, first bad row, spare */
+    /* tensor-core prefill: fp16 hi / lo images and 32-column sums (hi, lo) of x [0-3], act [4-7], shared act [8-11] */
+    void *half[12];
+    void *groups32, *shared_groups32;  /* groups of <= 32 rows (16 bytes each): routed, shared */
+    uint32_t *n_groups32;         /* [2]: routed, shared */
+    uint32_t *dispatch_scratch;   /* [2 * experts * ceil(cap / 32) + experts]: token bitmaps, word prefixes, counts */
     uint32_t *sync;               /* [256]: grid-barrier counters, phase clocks and row maxima of the one-kernel decode path */
     void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
@@ -134,6 +139,21 @@ void qw4sh_set_fused_decode(int mode);
 int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                        uint32_t *ids_out, float *weights_out, int router_mode, int sm_count);
 int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]);
+
+/* Tensor-core prefill path (prefill_tc.cu): Q4_K experts, groups of <= 32 token rows, tcgen05
+ * MMAs with TMEM accumulators.  supported: 1 when a tensor fits it. */
+int qw4sh_prefill_supported(const QW4ShTensor *w, int mode);
+void qw4sh_set_prefill_path(int path);      /* -1 automatic (default), 0 never */
+/* Profiling aid: device array of 64 x 8 bytes (or NULL); CTA 0 of later prefill launches stores the cycles its
+ * five roles spent in their waits: [32 * mode + 4 * role + kind], kind 3 = the role's total. */
+void qw4sh_prefill_debug(void *device_words);
+int qw4sh_split_rows(const float *x, uint32_t rows, uint32_t k, void *hi, void *lo, void *sum_hi, void *sum_lo, void *stream);
+int qw4sh_build_groups32(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream);
+int qw4sh_build_dense_groups32(uint32_t tokens, void *groups, uint32_t *n_groups, void *stream);
+int qw4sh_prefill_tc(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
+                     const uint32_t *row_to_pair, uint32_t k_div, const void *in_hi, const void *in_lo, const void *sum_hi,
+                     const void *sum_lo, void *out_hi, void *out_lo, void *osum_hi, void *osum_lo, float *out, uint32_t *status,
+                     int ctas, void *stream);
 
 /* Expert-parallel pieces of the layer (see include/qwen4_moe_b200.h). */
 int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode);

@@ -351,6 +351,68 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
     }
 }
 
+// Router logits for large batches: a register-tiled FP32 GEMM (64 tokens x 64 router rows per
+// CTA, 4 x 4 outputs per thread).  Every output still adds its products in ascending k with a
+// separately rounded multiply and add when EXACT (the reference's order and bits,
+// src/qwen4_packed.c:164-173); outputs are independent chains, so sixteen of them interleave in
+// each thread.  Row `experts` is the shared expert's gate.
+template <bool EXACT>
+__global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
+                                                          float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ __align__(16) float xs[2][BK][BM + 4], ws[2][BK][BN + 4];
+    const uint32_t experts = router.n_out, K = router.k_logical;
+    const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
+    const uint32_t t0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
+    // loader: thread -> (row tid / 4, float4 tid % 4) of each 64 x 16 tile
+    const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4;
+    const uint32_t gt = t0 + lr, ge = e0 + lr;
+    const float *xrow = gt < tokens ? x + (uint64_t)gt * K : nullptr;
+    const float *wrow = ge < experts ? (const float *)(router.data + (uint64_t)ge * router.row_bytes) : (ge == experts ? (const float *)srouter.data : nullptr);
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    float4 xa = xrow ? *reinterpret_cast<const float4 *>(xrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 wa = wrow ? *reinterpret_cast<const float4 *>(wrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint32_t steps = K / BK;
+    for (uint32_t s = 0; s < steps; s++) {
+        const uint32_t b = s & 1u;
+        xs[b][lc][lr] = xa.x; xs[b][lc + 1][lr] = xa.y; xs[b][lc + 2][lr] = xa.z; xs[b][lc + 3][lr] = xa.w;
+        ws[b][lc][lr] = wa.x; ws[b][lc + 1][lr] = wa.y; ws[b][lc + 2][lr] = wa.z; ws[b][lc + 3][lr] = wa.w;
+        __syncthreads();
+        if (s + 1 < steps) {
+            xa = xrow ? *reinterpret_cast<const float4 *>(xrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
+            wa = wrow ? *reinterpret_cast<const float4 *>(wrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            const float4 a4 = *reinterpret_cast<const float4 *>(&xs[b][kk][ty * 4]), b4 = *reinterpret_cast<const float4 *>(&ws[b][kk][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = EXACT ? __fadd_rn(acc[i][j], __fmul_rn(bv[j], av[i])) : fmaf(bv[j], av[i], acc[i][j]);
+        }
+    }
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t t = t0 + ty * 4 + i;
+        if (t >= tokens) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t e = e0 + tx * 4 + j;
+            if (e > experts) continue;
+            bad |= !finite_f32(acc[i][j]);
+            if (e < experts) logits[(uint64_t)t * experts + e] = acc[i][j];
+            else shared_logit[t] = acc[i][j];
+        }
+    }
+    if (bad) atomicOr(status, QW4SH_ERR_NONFINITE);
+}
+
 // ------------------------------------------------------------------------------------
 // Route: one warp per token (src/qwen4_moe.c:209-247).  The exp-sum runs serially over
 // e = 0..E-1 on one lane, the reference's order, so probabilities and weights carry its bits;
@@ -589,6 +651,97 @@ __global__ void __launch_bounds__(1024) group_kernel(uint32_t experts, uint32_t 
         for (uint32_t p = 0; p < pairs && cursor < end; p++)
             if (ids[p] == e) { pair_to_row[p] = cursor; row_to_pair[cursor] = p; cursor++; }
     }
+}
+
+// Dispatch for large batches.  A token routes to an expert at most once, so the order of an
+// expert's rows (ascending pair) is the order of its tokens: one bit per (expert, token), and a
+// pair's rank inside its expert is the number of set bits below its token.  Four small launches:
+// mark bits, per-expert word prefixes and counts, exclusive prefix over experts, placement.
+__global__ void __launch_bounds__(256) dispatch_mark_kernel(const uint32_t *__restrict__ ids, uint32_t pairs, uint32_t k, uint32_t experts,
+                                                            uint32_t words, uint32_t *bitmap, uint32_t *status) {
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= pairs) return;
+    const uint32_t e = ids[p], t = p / k;
+    if (e < experts) atomicOr(&bitmap[(uint64_t)e * words + (t >> 5)], 1u << (t & 31u));
+    else if (e != 0xffffffffu) atomicOr(status, QW4SH_ERR_BOUNDS);
+}
+__global__ void __launch_bounds__(256) dispatch_count_kernel(const uint32_t *__restrict__ bitmap, uint32_t experts, uint32_t words,
+                                                             uint32_t *__restrict__ wordprefix, uint32_t *__restrict__ counts) {
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (e >= experts) return;
+    uint32_t running = 0;
+    for (uint32_t w0 = 0; w0 < words; w0 += 32) {
+        const uint32_t w = w0 + lane, c = w < words ? __popc(bitmap[(uint64_t)e * words + w]) : 0;
+        uint32_t scan = c;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(0xffffffffu, scan, o); if (lane >= (uint32_t)o) scan += v; }
+        if (w < words) wordprefix[(uint64_t)e * words + w] = running + scan - c;
+        running += __shfl_sync(0xffffffffu, scan, 31);
+    }
+    if (lane == 0) counts[e] = running;
+}
+__global__ void __launch_bounds__(1024) dispatch_offsets_kernel(const uint32_t *__restrict__ counts, uint32_t experts, uint32_t *__restrict__ offsets,
+                                                                uint32_t *__restrict__ active) {
+    __shared__ uint32_t wsum[32], wact[32];
+    __shared__ uint32_t carry[2];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) { carry[0] = 0; carry[1] = 0; }
+    __syncthreads();
+    for (uint32_t e0 = 0; e0 < experts; e0 += 1024) {
+        const uint32_t e = e0 + tid, c = e < experts ? counts[e] : 0, f = c ? 1u : 0u;
+        uint32_t scan = c, ascan = f;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, scan, o), u = __shfl_up_sync(0xffffffffu, ascan, o);
+            if (lane >= (uint32_t)o) { scan += v; ascan += u; }
+        }
+        if (lane == 31) { wsum[warp] = scan; wact[warp] = ascan; }
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t v = wsum[lane], u = wact[lane];
+            uint32_t sv = v, su = u;
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t a = __shfl_up_sync(0xffffffffu, sv, o), b = __shfl_up_sync(0xffffffffu, su, o);
+                if (lane >= (uint32_t)o) { sv += a; su += b; }
+            }
+            wsum[lane] = sv - v; wact[lane] = su - u;
+        }
+        __syncthreads();
+        const uint32_t first = carry[0] + wsum[warp] + scan - c, rank = carry[1] + wact[warp] + ascan - f;
+        if (e < experts) { offsets[e] = first; if (c) active[1 + rank] = e; }
+        __syncthreads();
+        if (tid == 1023) { carry[0] = first + c; carry[1] = rank + f; }
+        __syncthreads();
+    }
+    if (tid == 0) { offsets[experts] = carry[0]; active[0] = carry[1]; }
+}
+__global__ void __launch_bounds__(256) dispatch_place_kernel(const uint32_t *__restrict__ ids, uint32_t pairs, uint32_t k, uint32_t experts,
+                                                             uint32_t words, const uint32_t *__restrict__ bitmap,
+                                                             const uint32_t *__restrict__ wordprefix, const uint32_t *__restrict__ offsets,
+                                                             uint32_t *__restrict__ pair_to_row, uint32_t *__restrict__ row_to_pair) {
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= pairs) return;
+    const uint32_t e = ids[p], t = p / k;
+    if (e >= experts) return;
+    const uint64_t at = (uint64_t)e * words + (t >> 5);
+    const uint32_t row = offsets[e] + wordprefix[at] + __popc(bitmap[at] & ((1u << (t & 31u)) - 1u));
+    pair_to_row[p] = row;
+    row_to_pair[row] = p;
+}
+// scratch: 2 * experts * ceil(tokens / 32) + experts words.
+extern "C" int qw4sh_group_large(uint32_t experts, uint32_t k, size_t tokens, const uint32_t *ids, uint32_t *offsets, uint32_t *pair_to_row,
+                                 uint32_t *row_to_pair, uint32_t *active, uint32_t *scratch, uint32_t *status, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const uint32_t words = (uint32_t)((tokens + 31) / 32), pairs = (uint32_t)(tokens * k);
+    uint32_t *bitmap = scratch, *wordprefix = scratch + (size_t)experts * words, *counts = wordprefix + (size_t)experts * words;
+    CU(cudaMemsetAsync(bitmap, 0, (size_t)experts * words * 4, stream));
+    dispatch_mark_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, k, experts, words, bitmap, status);
+    LAUNCHED("dispatch_mark_kernel");
+    dispatch_count_kernel<<<(experts + 7) / 8, 256, 0, stream>>>(bitmap, experts, words, wordprefix, counts);
+    LAUNCHED("dispatch_count_kernel");
+    dispatch_offsets_kernel<<<1, 1024, 0, stream>>>(counts, experts, offsets, active);
+    LAUNCHED("dispatch_offsets_kernel");
+    dispatch_place_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, k, experts, words, bitmap, wordprefix, offsets, pair_to_row, row_to_pair);
+    LAUNCHED("dispatch_place_kernel");
+    return 0;
 }
 
 // ------------------------------------------------------------------------------------
@@ -932,6 +1085,11 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (allow_smem(router_exact_small_kernel, smem)) return -1;
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
         LAUNCHED("router_exact_small_kernel");
+    } else if (tokens > 16 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
+        const dim3 grid((unsigned)((tokens + 63) / 64), (rows + 63) / 64);
+        if (mode == 0) router_gemm_kernel<true><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        else router_gemm_kernel<false><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        LAUNCHED("router_gemm_kernel");
     } else if (mode == 0) {
         if (tokens <= 1) {
             router_exact_kernel<1><<<dim3((rows + 31) / 32, (unsigned)tokens), dim3(32, 1), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
@@ -1086,6 +1244,15 @@ static bool mma_path(const QW4ShLayer *layer, size_t tokens) {
            qw4sh_mma_supported(&layer->w[4], 0) && qw4sh_mma_supported(&layer->w[5], 0) && qw4sh_mma_supported(&layer->w[6], 1);
 }
 
+// Batches of more than MMA_MAX_TOKENS rows take the tcgen05 prefill kernels when every expert tensor is Q4_K.
+static int g_prefill_path = -1;                    // -1 automatic, 0 never
+extern "C" void qw4sh_set_prefill_path(int path) { g_prefill_path = path; }
+static bool prefill_path(const QW4ShLayer *layer, size_t tokens) {
+    if (g_prefill_path == 0 || g_expert_path == 0 || tokens <= MMA_MAX_TOKENS) return false;
+    for (int i = 1; i <= 6; i++) if (!qw4sh_prefill_supported(&layer->w[i], i == 3 || i == 6)) return false;
+    return layer->inter % 32 == 0 && layer->shared_inter % 32 == 0;
+}
+
 static cudaStream_t g_side_stream[64] = {nullptr};
 static cudaEvent_t g_side_event[64][4] = {{nullptr}};
 static int side_stream(cudaStream_t *stream, cudaEvent_t **events) {
@@ -1161,7 +1328,10 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
     } else {
         if ((rc = qw4sh_route(E, k, layer->norm, work->logits, E, tokens, work->probs, work->ids, work->weights, work->status, stream))) return rc;
         STAGE_MARK();
-        if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+        if (tokens > 64 && work->dispatch_scratch) {
+            if ((rc = qw4sh_group_large(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                                        work->dispatch_scratch, work->status, stream))) return rc;
+        } else if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
         if (mma && (rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         STAGE_MARK();
     }
@@ -1184,6 +1354,27 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         STAGE_MARK();
         if (overlap) CU(cudaStreamWaitEvent(stream, ev[3], 0));
         if (STEP(9) && (rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
+        STAGE_MARK();
+    } else if (prefill_path(layer, tokens)) {
+        // tensor-core prefill: groups of <= 32 rows, tcgen05 MMAs on exact integer codes
+        const int ctas = sm_count();
+        void *const *hf = work->half;
+        if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+        if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, stream))) return rc;
+        if ((rc = qw4sh_split_rows(x, T, H, hf[0], hf[1], hf[2], hf[3], stream))) return rc;
+        if ((rc = qw4sh_prefill_tc(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, k, hf[0], hf[1], hf[2],
+                                   hf[3], hf[4], hf[5], hf[6], hf[7], nullptr, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_prefill_tc(0, &layer->w[4], &layer->w[5], work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[0], hf[1], hf[2],
+                                   hf[3], hf[8], hf[9], hf[10], hf[11], nullptr, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_prefill_tc(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, hf[4], hf[5], hf[6], hf[7],
+                                   nullptr, nullptr, nullptr, nullptr, work->out, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_prefill_tc(1, &layer->w[6], nullptr, work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[8], hf[9], hf[10],
+                                   hf[11], nullptr, nullptr, nullptr, nullptr, work->shared_out, work->status, ctas, stream))) return rc;
+        STAGE_MARK();
+        if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
         STAGE_MARK();
     } else {
         const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
@@ -1226,7 +1417,10 @@ extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *w
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t R = (uint32_t)rows, H = layer->hidden;
     int rc;
-    if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    if (rows > 64 && work->dispatch_scratch) {
+        if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                                    work->dispatch_scratch, work->status, stream))) return rc;
+    } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
     const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
                      qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) && (g_expert_path == 1 || rows <= 2048);
     if (mma) {

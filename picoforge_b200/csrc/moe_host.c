@@ -220,8 +220,10 @@ static int status_clear(Qwen4MoeWork *w) {
     status_start(w);
     return qw4sh_memcpy2d_async(w->d.status, 16, w->status_host, 16, 16, 1, 1, w->d.stream);
 }
-typedef struct { size_t offset[40], total; } Plan;
+typedef struct { size_t offset[64], total; } Plan;
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static size_t pairs_of(const Qwen4Moe *m, size_t chunk) { return chunk * m->c.top_k; }
 
 static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan *plan, Qwen4Error *err) {
     if (!m || !m->alive) return report(err, QW4_BAD_STATE, "inactive MoE");
@@ -230,15 +232,22 @@ static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan 
     const size_t pairs = t * k;
     const size_t i = m->c.intermediate, si = m->c.shared_intermediate;
     /* sizes in 4-byte words */
-    const size_t count[34] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
+    const size_t g32 = pairs / 32 + e + 2;                   /* groups of <= 32 rows: at most pairs/32 + experts */
+    const size_t count[49] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
         pairs * i, t * si, t * h, 4,
         pairs * h, t * h,                                   /* 15 out, 16 shared_out */
         t * h / 2 + 8, t * h / 2 + 8, t * (h / 32 + 1) * 2, t,                 /* 17 xq, 18 xneg, 19 xsum, 20 xscale */
         pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) * 2, pairs,  /* 21 aq, 22 aneg, 23 asum, 24 ascale */
         t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) * 2, t,              /* 25 sq, 26 sneg, 27 ssum, 28 sscale */
-        pairs * 4 + t + 16, t + 8, 4, 256, 0};                                  /* 29 groups, 30 spare, 31 n_groups, 32 sync */
+        pairs * 4 + t + 16, t + 8, 4, 256, 0,
+        /* 34.. tensor-core prefill: fp16 hi/lo images (2 bytes per value) and 32-column sums of x, act, shared act; groups */
+        t * h / 2 + 8, t * h / 2 + 8, t * (h / 32) / 2 + 8, t * (h / 32) / 2 + 8,               /* 34 xh_hi, 35 xh_lo, 36 xs_hi, 37 xs_lo */
+        pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) / 2 + 8, pairs * (i / 32 + 1) / 2 + 8,   /* 38-41 act */
+        t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) / 2 + 8, t * (si / 32 + 1) / 2 + 8,           /* 42-45 shared act */
+        g32 * 4 + (t / 32 + 2) * 4, 8,
+        2 * e * (t / 32 + 1) + e + 8};                                                      /* 48 dispatch scratch */                                                      /* 46 groups32 (routed, then shared), 47 counts */                                  /* 29 groups, 30 spare, 31 n_groups, 32 sync */
     size_t at = 0;
-    for (int j = 0; j < 34; j++) {
+    for (int j = 0; j < 49; j++) {
         if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
         plan->offset[j] = at;
         at += align256(count[j] * 4 + 4);
@@ -312,6 +321,11 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->d.groups = base + plan.offset[29]; w->d.shared_groups = base + plan.offset[30];
     w->d.n_groups = (uint32_t *)(base + plan.offset[31]);
     w->d.sync = (uint32_t *)(base + plan.offset[32]);
+    for (int j = 0; j < 12; j++) w->d.half[j] = base + plan.offset[34 + j];
+    w->d.groups32 = base + plan.offset[46];
+    w->d.shared_groups32 = (char *)w->d.groups32 + (pairs_of(m, chunk) / 32 + m->c.experts + 2) * 16;
+    w->d.n_groups32 = (uint32_t *)(base + plan.offset[47]);
+    w->d.dispatch_scratch = (uint32_t *)(base + plan.offset[48]);
     if (qw4sh_prepare_mma()) {
         Qwen4Status st = cuda_failure(err, "tensor-core tables");
         qwen4_moe_work_destroy(w);
@@ -673,6 +687,8 @@ void qw4cu_set_stage_timing(int on) { qw4sh_set_stage_timing(on); }
 void qw4cu_set_expert_path(int path) { qw4sh_set_expert_path(path); }
 void qw4cu_set_only_step(int step) { qw4sh_set_only_step(step); }
 void qw4cu_set_fused_decode(int mode) { qw4sh_set_fused_decode(mode); }
+void qw4cu_set_prefill_path(int path) { qw4sh_set_prefill_path(path); }
+void qw4cu_prefill_debug(void *device_words) { qw4sh_prefill_debug(device_words); }
 int qw4cu_decode_phase_clocks(const Qwen4MoeWork *w, uint64_t clocks[16]) { return w ? qw4sh_fused_phase_clocks(&w->d, clocks) : -1; }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
