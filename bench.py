@@ -382,8 +382,36 @@ def main():
                          f"tokens sharded over {threads} threads"}
 
     layer_bytes = sum(bytes_by_stage.values())
-    achieved = bytes_by_stage[dominant] / (stage_us[dominant] * 1e-6) / 1e9 if stage_us[dominant] > 0 else 0.0
     layer_gbs = layer_bytes / (ms_per_step * 1e-3) / 1e9
+    phases = None
+    if launches == args.steps:
+        # one launch per step: the whole layer ran as the one-kernel decode path.  Its duration is the
+        # event-timed step (launch gaps included, so the fraction is a lower bound) and its algorithmic
+        # bytes are every weight byte the step must read once.
+        dominant = "fused_decode_kernel"
+        kernel_us, kernel_bytes = ms_per_step * 1e3, layer_bytes
+        clocks16 = (C.c_uint64 * 16)()
+        lib.qw4cu_decode_phase_clocks(layers[(args.steps - 1) % len(layers)].work, clocks16)
+        ticks = [int(v) for v in clocks16[:13]]
+        names = ["stage_x", "digitise_x", "router_rows", "barrier_1", "load_logits", "route", "list_experts", "gate_up_slices",
+                 "store_units", "barrier_2", "digitise_act", "down_combine"]
+        phases = {name: ticks[j + 1] - ticks[j] for j, name in enumerate(names)}
+        phases["unit"] = "SM cycles of CTA 0, last timed launch"
+    else:
+        kernel_us, kernel_bytes = stage_us[dominant], bytes_by_stage[dominant]
+    achieved = kernel_bytes / (kernel_us * 1e-6) / 1e9 if kernel_us > 0 else 0.0
+    tensor = None
+    if args.workload == "c2":
+        # FLOPs of the chunk (routed 2 * pairs * 3 * H * I, shared, router) against the measured dense bf16 rate
+        spec0 = specs[0]
+        pairs = tokens * spec0.top_k
+        flops = 2.0 * pairs * 3 * spec0.hidden * spec0.inter + 2.0 * tokens * 3 * spec0.hidden * spec0.shared_inter \
+            + 2.0 * tokens * spec0.hidden * (spec0.experts + 1)
+        peak_tf = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops_sustained", 1422.1) \
+            if (ROOT / "MEASURED_PEAKS.json").exists() else 1400.0
+        tensor = {"bound": "tensor", "flop_per_step": flops, "achieved": flops / (ms_per_step * 1e-3) / 1e12, "peak": peak_tf,
+                  "unit": "TFLOP/s", "frac": flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
+                  "note": "whole step against the sustained dense bf16 rate; at about 20 rows per expert the binding roof is HBM"}
     traffic_path = ROOT / "profiles" / "traffic.json"
     traffic = None
     if traffic_path.exists():
@@ -394,15 +422,18 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": desc, "tokens_per_step": tokens, "parallelism": "single GPU" if world == 1 else f"{world} replicas",
-                   "router": args.router, "launch": "direct" if args.no_graph else "cuda-graph replay per layer",
+                   "router": args.router, "launch": "one persistent kernel per layer" if phases else ("direct" if args.no_graph else "cuda-graph replay per layer"),
                    "l2": f"rotating {len(layers)} weight sets ({layer_bytes * len(layers) / 1e6:.0f} MB touched between reuse of a set; L2 is 126 MB)",
                    "distinct_experts_per_step": distinct, "spinup_ms": 300},
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": traffic,
-                     "algorithmic_bytes": bytes_by_stage[dominant], "kernel_us": stage_us[dominant]},
+                     "algorithmic_bytes": kernel_bytes, "kernel_us": kernel_us},
+        "roofline_tensor": tensor,
+        "phases": phases,
+        "tokens_per_s": tokens * world / (ms_per_step * 1e-3),
         "layer": {"weight_bytes": layer_bytes, "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / hbm_peak,
                   "frac_of_nominal_8tbs": layer_gbs / NOMINAL_HBM_GBS,
-                  "stage_us": stage_us, "stage_bytes": bytes_by_stage},
+                  "stage_us_multi_kernel_path": stage_us, "stage_bytes": bytes_by_stage},
         "e2e": {"value": e2e_us_per_token, "unit": "us/token", "h2d_bytes_per_step": int(x.nbytes) + 16,
                 "d2h_bytes_per_step": int(x.nbytes) + 16, "steps": e2e_steps},
         "gpu_launches": int(launches),

@@ -81,7 +81,7 @@ struct FPlan {
     uint32_t bars, ids, wts, misc, tokmask, slotmap, src, lut, region, total;
     uint32_t kp;                                // pitch of one digit row of x
     uint32_t xq, xsum;                          // phases A and B (inside region)
-    uint32_t xf, xf_pitch, rows, row_pitch;     // phase A
+    uint32_t xf, xf_pitch, rows, row_pitch, prod;   // phase A
     uint32_t zs, ring, partial;                 // phase B
     uint32_t aq, ap, asum, ascale, aconst, tiles, cpartial;   // phase C
 };
@@ -109,6 +109,7 @@ __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max,
     p.xf = a; a += FTOK * p.xf_pitch;
     p.row_pitch = hidden * 4 + 16;
     p.rows = a; a += FRMAX * p.row_pitch;
+    p.prod = a; a += 2 * 16 * (hidden / FRCH + 4) * 4;
     // phase B: the logits / probabilities are dead before the first copy lands in the ring
     uint32_t b = head;
     p.zs = b;
@@ -352,11 +353,11 @@ __device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t
 }
 
 // Rows of `k` floats (k % 32 == 0) with known maxima -> digit images, digit sums per 32-column
-// chunk and scales.  CTA-wide; `rows * k / 4` float4 items are dealt to the threads, four per
-// thread in flight; eight consecutive lanes cover one chunk.  `amax` holds the maxima on entry
+// chunk and scales.  CTA-wide; `rows * k / 4` float4 items are dealt to the threads, BATCH per
+// thread in flight (one from shared memory, four from global memory, whose latency they share); eight consecutive lanes cover one chunk.  `amax` holds the maxima on entry
 // and the scales (max / 127, or 0 for an unusable row) on return; `consts` is scratch, one
 // float4 per row.
-template <bool GLOBAL>
+template <bool GLOBAL, int BATCH>
 __device__ __noinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
                                            uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts) {
     for (uint32_t r = threadIdx.x; r < rows; r += FT) {
@@ -368,12 +369,12 @@ __device__ __noinline__ void digitise_rows(const float *src, uint32_t src_pitch,
     __syncthreads();
     const uint32_t per_row = k >> 2, items = rows * per_row;
 #pragma unroll 1
-    for (uint32_t first = 0; first < items; first += 4 * FT) {
-        float4 v[4];
-        uint32_t r[4], c4[4];
-        bool live[4];
+    for (uint32_t first = 0; first < items; first += BATCH * FT) {
+        float4 v[BATCH];
+        uint32_t r[BATCH], c4[BATCH];
+        bool live[BATCH];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < BATCH; j++) {
             const uint32_t i = first + j * FT + threadIdx.x;
             live[j] = i < items;
             r[j] = live[j] ? i / per_row : 0; c4[j] = live[j] ? i % per_row : 0;
@@ -382,7 +383,7 @@ __device__ __noinline__ void digitise_rows(const float *src, uint32_t src_pitch,
                                        : *(reinterpret_cast<const float4 *>(src + (uint64_t)r[j] * src_pitch) + c4[j]);
         }
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < BATCH; j++) {
             uint32_t hi, lo;
             int s1 = 0, s2 = 0;
             digits4(v[j], consts[r[j]], hi, lo, s1, s2);
@@ -546,17 +547,29 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             if (from < bytes) fprefetch_l2(a.w[m].data + from, (uint32_t)(from + sub <= bytes ? sub : bytes - from));
         }
     }
-    // x -> shared memory (float) with the row maxima, then digits
+    // x -> shared memory (float) with the row maxima, then digits; token rows beyond T stay zero
     {
+        constexpr int XL = 6;                                                  // float4 per thread in flight
         float m[FTOK] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t i = tid; i < FTOK * (H >> 2); i += FT) {
-            const uint32_t r = i / (H >> 2), c4 = i % (H >> 2);
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < T) v = __ldg(reinterpret_cast<const float4 *>(a.x + (uint64_t)r * H) + c4);
-            *reinterpret_cast<float4 *>(xf + r * p.xf_pitch + c4 * 16) = v;
-            const float mm = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        for (uint32_t first = 0; first < T * (H >> 2); first += XL * FT) {
+            float4 v[XL];
 #pragma unroll
-            for (int q = 0; q < FTOK; q++) if (r == (uint32_t)q) m[q] = fmaxf(m[q], mm);
+            for (int j = 0; j < XL; j++) {
+                const uint32_t i = first + j * FT + tid;
+                v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < T * (H >> 2)) v[j] = __ldg(reinterpret_cast<const float4 *>(a.x) + i);
+            }
+#pragma unroll
+            for (int j = 0; j < XL; j++) {
+                const uint32_t i = first + j * FT + tid;
+                if (i < T * (H >> 2)) {
+                    const uint32_t r = i / (H >> 2), c4 = i % (H >> 2);
+                    *reinterpret_cast<float4 *>(xf + r * p.xf_pitch + c4 * 16) = v[j];
+                    const float mm = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+#pragma unroll
+                    for (int q = 0; q < FTOK; q++) if (r == (uint32_t)q) m[q] = fmaxf(m[q], mm);
+                }
+            }
         }
 #pragma unroll
         for (int q = 0; q < FTOK; q++) {
@@ -564,47 +577,57 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
             if (lane == 0 && v > 0.0f) atomicMax(reinterpret_cast<uint32_t *>(misc_f) + q, __float_as_uint(v));
         }
+        for (uint32_t i = tid; i < (FTOK - T) * 2 * (p.kp >> 4); i += FT)       // digit rows of absent tokens
+            reinterpret_cast<uint4 *>(xq + 2 * T * p.kp)[i] = make_uint4(0, 0, 0, 0);
+        for (uint32_t i = tid; i < (FTOK - T) * (H >> 5); i += FT) xsum[T * (H >> 5) + i] = make_int2(0, 0);
     }
     __syncthreads();
     CLOCK(1);
-    digitise_rows<false>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, FTOK, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
+    digitise_rows<false, 1>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
     CLOCK(2);
     // router rows
     bool alive = true;
     if (a.router_mode == 0) {
-        if (warp == FW - 1 && lane < n_rows * T) {                             // one lane per (row, token) chain
-            const uint32_t j = lane / T, tok = lane % T;
+        // Exact order: every (row, token) logit is one chain of K separately rounded adds, and a lone
+        // warp issues too slowly to also load and multiply.  So the other warps write the products
+        // (the same separately rounded multiplies) chunk by chunk into a two-buffer ring, and the
+        // last warp only loads and adds: lane = chain.  Named barriers 2/3 say "buffer filled",
+        // 4/5 "buffer drained".
+        float *prod = reinterpret_cast<float *>(region + p.prod);              // [2][16 chains][chunk + 4]
+        const uint32_t chunk = H / FRCH, ppitch = chunk + 4, chains = n_rows * T;
+        if (warp == FW - 1) {
             float sum = 0.0f;
 #pragma unroll 1
-            for (uint32_t c = 0; c < FRCH && alive; c++) {
-                alive = fbar_wait(&rowbar[c], 0, a.status);
-                if (!alive) break;
-                const float4 *wv = reinterpret_cast<const float4 *>(rows + j * p.row_pitch + c * chunk_bytes);
-                const float4 *xv = reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch + c * chunk_bytes);
-                const uint32_t n4 = chunk_bytes / 16;                          // a multiple of 4 (H % 1024 == 0)
-                float4 wn[4], xn[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) { wn[q] = wv[q]; xn[q] = xv[q]; }
-#pragma unroll 1
-                for (uint32_t i = 0; i < n4; i += 4) {                          // operands of the next four steps load under the chain
-                    float4 wc[4], xc[4];
-#pragma unroll
-                    for (int q = 0; q < 4; q++) { wc[q] = wn[q]; xc[q] = xn[q]; }
-                    if (i + 4 < n4) {
-#pragma unroll
-                        for (int q = 0; q < 4; q++) { wn[q] = wv[i + 4 + q]; xn[q] = xv[i + 4 + q]; }
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        sum = __fadd_rn(sum, __fmul_rn(wc[q].x, xc[q].x)); sum = __fadd_rn(sum, __fmul_rn(wc[q].y, xc[q].y));
-                        sum = __fadd_rn(sum, __fmul_rn(wc[q].z, xc[q].z)); sum = __fadd_rn(sum, __fmul_rn(wc[q].w, xc[q].w));
+            for (uint32_t c = 0; c < FRCH; c++) {
+                asm volatile("bar.sync %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
+                if (lane < chains) {
+                    const float4 *pv = reinterpret_cast<const float4 *>(prod + ((c & 1u) * 16 + lane) * ppitch);
+#pragma unroll 4
+                    for (uint32_t i = 0; i < chunk / 4; i++) {
+                        const float4 q = pv[i];
+                        sum = __fadd_rn(sum, q.x); sum = __fadd_rn(sum, q.y); sum = __fadd_rn(sum, q.z); sum = __fadd_rn(sum, q.w);
                     }
                 }
+                if (c + 2 < FRCH) asm volatile("bar.arrive %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
             }
-            if (alive) {
-                const uint32_t r = cta + j * grid;
+            if (lane < chains) {
+                const uint32_t j = lane / T, tok = lane % T, r = cta + j * grid;
                 if (!finite_f32(sum)) { atomicOr(a.status, QW4SH_ERR_NONFINITE); atomicMin(a.status + 1, tok); }
                 if (r < E) a.logits[(uint64_t)tok * E + r] = sum; else a.shared_logit[tok] = sum;
+            }
+        } else {
+#pragma unroll 1
+            for (uint32_t c = 0; c < FRCH; c++) {
+                if (alive) alive = fbar_wait(&rowbar[c], 0, a.status);           // on a failed wait the products are garbage, the flag is set
+                if (c >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
+                for (uint32_t i = tid; i < chains * (chunk / 4); i += FT - 32) {
+                    const uint32_t ch = i / (chunk / 4), q4 = i % (chunk / 4), j = ch / T, tok = ch % T;
+                    const float4 w4 = *reinterpret_cast<const float4 *>(rows + j * p.row_pitch + c * chunk_bytes + q4 * 16);
+                    const float4 x4 = *reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch + c * chunk_bytes + q4 * 16);
+                    *reinterpret_cast<float4 *>(prod + ((c & 1u) * 16 + ch) * ppitch + q4 * 4) =
+                        make_float4(__fmul_rn(w4.x, x4.x), __fmul_rn(w4.y, x4.y), __fmul_rn(w4.z, x4.z), __fmul_rn(w4.w, x4.w));
+                }
+                asm volatile("bar.arrive %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
             }
         }
     } else {
@@ -800,8 +823,8 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
         for (uint32_t r = tid; r < rows_c; r += FT) ascale[r] = __uint_as_float(__ldcg(amax_g + r));
         __syncthreads();
         float4 *aconsts = reinterpret_cast<float4 *>(region + p.aconst);
-        digitise_rows<true>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
-        digitise_rows<true>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
+        digitise_rows<true, 4>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
+        digitise_rows<true, 4>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
                             aconsts + pairs);
         CLOCK(11);
         uint32_t n = 0;
