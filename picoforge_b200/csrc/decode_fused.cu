@@ -26,8 +26,8 @@
 // operand in phase B; results of tokens not routed to an expert are simply not stored.
 //
 // Code that runs once per launch is kept compact on purpose (loops instead of unrolled
-// sequences, shared out-of-line helpers): a kernel of this kind executes most of its
-// instructions a handful of times, so instruction fetch, not issue, bounds it.
+// sequences, no per-thread arrays in local memory): a kernel of this kind executes most of its
+// instructions a handful of times.
 //
 // Every wait (mbarrier or grid barrier) is bounded: after about a second the kernel records
 // QW4SH_ERR_STATE and leaves.
@@ -73,7 +73,11 @@ struct FusedArgs {
 };
 
 // One distinct source of phase C / one expert of phase B.
-struct Src { uint16_t expert; uint8_t mask, shared; uint8_t slot[4]; };
+struct Src {
+    uint16_t expert; uint8_t mask, shared;
+    uint32_t slots;                             // slot of token t in byte t
+    __device__ __forceinline__ uint32_t slot(uint32_t t) const { return (slots >> (8 * t)) & 0xffu; }
+};
 
 // Shared-memory plan (byte offsets), the same on host and device.  `region` is reused by the
 // three phases; the digit image of x lives at its start through phases A and B.
@@ -147,7 +151,7 @@ __device__ __forceinline__ bool fbar_try(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait (about a second); false with the error bit set when it runs out.
-__device__ __noinline__ bool fbar_wait(uint64_t *bar, uint32_t parity, uint32_t *status) {
+__device__ __forceinline__ bool fbar_wait(uint64_t *bar, uint32_t parity, uint32_t *status) {
     if (fbar_try(bar, parity)) return true;
     const long long start = clock64();
     while (!fbar_try(bar, parity)) {
@@ -174,7 +178,7 @@ __device__ __forceinline__ void fmma_zero(int (&c)[4], uint32_t a0, uint32_t a1,
 }
 
 // All CTAs arrive, then wait until `expected` have.  False (CTA-uniform) when the wait ran out.
-__device__ __noinline__ bool grid_barrier(uint32_t *counter, uint32_t expected, uint32_t *status, uint32_t *flag_smem) {
+__device__ __forceinline__ bool grid_barrier(uint32_t *counter, uint32_t expected, uint32_t *status, uint32_t *flag_smem) {
     __syncthreads();
     if (threadIdx.x == 0) {
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
@@ -194,12 +198,12 @@ __device__ __noinline__ bool grid_barrier(uint32_t *counter, uint32_t expected, 
 // every 32-column chunk, for MMA rows g and g + 8 and for activation column g (token g >> 1,
 // digit g & 1).  f0 += row g . x[token t], f1 += row g+8 . x[token t], both in units of the
 // token's digit scale.  xq is the lane's digit pointer at the first chunk, xsum the token's digit
-// sums (Q4_K's min term).  Out of line: one copy per format serves phases B and C.
+// sums (Q4_K's min term).
 template <uint32_t TYPE> struct Halves;
 
 // Q4_K: r0 / r1 point at the first 144-byte block of the two rows; `halves` half blocks follow.
 template <> struct Halves<T_Q4_K> {
-    static __device__ __noinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t, const uint16_t *,
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t, const uint16_t *,
                                             const uint16_t *, const uint8_t *, uint32_t t, const uint8_t *xq, const int2 *xsum,
                                             float &f0, float &f1) {
 #pragma unroll 1
@@ -245,7 +249,7 @@ template <> struct Halves<T_Q4_K> {
 // groups from the row start, so the in-row swizzle `swz` applies to the local index); d0p / d1p
 // at the fp16 super-scales of the span's first block.
 template <> struct Halves<T_IQ2_XXS> {
-    static __device__ __noinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
                                             const uint16_t *d1p, const uint8_t *lut, uint32_t t, const uint8_t *xq, const int2 *,
                                             float &f0, float &f1) {
         const uint8_t *grid = lut + (threadIdx.x & 15u) * 8u;            // 64-bit reads: 16 copies
@@ -286,20 +290,18 @@ template <> struct FGeo<T_IQ2_XXS> { static constexpr uint32_t SLICE_BLOCKS = 4,
 // Copies of slice `s` of a gate/up unit (8 gate rows + 8 up rows from row `row0`) into `stage`:
 // row r at r * slice bytes; IQ2_XXS also gets the unit's super-scales behind the rows.
 template <uint32_t TYPE>
-__device__ __forceinline__ void issue_unit_slice(const DevTensor &gate, const DevTensor &up, uint32_t expert, uint32_t row0, uint32_t s,
-                                                 uint8_t *stage, uint64_t *bar, uint32_t lane) {
-    const uint32_t nb = gate.k_storage >> 8, row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
+__device__ __forceinline__ void issue_unit_slice(const uint8_t *gate_mat, const uint8_t *up_mat, uint32_t n_out, uint32_t nb, uint32_t row0,
+                                              uint32_t s, uint8_t *stage, uint64_t *bar, uint32_t lane) {
+    const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
     constexpr uint32_t slice_bytes = FGeo<TYPE>::SLICE_BLOCKS * FGeo<TYPE>::BLOCK_BYTES;
     if (lane == 0) fbar_expect(bar, 16 * slice_bytes + (TYPE == T_IQ2_XXS ? 2 * 8 * nb * 2 : 0));
     __syncwarp();
     if (lane < 16) {
-        const DevTensor &w = lane < 8 ? gate : up;
-        const uint8_t *mat = w.data + (uint64_t)expert * w.expert_bytes;
-        fbulk(stage + lane * slice_bytes, mat + (uint64_t)(row0 + (lane & 7u)) * row_bytes + s * slice_bytes, slice_bytes, bar);
+        const uint8_t *mat = lane < 8 ? gate_mat : up_mat;
+        fbulk(stage + lane * slice_bytes, mat + (row0 + (lane & 7u)) * row_bytes + s * slice_bytes, slice_bytes, bar);
     } else if (TYPE == T_IQ2_XXS && lane < 18) {
-        const DevTensor &w = lane == 16 ? gate : up;
-        const uint8_t *mat = w.data + (uint64_t)expert * w.expert_bytes;
-        fbulk(stage + 16 * slice_bytes + (lane - 16) * 8 * nb * 2, mat + (uint64_t)w.n_out * nb * 64u + (uint64_t)row0 * nb * 2u, 8 * nb * 2, bar);
+        const uint8_t *mat = lane == 16 ? gate_mat : up_mat;
+        fbulk(stage + 16 * slice_bytes + (lane - 16) * 8 * nb * 2, mat + n_out * nb * 64u + row0 * nb * 2u, 8 * nb * 2, bar);
     }
 }
 template <uint32_t TYPE>
@@ -314,14 +316,13 @@ __device__ __forceinline__ void consume_unit_slice(const uint8_t *stage, uint32_
 // Down tile: 16 rows x K (K <= 512 for Q4_K, <= 1024 for IQ2_XXS), fetched whole; IQ2_XXS
 // super-scales at +4096.
 template <uint32_t TYPE>
-__device__ __forceinline__ void issue_down_tile(const DevTensor &down, uint32_t expert, uint32_t row0, uint8_t *stage, uint64_t *bar,
-                                                uint32_t lane) {
-    const uint32_t nb = down.k_storage >> 8, row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
-    const uint8_t *mat = down.data + (uint64_t)expert * down.expert_bytes;
+__device__ __forceinline__ void issue_down_tile(const uint8_t *mat, uint32_t n_out, uint32_t nb, uint32_t row0, uint8_t *stage, uint64_t *bar,
+                                             uint32_t lane) {
+    const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
     if (lane == 0) {
         fbar_expect(bar, 16 * row_bytes + (TYPE == T_IQ2_XXS ? 16 * nb * 2 : 0));
-        fbulk(stage, mat + (uint64_t)row0 * row_bytes, 16 * row_bytes, bar);
-        if (TYPE == T_IQ2_XXS) fbulk(stage + 4096, mat + (uint64_t)down.n_out * nb * 64u + (uint64_t)row0 * nb * 2u, 16 * nb * 2, bar);
+        fbulk(stage, mat + row0 * row_bytes, 16 * row_bytes, bar);
+        if (TYPE == T_IQ2_XXS) fbulk(stage + 4096, mat + n_out * nb * 64u + row0 * nb * 2u, 16 * nb * 2, bar);
     }
 }
 template <uint32_t TYPE>
@@ -358,8 +359,9 @@ __device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t
 // and the scales (max / 127, or 0 for an unusable row) on return; `consts` is scratch, one
 // float4 per row.
 template <bool GLOBAL, int BATCH>
-__device__ __noinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
+__device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
                                            uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts) {
+#pragma unroll 1
     for (uint32_t r = threadIdx.x; r < rows; r += FT) {
         const float m = amax[r];
         const bool usable = finite_f32(m) && m > 0.0f;
@@ -396,6 +398,7 @@ __device__ __noinline__ void digitise_rows(const float *src, uint32_t src_pitch,
         }
     }
     __syncthreads();
+#pragma unroll 1
     for (uint32_t r = threadIdx.x; r < rows; r += FT) amax[r] = consts[r].x;
     __syncthreads();
 }
@@ -410,7 +413,7 @@ __device__ __forceinline__ float fast_sigmoid(float v) {
 // the lower id, and with `exact` the exp-sum runs serially over e = 0..E-1 (the reference's
 // bits); otherwise it is a warp tree sum.  Returns false (CTA-uniform) when a logit is not
 // finite; the first bad row is recorded.
-__device__ __noinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int norm, uint32_t T, bool exact, uint32_t *ids_s, float *wts_s,
+__device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int norm, uint32_t T, bool exact, uint32_t *ids_s, float *wts_s,
                                           float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) *flag = 1;
@@ -418,6 +421,7 @@ __device__ __noinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int
     if (warp < T) {                                                       // row maximum and finiteness
         float m = -CUDART_INF_F;
         bool bad = false;
+#pragma unroll 1
         for (uint32_t e = lane; e < E; e += 32) { const float v = zs[warp * FMAXE + e]; bad |= !finite_f32(v); m = fmaxf(m, v); }
         for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         bad = __any_sync(0xffffffffu, bad);
@@ -428,6 +432,7 @@ __device__ __noinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int
     }
     __syncthreads();
     if (!*flag) return false;
+#pragma unroll 1
     for (uint32_t i = tid; i < T * E; i += FT) {                           // p = expf(z - max)
         const uint32_t r = i / E, e = i % E;
         zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], scratch[r]), exp_table);
@@ -449,30 +454,31 @@ __device__ __noinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int
             }
             sum = __shfl_sync(0xffffffffu, sum, 0);
         } else {
+#pragma unroll 1
             for (uint32_t e = lane; e < E; e += 32) sum += p[e];
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        // keys: bits of p / sum (>= 0, so ordered as integers) + 1; 0 = absent or already chosen
+        // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
+        // The row stays in shared memory: sixteen reads per lane and round, no per-lane array.
 #pragma unroll 1
         for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], sum);      // one division site: the loop stays small
-        uint32_t key[FMAXE / 32];
-#pragma unroll
-        for (int i = 0; i < FMAXE / 32; i++) { const uint32_t e = lane + 32 * i; key[i] = e < E ? __float_as_uint(p[e]) + 1u : 0u; }
+        __syncwarp();
         float selected = 0.0f, mine = 0.0f;
 #pragma unroll 1
         for (uint32_t slot = 0; slot < k; slot++) {
-            uint32_t best = 0, best_i = 0;
-#pragma unroll
-            for (int i = 0; i < FMAXE / 32; i++) if (key[i] > best) { best = key[i]; best_i = i; }     // lowest i (lowest id) among equals
+            uint32_t best = 0, best_e = 0xffffffffu;
+#pragma unroll 4
+            for (uint32_t e = lane; e < E; e += 32) {                              // ascending e: the lowest id wins among equals
+                const float v = p[e];
+                const uint32_t key = v < 0.0f ? 0u : __float_as_uint(v) + 1u;
+                if (key > best) { best = key; best_e = e; }
+            }
             const uint32_t top = __reduce_max_sync(0xffffffffu, best);
-            const uint32_t e_win = __reduce_min_sync(0xffffffffu, best == top ? lane + 32 * best_i : 0xffffffffu);
+            const uint32_t e_win = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0xffffffffu);
             const float value = __uint_as_float(top - 1u);
             if (lane == 0) ids_s[warp * k + slot] = e_win;
             if (slot == lane) mine = value;
-            if ((e_win & 31u) == lane) {
-#pragma unroll
-                for (int i = 0; i < FMAXE / 32; i++) if ((uint32_t)i == (e_win >> 5)) key[i] = 0;
-            }
+            if ((e_win & 31u) == lane) p[e_win] = -1.0f;
             selected = __fadd_rn(selected, value);
         }
         if (lane < k) wts_s[warp * k + lane] = norm ? __fdiv_rn(mine, selected) : mine;
@@ -511,7 +517,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     CLOCK(0);
 
     if (tid == 0) {
+#pragma unroll 1
         for (uint32_t i = 0; i < FW * FNS; i++) fbar_init(&ringbar[i], 1);
+#pragma unroll 1
         for (uint32_t i = 0; i < FRCH; i++) fbar_init(&rowbar[i], 1);
         fbar_init(lutbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -540,17 +548,19 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             fbulk(smem + p.lut, a.lut, F_LUT_BYTES, lutbar);
         }
     } else if (warp == 1) {                                                    // the shared expert's tensors -> L2
-        for (uint32_t m = 4; m <= 6; m++) {
-            const uint64_t bytes = a.w[m].expert_bytes & ~15ull;
-            const uint64_t sub = ((bytes / ((uint64_t)grid * 32u)) + 16u) & ~15ull;
-            const uint64_t from = ((uint64_t)cta * 32u + lane) * sub;
-            if (from < bytes) fprefetch_l2(a.w[m].data + from, (uint32_t)(from + sub <= bytes ? sub : bytes - from));
+#pragma unroll
+        for (uint32_t m = 4; m <= 6; m++) {                                     // shared tensors are far below 4 GB
+            const uint32_t bytes = (uint32_t)a.w[m].expert_bytes & ~15u;
+            const uint32_t sub = ((bytes / (grid * 32u)) + 16u) & ~15u;
+            const uint32_t from = (cta * 32u + lane) * sub;
+            if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
         }
     }
     // x -> shared memory (float) with the row maxima, then digits; token rows beyond T stay zero
     {
         constexpr int XL = 6;                                                  // float4 per thread in flight
         float m[FTOK] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
         for (uint32_t first = 0; first < T * (H >> 2); first += XL * FT) {
             float4 v[XL];
 #pragma unroll
@@ -577,8 +587,10 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
             if (lane == 0 && v > 0.0f) atomicMax(reinterpret_cast<uint32_t *>(misc_f) + q, __float_as_uint(v));
         }
+#pragma unroll 1
         for (uint32_t i = tid; i < (FTOK - T) * 2 * (p.kp >> 4); i += FT)       // digit rows of absent tokens
             reinterpret_cast<uint4 *>(xq + 2 * T * p.kp)[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
         for (uint32_t i = tid; i < (FTOK - T) * (H >> 5); i += FT) xsum[T * (H >> 5) + i] = make_int2(0, 0);
     }
     __syncthreads();
@@ -620,6 +632,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             for (uint32_t c = 0; c < FRCH; c++) {
                 if (alive) alive = fbar_wait(&rowbar[c], 0, a.status);           // on a failed wait the products are garbage, the flag is set
                 if (c >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
+#pragma unroll 1
                 for (uint32_t i = tid; i < chains * (chunk / 4); i += FT - 32) {
                     const uint32_t ch = i / (chunk / 4), q4 = i % (chunk / 4), j = ch / T, tok = ch % T;
                     const float4 w4 = *reinterpret_cast<const float4 *>(rows + j * p.row_pitch + c * chunk_bytes + q4 * 16);
@@ -631,12 +644,15 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             }
         }
     } else {
+#pragma unroll 1
         for (uint32_t c = 0; c < FRCH && alive; c++) alive = fbar_wait(&rowbar[c], 0, a.status);
+#pragma unroll 1
         for (uint32_t dot = warp; dot < n_rows * T && alive; dot += FW) {
             const uint32_t j = dot / T, tok = dot % T;
             const float4 *wv = reinterpret_cast<const float4 *>(rows + j * p.row_pitch);
             const float4 *xv = reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch);
             float acc = 0.0f;
+#pragma unroll 1
             for (uint32_t i = lane; i < (H >> 2); i += 32) {
                 const float4 w4 = wv[i], x4 = xv[i];
                 acc = fmaf(w4.x, x4.x, fmaf(w4.y, x4.y, fmaf(w4.z, x4.z, fmaf(w4.w, x4.w, acc))));
@@ -656,8 +672,10 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
 
     // ================================ phase B ================================
     float *zs = reinterpret_cast<float *>(region + p.zs);
+#pragma unroll 1
     for (uint32_t i = tid; i < T * E; i += FT) zs[(i / E) * FMAXE + (i % E)] = __ldcg(a.logits + i);
     if (tid < T) misc_f[4 + tid] = __ldcg(a.shared_logit + tid);
+#pragma unroll 1
     for (uint32_t i = tid; i < FMAXE; i += FT) tokmask[i] = 0;
     __syncthreads();
     CLOCK(5);
@@ -676,6 +694,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
         }
         __syncthreads();
         // distinct experts in ascending order behind the shared expert (source 0)
+#pragma unroll 1
         for (uint32_t c = warp; c < (E + 31) / 32; c += FW) {
             const uint32_t e = c * 32 + lane;
             const uint32_t any = __ballot_sync(0xffffffffu, e < E && tokmask[e] != 0);
@@ -684,19 +703,21 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
         __syncthreads();
         if (tid == 0) {
             uint32_t running = 1;
+#pragma unroll 1
             for (uint32_t c = 0; c < (E + 31) / 32; c++) { const uint32_t n = misc_u[4 + c]; misc_u[4 + c] = running; running += n; }
             misc_u[2] = running;
-            Src s; s.expert = 0xffffu; s.mask = (uint8_t)((1u << T) - 1u); s.shared = 1; s.slot[0] = s.slot[1] = s.slot[2] = s.slot[3] = 0;
+            Src s; s.expert = 0xffffu; s.mask = (uint8_t)((1u << T) - 1u); s.shared = 1; s.slots = 0;
             srcs[0] = s;
         }
         __syncthreads();
+#pragma unroll 1
         for (uint32_t c = warp; c < (E + 31) / 32; c += FW) {
             const uint32_t e = c * 32 + lane;
             const bool has = e < E && tokmask[e] != 0;
             const uint32_t any = __ballot_sync(0xffffffffu, has);
             if (has) {
                 Src s; s.expert = (uint16_t)e; s.mask = tokmask[e]; s.shared = 0;
-                for (int q = 0; q < 4; q++) s.slot[q] = slotmap[e * 4 + q];
+                s.slots = *reinterpret_cast<const uint32_t *>(slotmap + e * 4);
                 srcs[misc_u[4 + c] + __popc(any & ((1u << lane) - 1u))] = s;
             }
         }
@@ -709,7 +730,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     if (routed_ok) {
         // gate/up units: shared expert first, then the routed experts; whole units per CTA
         const uint32_t us = IS >> 3, ur = I >> 3, total = us + (n_src - 1) * ur;
-        const uint32_t u0 = (uint32_t)((uint64_t)total * cta / grid), u1 = (uint32_t)((uint64_t)total * (cta + 1) / grid);
+        const uint32_t u0 = total * cta / grid, u1 = total * (cta + 1) / grid;            // total <= 65 * 128: no overflow
         const uint32_t n_shu = u0 < us ? min(us, u1) - u0 : 0;                 // shared units of this CTA come first
         const uint32_t nbh = H >> 8;
         const uint32_t spu_s = nbh / FGeo<ST>::SLICE_BLOCKS, spu_r = nbh / FGeo<RT>::SLICE_BLOCKS;
@@ -728,20 +749,22 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             locate(warp + i * FW, ul, s, sh);
             const uint32_t u = u0 + ul;
             uint8_t *stage = ring + (i % FNS) * FSTAGE;
-            if (sh) issue_unit_slice<ST>(a.w[4], a.w[5], 0, u * 8, s, stage, &bar[i % FNS], lane);
+            if (sh) issue_unit_slice<ST>(a.w[4].data, a.w[5].data, IS, nbh, u * 8, s, stage, &bar[i % FNS], lane);
             else {
-                const uint32_t v = u - us;
-                issue_unit_slice<RT>(a.w[1], a.w[2], srcs[1 + v / ur].expert, (v % ur) * 8, s, stage, &bar[i % FNS], lane);
+                const uint32_t v = u - us, e = srcs[1 + v / ur].expert;
+                issue_unit_slice<RT>(a.w[1].data + (uint64_t)e * a.w[1].expert_bytes, a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, I, nbh,
+                                     (v % ur) * 8, s, stage, &bar[i % FNS], lane);
             }
         };
         if (alive) for (uint32_t i = 0; i < FNS && i < mine; i++) issue(i);
         // down tiles of this CTA's columns -> L2, ahead of phase C
+#pragma unroll 1
         for (uint32_t tile = cta; tile < (H >> 4); tile += grid)
             for (uint32_t j = tid; j < n_src; j += FT) {
                 const Src s = srcs[j];
-                const DevTensor &d = s.shared ? a.w[6] : a.w[3];
-                const uint32_t nbd = d.k_storage >> 8, rb = nbd * (d.type == T_Q4_K ? 144u : 64u);
-                fprefetch_l2(d.data + (uint64_t)(s.shared ? 0 : s.expert) * d.expert_bytes + (uint64_t)tile * 16 * rb, 16 * rb);
+                const uint32_t rb = s.shared ? (IS >> 8) * (ST == T_Q4_K ? 144u : 64u) : (I >> 8) * (RT == T_Q4_K ? 144u : 64u);
+                const uint8_t *mat = s.shared ? a.w[6].data : a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes;
+                fprefetch_l2(mat + tile * 16 * rb, 16 * rb);
             }
         const uint8_t *xq_lane = xq + g * p.kp + 8 * t;
         const int2 *xsum_tok = xsum + t * (H >> 5);
@@ -773,6 +796,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             const uint32_t n0 = sh ? ul * spu_s : n_shu * spu_s + (ul - n_shu) * spu_r;
             if (n0 + spu > slices) break;                                      // beyond the partial buffer (never for supported shapes)
             float f0 = 0.0f, f1 = 0.0f;
+#pragma unroll 1
             for (uint32_t s = 0; s < spu; s++) { const float2 v = partial[(n0 + s) * 32 + lane]; f0 += v.x; f1 += v.y; }
             const uint32_t u = u0 + ul;
             float v = 0.0f;
@@ -786,7 +810,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
                 else {
                     const uint32_t vu = u - us;
                     const Src sr = srcs[1 + vu / ur];
-                    if ((sr.mask >> t) & 1u) { live = true; row = t * k + sr.slot[t]; a.act[(uint64_t)row * I + (vu % ur) * 8 + g] = v; }
+                    if ((sr.mask >> t) & 1u) { live = true; row = t * k + sr.slot(t); a.act[(uint64_t)row * I + (vu % ur) * 8 + g] = v; }
                 }
                 if (live && !finite_f32(v)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
             }
@@ -814,12 +838,13 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             const Src s = srcs[j];
             const uint32_t at = ring_count + n;
             uint8_t *stage = tiles + (at % FNS) * FSTAGE;
-            if (s.shared) issue_down_tile<ST>(a.w[6], 0, tile * 16, stage, &bar[at % FNS], lane);
-            else issue_down_tile<RT>(a.w[3], s.expert, tile * 16, stage, &bar[at % FNS], lane);
+            if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &bar[at % FNS], lane);
+            else issue_down_tile<RT>(a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes, H, I >> 8, tile * 16, stage, &bar[at % FNS], lane);
         };
         fproxy_fence();
         if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
         // digit images of the activation rows: pairs first, then the shared expert's rows
+#pragma unroll 1
         for (uint32_t r = tid; r < rows_c; r += FT) ascale[r] = __uint_as_float(__ldcg(amax_g + r));
         __syncthreads();
         float4 *aconsts = reinterpret_cast<float4 *>(region + p.aconst);
@@ -836,9 +861,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             for (uint32_t si = 0; si < my_src; si++, n++) {
                 const Src s = srcs[warp + si * FW];
                 const uint32_t tokg = g >> 1;
-                const uint32_t row_g = s.shared ? pairs + (tokg < T ? tokg : 0) : (((s.mask >> tokg) & 1u) ? tokg * k + s.slot[tokg] : 0);
+                const uint32_t row_g = s.shared ? pairs + (tokg < T ? tokg : 0) : (((s.mask >> tokg) & 1u) ? tokg * k + s.slot(tokg) : 0);
                 const bool live_t = t < T && ((s.mask >> t) & 1u);
-                const uint32_t row_t = s.shared ? pairs + (t < T ? t : 0) : (live_t ? t * k + s.slot[t] : 0);
+                const uint32_t row_t = s.shared ? pairs + (t < T ? t : 0) : (live_t ? t * k + s.slot(t) : 0);
                 const uint8_t *aq_lane = aq + (2 * row_g + (g & 1u)) * p.ap + 8 * t;
                 const int2 *asum_tok = asum + row_t * (imax >> 5);
                 const uint32_t at = ring_count + n;
@@ -854,7 +879,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
                 fproxy_fence();
                 if (alive && n + FNS < steps) issue(n + FNS);
                 if (live_t) {
-                    const float coef = (s.shared ? fast_sigmoid(misc_f[4 + t]) : wts_s[t * k + s.slot[t]]) * ascale[row_t];
+                    const float coef = (s.shared ? fast_sigmoid(misc_f[4 + t]) : wts_s[t * k + s.slot(t)]) * ascale[row_t];
                     acc0 = fmaf(coef, f0, acc0); acc1 = fmaf(coef, f1, acc1);
                 }
             }
@@ -863,6 +888,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             if (tid < 64) {                                                    // rows g (threads 0-31) and g + 8 (32-63), warps added in order
                 const uint32_t l = tid & 31u, gg = l >> 2, tt = l & 3u, hi = tid >> 5;
                 float sum = 0.0f;
+#pragma unroll 1
                 for (uint32_t w = 0; w < FW; w++) {
                     const float2 v = cpartial[w * 32 + l];
                     sum += hi ? v.y : v.x;
@@ -884,6 +910,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     }
     __syncthreads();
     if (misc_u[0]) {
+#pragma unroll 1
         for (uint32_t r = tid; r < rows_c; r += FT) amax_g[r] = 0;
         if (tid == 0) { a.sync[0] = 0; a.sync[1] = 0; a.sync[2] = 0; }
         __threadfence();
