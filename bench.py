@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 Qwen4 MoE layer.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2|c4] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of synthetic tokens.  The default workload
 (N = 1) is the 4-token decode / multi-token-verify batch with IQ2_XXS routed experts and a
@@ -16,6 +16,10 @@ One JSON line is printed by rank 0:
   layer      the whole layer's weight bytes touched / step time, against the HBM peak
   cpu_baseline  the reference's own CPU MoE path timed here on the host cores
 `--impl reference` times only that CPU path and prints the same line shape.
+
+With N > 1 (torchrun, one rank per GPU) the workload is the sharded one: batched decode of 64
+sequences through 48 Q4_K layers with the 512 experts cut into N blocks (expert parallel), rows
+exchanged by all-to-all over NCCL; `--workload c4` runs the same batch on one GPU for comparison.
 """
 from __future__ import annotations
 
@@ -69,6 +73,15 @@ def workload(name: str, layers: int):
         x = synth.activations(2, 1024)
         x[:, 0] = 1.0
         desc = "c2: 1024-token prefill chunk, Q4_K, Zipf(1.1) expert popularity"
+    elif name == "c4":
+        specs = []
+        for l in range(layers):
+            spec = synth.make_layer(4, layer=l, routed_type=abi.Q4_K, shared_type=abi.Q4_K)
+            synth.zipf_router_bias(spec, 4 + l)
+            specs.append(spec)
+        x = synth.activations(4, 64)
+        x[:, 0] = 1.0
+        desc = "c4 (one GPU): batched decode, 64 sequences x 1 token, Q4_K, Zipf(1.1) expert popularity"
     else:
         raise SystemExit(f"unknown workload {name}")
     return desc, x.shape[0], specs, x
@@ -177,6 +190,116 @@ def cpu_reference_step(specs, x, repeats: int, warmup: int):
 
 
 # ---- main --------------------------------------------------------------------------------------
+# ---- expert-parallel batched decode (C4) ------------------------------------------------------------
+def run_expert_parallel(args, rank: int, local_rank: int, world: int) -> None:
+    """64 concurrent sequences, one token each, through `--ep-layers` Q4_K layers with Zipf(1.1) expert
+    popularity; the 512 experts are cut into `world` contiguous blocks, tokens are data-parallel, and
+    rows travel to the experts' owners and back by all-to-all over NCCL (picoforge_b200/expert_parallel.py).
+    Total work is fixed as N grows ("strong" scaling).  Time: CUDA events on the stream everything is
+    enqueued on, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    from picoforge_b200.expert_parallel import EpLayer, TorchExchange
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    api = abi.product()
+    lib = api.lib
+    if lib.qw4cu_set_device(local_rank) != 0:
+        raise SystemExit(lib.qw4cu_last_error().decode())
+    lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
+    tokens, n_layers = 64, args.ep_layers
+    per, epr = tokens // world, 512 // world
+    x_all = synth.activations(4, tokens)
+    x_all[:, 0] = 1.0
+    specs, layers = [], []
+    for l in range(n_layers):
+        spec = synth.make_layer(4, layer=l, routed_type=abi.Q4_K, shared_type=abi.Q4_K, shard=(rank * epr, epr))
+        synth.zipf_router_bias(spec, 4 + l)
+        specs.append(spec)
+        layers.append(EpLayer(api, spec, per, world, rank, TorchExchange()))
+    stream = torch.cuda.Stream()
+    pinned_x = torch.from_numpy(x_all[rank * per:(rank + 1) * per].copy()).pin_memory()
+    pinned_y = torch.empty_like(pinned_x).pin_memory()
+    with torch.cuda.stream(stream):
+        x = pinned_x.cuda(non_blocking=True)
+
+        def step():
+            y = None
+            for layer in layers:
+                y = layer.forward(x)
+            return y
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        for layer in layers:
+            layer.sync()
+        dist.barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            before = lib.qw4cu_launch_count()
+            begin.record(stream)
+            for _ in range(args.steps):
+                y = step()
+            end.record(stream)
+            stream.synchronize()
+            launches = lib.qw4cu_launch_count() - before
+        for layer in layers:
+            layer.sync()                                                      # error words of every layer
+        dist.barrier()
+        elapsed = torch.tensor([begin.elapsed_time(end)], device="cuda")
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        ms_per_step = float(elapsed.item()) / args.steps
+        assert bool(torch.isfinite(y).all())
+        # end to end: pinned host x in, y back out, every step
+        e2e_steps = max(1, min(args.steps, 50))
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            x.copy_(pinned_x, non_blocking=True)
+            y = step()
+            pinned_y.copy_(y, non_blocking=True)
+            stream.synchronize()
+        e2e = torch.tensor([time.perf_counter() - t0], device="cuda")
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+        # distinct experts per layer over all ranks (weight bytes actually touched)
+        ids = torch.stack([layer.ids for layer in layers]).to(torch.int64)        # [L, per, k]
+        gathered = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(gathered, ids)
+        distinct = float(sum(len(torch.unique(torch.cat([g[l] for g in gathered]))) for l in range(n_layers)))
+    if rank == 0:
+        hbm_peak, peak_kind = peaks()
+        layouts = specs[0].layouts()
+        expert_bytes = layouts[1].expert_bytes + layouts[2].expert_bytes + layouts[3].expert_bytes
+        replicated = layouts[0].tensor_bytes + layouts[7].tensor_bytes + sum(layouts[i].tensor_bytes for i in (4, 5, 6))
+        touched = distinct * expert_bytes + n_layers * world * replicated
+        us = ms_per_step * 1e3 / (tokens * n_layers)
+        achieved = touched / (ms_per_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "moe_layer_us_per_token_decode", "value": us, "unit": "us/token", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"c4: batched decode, 64 sequences x 1 token through {n_layers} Q4_K layers, Zipf(1.1) expert popularity",
+                       "tokens_per_step": tokens, "layers": n_layers,
+                       "parallelism": f"expert parallel, {epr} experts per GPU, router and shared expert replicated, tokens data-parallel",
+                       "exchange": "torch.distributed all_to_all_single over NCCL, three per layer (rows, ids, outputs)",
+                       "router": args.router, "l2": f"{n_layers} layers of weights per step ({touched / world / 1e6:.0f} MB per GPU), L2 is 126 MB",
+                       "distinct_experts_per_layer": distinct / n_layers},
+            "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
+                         "frac": achieved / (hbm_peak * world), "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes": touched,
+                         "kernel_us": ms_per_step * 1e3},
+            "e2e": {"value": float(e2e.item()) / e2e_steps * 1e6 / (tokens * n_layers), "unit": "us/token",
+                    "h2d_bytes_per_step": int(pinned_x.numel() * 4 * world), "d2h_bytes_per_step": int(pinned_y.numel() * 4 * world),
+                    "steps": e2e_steps},
+            "gpu_launches": int(launches), "clocks": clocks.summary(), "cpu_baseline": None,
+        }))
+    for layer in layers:
+        layer.close()
+    lib.qw4cu_set_stream(None)
+    dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -189,6 +312,7 @@ def main():
     parser.add_argument("--no-graph", action="store_true")
     parser.add_argument("--expert-path", type=int, default=-1, help="-1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
+    parser.add_argument("--ep-layers", type=int, default=48, help="layers of the expert-parallel workload (N > 1)")
     parser.add_argument("--profile", action="store_true",
                         help="only W + K directly launched steps (the command to run under ncu); prints no bench line")
     args = parser.parse_args()
@@ -218,6 +342,9 @@ def main():
             "e2e": {"value": us_per_token, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
         return
+
+    if world > 1:
+        return run_expert_parallel(args, rank, local_rank, world)
 
     api = abi.product()
     lib = api.lib

@@ -1085,7 +1085,7 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (allow_smem(router_exact_small_kernel, smem)) return -1;
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
         LAUNCHED("router_exact_small_kernel");
-    } else if (tokens > 16 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
+    } else if (tokens > 128 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {   // enough tiles to fill the GPU
         const dim3 grid((unsigned)((tokens + 63) / 64), (rows + 63) / 64);
         if (mode == 0) router_gemm_kernel<true><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         else router_gemm_kernel<false><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);

@@ -116,3 +116,51 @@ def test_shard_bytes_equal_the_slice_of_the_whole_tensor():
     sliced = whole.shard(2, 4)
     for a, b in zip(part.tensors, sliced.tensors):
         np.testing.assert_array_equal(a, b)
+
+
+def _nccl_worker(rank, world, port, routed, tokens, results):
+    import torch
+    import torch.distributed as dist
+    from picoforge_b200 import abi, synth
+    from picoforge_b200.expert_parallel import EpLayer, TorchExchange
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        api = abi.product()
+        assert api.lib.qw4cu_set_device(rank) == 0
+        per, epr = tokens // world, 32 // world
+        spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4, shard=(rank * epr, epr))
+        x = synth.activations(300 + world, tokens)[rank * per:(rank + 1) * per]
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            layer = EpLayer(api, spec, per, world, rank, TorchExchange())
+            y = layer.forward(torch.tensor(x).cuda().contiguous())
+            layer.sync()
+            results[rank] = (y.cpu().numpy(), layer.ids.cpu().numpy().astype(np.uint32))
+            layer.close()
+        api.lib.qw4cu_set_stream(None)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("routed", [12, 16])
+def test_sharded_layer_over_nccl_on_two_gpus(gpu, routed):
+    """One process per GPU, rows exchanged by NCCL all-to-all; skipped on a one-GPU box."""
+    import torch
+    import torch.multiprocessing as mp
+    import oracle
+    from picoforge_b200 import abi, synth
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, tokens = 2, 12
+    spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4)
+    x = synth.activations(300 + world, tokens)
+    want = oracle.forward(spec, x, threads=synth.threads())
+    results = mp.Manager().dict()
+    mp.spawn(_nccl_worker, args=(world, 29600 + os.getpid() % 300, routed, tokens, results), nprocs=world, join=True)
+    y = np.concatenate([results[r][0] for r in range(world)])
+    ids = np.concatenate([results[r][1] for r in range(world)])
+    np.testing.assert_array_equal(ids, want["ids"])
+    assert np.abs(y - want["y"]).max() <= 1e-3
