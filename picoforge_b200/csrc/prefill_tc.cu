@@ -25,8 +25,8 @@
 //          with tcgen05.ld, scale, accumulate; at the end SwiGLU (gate/up) or a plain store (down).
 //          gate/up writes the activation directly as the down product's B operand (fp16 hi/lo,
 //          32-column sums), so no separate conversion pass runs in between.
-//   4-11   dequantise: packed block rows (shared memory, from TMA) -> fp16 operand tiles in the
-//          canonical no-swizzle K-major core-matrix layout ([k/8][row][8 halves]).
+//   4-11   dequantise: packed block rows (shared memory, from TMA) -> fp16 operand tiles, K-major rows of
+//          128 bytes (64 columns) with the 128-byte swizzle the tensor cores read at full rate.
 //   12     TMA producer: one 2-D tensor copy (128 rows x 144 bytes) per matrix and block.
 //   13     MMA issuer: one elected lane issues tcgen05.mma / tcgen05.commit.
 //   14     activation loader: 16-byte cp.async gathers of the group's token rows.
@@ -59,12 +59,13 @@ constexpr uint32_t PT_TMEM_COLS = 512;                      // 2 buffers x (Q ga
 // Shared-memory map (bytes).
 constexpr uint32_t PT_BARS = 0;                             // mbarriers
 constexpr uint32_t PT_TMEMPTR = 1024;
-constexpr uint32_t PT_DSC = 1152;                           // [2][2][128] (d, dmin) words
-constexpr uint32_t PT_PK = PT_DSC + 2 * 2 * 128 * 4;        // [2][2][128 x 144]
+constexpr uint32_t PT_DSC = 2048;                           // [2][2][128] (d, dmin) words
+constexpr uint32_t PT_PK = 4096;                            // [2][2][128 x 144]; the operand tiles behind it start on a 1024-byte boundary
 constexpr uint32_t PT_PK_ONE = PT_ROWS * PT_BLOCK;          // 18432
-constexpr uint32_t PT_A = PT_PK + 2 * 2 * PT_PK_ONE;        // [stages][2][8][128][16]
+constexpr uint32_t PT_A = PT_PK + 2 * 2 * PT_PK_ONE;        // [stages][2][128 rows][128 bytes], 128-byte swizzle
+static_assert(PT_A % 1024 == 0, "swizzled operand tiles need 1024-byte alignment");
 constexpr uint32_t PT_A_ONE = 8 * PT_ROWS * 16;             // 16384
-constexpr uint32_t PT_B = PT_A + PT_STAGES * 2 * PT_A_ONE;  // [b stages][8][64][16]: column n < 32 hi of token n, else lo of token n - 32
+constexpr uint32_t PT_B = PT_A + PT_STAGES * 2 * PT_A_ONE;  // [b stages][64 rows][128 bytes], 128-byte swizzle: row n < 32 hi of token n, else lo of token n - 32
 constexpr uint32_t PT_B_ONE = 8 * PT_TOK * 16;              // 4096: half a stage
 constexpr uint32_t PT_AM = PT_B + PT_BSTAGES * 2 * PT_B_ONE; // [2][2][2][128][16]
 constexpr uint32_t PT_AM_ONE = 2 * PT_ROWS * 16;            // 4096
@@ -161,6 +162,11 @@ __device__ __forceinline__ uint64_t pdesc(uint32_t smem_addr, uint32_t lbo, uint
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) |
            (1ull << 46);
 }
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows with the 128-byte swizzle (the
+// 16-byte piece c of row r sits at piece c ^ (r & 7)); 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t pdesc_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
 // Instruction descriptor: D = F32, A = B = F16, both K-major, N = 64, M = 128.
 constexpr uint32_t PT_IDESC = (1u << 4) | ((PT_N >> 3) << 17) | ((PT_ROWS >> 4) << 24);
 
@@ -252,8 +258,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_tc_kernel(const __grid_
                     // lane = token row; eight 16-byte pieces of hi and of lo
 #pragma unroll
                     for (uint32_t k8 = 0; k8 < 8; k8++) {
-                        pcp_async16(dst + (k8 * PT_N + lane) * 16, a.in_hi + (uint64_t)src_row * a.k + col0 + k8 * 8, bytes);
-                        pcp_async16(dst + (k8 * PT_N + PT_TOK + lane) * 16, a.in_lo + (uint64_t)src_row * a.k + col0 + k8 * 8, bytes);
+                        pcp_async16(dst + lane * 128 + ((k8 ^ (lane & 7u)) << 4), a.in_hi + (uint64_t)src_row * a.k + col0 + k8 * 8, bytes);
+                        pcp_async16(dst + (PT_TOK + lane) * 128 + ((k8 ^ (lane & 7u)) << 4), a.in_lo + (uint64_t)src_row * a.k + col0 + k8 * 8, bytes);
                     }
                     if (c == 0) {                                                // the block's eight 32-column sums
                         uint8_t *sd = smem + PT_BS + (blk & 1u) * 2 * PT_BS_ONE;
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_tc_kernel(const __grid_
         uint32_t st = 0, blk = 0;
         bool ok = true;
         // operand descriptors: slot / buffer / k-step offsets are added to the 16-byte address field
-        const uint64_t a_desc0 = pdesc(ps_u32(smem + PT_A), PT_ROWS * 16, 128), b_desc0 = pdesc(ps_u32(smem + PT_B), PT_N * 16, 128);
+        const uint64_t a_desc0 = pdesc_sw128(ps_u32(smem + PT_A)), b_desc0 = pdesc_sw128(ps_u32(smem + PT_B));
         const uint64_t am_desc0 = pdesc(ps_u32(smem + PT_AM), PT_ROWS * 16, 128), bs_desc0 = pdesc(ps_u32(smem + PT_BS), PT_N * 16, 128);
         for (uint32_t it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
             for (uint32_t b = 0; b < nb && ok; b++, blk++) {
@@ -287,10 +293,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_tc_kernel(const __grid_
                         const uint32_t acc = tmem_base + p * 256;
 #pragma unroll
                         for (uint32_t j = 0; j < PT_KS / 16; j++) {
-                            const uint64_t bd = b_desc0 + bslot * ((2 * PT_B_ONE) >> 4) + j * ((2 * PT_N * 16) >> 4);
+                            const uint64_t bd = b_desc0 + bslot * ((2 * PT_B_ONE) >> 4) + j * 2;       // 32 bytes (16 columns) along the row per k-step
 #pragma unroll
                             for (uint32_t m = 0; m < MATS; m++)
-                                ptc_mma_f16(acc + m * 128, a_desc0 + (slot * 2 + m) * (PT_A_ONE >> 4) + j * ((2 * PT_ROWS * 16) >> 4), bd, PT_IDESC,
+                                ptc_mma_f16(acc + m * 128, a_desc0 + (slot * 2 + m) * (PT_A_ONE >> 4) + j * 2, bd, PT_IDESC,
                                             (c | j) ? 1u : 0u);
                         }
                         if (c == 0) {                                            // min term of this block
@@ -353,7 +359,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_tc_kernel(const __grid_
                         const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo)), s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
                         const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
                         const uint8_t *qs = smem + PT_PK + (pb * 2 + m) * PT_PK_ONE + row * PT_BLOCK + 16 + c * 32;
-                        uint8_t *dst = smem + PT_A + (slot * 2 + m) * PT_A_ONE + row * 16;
+                        uint8_t *dst = smem + PT_A + (slot * 2 + m) * PT_A_ONE + row * 128;
 #pragma unroll
                         for (uint32_t ii = 0; ii < 2; ii++) {
                             const uint32_t i = ii * 2 + isel;                    // bytes 8i..8i+7: columns 8i.. (low nibbles) and 32 + 8i.. (high)
@@ -372,8 +378,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) prefill_tc_kernel(const __grid_
                                 lo[2 * h] = *reinterpret_cast<const uint32_t *>(&a0); lo[2 * h + 1] = *reinterpret_cast<const uint32_t *>(&a1);
                                 hi[2 * h] = *reinterpret_cast<const uint32_t *>(&b0); hi[2 * h + 1] = *reinterpret_cast<const uint32_t *>(&b1);
                             }
-                            *reinterpret_cast<uint4 *>(dst + i * PT_ROWS * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                            *reinterpret_cast<uint4 *>(dst + (4 + i) * PT_ROWS * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                            *reinterpret_cast<uint4 *>(dst + ((i ^ (row & 7u)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                            *reinterpret_cast<uint4 *>(dst + (((4 + i) ^ (row & 7u)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                         }
                     }
                     pfence_async();
