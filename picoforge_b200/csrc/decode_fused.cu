@@ -358,27 +358,32 @@ __device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t
 // thread in flight (one from shared memory, four from global memory, whose latency they share); eight consecutive lanes cover one chunk.  `amax` holds the maxima on entry
 // and the scales (max / 127, or 0 for an unusable row) on return; `consts` is scratch, one
 // float4 per row.
-template <bool GLOBAL, int BATCH>
+// The first `NT` threads of the CTA take part and meet at named barrier `BAR` (0 with NT = FT is the
+// CTA barrier).
+template <bool GLOBAL, int BATCH, int NT = FT, int BAR = 0>
 __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
-                                           uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts) {
+                                           uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts, uint32_t rotate = 0) {
+    auto meet = [] { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(NT) : "memory"); };
 #pragma unroll 1
-    for (uint32_t r = threadIdx.x; r < rows; r += FT) {
+    for (uint32_t r = threadIdx.x; r < rows; r += NT) {
         const float m = amax[r];
         const bool usable = finite_f32(m) && m > 0.0f;
         const float inv = usable ? __fdividef(127.0f, m) : 0.0f;
         consts[r] = make_float4(usable ? m * (1.0f / 127.0f) : 0.0f, inv, 2.0f * inv * 127.0f, 0.0f);
     }
-    __syncthreads();
-    const uint32_t per_row = k >> 2, items = rows * per_row;
+    meet();
+    // `rotate`: every CTA reads the same rows from L2; starting each at a different item (a multiple of
+    // eight, so a chunk's eight items stay in one warp) keeps them off the same lines at the same time
+    const uint32_t per_row = k >> 2, items = rows * per_row, shift = items ? ((rotate * 5u) % (items >> 3)) << 3 : 0;
 #pragma unroll 1
-    for (uint32_t first = 0; first < items; first += BATCH * FT) {
+    for (uint32_t first = 0; first < items; first += BATCH * NT) {
         float4 v[BATCH];
         uint32_t r[BATCH], c4[BATCH];
         bool live[BATCH];
 #pragma unroll
         for (int j = 0; j < BATCH; j++) {
-            const uint32_t i = first + j * FT + threadIdx.x;
-            live[j] = i < items;
+            const uint32_t i0 = first + j * NT + threadIdx.x, i = i0 + shift < items ? i0 + shift : i0 + shift - items;
+            live[j] = i0 < items;
             r[j] = live[j] ? i / per_row : 0; c4[j] = live[j] ? i % per_row : 0;
             v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (live[j]) v[j] = GLOBAL ? __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)r[j] * src_pitch) + c4[j])
@@ -397,10 +402,10 @@ __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pit
             if (live[j] && (c4[j] & 7u) == 0) sums[r[j] * sums_pitch + (c4[j] >> 3)] = make_int2(s1, s2);
         }
     }
-    __syncthreads();
+    meet();
 #pragma unroll 1
-    for (uint32_t r = threadIdx.x; r < rows; r += FT) amax[r] = consts[r].x;
-    __syncthreads();
+    for (uint32_t r = threadIdx.x; r < rows; r += NT) amax[r] = consts[r].x;
+    meet();
 }
 
 __device__ __forceinline__ float fast_sigmoid(float v) {
@@ -489,8 +494,15 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
 
 // ---- the kernel ---------------------------------------------------------------------------------
 template <uint32_t RT, uint32_t ST>
-__global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) {
+__global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_constant__ FusedArgs args) {
     extern __shared__ __align__(128) uint8_t smem[];
+    // The arguments span four cache lines of the constant bank, and a first touch of each line costs a
+    // miss that every SM takes at the same moment.  All lines are fetched at once here, into shared
+    // memory, and read from there afterwards.
+    __shared__ FusedArgs a;
+    for (uint32_t i = threadIdx.x; i < sizeof(FusedArgs) / 4; i += FT)
+        reinterpret_cast<uint32_t *>(&a)[i] = reinterpret_cast<const uint32_t *>(&args)[i];
+    __syncthreads();
     const uint32_t T = a.tokens, H = a.hidden, E = a.experts, k = a.top_k, I = a.inter, IS = a.shared_inter;
     const uint32_t pairs = T * k, rows_c = pairs + T, imax = I > IS ? I : IS;
     constexpr bool LUT = RT == T_IQ2_XXS || ST == T_IQ2_XXS;
@@ -513,7 +525,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     uint32_t *amax_g = a.sync + F_SYNC_AMAX;                                   // row maxima of act / shared_act (float bits)
     unsigned long long *clocks = reinterpret_cast<unsigned long long *>(a.sync + F_SYNC_CLOCKS);
     const bool clocked = cta == 0 && tid == 0;
+#ifdef QW4_NO_PHASE_CLOCKS
+#define CLOCK(i) do { } while (0)
+#else
 #define CLOCK(i) do { if (clocked) clocks[i] = clock64(); } while (0)
+#endif
     CLOCK(0);
 
     if (tid == 0) {
@@ -565,14 +581,14 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
             float4 v[XL];
 #pragma unroll
             for (int j = 0; j < XL; j++) {
-                const uint32_t i = first + j * FT + tid;
+                const uint32_t i0 = first + j * FT + tid, i = (i0 + cta * 24u) % (T * (H >> 2));
                 v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < T * (H >> 2)) v[j] = __ldg(reinterpret_cast<const float4 *>(a.x) + i);
+                if (i0 < T * (H >> 2)) v[j] = __ldg(reinterpret_cast<const float4 *>(a.x) + i);
             }
 #pragma unroll
             for (int j = 0; j < XL; j++) {
-                const uint32_t i = first + j * FT + tid;
-                if (i < T * (H >> 2)) {
+                const uint32_t i0 = first + j * FT + tid, i = (i0 + cta * 24u) % (T * (H >> 2));
+                if (i0 < T * (H >> 2)) {
                     const uint32_t r = i / (H >> 2), c4 = i % (H >> 2);
                     *reinterpret_cast<float4 *>(xf + r * p.xf_pitch + c4 * 16) = v[j];
                     const float mm = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
@@ -595,7 +611,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     }
     __syncthreads();
     CLOCK(1);
-    digitise_rows<false, 1>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
+    if (a.router_mode != 0) digitise_rows<false, 1>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
     CLOCK(2);
     // router rows
     bool alive = true;
@@ -641,6 +657,10 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
                         make_float4(__fmul_rn(w4.x, x4.x), __fmul_rn(w4.y, x4.y), __fmul_rn(w4.z, x4.z), __fmul_rn(w4.w, x4.w));
                 }
                 asm volatile("bar.arrive %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
+                // both product buffers are full and the chain warp is busy with them: the digit image of x is
+                // built here, under the chain
+                if (c == 1) digitise_rows<false, 1, FT - 32, 6>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum,
+                                                              H >> 5, xconsts);
             }
         }
     } else {
@@ -673,7 +693,10 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
     // ================================ phase B ================================
     float *zs = reinterpret_cast<float *>(region + p.zs);
 #pragma unroll 1
-    for (uint32_t i = tid; i < T * E; i += FT) zs[(i / E) * FMAXE + (i % E)] = __ldcg(a.logits + i);
+    for (uint32_t i0 = tid; i0 < T * E; i0 += FT) {                           // each CTA starts somewhere else in the array
+        const uint32_t i = (i0 + cta * 56u) % (T * E);
+        zs[(i / E) * FMAXE + (i % E)] = __ldcg(a.logits + i);
+    }
     if (tid < T) misc_f[4 + tid] = __ldcg(a.shared_logit + tid);
 #pragma unroll 1
     for (uint32_t i = tid; i < FMAXE; i += FT) tokmask[i] = 0;
@@ -848,9 +871,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const FusedArgs a) 
         for (uint32_t r = tid; r < rows_c; r += FT) ascale[r] = __uint_as_float(__ldcg(amax_g + r));
         __syncthreads();
         float4 *aconsts = reinterpret_cast<float4 *>(region + p.aconst);
-        digitise_rows<true, 4>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
+        digitise_rows<true, 4>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts, cta);
         digitise_rows<true, 4>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
-                            aconsts + pairs);
+                            aconsts + pairs, cta);
         CLOCK(11);
         uint32_t n = 0;
 #pragma unroll 1
