@@ -275,6 +275,25 @@ Qwen4Status qw4cu_moe_experts_device(const Qwen4Moe *moe, const float *rows_dev,
 Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
                                      const float *pair_out_dev, float *y_dev, Qwen4MoeWork *work,
                                      Qwen4Error *err);
+/* The same step with packed exchange messages, for an all-to-all of equal blocks.  A message has one block per
+ * rank of `slots_per_rank` slots; a slot is qw4cu_ep_slot_floats(moe) floats: the token's activations, one word
+ * with the expert's index inside the destination's shard (0xffffffff: unused slot), padding.
+ *   route_pack  routes the rank's tokens, writes msg_dev (pairs in pair order inside each block) and the slot of
+ *               every pair into slots_dev [tokens * k] (and the global expert ids into ids_dev [tokens, k] if
+ *               not NULL), and starts the shared expert on a second stream so that it runs under the exchange
+ *   experts     rows slots as received -> out_dev [rows, hidden], row r for slot r
+ *   combine     back_dev [ranks * slots_per_rank, hidden]: the outputs returned for this rank's message;
+ *               gathers them into pair order, joins the shared expert, writes y
+ * slots_per_rank >= tokens * k.  The workspace must hold ranks * slots_per_rank rows; with tokens more rows
+ * than that the shared expert never has to wait for the routed experts' buffers. */
+size_t qw4cu_ep_slot_floats(const Qwen4Moe *moe);
+Qwen4Status qw4cu_moe_ep_route_pack_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens, size_t slots_per_rank,
+                                           float *msg_dev, uint32_t *slots_dev, uint32_t *ids_dev, Qwen4MoeWork *work,
+                                           Qwen4Error *err);
+Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *moe, const float *msg_dev, size_t rows, float *out_dev,
+                                        Qwen4MoeWork *work, Qwen4Error *err);
+Qwen4Status qw4cu_moe_ep_combine_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens, const float *back_dev,
+                                        const uint32_t *slots_dev, float *y_dev, Qwen4MoeWork *work, Qwen4Error *err);
 /* Makes every later call on this device enqueue on the caller's CUDA stream (a cudaStream_t
  * passed as void *), so that the library's kernels order with the caller's own work, e.g. the
  * NCCL all-to-all of an expert-parallel step.  NULL restores the library's own stream; the legacy
@@ -311,6 +330,11 @@ void qw4cu_set_fused_decode(int mode);
  * TMEM accumulators (groups of <= 32 token rows per expert, exact integer codes as fp16 operands,
  * activations split into fp16 hi + lo).  -1 (default): used whenever the layer fits; 0: never. */
 void qw4cu_set_prefill_path(int path);
+/* Tile kernels: int8 tensor-core MMAs whose weight fragments are built once per group of <= 32 rows of an
+ * expert (two-int8-digit activations, as in the decode kernels), for Q4_K and IQ2_XXS tensors.
+ * -1 (default): batches of more than 64 rows that the tcgen05 prefill cannot take (IQ2_XXS tensors);
+ * 0: never; 1: every batch of more than four rows. */
+void qw4cu_set_tile_path(int path);
 /* Profiling aid of the tensor-core prefill kernels: device_words is a device array of 64 x 8 bytes (NULL: off).
  * CTA 0 of every later launch stores the SM cycles its roles (0 epilogue, 1 dequantise, 2 TMA, 3 MMA issue,
  * 4 activation loader) spent waiting, at [32 * mode + 4 * role + kind]; kind 3 is the role's whole run. */
@@ -331,6 +355,10 @@ void qw4cu_set_stage_timing(int on);
 int qw4cu_stage_times(double *ms, uint64_t *forwards);
 /* Kernels launched by this library in this process so far. */
 uint64_t qw4cu_launch_count(void);
+/* Names of the kernels launched after qw4cu_launch_log_begin (the first 512), comma-separated into out[cap];
+ * returns how many were logged.  Not thread-safe: a test and profiling aid. */
+void qw4cu_launch_log_begin(void);
+size_t qw4cu_launch_log(char *out, size_t cap);
 
 /* Decodes rows [row0, row0 + rows) of one expert of a resident tensor (index 0-7 in
  * Qwen4MoeWeights order) FROM THE DEVICE IMAGE into host floats [rows, k_storage].  Used to

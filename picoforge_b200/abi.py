@@ -178,6 +178,12 @@ class MoeApi:
                          "qwen4_moe_route", "qwen4_moe_forward", "qw4_moe_group_pairs",
                          "qw4_moe_observe")
 
+    def launch_names(self) -> list[str]:
+        """Kernel names launched since `lib.qw4cu_launch_log_begin()` (product library only)."""
+        buf = C.create_string_buffer(1 << 16)
+        self.lib.qw4cu_launch_log(buf, len(buf))
+        return [n for n in buf.value.decode().split(",") if n]
+
     def _bind_extensions(self):
         lib, P, E = self.lib, C.c_void_p, C.POINTER(Qwen4Error)
         sig = {
@@ -194,11 +200,17 @@ class MoeApi:
             "qw4cu_moe_route_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
             "qw4cu_moe_experts_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
             "qw4cu_moe_combine_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
+            "qw4cu_ep_slot_floats": ([P], C.c_size_t),
+            "qw4cu_moe_ep_route_pack_device": ([P, P, C.c_size_t, C.c_size_t, P, P, P, P, E], C.c_int),
+            "qw4cu_moe_ep_experts_device": ([P, P, C.c_size_t, P, P, E], C.c_int),
+            "qw4cu_moe_ep_combine_device": ([P, P, C.c_size_t, P, P, P, P, E], C.c_int),
             "qw4cu_set_stream": ([P], C.c_int),
             "qw4cu_moe_work_timer_begin": ([P], C.c_int),
             "qw4cu_moe_work_timer_end": ([P], C.c_int),
             "qw4cu_moe_work_timer_elapsed_ms": ([P], C.c_float),
             "qw4cu_launch_count": ([], C.c_uint64),
+            "qw4cu_launch_log_begin": ([], None),
+            "qw4cu_launch_log": ([C.c_char_p, C.c_size_t], C.c_size_t),
             "qw4cu_set_graph_mode": ([C.c_int], None),
             "qw4cu_get_graph_mode": ([], C.c_int),
             "qw4cu_set_stage_timing": ([C.c_int], None),
@@ -206,6 +218,7 @@ class MoeApi:
             "qw4cu_set_only_step": ([C.c_int], None),
             "qw4cu_set_fused_decode": ([C.c_int], None),
             "qw4cu_set_prefill_path": ([C.c_int], None),
+            "qw4cu_set_tile_path": ([C.c_int], None),
             "qw4cu_prefill_debug": ([P], None),
             "qw4cu_decode_phase_clocks": ([P, C.POINTER(C.c_uint64)], C.c_int),
             "qw4cu_stage_times": ([C.POINTER(C.c_double), C.POINTER(C.c_uint64)], C.c_int),

@@ -142,6 +142,27 @@ int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]);
 
 /* Tensor-core prefill path (prefill_tc.cu): Q4_K experts, groups of <= 32 token rows, tcgen05
  * MMAs with TMEM accumulators.  supported: 1 when a tensor fits it. */
+/* Expert-parallel exchange messages (ep_exchange.cu) and the pieces that use them. */
+uint32_t qw4sh_ep_pitch(uint32_t hidden);
+int qw4sh_ep_pack(const float *x, uint32_t tokens, uint32_t k, uint32_t hidden, const uint32_t *ids, uint32_t experts_per_rank,
+                  uint32_t world, uint32_t cap, float *msg, uint32_t *slot_of_pair, uint32_t *status, void *stream);
+int qw4sh_ep_ids(const float *msg, uint32_t hidden, uint32_t rows, uint32_t *ids, void *stream);
+int qw4sh_ep_gather(const float *back, uint32_t hidden, const uint32_t *slot_of_pair, uint32_t pairs, float *pair_out, void *stream);
+int qw4sh_ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens);
+int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg, size_t rows, uint32_t local_experts,
+                             float *out, size_t shared_tokens);
+int qw4sh_ep_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *back,
+                             const uint32_t *slots, float *y, int shared_started);
+int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum,
+                                float *xscale, void *stream);
+void qw4sh_launch_log_begin(void);
+size_t qw4sh_launch_log(char *out, size_t cap);
+/* Tile kernels (experts_tile.cu): int8 tensor-core products for groups of <= 32 rows. */
+int qw4sh_tile_supported(const QW4ShTensor *w, int mode);
+void qw4sh_set_tile_path(int path);         /* -1 automatic (default), 0 never, 1 every batch of > 4 rows */
+int qw4sh_expert_tiles(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
+                       const uint32_t *row_to_pair, uint32_t k_div, const int8_t *digits, const int *sums, const float *scale,
+                       float *out, uint32_t *status, int ctas, void *stream);
 int qw4sh_prefill_supported(const QW4ShTensor *w, int mode);
 void qw4sh_set_prefill_path(int path);      /* -1 automatic (default), 0 never */
 /* Profiling aid: device array of 64 x 8 bytes (or NULL); CTA 0 of later prefill launches stores the cycles its

@@ -335,32 +335,35 @@ __device__ __forceinline__ void consume_down_tile(const uint8_t *stage, uint32_t
 }
 
 // Two int8 digits per value: v ~ dx * (q1 + q2 / 254), |v| <= 127 dx.  Rounding by the
-// 1.5 * 2^23 trick (no conversion instructions): the integer sits in the low mantissa bits.
-__device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t &hi, uint32_t &lo, int &s1, int &s2) {
+// 1.5 * 2^23 trick (no conversion instructions): the integer sits in the low mantissa bits, so
+// the low byte of the rounded float's bit pattern IS the int8 digit and four of them are packed
+// with byte permutes.  `s` accumulates both digit sums: the first in its low half, the second
+// in its high half (each below 2^15 in magnitude for a 32-column chunk).
+__device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t &hi, uint32_t &lo, int &s) {
     const float vv[4] = {v.x, v.y, v.z, v.w};
     const float magic = 12582912.0f;
-    hi = 0; lo = 0;
+    uint32_t ra[4], rb[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const float r1 = fmaf(vv[j], c.y, magic);
-        const int a = __float_as_int(r1) - 0x4B400000;
         const float q1 = r1 - magic;
-        const float r2 = fmaf(fmaf(-q1, c.x, vv[j]), c.z, magic);
-        const int b = max(-127, min(127, __float_as_int(r2) - 0x4B400000));
-        s1 += a; s2 += b;
-        hi |= ((uint32_t)a & 0xffu) << (8 * j);
-        lo |= ((uint32_t)b & 0xffu) << (8 * j);
+        // second digit clamped to [-127, 127] in the float domain, before the rounding add
+        const float r2 = fmaxf(-127.0f, fminf(127.0f, fmaf(-q1, c.x, vv[j]) * c.z)) + magic;
+        ra[j] = __float_as_uint(r1); rb[j] = __float_as_uint(r2);
     }
+    hi = __byte_perm(__byte_perm(ra[0], ra[1], 0x0040), __byte_perm(ra[2], ra[3], 0x0040), 0x5410);
+    lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
+    s += __dp4a((int)hi, 0x01010101, 0) + (__dp4a((int)lo, 0x01010101, 0) << 16);
 }
 
-// Rows of `k` floats (k % 32 == 0) with known maxima -> digit images, digit sums per 32-column
-// chunk and scales.  CTA-wide; `rows * k / 4` float4 items are dealt to the threads, BATCH per
-// thread in flight (one from shared memory, four from global memory, whose latency they share); eight consecutive lanes cover one chunk.  `amax` holds the maxima on entry
-// and the scales (max / 127, or 0 for an unusable row) on return; `consts` is scratch, one
-// float4 per row.
+// Rows of `k` floats (k % 256 == 0) with known maxima -> digit images, digit sums per 32-column
+// chunk and scales.  A warp takes one 256-column segment of one row at a time: two float4 per
+// lane, eight consecutive lanes cover one chunk, no index arithmetic beyond the segment's.
+// `amax` holds the maxima on entry and the scales (max / 127, or 0 for an unusable row) on
+// return; `consts` is scratch, one float4 per row.
 // The first `NT` threads of the CTA take part and meet at named barrier `BAR` (0 with NT = FT is the
 // CTA barrier).
-template <bool GLOBAL, int BATCH, int NT = FT, int BAR = 0>
+template <bool GLOBAL, int NT = FT, int BAR = 0>
 __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
                                            uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts, uint32_t rotate = 0) {
     auto meet = [] { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(NT) : "memory"); };
@@ -372,34 +375,29 @@ __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pit
         consts[r] = make_float4(usable ? m * (1.0f / 127.0f) : 0.0f, inv, 2.0f * inv * 127.0f, 0.0f);
     }
     meet();
-    // `rotate`: every CTA reads the same rows from L2; starting each at a different item (a multiple of
-    // eight, so a chunk's eight items stay in one warp) keeps them off the same lines at the same time
-    const uint32_t per_row = k >> 2, items = rows * per_row, shift = items ? ((rotate * 5u) % (items >> 3)) << 3 : 0;
+    // `rotate`: every CTA reads the same rows from L2; starting each at a different unit keeps them
+    // off the same lines at the same time
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, segs = k >> 8, units = rows * segs;
 #pragma unroll 1
-    for (uint32_t first = 0; first < items; first += BATCH * NT) {
-        float4 v[BATCH];
-        uint32_t r[BATCH], c4[BATCH];
-        bool live[BATCH];
-#pragma unroll
-        for (int j = 0; j < BATCH; j++) {
-            const uint32_t i0 = first + j * NT + threadIdx.x, i = i0 + shift < items ? i0 + shift : i0 + shift - items;
-            live[j] = i0 < items;
-            r[j] = live[j] ? i / per_row : 0; c4[j] = live[j] ? i % per_row : 0;
-            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live[j]) v[j] = GLOBAL ? __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)r[j] * src_pitch) + c4[j])
-                                       : *(reinterpret_cast<const float4 *>(src + (uint64_t)r[j] * src_pitch) + c4[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < BATCH; j++) {
-            uint32_t hi, lo;
-            int s1 = 0, s2 = 0;
-            digits4(v[j], consts[r[j]], hi, lo, s1, s2);
-            if (live[j]) {
-                *reinterpret_cast<uint32_t *>(dq + (2 * r[j]) * dq_pitch + c4[j] * 4) = hi;
-                *reinterpret_cast<uint32_t *>(dq + (2 * r[j] + 1) * dq_pitch + c4[j] * 4) = lo;
-            }
-            for (int o = 1; o < 8; o <<= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
-            if (live[j] && (c4[j] & 7u) == 0) sums[r[j] * sums_pitch + (c4[j] >> 3)] = make_int2(s1, s2);
+    for (uint32_t u0 = warp; u0 < units; u0 += NT / 32) {
+        const uint32_t u = GLOBAL ? (u0 + rotate * 5u) % units : u0;
+        const uint32_t r = u / segs, seg = u - r * segs;
+        const float4 *from = reinterpret_cast<const float4 *>(src + (uint64_t)r * src_pitch) + seg * 64u + lane;
+        const float4 v0 = GLOBAL ? __ldcg(from) : *from, v1 = GLOBAL ? __ldcg(from + 32) : *(from + 32);
+        const float4 c = consts[r];
+        uint32_t hi0, lo0, hi1, lo1;
+        int s0 = 0, s1 = 0;
+        digits4(v0, c, hi0, lo0, s0);
+        digits4(v1, c, hi1, lo1, s1);
+        uint8_t *out = dq + (2 * r) * dq_pitch + seg * 256u + lane * 4u;
+        *reinterpret_cast<uint32_t *>(out) = hi0; *reinterpret_cast<uint32_t *>(out + 128) = hi1;
+        *reinterpret_cast<uint32_t *>(out + dq_pitch) = lo0; *reinterpret_cast<uint32_t *>(out + dq_pitch + 128) = lo1;
+        for (int o = 1; o < 8; o <<= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); s1 += __shfl_xor_sync(0xffffffffu, s1, o); }
+        if ((lane & 7u) == 0) {
+            const int a0 = (int)(short)(s0 & 0xffff), a1 = (int)(short)(s1 & 0xffff);
+            int2 *to = sums + r * sums_pitch + seg * 8u + (lane >> 3);
+            to[0] = make_int2(a0, (s0 - a0) >> 16);
+            to[4] = make_int2(a1, (s1 - a1) >> 16);
         }
     }
     meet();
@@ -426,7 +424,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
     if (warp < T) {                                                       // row maximum and finiteness
         float m = -CUDART_INF_F;
         bool bad = false;
-#pragma unroll 1
+#pragma unroll 4
         for (uint32_t e = lane; e < E; e += 32) { const float v = zs[warp * FMAXE + e]; bad |= !finite_f32(v); m = fmaxf(m, v); }
         for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         bad = __any_sync(0xffffffffu, bad);
@@ -438,9 +436,10 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
     __syncthreads();
     if (!*flag) return false;
 #pragma unroll 1
-    for (uint32_t i = tid; i < T * E; i += FT) {                           // p = expf(z - max)
-        const uint32_t r = i / E, e = i % E;
-        zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], scratch[r]), exp_table);
+    for (uint32_t r = 0; r < T; r++) {                                     // p = expf(z - max)
+        const float m = scratch[r];
+#pragma unroll 1
+        for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], m), exp_table);
     }
     __syncthreads();
     if (warp < T) {
@@ -459,31 +458,43 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
             }
             sum = __shfl_sync(0xffffffffu, sum, 0);
         } else {
-#pragma unroll 1
+#pragma unroll 4
             for (uint32_t e = lane; e < E; e += 32) sum += p[e];
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
         // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
-        // The row stays in shared memory: sixteen reads per lane and round, no per-lane array.
-#pragma unroll 1
-        for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], sum);      // one division site: the loop stays small
-        __syncwarp();
-        float selected = 0.0f, mine = 0.0f;
-#pragma unroll 1
-        for (uint32_t slot = 0; slot < k; slot++) {
-            uint32_t best = 0, best_e = 0xffffffffu;
+        // The row stays in shared memory; every lane keeps the best two keys of its elements (e = lane,
+        // lane + 32, ...), so a round is two warp reductions, and a lane rescans its elements only
+        // when it wins a second time after its last scan.
+        auto scan2 = [&](uint32_t &b1, uint32_t &e1, uint32_t &b2, uint32_t &e2) {
+            b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu;
 #pragma unroll 4
             for (uint32_t e = lane; e < E; e += 32) {                              // ascending e: the lowest id wins among equals
                 const float v = p[e];
                 const uint32_t key = v < 0.0f ? 0u : __float_as_uint(v) + 1u;
-                if (key > best) { best = key; best_e = e; }
+                if (key > b1) { b2 = b1; e2 = e1; b1 = key; e1 = e; }
+                else if (key > b2) { b2 = key; e2 = e; }
             }
-            const uint32_t top = __reduce_max_sync(0xffffffffu, best);
-            const uint32_t e_win = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0xffffffffu);
+        };
+#pragma unroll 4
+        for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], sum);
+        __syncwarp();
+        uint32_t b1, e1, b2, e2;
+        scan2(b1, e1, b2, e2);
+        bool second_valid = true;
+        float selected = 0.0f, mine = 0.0f;
+#pragma unroll 1
+        for (uint32_t slot = 0; slot < k; slot++) {
+            const uint32_t top = __reduce_max_sync(0xffffffffu, b1);
+            const uint32_t e_win = __reduce_min_sync(0xffffffffu, b1 == top ? e1 : 0xffffffffu);
             const float value = __uint_as_float(top - 1u);
             if (lane == 0) ids_s[warp * k + slot] = e_win;
             if (slot == lane) mine = value;
-            if ((e_win & 31u) == lane) p[e_win] = -1.0f;
+            if ((e_win & 31u) == lane) {                                           // only this lane's elements changed
+                p[e_win] = -1.0f;
+                if (second_valid) { b1 = b2; e1 = e2; second_valid = false; }
+                else { scan2(b1, e1, b2, e2); second_valid = true; }
+            }
             selected = __fadd_rn(selected, value);
         }
         if (lane < k) wts_s[warp * k + lane] = norm ? __fdiv_rn(mine, selected) : mine;
@@ -512,6 +523,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     uint64_t *ringbar = reinterpret_cast<uint64_t *>(smem + p.bars);           // [FW][FNS]
     uint64_t *rowbar = ringbar + FW * FNS;                                     // [FRCH]
     uint64_t *lutbar = rowbar + FRCH;
+    uint64_t *xbar = lutbar + 1;                                               // x rows (phase A), then the logits (phase B)
     uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + p.ids);
     float *wts_s = reinterpret_cast<float *>(smem + p.wts);
     float *misc_f = reinterpret_cast<float *>(smem + p.misc);                  // [0..3] x maxima then scales, [4..7] shared logits, [8..15] scratch
@@ -538,6 +550,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
 #pragma unroll 1
         for (uint32_t i = 0; i < FRCH; i++) fbar_init(&rowbar[i], 1);
         fbar_init(lutbar, 1);
+        fbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 8) misc_f[tid] = 0.0f;
@@ -563,6 +576,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             fbar_expect(lutbar, F_LUT_BYTES);
             fbulk(smem + p.lut, a.lut, F_LUT_BYTES, lutbar);
         }
+        if (lane == 30) fbar_expect(xbar, T * H * 4u);
+        __syncwarp();
+        if (lane < T) fbulk(xf + lane * p.xf_pitch, a.x + (uint64_t)lane * H, H * 4u, xbar);
     } else if (warp == 1) {                                                    // the shared expert's tensors -> L2
 #pragma unroll
         for (uint32_t m = 4; m <= 6; m++) {                                     // shared tensors are far below 4 GB
@@ -572,28 +588,17 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
         }
     }
-    // x -> shared memory (float) with the row maxima, then digits; token rows beyond T stay zero
+    // x -> shared memory (float, one bulk copy per row) with the row maxima, then digits; token rows beyond T stay zero
+    bool alive = fbar_wait(xbar, 0, a.status);
     {
-        constexpr int XL = 6;                                                  // float4 per thread in flight
         float m[FTOK] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-        for (uint32_t first = 0; first < T * (H >> 2); first += XL * FT) {
-            float4 v[XL];
 #pragma unroll
-            for (int j = 0; j < XL; j++) {
-                const uint32_t i0 = first + j * FT + tid, i = (i0 + cta * 24u) % (T * (H >> 2));
-                v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i0 < T * (H >> 2)) v[j] = __ldg(reinterpret_cast<const float4 *>(a.x) + i);
-            }
-#pragma unroll
-            for (int j = 0; j < XL; j++) {
-                const uint32_t i0 = first + j * FT + tid, i = (i0 + cta * 24u) % (T * (H >> 2));
-                if (i0 < T * (H >> 2)) {
-                    const uint32_t r = i / (H >> 2), c4 = i % (H >> 2);
-                    *reinterpret_cast<float4 *>(xf + r * p.xf_pitch + c4 * 16) = v[j];
-                    const float mm = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
-#pragma unroll
-                    for (int q = 0; q < FTOK; q++) if (r == (uint32_t)q) m[q] = fmaxf(m[q], mm);
+        for (int q = 0; q < FTOK; q++) {
+            if ((uint32_t)q < T && alive) {
+#pragma unroll 2
+                for (uint32_t c4 = tid; c4 < (H >> 2); c4 += FT) {
+                    const float4 v = *reinterpret_cast<const float4 *>(xf + q * p.xf_pitch + c4 * 16);
+                    m[q] = fmaxf(m[q], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
             }
         }
@@ -611,10 +616,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     }
     __syncthreads();
     CLOCK(1);
-    if (a.router_mode != 0) digitise_rows<false, 1>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
+    if (a.router_mode != 0) digitise_rows<false>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
     CLOCK(2);
     // router rows
-    bool alive = true;
     if (a.router_mode == 0) {
         // Exact order: every (row, token) logit is one chain of K separately rounded adds, and a lone
         // warp issues too slowly to also load and multiply.  So the other warps write the products
@@ -623,6 +627,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         // 4/5 "buffer drained".
         float *prod = reinterpret_cast<float *>(region + p.prod);              // [2][16 chains][chunk + 4]
         const uint32_t chunk = H / FRCH, ppitch = chunk + 4, chains = n_rows * T;
+        uint8_t *chain_map = smem + p.misc + 640;                              // chain -> router row of this CTA | token << 4
+        if (tid < chains) chain_map[tid] = (uint8_t)((tid / T) | ((tid % T) << 4));
+        __syncthreads();
         if (warp == FW - 1) {
             float sum = 0.0f;
 #pragma unroll 1
@@ -648,9 +655,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             for (uint32_t c = 0; c < FRCH; c++) {
                 if (alive) alive = fbar_wait(&rowbar[c], 0, a.status);           // on a failed wait the products are garbage, the flag is set
                 if (c >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
+                // one unit = 32 float4 of one chain: no index arithmetic beyond a table look-up per unit
 #pragma unroll 1
-                for (uint32_t i = tid; i < chains * (chunk / 4); i += FT - 32) {
-                    const uint32_t ch = i / (chunk / 4), q4 = i % (chunk / 4), j = ch / T, tok = ch % T;
+                for (uint32_t u = warp; u < chains * (chunk / 128); u += FW - 1) {
+                    const uint32_t ch = u / (chunk / 128), q4 = (u % (chunk / 128)) * 32 + lane;
+                    const uint32_t jt = chain_map[ch], j = jt & 15u, tok = jt >> 4;
                     const float4 w4 = *reinterpret_cast<const float4 *>(rows + j * p.row_pitch + c * chunk_bytes + q4 * 16);
                     const float4 x4 = *reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch + c * chunk_bytes + q4 * 16);
                     *reinterpret_cast<float4 *>(prod + ((c & 1u) * 16 + ch) * ppitch + q4 * 4) =
@@ -659,7 +668,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 asm volatile("bar.arrive %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
                 // both product buffers are full and the chain warp is busy with them: the digit image of x is
                 // built here, under the chain
-                if (c == 1) digitise_rows<false, 1, FT - 32, 6>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum,
+                if (c == 1) digitise_rows<false, FT - 32, 6>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum,
                                                               H >> 5, xconsts);
             }
         }
@@ -692,14 +701,24 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
 
     // ================================ phase B ================================
     float *zs = reinterpret_cast<float *>(region + p.zs);
+    const bool bulk_logits = (E & 3u) == 0;                                   // whole 16-byte pieces: one bulk copy per token row
+    if (bulk_logits) {
+        if (warp == 0 && alive) {
+            asm volatile("fence.proxy.async;" ::: "memory");                      // generic-proxy writes (the logits; phase A's use of this memory) before the copy
+            if (lane == 0) fbar_expect(xbar, T * E * 4u);
+            __syncwarp();
+            if (lane < T) fbulk(zs + lane * FMAXE, a.logits + (uint64_t)lane * E, E * 4u, xbar);
+        }
+    } else {
 #pragma unroll 1
-    for (uint32_t i0 = tid; i0 < T * E; i0 += FT) {                           // each CTA starts somewhere else in the array
-        const uint32_t i = (i0 + cta * 56u) % (T * E);
-        zs[(i / E) * FMAXE + (i % E)] = __ldcg(a.logits + i);
+        for (uint32_t r = 0; r < T; r++)
+#pragma unroll 1
+            for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = __ldcg(a.logits + (uint64_t)r * E + e);
     }
     if (tid < T) misc_f[4 + tid] = __ldcg(a.shared_logit + tid);
 #pragma unroll 1
     for (uint32_t i = tid; i < FMAXE; i += FT) tokmask[i] = 0;
+    if (bulk_logits && alive) alive = fbar_wait(xbar, 1, a.status);            // second use of this barrier: phase parity 1
     __syncthreads();
     CLOCK(5);
     const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status);
@@ -864,16 +883,49 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &bar[at % FNS], lane);
             else issue_down_tile<RT>(a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes, H, I >> 8, tile * 16, stage, &bar[at % FNS], lane);
         };
-        fproxy_fence();
-        if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
         // digit images of the activation rows: pairs first, then the shared expert's rows
 #pragma unroll 1
         for (uint32_t r = tid; r < rows_c; r += FT) ascale[r] = __uint_as_float(__ldcg(amax_g + r));
-        __syncthreads();
         float4 *aconsts = reinterpret_cast<float4 *>(region + p.aconst);
-        digitise_rows<true, 4>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts, cta);
-        digitise_rows<true, 4>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
-                            aconsts + pairs, cta);
+        // The rows were written by other CTAs a moment ago and every CTA needs all of them.  Read with ordinary
+        // loads they cost a chain of L2 round trips; when they fit the (still idle) tile ring they come in with
+        // one bulk copy per row instead and are digitised out of shared memory.
+        const bool staged = rows_c * imax * 4u <= FW * FNS * FSTAGE && ((I | IS) & 3u) == 0;
+        if (staged) {
+            float *stage = reinterpret_cast<float *>(region + p.tiles);
+            bool ok = __syncthreads_and(alive);                                    // CTA-uniform from here on: the digitiser meets at CTA barriers
+            if (ok) {
+                if (warp == 0) {
+                    asm volatile("fence.proxy.async;" ::: "memory");              // the rows were written through the generic proxy
+                    if (lane == 0) fbar_expect(&rowbar[0], (pairs * I + T * IS) * 4u);
+                    __syncwarp();
+#pragma unroll 1
+                    for (uint32_t r = lane; r < rows_c; r += 32) {
+                        if (r < pairs) fbulk(stage + r * I, a.act + (uint64_t)r * I, I * 4u, &rowbar[0]);
+                        else fbulk(stage + pairs * I + (r - pairs) * IS, a.shared_act + (uint64_t)(r - pairs) * IS, IS * 4u, &rowbar[0]);
+                    }
+                }
+                ok = __syncthreads_and(fbar_wait(&rowbar[0], 1, a.status));         // second use of this barrier: phase parity 1
+            }
+            if (ok) {
+                if (I == IS) digitise_rows<false>(stage, I, rows_c, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
+                else {
+                    digitise_rows<false>(stage, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
+                    digitise_rows<false>(stage + pairs * I, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5),
+                                            imax >> 5, aconsts + pairs);
+                }
+            }
+            alive = ok;
+            fproxy_fence();                                                        // the ring goes back to the bulk copies
+            if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
+        } else {
+            fproxy_fence();
+            if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
+            __syncthreads();
+            digitise_rows<true>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts, cta);
+            digitise_rows<true>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
+                                   aconsts + pairs, cta);
+        }
         CLOCK(11);
         uint32_t n = 0;
 #pragma unroll 1

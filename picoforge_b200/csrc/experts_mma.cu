@@ -422,11 +422,11 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
 // Two int8 digits per activation: x ~ dx * (q1 + q2 / 254), dx = max|x| / 127 per row.
 // One CTA per row.  Also writes the negated digits (IQ2_XXS sign correction) and the per-chunk
 // digit sums (Q4_K min term).  k is a multiple of 32.
-__global__ void __launch_bounds__(512) quantize_rows_kernel(const float *__restrict__ x, uint32_t k, int8_t *__restrict__ xq,
+__global__ void __launch_bounds__(512) quantize_rows_kernel(const float *__restrict__ x, uint32_t pitch, uint32_t k, int8_t *__restrict__ xq,
                                                             int8_t *__restrict__ xneg, int *__restrict__ xsum, float *__restrict__ xscale) {
     __shared__ float red[16];
     const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const float *src = x + (uint64_t)row * k;
+    const float *src = x + (uint64_t)row * pitch;
     float amax = 0.0f;
     for (uint32_t c = tid; c < k; c += 512) amax = fmaxf(amax, fabsf(src[c]));
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -576,10 +576,15 @@ extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTen
 extern "C" int qw4sh_prepare_mma(void) { return lut_image() ? 0 : -1; }
 extern "C" const uint8_t *qw4sh_lut_image(void) { return lut_image(); }
 
-extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {
+// Rows of k floats, `pitch` floats apart.
+extern "C" int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum,
+                                           float *xscale, void *stream) {
     if (!rows) return 0;
-    quantize_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(x, k, xq, xneg, xsum, xscale);
+    quantize_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale);
     return qw4sh_note_launch("quantize_rows_kernel");
+}
+extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {
+    return qw4sh_quantize_rows_pitched(x, k, rows, k, xq, xneg, xsum, xscale, stream);
 }
 extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,
                              uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, void *stream) {

@@ -30,13 +30,34 @@ static int fail(cudaError_t e, const char *where) {
     return (int)e ? (int)e : -1;
 }
 #define CU(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(e_, #call); } while (0)
-#define LAUNCHED(name) do { __sync_fetch_and_add(&g_launches, 1ull); cudaError_t e_ = cudaGetLastError(); \
+// Names of the kernels launched since qw4sh_launch_log_begin (string literals; the first LOG_CAP are kept).
+static const unsigned LOG_CAP = 512;
+static const char *g_log[LOG_CAP];
+static unsigned g_log_n = LOG_CAP;                // full: logging off until the first begin
+static inline void log_launch(const char *name) {
+    __sync_fetch_and_add(&g_launches, 1ull);
+    const unsigned at = g_log_n;
+    if (at < LOG_CAP) { g_log[at] = name; g_log_n = at + 1; }
+}
+#define LAUNCHED(name) do { log_launch(name); cudaError_t e_ = cudaGetLastError(); \
     if (e_ != cudaSuccess) return fail(e_, name); } while (0)
 
 extern "C" int qw4sh_note_launch(const char *name) {
-    __sync_fetch_and_add(&g_launches, 1ull);
+    log_launch(name);
     cudaError_t e = cudaGetLastError();
     return e != cudaSuccess ? fail(e, name) : 0;
+}
+extern "C" void qw4sh_launch_log_begin(void) { g_log_n = 0; }
+// Comma-separated names since the last begin, truncated to `cap` bytes; returns the number of launches logged.
+extern "C" size_t qw4sh_launch_log(char *out, size_t cap) {
+    size_t at = 0;
+    const unsigned n = g_log_n < LOG_CAP ? g_log_n : LOG_CAP;
+    for (unsigned i = 0; i < n && cap; i++) {
+        for (const char *c = g_log[i]; *c && at + 2 < cap; c++) out[at++] = *c;
+        if (i + 1 < n && at + 2 < cap) out[at++] = ',';
+    }
+    if (cap) out[at] = 0;
+    return n;
 }
 
 static bool g_constants_ready[64] = {false};
@@ -236,6 +257,63 @@ __global__ void __launch_bounds__(32 * TT) router_exact_kernel(DevTensor router,
         }
         __syncthreads();
     }
+    if (t < tokens && e <= experts) {
+        if (!finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
+        if (e < experts) logits[(uint64_t)t * experts + e] = sum;
+        else shared_logit[t] = sum;
+    }
+}
+
+// Exact, mid-sized batches: 16 router rows x 16 tokens per CTA, one serial chain per thread.  Both tiles go
+// through a four-stage cp.async ring in chunks of 128 columns (three chunks, about 2000 cycles of chain, are
+// in flight ahead of the adds: more than a DRAM round trip), and every thread reads four columns of its row
+// and of its token with one 128-bit load each (row pitch 132 floats: the eight lanes of a quarter warp hit
+// eight different 16-byte bank groups), so a chain step costs 2.5 instructions.
+constexpr int RC_ROWS = 16, RC_K = 128, RC_PITCH = 132, RC_STAGES = 4;
+constexpr size_t RC_SMEM = (size_t)RC_STAGES * 2 * RC_ROWS * RC_PITCH * sizeof(float);
+__device__ __forceinline__ void rc_copy16(void *dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__global__ void __launch_bounds__(256) router_chain_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
+                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
+    extern __shared__ __align__(16) uint8_t rc_smem[];
+    float (*tile)[2 * RC_ROWS][RC_PITCH] = reinterpret_cast<float (*)[2 * RC_ROWS][RC_PITCH]>(rc_smem);   // rows 0-15 router rows, 16-31 tokens
+    const uint32_t experts = router.n_out, K = router.k_logical, tid = threadIdx.x;
+    const uint32_t row = tid >> 4, col = (tid & 15u) * 4;                        // as loader: two 16-byte pieces of each tile
+    const uint32_t le = blockIdx.x * RC_ROWS + row, lt = min(blockIdx.y * RC_ROWS + row, tokens - 1);
+    const float *wsrc = (le < experts ? (const float *)(router.data + (uint64_t)le * router.row_bytes) : (const float *)srouter.data) + col;
+    const float *xsrc = x + (uint64_t)lt * K + col;
+    const uint32_t chunks = K / RC_K;
+    auto load = [&](uint32_t c) {
+        if (c < chunks) {
+#pragma unroll
+            for (int half = 0; half < RC_K; half += 64) {
+                rc_copy16(&tile[c % RC_STAGES][row][half + col], wsrc + c * RC_K + half);
+                rc_copy16(&tile[c % RC_STAGES][RC_ROWS + row][half + col], xsrc + c * RC_K + half);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (uint32_t c = 0; c + 1 < RC_STAGES; c++) load(c);
+    const uint32_t e_l = tid >> 4, t_l = tid & 15u;                              // as worker: chain (row e_l, token t_l)
+    float sum = 0.0f;
+    for (uint32_t c = 0; c < chunks; c++) {
+        load(c + RC_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(RC_STAGES - 1) : "memory");
+        __syncthreads();
+        const float4 *w4 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][e_l]);
+        const float4 *x4 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][RC_ROWS + t_l]);
+#pragma unroll
+        for (int i = 0; i < RC_K / 4; i++) {
+            const float4 w = w4[i], v = x4[i];
+            sum = __fadd_rn(sum, __fmul_rn(w.x, v.x));
+            sum = __fadd_rn(sum, __fmul_rn(w.y, v.y));
+            sum = __fadd_rn(sum, __fmul_rn(w.z, v.z));
+            sum = __fadd_rn(sum, __fmul_rn(w.w, v.w));
+        }
+        __syncthreads();
+    }
+    const uint32_t e = blockIdx.x * RC_ROWS + e_l, t = blockIdx.y * RC_ROWS + t_l;
     if (t < tokens && e <= experts) {
         if (!finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
         if (e < experts) logits[(uint64_t)t * experts + e] = sum;
@@ -574,11 +652,20 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
     if (!s_last) return;
     if (e == 0) n_groups[2] = 0;                                // ready for the next call
     __threadfence();
+    // An expert takes a token at most once, so its list is a 64-bit set of tokens (tokens <= 64) plus the slot it
+    // has in each: thread q marks pair q, thread e then walks only its own set bits, in ascending token order.
     const uint32_t pairs = tokens * k;
-    for (uint32_t q = e; q < pairs; q += blockDim.x) sids[q] = __ldcg(ids + q);
+    __shared__ unsigned long long s_tokens[512];
+    s_tokens[e] = 0ull;
     __syncthreads();
-    uint32_t count = 0;
-    if (e < experts) for (uint32_t q = 0; q < pairs; q++) count += sids[q] == e;
+    for (uint32_t q = e; q < pairs; q += blockDim.x) {
+        const uint32_t id = __ldcg(ids + q);
+        sids[q] = id;
+        if (id < experts) atomicOr(&s_tokens[id], 1ull << (q / k));
+    }
+    __syncthreads();
+    const unsigned long long my_tokens = e < experts ? s_tokens[e] : 0ull;
+    const uint32_t count = __popcll(my_tokens);
     // packed: bits 0-11 rows, 12-21 groups of four, 22-31 non-empty flag
     const uint32_t packed = count | (((count + 3) >> 2) << 12) | ((count ? 1u : 0u) << 22);
     uint32_t scan = packed;
@@ -599,8 +686,12 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
             active[1 + arank] = e;
             for (uint32_t j = 0; j < (count + 3) >> 2; j++) groups[gfirst + j] = Group4{e, first + 4 * j, min(4u, count - 4 * j), 0};
             uint32_t cursor = first;
-            for (uint32_t q = 0; q < pairs; q++)
-                if (sids[q] == e) { pair_to_row[q] = cursor; row_to_pair[cursor] = q; cursor++; }
+            for (unsigned long long rest = my_tokens; rest; rest &= rest - 1) {
+                const uint32_t tok = __ffsll((long long)rest) - 1;
+                uint32_t q = tok * k;
+                while (sids[q] != e) q++;                           // the slot this expert has in the token (it is there: the bit is set)
+                pair_to_row[q] = cursor; row_to_pair[cursor] = q; cursor++;
+            }
         }
     }
     if (e == blockDim.x - 1) {                                   // inclusive total sits in the last thread
@@ -1090,6 +1181,12 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (mode == 0) router_gemm_kernel<true><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         else router_gemm_kernel<false><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         LAUNCHED("router_gemm_kernel");
+    } else if (mode == 0 && tokens > 4 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
+               ((uintptr_t)router.data & 15u) == 0 && ((uintptr_t)srouter.data & 15u) == 0) {
+        if (allow_smem(router_chain_kernel, RC_SMEM)) return -1;
+        router_chain_kernel<<<dim3((rows + RC_ROWS - 1) / RC_ROWS, (unsigned)((tokens + RC_ROWS - 1) / RC_ROWS)), 256, RC_SMEM, stream>>>(
+            router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        LAUNCHED("router_chain_kernel");
     } else if (mode == 0) {
         if (tokens <= 1) {
             router_exact_kernel<1><<<dim3((rows + 31) / 32, (unsigned)tokens), dim3(32, 1), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
@@ -1253,6 +1350,23 @@ static bool prefill_path(const QW4ShLayer *layer, size_t tokens) {
     return layer->inter % 32 == 0 && layer->shared_inter % 32 == 0;
 }
 
+// Batches of more than four rows (and any batch the one-kernel decode or the tcgen05 prefill cannot take) run the
+// expert products on the tile kernels: weight fragments built once per 32-row group instead of once per 4 rows.
+static int g_tile_path = -1;                       // -1 automatic, 0 never, 1 whenever the types allow
+extern "C" void qw4sh_set_tile_path(int path) { g_tile_path = path; }
+static bool tile_types(const QW4ShLayer *layer) {
+    return layer->w[1].type == layer->w[2].type && qw4sh_tile_supported(&layer->w[1], 0) && qw4sh_tile_supported(&layer->w[2], 0) &&
+           qw4sh_tile_supported(&layer->w[3], 1);
+}
+static bool tile_path(const QW4ShLayer *layer, size_t tokens) {
+    if (g_tile_path == 0 || g_expert_path == 0 || (g_tile_path > 0 && tokens <= 4)) return false;
+    // automatic: batches that neither the four-row kernels (<= 64 rows, Q4_K / IQ2_XXS) nor the tcgen05 prefill
+    // (Q4_K) can take: IQ2_XXS beyond 64 rows, Q2_K at any size; 1: every batch of more than four rows
+    if (g_tile_path < 0 && (tokens <= MMA_MAX_TOKENS ? mma_path(layer, tokens) : prefill_path(layer, tokens))) return false;
+    return tile_types(layer) && layer->w[4].type == layer->w[5].type && qw4sh_tile_supported(&layer->w[4], 0) &&
+           qw4sh_tile_supported(&layer->w[5], 0) && qw4sh_tile_supported(&layer->w[6], 1);
+}
+
 static cudaStream_t g_side_stream[64] = {nullptr};
 static cudaEvent_t g_side_event[64][4] = {{nullptr}};
 static int side_stream(cudaStream_t *stream, cudaEvent_t **events) {
@@ -1282,7 +1396,8 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
     const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
     if (!timed && g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count()))
         return qw4sh_fused_decode(layer, work, x, y, tokens, ids_out, weights_out, router_mode, sm_count());
-    const bool mma = mma_path(layer, tokens);
+    const bool tile = tile_path(layer, tokens);
+    const bool mma = tile || mma_path(layer, tokens);
     const bool fused_route = mma && T <= 64 && E <= 512 && k <= E && T * k < 4096;
     int rc, stage = 0;
 #define STAGE_MARK() do { if (timed) CU(cudaEventRecord(g_stage_event[stage++], stream)); } while (0)
@@ -1304,17 +1419,25 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         if (overlap) CU(cudaEventRecord(ev[1], side));
     }
     const int ctas = sm_count();
+    // expert products of one stage: tile kernels over groups of <= 32 rows, or the 4-row grouped kernel
+    auto products = [&](int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, bool shared, const uint32_t *r2p, uint32_t k_div, const int8_t *q,
+                        const int8_t *neg, const int *sums, const float *scale, float *out, cudaStream_t strm) -> int {
+        if (tile)
+            return qw4sh_expert_tiles(mode, w0, w1, shared ? work->shared_groups32 : work->groups32, work->n_groups32 + (shared ? 1 : 0), r2p, k_div,
+                                      q, sums, scale, out, work->status, ctas, strm);
+        return qw4sh_grouped_mma(mode, w0, w1, shared ? (void *)shared_groups : work->groups, work->n_groups + (shared ? 1 : 0), r2p, k_div, q, neg,
+                                 sums, scale, out, work->status, ctas, strm);
+    };
     auto shared_branch = [&](int which) -> int {
         if (which == 0) {
-            if (!fused_route && (rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, side))) return rc;
+            if (tile) { if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, side))) return rc; }
+            else if (!fused_route && (rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, side))) return rc;
             if (!STEP(4)) return 0;
-            return qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], shared_groups, work->n_groups + 1, nullptr, 1, work->xq, work->xneg,
-                                     work->xsum, work->xscale, work->shared_act, work->status, ctas, side);
+            return products(0, &layer->w[4], &layer->w[5], true, nullptr, 1, work->xq, work->xneg, work->xsum, work->xscale, work->shared_act, side);
         }
         if (STEP(7) && (rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
         if (!STEP(8)) return 0;
-        return qw4sh_grouped_mma(1, &layer->w[6], nullptr, shared_groups, work->n_groups + 1, nullptr, 1, work->sq, work->sneg, work->ssum,
-                                 work->sscale, work->shared_out, work->status, ctas, side);
+        return products(1, &layer->w[6], nullptr, true, nullptr, 1, work->sq, work->sneg, work->ssum, work->sscale, work->shared_out, side);
     };
     if (STEP(0) && (rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, stream))) return rc;
     STAGE_MARK();
@@ -1332,23 +1455,24 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
             if ((rc = qw4sh_group_large(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
                                         work->dispatch_scratch, work->status, stream))) return rc;
         } else if ((rc = qw4sh_group(E, k, tokens, work->ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
-        if (mma && (rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if (mma && !tile && (rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         STAGE_MARK();
     }
+    if (tile && (rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
     if (mma) {
         if (overlap) {
             if ((rc = shared_branch(0)) || (rc = shared_branch(1))) return rc;
             CU(cudaEventRecord(ev[3], side));
             CU(cudaStreamWaitEvent(stream, ev[1], 0));
         }
-        if (STEP(3) && (rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq,
-                                    work->xneg, work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if (STEP(3) && (rc = products(0, &layer->w[1], &layer->w[2], false, work->row_to_pair, k, work->xq, work->xneg, work->xsum, work->xscale,
+                                      work->act, stream))) return rc;
         STAGE_MARK();
         if (!overlap && (rc = shared_branch(0))) return rc;
         STAGE_MARK();
         if (STEP(5) && (rc = qw4sh_quantize_rows(work->act, T * k, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        if (STEP(6) && (rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
-                                    work->asum, work->ascale, work->out, work->status, ctas, stream))) return rc;
+        if (STEP(6) && (rc = products(1, &layer->w[3], nullptr, false, work->row_to_pair, 1, work->aq, work->aneg, work->asum, work->ascale,
+                                      work->out, stream))) return rc;
         STAGE_MARK();
         if (!overlap && (rc = shared_branch(1))) return rc;
         STAGE_MARK();
@@ -1423,6 +1547,16 @@ extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *w
     } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
     const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
                      qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) && (g_expert_path == 1 || rows <= 2048);
+    if ((g_tile_path > 0 ? rows > 4 : g_tile_path < 0 && (rows > 2048 || !mma)) && g_expert_path != 0 && tile_types(layer)) {
+        const int ctas = sm_count();
+        if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(rows_x, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, 1, work->xq, work->xsum,
+                                     work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
+        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, work->aq, work->asum,
+                                  work->ascale, out, work->status, ctas, stream);
+    }
     if (mma) {
         const int ctas = sm_count();
         if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
@@ -1460,6 +1594,106 @@ extern "C" int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *w
     if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, shared_groups, work->n_groups + 1, nullptr, 1, work->sq, work->sneg, work->ssum,
                                 work->sscale, work->shared_out, work->status, ctas, stream))) return rc;
     return qw4sh_combine(pair_out, work->shared_out, work->weights, work->shared_logit, layer->top_k, H, T, y, nullptr, work->status, stream);
+}
+
+// ---- expert-parallel pieces with packed messages (ep_exchange.cu) and the shared expert under the exchange ----
+// The shared expert needs only x.  Started here on the side stream, right after the routing, it runs while the
+// rows travel; its x digits live in the LAST rows of the quantisation buffers, which the routed experts (rows
+// 0 .. R-1 of the same buffers) leave alone as long as R + tokens <= capacity.
+extern "C" int qw4sh_ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens) {
+    if (!tokens) return 0;
+    if (tokens > work->cap) return fail(cudaErrorInvalidValue, "token count beyond the workspace");
+    if (layer->w[4].type != layer->w[5].type || !qw4sh_mma_supported(&layer->w[4], 0) || !qw4sh_mma_supported(&layer->w[5], 0) ||
+        !qw4sh_mma_supported(&layer->w[6], 1))
+        return fail(cudaErrorNotSupported, "expert-parallel combine needs a Q4_K or IQ2_XXS shared expert");
+    cudaStream_t stream = (cudaStream_t)work->stream, side;
+    cudaEvent_t *ev;
+    int rc;
+    if ((rc = side_stream(&side, &ev))) return rc;
+    const uint32_t T = (uint32_t)tokens, H = layer->hidden;
+    const size_t off = work->cap - tokens;
+    int8_t *xq = work->xq + off * 2 * H, *xneg = work->xneg + off * 2 * H;
+    int *xsum = work->xsum + off * (H / 32) * 2;
+    float *xscale = work->xscale + off;
+    const int ctas = sm_count();
+    CU(cudaEventRecord(ev[0], stream));
+    CU(cudaStreamWaitEvent(side, ev[0], 0));
+    if ((rc = qw4sh_build_dense_groups(T, work->shared_groups, work->n_groups + 3, side))) return rc;
+    if ((rc = qw4sh_quantize_rows(x, T, H, xq, xneg, xsum, xscale, side))) return rc;
+    if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 3, nullptr, 1, xq, xneg, xsum, xscale,
+                                work->shared_act, work->status, ctas, side))) return rc;
+    if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
+    if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 3, nullptr, 1, work->sq, work->sneg, work->ssum,
+                                work->sscale, work->shared_out, work->status, ctas, side))) return rc;
+    CU(cudaEventRecord(ev[3], side));
+    return 0;
+}
+
+// Rows as they arrived: `rows` message slots (hidden floats, the local expert id, padding).  `shared_tokens` > 0: a
+// shared-expert branch of that many tokens may still be running on the side stream.
+extern "C" int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg, size_t rows, uint32_t local_experts,
+                                        float *out, size_t shared_tokens) {
+    if (!rows) return 0;
+    if (ensure_constants()) return -1;
+    if (rows > work->cap) return fail(cudaErrorInvalidValue, "more rows than the workspace holds");
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t R = (uint32_t)rows, H = layer->hidden, pitch = qw4sh_ep_pitch(H);
+    int rc;
+    if (shared_tokens && rows + shared_tokens > work->cap) {              // the tail rows are in use: let the shared expert finish first
+        cudaStream_t side; cudaEvent_t *ev;
+        if ((rc = side_stream(&side, &ev))) return rc;
+        CU(cudaStreamWaitEvent(stream, ev[3], 0));
+    }
+    uint32_t *local_ids = work->ids;
+    if ((rc = qw4sh_ep_ids(msg, H, R, local_ids, stream))) return rc;
+    if (rows > 64 && work->dispatch_scratch) {
+        if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                                    work->dispatch_scratch, work->status, stream))) return rc;
+    } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
+    const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
+                     qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1);
+    const int ctas = sm_count();
+    if ((g_tile_path > 0 || (g_tile_path < 0 && (rows > 2048 || !mma))) && g_expert_path != 0 && tile_types(layer)) {
+        if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_pitched(msg, pitch, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, 1, work->xq, work->xsum,
+                                     work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
+        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, work->aq, work->asum,
+                                  work->ascale, out, work->status, ctas, stream);
+    }
+    if (mma) {
+        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_pitched(msg, pitch, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xneg,
+                                    work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
+        return qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
+                                 work->asum, work->ascale, out, work->status, ctas, stream);
+    }
+    // any other format: rows made contiguous in the staging buffer, CUDA-core kernels
+    CU(cudaMemcpy2DAsync(work->x, (size_t)H * 4, msg, (size_t)pitch * 4, (size_t)H * 4, R, cudaMemcpyDeviceToDevice, stream));
+    const uint32_t groups = R < local_experts ? R : local_experts;
+    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), work->x, H, work->offsets, work->row_to_pair, work->active, 1, R,
+                             groups, work->act, work->status, stream))) return rc;
+    return launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, nullptr, local_ids, nullptr, nullptr, 1, R, out, nullptr,
+                       work->status, stream);
+}
+
+// back: the returned outputs, one row of `hidden` floats per slot this rank sent; slots: slot of every pair.
+extern "C" int qw4sh_ep_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *back,
+                                        const uint32_t *slots, float *y, int shared_started) {
+    if (!tokens) return 0;
+    if (ensure_constants()) return -1;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t T = (uint32_t)tokens, H = layer->hidden;
+    int rc;
+    if (!shared_started && (rc = qw4sh_ep_shared_begin(layer, work, x, tokens))) return rc;
+    if ((rc = qw4sh_ep_gather(back, H, slots, T * layer->top_k, work->out, stream))) return rc;
+    cudaStream_t side; cudaEvent_t *ev;
+    if ((rc = side_stream(&side, &ev))) return rc;
+    CU(cudaStreamWaitEvent(stream, ev[3], 0));
+    return qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, layer->top_k, H, T, y, nullptr, work->status, stream);
 }
 
 // The stream every workspace created afterwards (and every existing one, through

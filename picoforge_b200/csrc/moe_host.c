@@ -32,6 +32,8 @@ struct Qwen4MoeWork {
     Qwen4Moe *owner;
     size_t cap, chunk, host_bytes, device_bytes;
     bool busy, failed;
+    bool status_clean;            /* the device status words are known to be zero (last read back as zero, nothing launched since) */
+    size_t shared_tokens;         /* expert-parallel step: tokens of a shared-expert branch started by the pack call */
     QW4ShWork d;
     void *device_block;           /* one allocation carved into d.* */
     uint32_t *status_host;        /* pinned [4] */
@@ -382,6 +384,7 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *m, const float *x_dev, floa
     if (tokens && (!x_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
     if (m->local_experts != m->c.experts) return report(err, QW4_BAD_STATE, "sharded handle: use the route/experts/combine calls");
     use_current_stream(w);
+    w->status_clean = false;
     const size_t h = m->c.hidden_size, k = m->c.top_k;
     for (size_t start = 0; start < tokens; start += w->chunk) {
         const size_t n = tokens - start < w->chunk ? tokens - start : w->chunk;
@@ -401,6 +404,7 @@ static Qwen4Status piece_checks(const Qwen4Moe *m, Qwen4MoeWork *w, size_t rows,
     if (w->busy) return report(err, QW4_BUSY, "workspace executing");
     if (rows > w->chunk) return report(err, QW4_CAPACITY, "batch exceeds the workspace (cap and 2048-row chunk)");
     use_current_stream(w);
+    w->status_clean = false;
     return QW4_OK;
 }
 Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, uint32_t *ids_dev, float *weights_dev,
@@ -425,6 +429,43 @@ Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *m, const float *x_dev, size
     TRY(piece_checks(m, w, tokens, err));
     if (tokens && (!x_dev || !pair_out_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
     if (qw4sh_combine_forward(&m->layer, &w->d, x_dev, tokens, pair_out_dev, y_dev)) return cuda_failure(err, "combine launch");
+    return report(err, QW4_OK, "");
+}
+/* The same three steps with packed exchange messages and the shared expert under the exchange. */
+size_t qw4cu_ep_slot_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_pitch((uint32_t)m->c.hidden_size) : 0; }
+Qwen4Status qw4cu_moe_ep_route_pack_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, size_t slots_per_rank, float *msg_dev,
+                                           uint32_t *slots_dev, uint32_t *ids_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens, err));
+    if (tokens && (!x_dev || !msg_dev || !slots_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (!m->local_experts || m->c.experts % m->local_experts) return report(err, QW4_BAD_STATE, "expert shards must be equal blocks");
+    const uint32_t world = (uint32_t)(m->c.experts / m->local_experts);
+    if (world > 64) return report(err, QW4_INVALID_ARGUMENT, "more than 64 ranks");
+    if (slots_per_rank < tokens * m->c.top_k) return report(err, QW4_CAPACITY, "a destination block must hold every pair of this rank");
+    if (qw4sh_route_forward(&m->layer, &w->d, x_dev, tokens, current_router_mode())) return cuda_failure(err, "route launch");
+    if (qw4sh_ep_pack(x_dev, (uint32_t)tokens, (uint32_t)m->c.top_k, (uint32_t)m->c.hidden_size, w->d.ids, m->local_experts, world,
+                      (uint32_t)slots_per_rank, msg_dev, slots_dev, w->d.status, w->d.stream)) return cuda_failure(err, "pack launch");
+    const size_t id_bytes = tokens * m->c.top_k * 4;
+    if (tokens && ids_dev && qw4sh_memcpy2d_async(ids_dev, id_bytes, w->d.ids, id_bytes, id_bytes, 1, 2, w->d.stream)) return cuda_failure(err, "ids copy");
+    w->shared_tokens = 0;
+    if (qw4sh_ep_shared_begin(&m->layer, &w->d, x_dev, tokens)) return cuda_failure(err, "shared expert launch");
+    w->shared_tokens = tokens;
+    return report(err, QW4_OK, "");
+}
+Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *m, const float *msg_dev, size_t rows, float *out_dev, Qwen4MoeWork *w,
+                                        Qwen4Error *err) {
+    TRY(piece_checks(m, w, rows, err));
+    if (rows && (!msg_dev || !out_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (qw4sh_ep_experts_forward(&m->layer, &w->d, msg_dev, rows, m->local_experts, out_dev, w->shared_tokens))
+        return cuda_failure(err, "experts launch");
+    return report(err, QW4_OK, "");
+}
+Qwen4Status qw4cu_moe_ep_combine_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, const float *back_dev,
+                                        const uint32_t *slots_dev, float *y_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens, err));
+    if (tokens && (!x_dev || !back_dev || !slots_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    const int started = w->shared_tokens == tokens && tokens != 0;
+    w->shared_tokens = 0;
+    if (qw4sh_ep_combine_forward(&m->layer, &w->d, x_dev, tokens, back_dev, slots_dev, y_dev, started)) return cuda_failure(err, "combine launch");
     return report(err, QW4_OK, "");
 }
 int qw4cu_set_stream(void *cuda_stream) { return qw4sh_set_stream(cuda_stream); }
@@ -488,7 +529,8 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
         float *pin_x = (float *)w->pin, *pin_y = (float *)(w->pin + x_bytes);
         uint32_t *pin_ids = (uint32_t *)(w->pin + 2 * x_bytes);
         float *pin_w = (float *)(w->pin + 2 * x_bytes + r_bytes);
-        int rc = status_clear(w);
+        int rc = w->status_clean ? 0 : status_clear(w);
+        w->status_clean = false;
         if (small) {
             for (size_t row = 0; row < n; row++) memcpy(pin_x + row * h, xs + row * (x.stride_bytes[0] / 4), h * 4);
             rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, pin_x, h * 4, h * 4, n, 1, w->d.stream);
@@ -505,6 +547,7 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
         if (!rc) rc = qw4sh_stream_sync(w->d.stream);
         if (rc) { st = cuda_failure(err, "layer execution"); break; }
         if ((st = status_result(w, err)) != QW4_OK) break;
+        w->status_clean = true;
         if (small) {
             for (size_t row = 0; row < n; row++) {
                 memcpy(ys + row * (y.stride_bytes[0] / 4), pin_y + row * h, h * 4);
@@ -673,6 +716,8 @@ int qw4cu_device_count(void) { return qw4sh_device_count(); }
 int qw4cu_set_device(int device) { return qw4sh_set_device(device); }
 const char *qw4cu_last_error(void) { return qw4sh_last_error(); }
 uint64_t qw4cu_launch_count(void) { return qw4sh_launch_count(); }
+void qw4cu_launch_log_begin(void) { qw4sh_launch_log_begin(); }
+size_t qw4cu_launch_log(char *out, size_t cap) { return qw4sh_launch_log(out, cap); }
 void *qw4cu_malloc(size_t bytes) { return qw4sh_malloc(bytes); }
 void qw4cu_free(void *p) { qw4sh_free(p); }
 void *qw4cu_host_alloc(size_t bytes) { return qw4sh_host_alloc(bytes); }
@@ -688,6 +733,7 @@ void qw4cu_set_expert_path(int path) { qw4sh_set_expert_path(path); }
 void qw4cu_set_only_step(int step) { qw4sh_set_only_step(step); }
 void qw4cu_set_fused_decode(int mode) { qw4sh_set_fused_decode(mode); }
 void qw4cu_set_prefill_path(int path) { qw4sh_set_prefill_path(path); }
+void qw4cu_set_tile_path(int path) { qw4sh_set_tile_path(path); }
 void qw4cu_prefill_debug(void *device_words) { qw4sh_prefill_debug(device_words); }
 int qw4cu_decode_phase_clocks(const Qwen4MoeWork *w, uint64_t clocks[16]) { return w ? qw4sh_fused_phase_clocks(&w->d, clocks) : -1; }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }

@@ -8,10 +8,17 @@ are data-parallel.  One layer step on a rank:
     ->  experts (rows received from every rank)  ->  combine all-to-all (outputs back)
     ->  slot-order weighted sum + shared expert (own tokens)
 
-The three compute pieces are the library's `qw4cu_moe_{route,experts,combine}_device`; this file
-only plans and moves rows (torch tensors as device buffers, `torch.distributed` all-to-all over
-NCCL/NVLink).  Exchange buffers have a fixed capacity per destination (every pair could go to one
-rank), so no step needs a host round trip for sizes; unused rows carry the id 0xffffffff.
+The three compute pieces are the library's; this file owns the buffers (torch tensors) and calls
+`torch.distributed` all-to-all over NCCL/NVLink between them.  Exchange buffers have a fixed capacity per
+destination (every pair could go to one rank), so no step needs a host round trip for sizes; unused
+slots carry the id 0xffffffff.
+
+Two forms of the same step:
+  packed (default)  `qw4cu_moe_ep_{route_pack,experts,combine}_device`: the library plans and packs the message
+                    itself (rows and ids in one message: two all-to-alls per layer) and runs the shared expert
+                    on a second stream under the exchange
+  plain             `qw4cu_moe_{route,experts,combine}_device` with the plan in torch ops and separate row / id
+                    messages (three all-to-alls); kept as the cross-check of the packed form
 """
 from __future__ import annotations
 
@@ -56,15 +63,19 @@ class TorchExchange:
 class EpLayer:
     """One rank's share of one layer."""
 
-    def __init__(self, api: abi.MoeApi, spec: LayerSpec, tokens_local: int, world: int, rank: int, exchange):
+    def __init__(self, api: abi.MoeApi, spec: LayerSpec, tokens_local: int, world: int, rank: int, exchange, packed: bool = True):
         assert spec.experts % world == 0
-        self.api, self.world, self.rank, self.exchange = api, world, rank, exchange
+        self.api, self.world, self.rank, self.exchange, self.packed = api, world, rank, exchange, packed
         self.epr = spec.experts // world
         assert spec.local_experts == self.epr and spec.first_expert == rank * self.epr
         self.spec, self.tokens, self.k, self.hidden = spec, tokens_local, spec.top_k, spec.hidden
         self.cap = tokens_local * spec.top_k                 # rows one source may send to one destination
-        self.layer = MoeLayer(api, spec, max(tokens_local, world * self.cap))
+        # tokens_local rows beyond the exchange capacity: room for the shared expert's x digits beside the routed rows
+        self.layer = MoeLayer(api, spec, world * self.cap + tokens_local)
         dev = torch.device("cuda", torch.cuda.current_device())
+        self.slot_floats = api.lib.qw4cu_ep_slot_floats(self.layer.moe)
+        self.msg = torch.zeros((world, self.cap, self.slot_floats), dtype=torch.float32, device=dev)
+        self.slots = torch.empty((tokens_local * self.k,), dtype=torch.int32, device=dev)
         self.ids = torch.empty((tokens_local, self.k), dtype=torch.int32, device=dev)
         self.send_rows = torch.zeros((world, self.cap, self.hidden), dtype=torch.float32, device=dev)
         self.send_ids = torch.empty((world, self.cap), dtype=torch.int32, device=dev)
@@ -114,9 +125,34 @@ class EpLayer:
                                                           self.y.data_ptr(), self.layer.work, C.byref(self.err)))
         return self.y
 
+    # ---- packed form ----
+    def packed_route(self, x: torch.Tensor) -> torch.Tensor:
+        assert x.is_contiguous() and x.shape == (self.tokens, self.hidden)
+        self._use_torch_stream()
+        self._check(self.api.lib.qw4cu_moe_ep_route_pack_device(self.layer.moe, x.data_ptr(), self.tokens, self.cap, self.msg.data_ptr(),
+                                                                self.slots.data_ptr(), self.ids.data_ptr(), self.layer.work,
+                                                                C.byref(self.err)))
+        return self.msg
+
+    def packed_experts(self, recv: torch.Tensor) -> torch.Tensor:
+        self._use_torch_stream()
+        self._check(self.api.lib.qw4cu_moe_ep_experts_device(self.layer.moe, recv.data_ptr(), self.world * self.cap, self.out_rows.data_ptr(),
+                                                             self.layer.work, C.byref(self.err)))
+        return self.out_rows.view(self.world, self.cap, self.hidden)
+
+    def packed_combine(self, x: torch.Tensor, back: torch.Tensor) -> torch.Tensor:
+        self._use_torch_stream()
+        self._check(self.api.lib.qw4cu_moe_ep_combine_device(self.layer.moe, x.data_ptr(), self.tokens, back.data_ptr(), self.slots.data_ptr(),
+                                                             self.y.data_ptr(), self.layer.work, C.byref(self.err)))
+        return self.y
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x [tokens_local, hidden] float32 on this rank's GPU.  Work is enqueued on torch's current
         stream (the library is pointed at it), so it orders with the NCCL all-to-alls."""
+        if self.packed:
+            recv = self.exchange.all_to_all(self.packed_route(x))
+            back = self.exchange.all_to_all(self.packed_experts(recv))
+            return self.packed_combine(x, back)
         send_rows, send_ids = self.phase_route(x)
         recv_rows = self.exchange.all_to_all(send_rows)
         recv_ids = self.exchange.all_to_all(send_ids)
@@ -137,6 +173,10 @@ def transpose_blocks(sends):
 
 def forward_emulated(layers, xs):
     """Runs the ranks of `layers` (EpLayer objects sharing one GPU) in lockstep."""
+    if layers[0].packed:
+        recvs = transpose_blocks([layer.packed_route(x) for layer, x in zip(layers, xs)])
+        backs = transpose_blocks([layer.packed_experts(r) for layer, r in zip(layers, recvs)])
+        return [layer.packed_combine(x, b.contiguous()).clone() for layer, x, b in zip(layers, xs, backs)]
     sends = [layer.phase_route(x) for layer, x in zip(layers, xs)]
     recv_rows = transpose_blocks([s[0] for s in sends])
     recv_ids = transpose_blocks([s[1] for s in sends])

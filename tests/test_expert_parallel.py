@@ -77,10 +77,12 @@ def test_dispatch_plan_matches_the_oracle_grouping():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("packed", [True, False])
 @pytest.mark.parametrize("routed,world,tokens", [(12, 4, 16), (16, 2, 6), (10, 4, 32)])
-def test_sharded_layer_matches_the_oracle_with_emulated_ranks(gpu, routed, world, tokens):
+def test_sharded_layer_matches_the_oracle_with_emulated_ranks(gpu, routed, world, tokens, packed):
     """`world` ranks share one GPU; the all-to-all is a block transpose.  Q4_K and IQ2_XXS shards
-    take the tensor-core grouped kernels, Q2_K the CUDA-core kernels."""
+    take the tensor-core grouped kernels, Q2_K the CUDA-core kernels.  Both forms of the step: packed
+    messages planned by the library (shared expert on a second stream), and the plan in torch ops."""
     import torch
     import oracle
     from picoforge_b200 import abi, synth
@@ -91,7 +93,7 @@ def test_sharded_layer_matches_the_oracle_with_emulated_ranks(gpu, routed, world
     per = tokens // world
     epr = spec.experts // world
     torch.cuda.set_device(0)
-    layers = [EpLayer(gpu, spec.shard(r * epr, epr), per, world, r, None) for r in range(world)]
+    layers = [EpLayer(gpu, spec.shard(r * epr, epr), per, world, r, None, packed) for r in range(world)]
     try:
         xs = [torch.tensor(x[r * per:(r + 1) * per]).cuda().contiguous() for r in range(world)]
         ys = forward_emulated(layers, xs)
