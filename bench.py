@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 Qwen4 MoE layer.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2|c3|c4] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of synthetic tokens.  The default workload
 (N = 1) is the 4-token decode / multi-token-verify batch with IQ2_XXS routed experts and a
@@ -81,6 +81,10 @@ def workload(name: str, layers: int):
         x = synth.activations(2, 1024)
         x[:, 0] = 1.0
         desc = "c2: 1024-token prefill chunk, Q4_K, Zipf(1.1) expert popularity"
+    elif name == "c3":
+        specs = [synth.make_layer(3, layer=l, routed_type=abi.Q2_K, shared_type=abi.Q4_K) for l in range(layers)]
+        x = synth.activations(3, 1024)
+        desc = "c3 (one GPU): 1024-token prefill chunk, Q2_K routed + Q4_K shared, uniform routing"
     elif name == "c4":
         specs = []
         for l in range(layers):
@@ -291,7 +295,7 @@ def run_expert_parallel(args, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": f"c4: batched decode, 64 sequences x 1 token through {n_layers} Q4_K layers, Zipf(1.1) expert popularity",
                        "tokens_per_step": tokens, "layers": n_layers,
                        "parallelism": f"expert parallel, {epr} experts per GPU, router and shared expert replicated, tokens data-parallel",
-                       "exchange": "torch.distributed all_to_all_single over NCCL, three per layer (rows, ids, outputs)",
+                       "exchange": "torch.distributed all_to_all_single over NCCL, two per layer (rows with their expert ids, outputs); the shared expert runs on a second stream under the exchange",
                        "router": args.router, "l2": f"{n_layers} layers of weights per step ({touched / world / 1e6:.0f} MB per GPU), L2 is 126 MB",
                        "distinct_experts_per_layer": distinct / n_layers},
             "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
@@ -536,7 +540,7 @@ def main():
         kernel_us, kernel_bytes = stage_us[dominant], bytes_by_stage[dominant]
     achieved = kernel_bytes / (kernel_us * 1e-6) / 1e9 if kernel_us > 0 else 0.0
     tensor = None
-    if args.workload == "c2":
+    if args.workload in ("c2", "c3"):
         # FLOPs of the chunk (routed 2 * pairs * 3 * H * I, shared, router) against the measured dense bf16 rate
         spec0 = specs[0]
         pairs = tokens * spec0.top_k
@@ -549,7 +553,7 @@ def main():
                   "note": "whole step against the sustained dense bf16 rate; at about 20 rows per expert the binding roof is HBM"}
     traffic = TRAFFIC.get(f"{args.workload}:{dominant}")
     line = {
-        "metric": "moe_layer_us_per_token_decode" if args.workload != "c2" else "moe_layer_us_per_token_prefill",
+        "metric": "moe_layer_us_per_token_decode" if args.workload not in ("c2", "c3") else "moe_layer_us_per_token_prefill",
         "value": us_per_token, "unit": "us/token", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",

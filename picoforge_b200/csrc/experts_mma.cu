@@ -422,30 +422,54 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
 // Two int8 digits per activation: x ~ dx * (q1 + q2 / 254), dx = max|x| / 127 per row.
 // One CTA per row.  Also writes the negated digits (IQ2_XXS sign correction) and the per-chunk
 // digit sums (Q4_K min term).  k is a multiple of 32.
-__global__ void __launch_bounds__(512) quantize_rows_kernel(const float *__restrict__ x, uint32_t pitch, uint32_t k, int8_t *__restrict__ xq,
+// One CTA of 128 threads per row, float4 items: the row maximum first, then two int8 digits per value by the
+// 1.5 * 2^23 rounding trick (the low byte of the rounded float's bit pattern is the digit), four digits packed
+// with byte permutes, chunk sums by dp4a and three shuffles (eight consecutive lanes hold one 32-column chunk;
+// both sums travel in one register, the second in the high half).  k % 32 == 0.
+__global__ void __launch_bounds__(128) quantize_rows_kernel(const float *__restrict__ x, uint32_t pitch, uint32_t k, int8_t *__restrict__ xq,
                                                             int8_t *__restrict__ xneg, int *__restrict__ xsum, float *__restrict__ xscale) {
-    __shared__ float red[16];
-    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const float *src = x + (uint64_t)row * pitch;
+    __shared__ float red[4];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, items = k >> 2;
+    const float4 *src = reinterpret_cast<const float4 *>(x + (uint64_t)row * pitch);
     float amax = 0.0f;
-    for (uint32_t c = tid; c < k; c += 512) amax = fmaxf(amax, fabsf(src[c]));
+    for (uint32_t i = tid; i < items; i += 128) {
+        const float4 v = src[i];
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if (lane == 0) red[warp] = amax;
     __syncthreads();
-    amax = 0.0f;
-    for (int w = 0; w < 16; w++) amax = fmaxf(amax, red[w]);
-    const float dx = amax > 0.0f ? amax / 127.0f : 1.0f, inv = 1.0f / dx, inv2 = 254.0f / dx;
-    if (tid == 0) xscale[row] = amax > 0.0f ? dx : 0.0f;
-    for (uint32_t c = tid; c < k; c += 512) {                            // whole warps per 32-column chunk
-        const float v = src[c], q1 = rintf(v * inv);
-        const float q2 = fminf(fmaxf(rintf((v - q1 * dx) * inv2), -127.0f), 127.0f);
-        int s1 = (int)q1, s2 = (int)q2;
-        xq[((uint64_t)row * 2) * k + c] = (int8_t)s1;
-        xq[((uint64_t)row * 2 + 1) * k + c] = (int8_t)s2;
-        xneg[((uint64_t)row * 2) * k + c] = (int8_t)(-s1);
-        xneg[((uint64_t)row * 2 + 1) * k + c] = (int8_t)(-s2);
-        for (int o = 16; o; o >>= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
-        if (lane == 0) { xsum[((uint64_t)row * (k >> 5) + (c >> 5)) * 2] = s1; xsum[((uint64_t)row * (k >> 5) + (c >> 5)) * 2 + 1] = s2; }
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const bool usable = amax > 0.0f && amax <= 3.0e38f;
+    const float dx = usable ? amax / 127.0f : 1.0f, inv = 1.0f / dx, inv2 = 254.0f / dx, magic = 12582912.0f;
+    if (tid == 0) xscale[row] = usable ? dx : 0.0f;
+    uint32_t *q1 = reinterpret_cast<uint32_t *>(xq + ((uint64_t)row * 2) * k), *q2 = reinterpret_cast<uint32_t *>(xq + ((uint64_t)row * 2 + 1) * k);
+    uint32_t *n1 = reinterpret_cast<uint32_t *>(xneg + ((uint64_t)row * 2) * k), *n2 = reinterpret_cast<uint32_t *>(xneg + ((uint64_t)row * 2 + 1) * k);
+    for (uint32_t i0 = 0; i0 < items; i0 += 128) {                      // items is a multiple of 8: whole groups of eight lanes
+        const uint32_t i = i0 + tid;
+        const bool live = i < items;
+        const float4 v4 = live ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+        uint32_t ra[4], rb[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v = usable ? vv[j] : 0.0f;
+            const float r1 = fmaf(v, inv, magic), d1 = r1 - magic;
+            const float r2 = fmaxf(-127.0f, fminf(127.0f, fmaf(-d1, dx, v) * inv2)) + magic;
+            ra[j] = __float_as_uint(r1); rb[j] = __float_as_uint(r2);
+        }
+        const uint32_t hi = __byte_perm(__byte_perm(ra[0], ra[1], 0x0040), __byte_perm(ra[2], ra[3], 0x0040), 0x5410);
+        const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
+        if (live) {
+            q1[i] = hi; q2[i] = lo;
+            n1[i] = __vneg4(hi); n2[i] = __vneg4(lo);
+        }
+        int s = __dp4a((int)hi, 0x01010101, 0) + (__dp4a((int)lo, 0x01010101, 0) << 16);
+        for (int o = 1; o < 8; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (live && (lane & 7u) == 0) {
+            const int s1 = (int)(short)(s & 0xffff);
+            reinterpret_cast<int2 *>(xsum)[(uint64_t)row * (k >> 5) + (i >> 3)] = make_int2(s1, (s - s1) >> 16);
+        }
     }
 }
 
@@ -580,7 +604,7 @@ extern "C" const uint8_t *qw4sh_lut_image(void) { return lut_image(); }
 extern "C" int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum,
                                            float *xscale, void *stream) {
     if (!rows) return 0;
-    quantize_rows_kernel<<<rows, 512, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale);
+    quantize_rows_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale);
     return qw4sh_note_launch("quantize_rows_kernel");
 }
 extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {

@@ -39,7 +39,7 @@ struct TileArgs {
     const uint32_t *row_to_pair;                // nullptr: pair = row (shared expert)
     uint32_t k_div;                             // input row = pair / k_div
     const int8_t *digits;                       // [rows][2][K]
-    const int *sums;                            // [rows][K / 32][2]
+    const int *sums;                            // [rows][K / 32][2] (not read: minima go through the tensor core)
     const float *scale;                         // [rows]
     const uint8_t *lut;                         // IQ2_XXS tables image
     float *out;                                 // gate/up: act [pairs][n_out]; down: out [pairs][n_out]
@@ -83,10 +83,10 @@ template <> struct TGeo<T_IQ2_XXS> { static constexpr uint32_t SLICE_BLOCKS = 4,
 template <> struct TGeo<T_Q2_K> { static constexpr uint32_t SLICE_BLOCKS = 4, BLOCK_BYTES = 64; };       // codes; scale bytes and super-scales apart
 
 // The lane's view of a group's activations: for column tile n, `bq[n]` is the byte offset of the
-// digit row of MMA column g (token 4n + g / 2, digit g & 1) at this lane's 8-column phase, `sx[n]`
-// the int2 index of token 4n + t's digit sums, `xs[n]` that token's scale.
+// digit row of MMA column g (token 4n + g / 2, digit g & 1) at this lane's 8-column phase, `xs[n]`
+// the scale of token 4n + t.
 struct LaneTokens {
-    uint32_t bq[TNT], sx[TNT];
+    uint32_t bq[TNT];
     float xs[TNT];
 };
 
@@ -97,19 +97,40 @@ struct RowView {
     uint32_t swz;                                // IQ2_XXS: group swizzle of these rows
 };
 
-// One span of `halves` half blocks (128 columns each) of rows r0 / r1 against every column tile.
+// The B operands (activation digits) come straight from global memory: lane (g, t) reads the eight bytes of MMA
+// column g (token 4n + g / 2, digit g & 1) at its column phase, for every column tile n.  To keep those loads off
+// the critical path each 128-byte line (one half block of one digit row) is brought into L1 one half block ahead
+// with prefetch.global.L1, and the fragments of chunk j + 1 are loaded into registers before the MMAs of chunk j.
+__device__ __forceinline__ void load_b(uint2 (&b)[TNT], const int8_t *digits, const LaneTokens &lt, uint32_t tiles, uint32_t col) {
+#pragma unroll
+    for (int n = 0; n < TNT; n++)
+        b[n] = (uint32_t)n < tiles ? __ldg(reinterpret_cast<const uint2 *>(digits + lt.bq[n] + col)) : make_uint2(0u, 0u);
+}
+__device__ __forceinline__ void prefetch_b(const int8_t *digits, const LaneTokens &lt, uint32_t tiles, uint32_t col) {
+#pragma unroll
+    for (int n = 0; n < TNT; n++)
+        if ((uint32_t)n < tiles) asm volatile("prefetch.global.L1 [%0];" ::"l"(digits + lt.bq[n] + col));
+}
+
+// One span of `halves` half blocks (128 columns each) of rows r0 / r1 against every column tile; the span starts at
+// half block `first_half` of a row of `row_halves`.
 // f[n][0] += row g . x[token 4n + t], f[n][1] += row g + 8 . x[token 4n + t] (in digit units).
 template <uint32_t TYPE> struct TileHalves;
 
+// Q4_K: the 4-bit codes are the A operand; the 6-bit sub-block minimum goes through a second MMA whose A operand
+// is the minimum replicated over the lane's columns, so both sums come out of the tensor core.
 template <> struct TileHalves<T_Q4_K> {
-    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, const uint8_t *, uint32_t t,
-                                               const int8_t *digits, const int2 *sums, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
+    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, uint32_t row_halves, const uint8_t *,
+                                               uint32_t t, const int8_t *digits, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
         const uint8_t *r0 = v.r0, *r1 = v.r1;
         const float lo = 1.0f / 254.0f;
+        uint2 bc[TNT], bn[TNT];
+        load_b(bc, digits, lt, tiles, first_half * 128u);
 #pragma unroll 1
         for (uint32_t h = 0; h < halves; h++) {
             const uint8_t *b0 = r0 + (h >> 1) * 144u, *b1 = r1 + (h >> 1) * 144u;
             const uint32_t hb = h & 1u, col0 = (first_half + h) * 128u;
+            if (first_half + h + 1 < row_halves) prefetch_b(digits, lt, tiles, col0 + 128u);
             const uint4 h0 = *reinterpret_cast<const uint4 *>(b0), h1 = *reinterpret_cast<const uint4 *>(b1);
             uint32_t sc0, mn0, sc1, mn1;
             if (hb == 0) { sc0 = h0.y & 0x3f3f3f3fu; mn0 = h0.z & 0x3f3f3f3fu; sc1 = h1.y & 0x3f3f3f3fu; mn1 = h1.z & 0x3f3f3f3fu; }
@@ -126,23 +147,24 @@ template <> struct TileHalves<T_Q4_K> {
 #pragma unroll
                 for (int nib = 0; nib < 2; nib++) {
                     const int j = cc * 2 + nib;
+                    if (j < 3) load_b(bn, digits, lt, tiles, col0 + (j + 1) * 32u);
+                    else if (h + 1 < halves) load_b(bn, digits, lt, tiles, col0 + 128u);
                     const uint32_t a0 = (q0.x >> (4 * nib)) & 0x0f0f0f0fu, a1 = (q1.x >> (4 * nib)) & 0x0f0f0f0fu;
                     const uint32_t a2 = (q0.y >> (4 * nib)) & 0x0f0f0f0fu, a3 = (q1.y >> (4 * nib)) & 0x0f0f0f0fu;
                     const float ds0 = d0 * (float)((sc0 >> (8 * j)) & 0xffu), ds1 = d1 * (float)((sc1 >> (8 * j)) & 0xffu);
-                    const float nm0 = n0 * (float)((mn0 >> (8 * j)) & 0xffu), nm1 = n1 * (float)((mn1 >> (8 * j)) & 0xffu);
-                    const uint32_t col = col0 + j * 32u;
+                    const uint32_t m0 = ((mn0 >> (8 * j)) & 0xffu) * 0x01010101u, m1 = ((mn1 >> (8 * j)) & 0xffu) * 0x01010101u;
 #pragma unroll
                     for (int n = 0; n < TNT; n++) {
                         if ((uint32_t)n < tiles) {
-                            const uint2 bq = __ldg(reinterpret_cast<const uint2 *>(digits + lt.bq[n] + col));
-                            const int2 sx = __ldg(sums + lt.sx[n] + (col >> 5));
-                            int c[4];
-                            tmma_zero(c, a0, a1, a2, a3, bq.x, bq.y);
-                            const float s = fmaf((float)sx.y, lo, (float)sx.x);
-                            f[n][0] += ds0 * fmaf((float)c[1], lo, (float)c[0]) - nm0 * s;
-                            f[n][1] += ds1 * fmaf((float)c[3], lo, (float)c[2]) - nm1 * s;
+                            int c[4], e[4];
+                            tmma_zero(c, a0, a1, a2, a3, bc[n].x, bc[n].y);
+                            tmma_zero(e, m0, m1, m0, m1, bc[n].x, bc[n].y);
+                            f[n][0] += ds0 * fmaf((float)c[1], lo, (float)c[0]) - n0 * fmaf((float)e[1], lo, (float)e[0]);
+                            f[n][1] += ds1 * fmaf((float)c[3], lo, (float)c[2]) - n1 * fmaf((float)e[3], lo, (float)e[2]);
                         }
                     }
+#pragma unroll
+                    for (int n = 0; n < TNT; n++) bc[n] = bn[n];
                 }
             }
         }
@@ -150,8 +172,8 @@ template <> struct TileHalves<T_Q4_K> {
 };
 
 template <> struct TileHalves<T_IQ2_XXS> {
-    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, const uint8_t *lut, uint32_t t,
-                                               const int8_t *digits, const int2 *, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
+    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, uint32_t row_halves, const uint8_t *lut,
+                                               uint32_t t, const int8_t *digits, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
         const uint8_t *r0 = v.r0, *r1 = v.r1;
         const uint16_t *d0p = reinterpret_cast<const uint16_t *>(v.dd0), *d1p = reinterpret_cast<const uint16_t *>(v.dd1);
         const uint32_t swz = v.swz;
@@ -159,12 +181,17 @@ template <> struct TileHalves<T_IQ2_XXS> {
         const uint8_t *sign = lut + T_LUT_GRID + (threadIdx.x & 7u) * 16u;
         const uint32_t pick = 0x4440u + t, shift_s = 7 * t;
         const float lo = 1.0f / 254.0f;
+        uint2 bc[TNT], bn[TNT];
+        load_b(bc, digits, lt, tiles, first_half * 128u);
 #pragma unroll 1
         for (uint32_t h = 0; h < halves; h++) {
             const uint32_t at = ((h * 4u) ^ swz) * 8u, col0 = (first_half + h) * 128u;
+            if (first_half + h + 1 < row_halves) prefetch_b(digits, lt, tiles, col0 + 128u);
             const float d0 = __half2float(__ushort_as_half(d0p[h >> 1])) * 0.125f, d1 = __half2float(__ushort_as_half(d1p[h >> 1])) * 0.125f;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
+                if (j < 3) load_b(bn, digits, lt, tiles, col0 + (j + 1) * 32u);
+                else if (h + 1 < halves) load_b(bn, digits, lt, tiles, col0 + 128u);
                 const uint2 g0 = *reinterpret_cast<const uint2 *>(r0 + at + 8 * j), g1 = *reinterpret_cast<const uint2 *>(r1 + at + 8 * j);
                 const uint32_t i0 = __byte_perm(g0.x, 0u, pick), i1 = __byte_perm(g1.x, 0u, pick);
                 const uint32_t s0 = (g0.y >> shift_s) & 127u, s1 = (g1.y >> shift_s) & 127u;
@@ -172,17 +199,17 @@ template <> struct TileHalves<T_IQ2_XXS> {
                 const uint4 m0 = *reinterpret_cast<const uint4 *>(sign + s0 * 128u), m1 = *reinterpret_cast<const uint4 *>(sign + s1 * 128u);
                 const uint32_t a0 = (v0.x ^ m0.x) + m0.z, a1 = (v1.x ^ m1.x) + m1.z, a2 = (v0.y ^ m0.y) + m0.w, a3 = (v1.y ^ m1.y) + m1.w;
                 const float ds0 = d0 * (float)((g0.y >> 27) | 1u), ds1 = d1 * (float)((g1.y >> 27) | 1u);
-                const uint32_t col = col0 + j * 32u;
 #pragma unroll
                 for (int n = 0; n < TNT; n++) {
                     if ((uint32_t)n < tiles) {
-                        const uint2 bq = __ldg(reinterpret_cast<const uint2 *>(digits + lt.bq[n] + col));
                         int c[4];
-                        tmma_zero(c, a0, a1, a2, a3, bq.x, bq.y);
+                        tmma_zero(c, a0, a1, a2, a3, bc[n].x, bc[n].y);
                         f[n][0] += ds0 * fmaf((float)c[1], lo, (float)c[0]);
                         f[n][1] += ds1 * fmaf((float)c[3], lo, (float)c[2]);
                     }
                 }
+#pragma unroll
+                for (int n = 0; n < TNT; n++) bc[n] = bn[n];
             }
         }
     }
@@ -195,13 +222,16 @@ template <> struct TileHalves<T_IQ2_XXS> {
 // the minimum replicated over the lane's columns: both sums come out of the tensor core, no per-16-column digit
 // sums needed.
 template <> struct TileHalves<T_Q2_K> {
-    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, const uint8_t *, uint32_t t,
-                                               const int8_t *digits, const int2 *, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
+    static __device__ __forceinline__ void run(const RowView &v, uint32_t halves, uint32_t first_half, uint32_t row_halves, const uint8_t *,
+                                               uint32_t t, const int8_t *digits, const LaneTokens &lt, uint32_t tiles, float (&f)[TNT][2]) {
         const float lo = 1.0f / 254.0f;
         const uint8_t *r0 = v.r0, *r1 = v.r1, *s0 = v.aux0, *s1 = v.aux1;
+        uint2 bc[TNT], bn[TNT];
+        load_b(bc, digits, lt, tiles, first_half * 128u);
 #pragma unroll 1
         for (uint32_t h = 0; h < halves; h++) {
             const uint32_t blk = h >> 1, hb = h & 1u, col0 = (first_half + h) * 128u;
+            if (first_half + h + 1 < row_halves) prefetch_b(digits, lt, tiles, col0 + 128u);
             const uint2 q0 = *reinterpret_cast<const uint2 *>(r0 + blk * 64u + hb * 32u + 8u * t);
             const uint2 q1 = *reinterpret_cast<const uint2 *>(r1 + blk * 64u + hb * 32u + 8u * t);
             const uint2 w0 = *reinterpret_cast<const uint2 *>(s0 + blk * 16u + hb * 8u), w1 = *reinterpret_cast<const uint2 *>(s1 + blk * 16u + hb * 8u);
@@ -210,23 +240,25 @@ template <> struct TileHalves<T_Q2_K> {
             const float d1 = __half2float(__ushort_as_half((uint16_t)(dd1 & 0xffffu))), n1 = __half2float(__ushort_as_half((uint16_t)(dd1 >> 16)));
 #pragma unroll
             for (int j = 0; j < 4; j++) {
+                if (j < 3) load_b(bn, digits, lt, tiles, col0 + (j + 1) * 32u);
+                else if (h + 1 < halves) load_b(bn, digits, lt, tiles, col0 + 128u);
                 const uint32_t sh = 8u * ((j & 1) * 2 + (t >> 1));
                 const uint32_t b0 = ((j < 2 ? w0.x : w0.y) >> sh) & 0xffu, b1 = ((j < 2 ? w1.x : w1.y) >> sh) & 0xffu;
                 const uint32_t sc0 = b0 & 15u, sc1 = b1 & 15u, m0 = (b0 >> 4) * 0x01010101u, m1 = (b1 >> 4) * 0x01010101u;
                 const uint32_t a0 = ((q0.x >> (2 * j)) & 0x03030303u) * sc0, a1 = ((q1.x >> (2 * j)) & 0x03030303u) * sc1;
                 const uint32_t a2 = ((q0.y >> (2 * j)) & 0x03030303u) * sc0, a3 = ((q1.y >> (2 * j)) & 0x03030303u) * sc1;
-                const uint32_t col = col0 + j * 32u;
 #pragma unroll
                 for (int n = 0; n < TNT; n++) {
                     if ((uint32_t)n < tiles) {
-                        const uint2 bq = __ldg(reinterpret_cast<const uint2 *>(digits + lt.bq[n] + col));
                         int c[4], e[4];
-                        tmma_zero(c, a0, a1, a2, a3, bq.x, bq.y);
-                        tmma_zero(e, m0, m1, m0, m1, bq.x, bq.y);
+                        tmma_zero(c, a0, a1, a2, a3, bc[n].x, bc[n].y);
+                        tmma_zero(e, m0, m1, m0, m1, bc[n].x, bc[n].y);
                         f[n][0] += d0 * fmaf((float)c[1], lo, (float)c[0]) - n0 * fmaf((float)e[1], lo, (float)e[0]);
                         f[n][1] += d1 * fmaf((float)c[3], lo, (float)c[2]) - n1 * fmaf((float)e[3], lo, (float)e[2]);
                     }
                 }
+#pragma unroll
+                for (int n = 0; n < TNT; n++) bc[n] = bn[n];
             }
         }
     }
@@ -323,7 +355,6 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
         }
     };
     if (alive) for (uint32_t n = 0; n < TNS && n < slices; n++) issue(n);
-    const int2 *sums = reinterpret_cast<const int2 *>(a.sums);
     LaneTokens lt;
     uint32_t pair_t[TNT];                                                      // pair of token 4n + t
     float f[TNT][2];
@@ -343,7 +374,6 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
                 const uint32_t row_t = __shfl_sync(0xffffffffu, my_row, (4 * q + t) & 31u);
                 pair_t[q] = __shfl_sync(0xffffffffu, my_pair, (4 * q + t) & 31u);
                 lt.bq[q] = (row_g * 2 + (g & 1u)) * K + 8 * t;
-                lt.sx[q] = row_t * (K >> 5);
                 lt.xs[q] = (uint32_t)q < n_tiles ? __ldg(a.scale + row_t) : 0.0f;
                 f[q][0] = f[q][1] = 0.0f;
             }
@@ -360,16 +390,16 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
                 v.r0 = stage + g * per_row * 64u; v.r1 = stage + (8 + g) * per_row * 64u;
                 v.aux0 = stage + 4096 + g * per_row * 16u; v.aux1 = stage + 4096 + (8 + g) * per_row * 16u;
                 v.dd0 = stage + 5120 + g * per_row * 4u; v.dd1 = stage + 5120 + (8 + g) * per_row * 4u;
-                TileHalves<TYPE>::run(v, per_row * 2, MODE == 0 ? s * SB * 2 : 0, lut, t, a.digits, sums, lt, n_tiles, f);
+                TileHalves<TYPE>::run(v, per_row * 2, MODE == 0 ? s * SB * 2 : 0, nb * 2, lut, t, a.digits, lt, n_tiles, f);
             } else if (MODE == 0) {
                 constexpr uint32_t slice_bytes = SB * BB;
                 v.r0 = stage + g * slice_bytes; v.r1 = stage + (8 + g) * slice_bytes;
                 v.dd0 = stage + 16 * slice_bytes + (g * nb + s * SB) * 2u; v.dd1 = stage + 16 * slice_bytes + ((8 + g) * nb + s * SB) * 2u;
-                TileHalves<TYPE>::run(v, SB * 2, s * SB * 2, lut, t, a.digits, sums, lt, n_tiles, f);
+                TileHalves<TYPE>::run(v, SB * 2, s * SB * 2, nb * 2, lut, t, a.digits, lt, n_tiles, f);
             } else {
                 v.r0 = stage + g * row_bytes; v.r1 = stage + (8 + g) * row_bytes;
                 v.dd0 = stage + 4096 + g * nb * 2u; v.dd1 = stage + 4096 + (8 + g) * nb * 2u;
-                TileHalves<TYPE>::run(v, nb * 2, 0, lut, t, a.digits, sums, lt, n_tiles, f);
+                TileHalves<TYPE>::run(v, nb * 2, 0, nb * 2, lut, t, a.digits, lt, n_tiles, f);
             }
         }
         __syncwarp();
