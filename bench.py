@@ -44,7 +44,7 @@ from picoforge_b200.layer import MoeLayer  # noqa: E402
 # summarised in profiles/ (ncu's replay adds cache write-backs to the write part; the read part equals
 # the algorithmic bytes).
 TRAFFIC = {
-    "c1:fused_decode_kernel": 32.92e6 + 38.14e6,
+    "c1:fused_decode_kernel": 32.91e6 + 30.85e6,
     "c2:gate_up_routed": 144.26e6 + 17.5e6,
 }
 
@@ -220,6 +220,7 @@ def run_expert_parallel(args, rank: int, local_rank: int, world: int) -> None:
     if lib.qw4cu_set_device(local_rank) != 0:
         raise SystemExit(lib.qw4cu_last_error().decode())
     lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
+    lib.qw4cu_set_tile_path(args.tile_path)
     tokens, n_layers = 64, args.ep_layers
     per, epr = tokens // world, 512 // world
     x_all = synth.activations(4, tokens)
@@ -323,6 +324,7 @@ def main():
     parser.add_argument("--router", default="exact", choices=["exact", "fast"])
     parser.add_argument("--no-graph", action="store_true")
     parser.add_argument("--expert-path", type=int, default=-1, help="-1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels")
+    parser.add_argument("--tile-path", type=int, default=-1, help="-1 auto, 0 never, 1 tile kernels for every batch of more than four rows")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--ep-layers", type=int, default=48, help="layers of the expert-parallel workload (N > 1)")
     parser.add_argument("--profile", action="store_true",
@@ -372,6 +374,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
+    lib.qw4cu_set_tile_path(args.tile_path)
     lib.qw4cu_set_expert_path(args.expert_path)
     desc, tokens, specs, x = workload(args.workload, args.layers)
     layers = [MoeLayer(api, spec, tokens) for spec in specs]

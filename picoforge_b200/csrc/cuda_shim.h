@@ -142,6 +142,9 @@ int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]);
 
 /* Tensor-core prefill path (prefill_tc.cu): Q4_K experts, groups of <= 32 token rows, tcgen05
  * MMAs with TMEM accumulators.  supported: 1 when a tensor fits it. */
+/* Stable per-expert lists of plain rows (one id per row; 0xffffffff: none), one CTA. */
+int qw4sh_group_rows(uint32_t experts, size_t rows, const uint32_t *ids, uint32_t *offsets, uint32_t *pair_to_row,
+                     uint32_t *row_to_pair, uint32_t *active, uint32_t *status, void *stream);
 /* Expert-parallel exchange messages (ep_exchange.cu) and the pieces that use them. */
 uint32_t qw4sh_ep_pitch(uint32_t hidden);
 int qw4sh_ep_pack(const float *x, uint32_t tokens, uint32_t k, uint32_t hidden, const uint32_t *ids, uint32_t experts_per_rank,

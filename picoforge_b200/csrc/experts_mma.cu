@@ -519,16 +519,39 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
     y[(uint64_t)t * hidden + c] = total;
 }
 
-// Groups of at most four rows out of the expert-sorted lists; one thread (lists are short).
-__global__ void build_groups_kernel(const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ active, VGroup *groups,
-                                    uint32_t *n_groups) {
-    if (threadIdx.x || blockIdx.x) return;
-    uint32_t n = 0;
-    for (uint32_t i = 0; i < active[0]; i++) {
-        const uint32_t e = active[1 + i], first = offsets[e], end = offsets[e + 1];
-        for (uint32_t r = first; r < end; r += TOK) groups[n++] = VGroup{e, r, min((uint32_t)TOK, end - r), 0};
+// Groups of at most four rows out of the expert-sorted lists.
+// One CTA, thread i owns active expert i (then i + 1024, ...); a block-wide exclusive scan of the group counts gives
+// every expert its place in the list: active experts in ascending order, each expert's groups by ascending row.
+__global__ void __launch_bounds__(1024) build_groups_kernel(const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ active,
+                                                            VGroup *groups, uint32_t *n_groups) {
+    __shared__ uint32_t wsum[32];
+    __shared__ uint32_t s_base;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, n_active = active[0];
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    for (uint32_t i0 = 0; i0 < n_active; i0 += 1024) {
+        const uint32_t i = i0 + tid;
+        uint32_t e = 0, first = 0, end = 0;
+        if (i < n_active) { e = active[1 + i]; first = offsets[e]; end = offsets[e + 1]; }
+        const uint32_t count = (end - first + TOK - 1) / TOK;
+        uint32_t scan = count;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(0xffffffffu, scan, o); if (lane >= (uint32_t)o) scan += v; }
+        if (lane == 31) wsum[warp] = scan;
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t v = wsum[lane];
+            uint32_t sc = v;
+            for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, sc, o); if (lane >= (uint32_t)o) sc += u; }
+            wsum[lane] = sc - v;
+        }
+        __syncthreads();
+        uint32_t at = s_base + wsum[warp] + scan - count;
+        for (uint32_t r = first; r < end; r += TOK) groups[at++] = VGroup{e, r, min((uint32_t)TOK, end - r), 0};
+        __syncthreads();
+        if (tid == 1023) s_base = at;                                // end of the last thread = end of the round
+        __syncthreads();
     }
-    *n_groups = n;
+    if (tid == 0) *n_groups = s_base;
 }
 __global__ void build_dense_groups_kernel(uint32_t tokens, VGroup *groups, uint32_t *n_groups) {
     const uint32_t n = (tokens + TOK - 1) / TOK;
@@ -616,7 +639,7 @@ extern "C" int qw4sh_combine(const float *out, const float *shared_out, const fl
     return qw4sh_note_launch("combine_kernel");
 }
 extern "C" int qw4sh_build_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream) {
-    build_groups_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(offsets, active, (VGroup *)groups, n_groups);
+    build_groups_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(offsets, active, (VGroup *)groups, n_groups);
     return qw4sh_note_launch("build_groups_kernel");
 }
 extern "C" int qw4sh_build_dense_groups(uint32_t tokens, void *groups, uint32_t *n_groups, void *stream) {

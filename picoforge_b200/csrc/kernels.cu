@@ -264,61 +264,74 @@ __global__ void __launch_bounds__(32 * TT) router_exact_kernel(DevTensor router,
     }
 }
 
-// Exact, mid-sized batches: 16 router rows x 16 tokens per CTA, one serial chain per thread.  Both tiles go
-// through a four-stage cp.async ring in chunks of 128 columns (three chunks, about 2000 cycles of chain, are
-// in flight ahead of the adds: more than a DRAM round trip), and every thread reads four columns of its row
-// and of its token with one 128-bit load each (row pitch 132 floats: the eight lanes of a quarter warp hit
-// eight different 16-byte bank groups), so a chain step costs 2.5 instructions.
-constexpr int RC_ROWS = 16, RC_K = 128, RC_PITCH = 132, RC_STAGES = 4;
-constexpr size_t RC_SMEM = (size_t)RC_STAGES * 2 * RC_ROWS * RC_PITCH * sizeof(float);
+// Exact, mid-sized batches: 16 router rows x 16 tokens per CTA of four warps (one per scheduler), every thread two
+// serial chains (one row x two tokens), so that three 128-bit shared-memory reads feed eight chain steps.  Measured
+// here: with one chain per thread (256 threads) the kernel is bound by shared-memory bandwidth, with four chains in
+// a lone warp per SM by that warp's issue rate (a warp issues at most every other cycle); this is the middle.
+// Both tiles go through a four-stage cp.async ring in chunks of 128 columns (three chunks are in flight ahead of
+// the adds: more than a DRAM round trip); row pitch 132 floats keeps the reads free of bank conflicts.
+constexpr int RC_ROWS = 16, RC_TOK = 16, RC_K = 128, RC_PITCH = 132, RC_STAGES = 4, RC_THREADS = 128;
+constexpr size_t RC_SMEM = (size_t)RC_STAGES * (RC_ROWS + RC_TOK) * RC_PITCH * sizeof(float);
 __device__ __forceinline__ void rc_copy16(void *dst_smem, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
 }
-__global__ void __launch_bounds__(256) router_chain_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
-                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
+__global__ void __launch_bounds__(RC_THREADS) router_chain_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
+                                                                  float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
     extern __shared__ __align__(16) uint8_t rc_smem[];
-    float (*tile)[2 * RC_ROWS][RC_PITCH] = reinterpret_cast<float (*)[2 * RC_ROWS][RC_PITCH]>(rc_smem);   // rows 0-15 router rows, 16-31 tokens
+    float (*tile)[RC_ROWS + RC_TOK][RC_PITCH] = reinterpret_cast<float (*)[RC_ROWS + RC_TOK][RC_PITCH]>(rc_smem);   // rows 0-15 router rows, 16-31 tokens
     const uint32_t experts = router.n_out, K = router.k_logical, tid = threadIdx.x;
-    const uint32_t row = tid >> 4, col = (tid & 15u) * 4;                        // as loader: two 16-byte pieces of each tile
-    const uint32_t le = blockIdx.x * RC_ROWS + row, lt = min(blockIdx.y * RC_ROWS + row, tokens - 1);
-    const float *wsrc = (le < experts ? (const float *)(router.data + (uint64_t)le * router.row_bytes) : (const float *)srouter.data) + col;
-    const float *xsrc = x + (uint64_t)lt * K + col;
+    const uint32_t e0 = blockIdx.x * RC_ROWS, t0 = blockIdx.y * RC_TOK;
     const uint32_t chunks = K / RC_K;
+    // loader role: thread t copies the 16-byte piece t % 32 of rows t / 32, t / 32 + 4, ... (32 pieces = 128 columns)
+    const uint32_t piece = (tid & 31u) * 4, lrow = tid >> 5;
+    const float *srcs[(RC_ROWS + RC_TOK) / 4];
+#pragma unroll
+    for (int j = 0; j < (RC_ROWS + RC_TOK) / 4; j++) {
+        const uint32_t r = lrow + 4 * j;
+        if (r < RC_ROWS) {
+            const uint32_t e = e0 + r;
+            srcs[j] = (e < experts ? (const float *)(router.data + (uint64_t)e * router.row_bytes) : (const float *)srouter.data) + piece;
+        } else srcs[j] = x + (uint64_t)min(t0 + r - RC_ROWS, tokens - 1) * K + piece;
+    }
     auto load = [&](uint32_t c) {
         if (c < chunks) {
 #pragma unroll
-            for (int half = 0; half < RC_K; half += 64) {
-                rc_copy16(&tile[c % RC_STAGES][row][half + col], wsrc + c * RC_K + half);
-                rc_copy16(&tile[c % RC_STAGES][RC_ROWS + row][half + col], xsrc + c * RC_K + half);
-            }
+            for (int j = 0; j < (RC_ROWS + RC_TOK) / 4; j++) rc_copy16(&tile[c % RC_STAGES][lrow + 4 * j][piece], srcs[j] + c * RC_K);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (uint32_t c = 0; c + 1 < RC_STAGES; c++) load(c);
-    const uint32_t e_l = tid >> 4, t_l = tid & 15u;                              // as worker: chain (row e_l, token t_l)
-    float sum = 0.0f;
+    const uint32_t er = tid >> 3, tc = tid & 7u;                                 // worker role: row er x tokens tc, tc + 8
+    float s0 = 0.0f, s1 = 0.0f;
     for (uint32_t c = 0; c < chunks; c++) {
         load(c + RC_STAGES - 1);
         asm volatile("cp.async.wait_group %0;" ::"n"(RC_STAGES - 1) : "memory");
         __syncthreads();
-        const float4 *w4 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][e_l]);
-        const float4 *x4 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][RC_ROWS + t_l]);
-#pragma unroll
+        const float4 *w4 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][er]);
+        const float4 *x0 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][RC_ROWS + tc]), *x1 = reinterpret_cast<const float4 *>(tile[c % RC_STAGES][RC_ROWS + tc + 8]);
+#pragma unroll 8
         for (int i = 0; i < RC_K / 4; i++) {
-            const float4 w = w4[i], v = x4[i];
-            sum = __fadd_rn(sum, __fmul_rn(w.x, v.x));
-            sum = __fadd_rn(sum, __fmul_rn(w.y, v.y));
-            sum = __fadd_rn(sum, __fmul_rn(w.z, v.z));
-            sum = __fadd_rn(sum, __fmul_rn(w.w, v.w));
+            const float4 a = w4[i], u = x0[i], v = x1[i];
+            const float p0 = __fmul_rn(a.x, u.x), p1 = __fmul_rn(a.x, v.x), p2 = __fmul_rn(a.y, u.y), p3 = __fmul_rn(a.y, v.y);
+            const float p4 = __fmul_rn(a.z, u.z), p5 = __fmul_rn(a.z, v.z), p6 = __fmul_rn(a.w, u.w), p7 = __fmul_rn(a.w, v.w);
+            s0 = __fadd_rn(s0, p0); s1 = __fadd_rn(s1, p1); s0 = __fadd_rn(s0, p2); s1 = __fadd_rn(s1, p3);
+            s0 = __fadd_rn(s0, p4); s1 = __fadd_rn(s1, p5); s0 = __fadd_rn(s0, p6); s1 = __fadd_rn(s1, p7);
         }
         __syncthreads();
     }
-    const uint32_t e = blockIdx.x * RC_ROWS + e_l, t = blockIdx.y * RC_ROWS + t_l;
-    if (t < tokens && e <= experts) {
-        if (!finite_f32(sum)) atomicOr(status, QW4SH_ERR_NONFINITE);
-        if (e < experts) logits[(uint64_t)t * experts + e] = sum;
-        else shared_logit[t] = sum;
+    const uint32_t e = e0 + er;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const uint32_t t = t0 + tc + 8 * j;
+        const float sum = j ? s1 : s0;
+        if (t < tokens && e <= experts) {
+            bad |= !finite_f32(sum);
+            if (e < experts) logits[(uint64_t)t * experts + e] = sum;
+            else shared_logit[t] = sum;
+        }
     }
+    if (bad) atomicOr(status, QW4SH_ERR_NONFINITE);
 }
 
 // Exact, few tokens: one warp per (32 router rows, token).  The serial chain of separately
@@ -652,10 +665,11 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
     if (!s_last) return;
     if (e == 0) n_groups[2] = 0;                                // ready for the next call
     __threadfence();
-    // An expert takes a token at most once, so its list is a 64-bit set of tokens (tokens <= 64) plus the slot it
-    // has in each: thread q marks pair q, thread e then walks only its own set bits, in ascending token order.
+    // An expert takes a token at most once, so its list is a 64-bit set of tokens (tokens <= 64): thread q marks
+    // pair q, thread e counts its set, and every pair finds its own row with one popcount.
     const uint32_t pairs = tokens * k;
     __shared__ unsigned long long s_tokens[512];
+    __shared__ uint32_t s_first[512];
     s_tokens[e] = 0ull;
     __syncthreads();
     for (uint32_t q = e; q < pairs; q += blockDim.x) {
@@ -685,13 +699,16 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
         if (count) {
             active[1 + arank] = e;
             for (uint32_t j = 0; j < (count + 3) >> 2; j++) groups[gfirst + j] = Group4{e, first + 4 * j, min(4u, count - 4 * j), 0};
-            uint32_t cursor = first;
-            for (unsigned long long rest = my_tokens; rest; rest &= rest - 1) {
-                const uint32_t tok = __ffsll((long long)rest) - 1;
-                uint32_t q = tok * k;
-                while (sids[q] != e) q++;                           // the slot this expert has in the token (it is there: the bit is set)
-                pair_to_row[q] = cursor; row_to_pair[cursor] = q; cursor++;
-            }
+        }
+    }
+    // placement by pair: a pair's row is its expert's first row plus the number of lower tokens in the expert's set
+    s_first[e] = first;
+    __syncthreads();
+    for (uint32_t q = e; q < pairs; q += blockDim.x) {
+        const uint32_t id = sids[q];
+        if (id < experts) {
+            const uint32_t row = s_first[id] + __popcll(s_tokens[id] & ((1ull << (q / k)) - 1ull));
+            pair_to_row[q] = row; row_to_pair[row] = q;
         }
     }
     if (e == blockDim.x - 1) {                                   // inclusive total sits in the last thread
@@ -741,6 +758,65 @@ __global__ void __launch_bounds__(1024) group_kernel(uint32_t experts, uint32_t 
         const uint32_t end = counts[e + 1];
         for (uint32_t p = 0; p < pairs && cursor < end; p++)
             if (ids[p] == e) { pair_to_row[p] = cursor; row_to_pair[cursor] = p; cursor++; }
+    }
+}
+
+// Dispatch of plain rows (one expert id per row, any id any number of times; 0xffffffff: no expert), as the
+// expert-parallel owner sees them: stable counting sort in one CTA.  Counts by shared-memory atomics, a block scan
+// over the experts, then placement in row order: within a warp a row's rank among equal ids comes from
+// __match_any_sync, and the warps of a round of 1024 rows take turns at the per-expert cursors, so the order inside
+// an expert is by ascending row.  experts <= 1024.
+__global__ void __launch_bounds__(1024) group_rows_kernel(uint32_t experts, uint32_t rows, const uint32_t *__restrict__ ids,
+                                                          uint32_t *__restrict__ offsets, uint32_t *__restrict__ pair_to_row,
+                                                          uint32_t *__restrict__ row_to_pair, uint32_t *__restrict__ active, uint32_t *status) {
+    __shared__ uint32_t cursor[1024];
+    __shared__ uint32_t wsum[32];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    cursor[tid] = 0;
+    __syncthreads();
+    bool bounds = false;
+    for (uint32_t r = tid; r < rows; r += 1024) {
+        const uint32_t e = ids[r];
+        if (e < experts) atomicAdd(&cursor[e], 1u); else if (e != 0xffffffffu) bounds = true;
+    }
+    if (bounds) atomicOr(status, QW4SH_ERR_BOUNDS);
+    __syncthreads();
+    // packed scan: rows in bits 0-19, non-empty experts from bit 20
+    const uint32_t count = tid < experts ? cursor[tid] : 0, packed = count | ((count ? 1u : 0u) << 20);
+    uint32_t scan = packed;
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t v = __shfl_up_sync(0xffffffffu, scan, o); if (lane >= (uint32_t)o) scan += v; }
+    if (lane == 31) wsum[warp] = scan;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t v = wsum[lane];
+        uint32_t sc = v;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, sc, o); if (lane >= (uint32_t)o) sc += u; }
+        wsum[lane] = sc - v;
+    }
+    __syncthreads();
+    const uint32_t exclusive = wsum[warp] + scan - packed, first = exclusive & 0xfffffu;
+    if (tid < experts) {
+        offsets[tid] = first;
+        if (count) active[1 + (exclusive >> 20)] = tid;
+    }
+    if (tid == 1023) { offsets[experts] = (exclusive + packed) & 0xfffffu; active[0] = (exclusive + packed) >> 20; }
+    __syncthreads();
+    cursor[tid] = first;
+    __syncthreads();
+    for (uint32_t r0 = 0; r0 < rows; r0 += 1024) {
+        const uint32_t r = r0 + tid;
+        const uint32_t e = r < rows ? ids[r] : 0xffffffffu;
+        const bool ok = e < experts;
+        const uint32_t same = __match_any_sync(0xffffffffu, ok ? e : 0xffffffffu);
+        const uint32_t rank = __popc(same & ((1u << lane) - 1u)), leader = __ffs(same) - 1;
+        const uint32_t warps = min(32u, (rows - r0 + 31) / 32);
+        uint32_t base = 0;
+        for (uint32_t w = 0; w < warps; w++) {                     // the warps of this round in turn: stable across warps
+            if (warp == w && ok && rank == 0) { base = cursor[e]; cursor[e] = base + __popc(same); }
+            __syncthreads();
+        }
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (ok) { pair_to_row[r] = base + rank; row_to_pair[base + rank] = r; }
     }
 }
 
@@ -1171,7 +1247,13 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
                          uint32_t *status, int mode, cudaStream_t stream) {
     const DevTensor router = as_dev(layer->w[0]), srouter = as_dev(layer->w[7]);
     const uint32_t rows = layer->experts + 1;
-    if (mode == 0 && tokens <= 16 && router.k_logical % 4 == 0 && router.k_logical <= 4096) {
+    if (mode == 0 && tokens > 4 && tokens <= 128 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
+               ((uintptr_t)router.data & 15u) == 0 && ((uintptr_t)srouter.data & 15u) == 0) {
+        if (allow_smem(router_chain_kernel, RC_SMEM)) return -1;
+        router_chain_kernel<<<dim3((rows + RC_ROWS - 1) / RC_ROWS, (unsigned)((tokens + RC_TOK - 1) / RC_TOK)), RC_THREADS, RC_SMEM, stream>>>(
+            router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+        LAUNCHED("router_chain_kernel");
+    } else if (mode == 0 && tokens <= 16 && router.k_logical % 4 == 0 && router.k_logical <= 4096) {
         const size_t smem = RS_STAGES * 32 * RS_PITCH + (((size_t)router.k_logical * 4 + 15) & ~(size_t)15) + 64;
         if (allow_smem(router_exact_small_kernel, smem)) return -1;
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
@@ -1181,12 +1263,6 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (mode == 0) router_gemm_kernel<true><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         else router_gemm_kernel<false><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
         LAUNCHED("router_gemm_kernel");
-    } else if (mode == 0 && tokens > 4 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
-               ((uintptr_t)router.data & 15u) == 0 && ((uintptr_t)srouter.data & 15u) == 0) {
-        if (allow_smem(router_chain_kernel, RC_SMEM)) return -1;
-        router_chain_kernel<<<dim3((rows + RC_ROWS - 1) / RC_ROWS, (unsigned)((tokens + RC_ROWS - 1) / RC_ROWS)), 256, RC_SMEM, stream>>>(
-            router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
-        LAUNCHED("router_chain_kernel");
     } else if (mode == 0) {
         if (tokens <= 1) {
             router_exact_kernel<1><<<dim3((rows + 31) / 32, (unsigned)tokens), dim3(32, 1), 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
@@ -1524,6 +1600,15 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
 // Expert-parallel pieces: route only / experts only (rows already gathered from all ranks,
 // ids local to this rank's shard, 0xffffffff = no expert) / shared expert + combine.
 // ------------------------------------------------------------------------------------
+extern "C" int qw4sh_group_rows(uint32_t experts, size_t rows, const uint32_t *ids, uint32_t *offsets, uint32_t *pair_to_row,
+                                uint32_t *row_to_pair, uint32_t *active, uint32_t *status, void *stream) {
+    if (!rows) return 0;
+    if (experts > 1024 || rows >= (1u << 20)) return fail(cudaErrorInvalidValue, "row dispatch: at most 1024 experts and 2^20 rows");
+    group_rows_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(experts, (uint32_t)rows, ids, offsets, pair_to_row, row_to_pair, active, status);
+    LAUNCHED("group_rows_kernel");
+    return 0;
+}
+
 extern "C" int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode) {
     if (!tokens) return 0;
     if (ensure_constants()) return -1;
@@ -1541,7 +1626,10 @@ extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *w
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t R = (uint32_t)rows, H = layer->hidden;
     int rc;
-    if (rows > 64 && work->dispatch_scratch) {
+    if (local_experts <= 1024) {
+        if ((rc = qw4sh_group_rows(local_experts, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status,
+                                   stream))) return rc;
+    } else if (rows > 64 && work->dispatch_scratch) {
         if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
                                     work->dispatch_scratch, work->status, stream))) return rc;
     } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
@@ -1646,7 +1734,10 @@ extern "C" int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork
     }
     uint32_t *local_ids = work->ids;
     if ((rc = qw4sh_ep_ids(msg, H, R, local_ids, stream))) return rc;
-    if (rows > 64 && work->dispatch_scratch) {
+    if (local_experts <= 1024) {
+        if ((rc = qw4sh_group_rows(local_experts, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status,
+                                   stream))) return rc;
+    } else if (rows > 64 && work->dispatch_scratch) {
         if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
                                     work->dispatch_scratch, work->status, stream))) return rc;
     } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
