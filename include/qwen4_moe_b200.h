@@ -330,8 +330,8 @@ void qw4cu_set_fused_decode(int mode);
  * TMEM accumulators (groups of <= 32 token rows per expert, exact integer codes as fp16 operands,
  * activations split into fp16 hi + lo).  -1 (default): used whenever the layer fits; 0: never. */
 void qw4cu_set_prefill_path(int path);
-/* Tile kernels: int8 tensor-core MMAs whose weight fragments are built once per group of <= 32 rows of an
- * expert (two-int8-digit activations, as in the decode kernels), for Q4_K and IQ2_XXS tensors.
+/* Tile kernels: int8 tensor-core MMAs whose weight fragments are built once per group of <= 16 rows of an
+ * expert (two-int8-digit activations staged in shared memory per group), for Q4_K, IQ2_XXS and Q2_K tensors.
  * -1 (default): batches of more than 64 rows that the tcgen05 prefill cannot take (IQ2_XXS tensors);
  * 0: never; 1: every batch of more than four rows. */
 void qw4cu_set_tile_path(int path);

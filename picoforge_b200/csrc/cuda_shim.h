@@ -160,9 +160,11 @@ int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, u
                                 float *xscale, void *stream);
 void qw4sh_launch_log_begin(void);
 size_t qw4sh_launch_log(char *out, size_t cap);
-/* Tile kernels (experts_tile.cu): int8 tensor-core products for groups of <= 32 rows. */
+/* Tile kernels (experts_tile.cu): int8 tensor-core products for groups of <= 16 rows. */
 int qw4sh_tile_supported(const QW4ShTensor *w, int mode);
 void qw4sh_set_tile_path(int path);         /* -1 automatic (default), 0 never, 1 every batch of > 4 rows */
+int qw4sh_build_tile_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream);
+int qw4sh_build_dense_tile_groups(uint32_t tokens, void *groups, uint32_t *n_groups, void *stream);
 int qw4sh_expert_tiles(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, const void *groups, const uint32_t *n_groups,
                        const uint32_t *row_to_pair, uint32_t k_div, const int8_t *digits, const int *sums, const float *scale,
                        float *out, uint32_t *status, int ctas, void *stream);

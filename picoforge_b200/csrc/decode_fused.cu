@@ -448,11 +448,16 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         if (exact) {
             if (lane == 0) {                                               // the reference's serial sum
                 uint32_t e = 0;
+                // the next eight values are loaded before the eight dependent adds of the current ones
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (E >= 8) { a = *reinterpret_cast<const float4 *>(p); b = *reinterpret_cast<const float4 *>(p + 4); }
 #pragma unroll 1
                 for (; e + 8 <= E; e += 8) {
-                    const float4 a = *reinterpret_cast<const float4 *>(p + e), b = *reinterpret_cast<const float4 *>(p + e + 4);
+                    float4 na = a, nb = b;
+                    if (e + 16 <= E) { na = *reinterpret_cast<const float4 *>(p + e + 8); nb = *reinterpret_cast<const float4 *>(p + e + 12); }
                     sum = __fadd_rn(sum, a.x); sum = __fadd_rn(sum, a.y); sum = __fadd_rn(sum, a.z); sum = __fadd_rn(sum, a.w);
                     sum = __fadd_rn(sum, b.x); sum = __fadd_rn(sum, b.y); sum = __fadd_rn(sum, b.z); sum = __fadd_rn(sum, b.w);
+                    a = na; b = nb;
                 }
                 for (; e < E; e++) sum = __fadd_rn(sum, p[e]);
             }

@@ -1499,14 +1499,14 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
     auto products = [&](int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, bool shared, const uint32_t *r2p, uint32_t k_div, const int8_t *q,
                         const int8_t *neg, const int *sums, const float *scale, float *out, cudaStream_t strm) -> int {
         if (tile)
-            return qw4sh_expert_tiles(mode, w0, w1, shared ? work->shared_groups32 : work->groups32, work->n_groups32 + (shared ? 1 : 0), r2p, k_div,
+            return qw4sh_expert_tiles(mode, w0, w1, shared ? (void *)shared_groups : work->groups, work->n_groups + (shared ? 1 : 0), r2p, k_div,
                                       q, sums, scale, out, work->status, ctas, strm);
         return qw4sh_grouped_mma(mode, w0, w1, shared ? (void *)shared_groups : work->groups, work->n_groups + (shared ? 1 : 0), r2p, k_div, q, neg,
                                  sums, scale, out, work->status, ctas, strm);
     };
     auto shared_branch = [&](int which) -> int {
         if (which == 0) {
-            if (tile) { if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, side))) return rc; }
+            if (tile) { if ((rc = qw4sh_build_dense_tile_groups(T, shared_groups, work->n_groups + 1, side))) return rc; }
             else if (!fused_route && (rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, side))) return rc;
             if (!STEP(4)) return 0;
             return products(0, &layer->w[4], &layer->w[5], true, nullptr, 1, work->xq, work->xneg, work->xsum, work->xscale, work->shared_act, side);
@@ -1534,7 +1534,7 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         if (mma && !tile && (rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         STAGE_MARK();
     }
-    if (tile && (rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+    if (tile && (rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
     if (mma) {
         if (overlap) {
             if ((rc = shared_branch(0)) || (rc = shared_branch(1))) return rc;
@@ -1637,12 +1637,12 @@ extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *w
                      qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) && (g_expert_path == 1 || rows <= 2048);
     if ((g_tile_path > 0 ? rows > 4 : g_tile_path < 0 && (rows > 2048 || !mma)) && g_expert_path != 0 && tile_types(layer)) {
         const int ctas = sm_count();
-        if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         if ((rc = qw4sh_quantize_rows(rows_x, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, 1, work->xq, work->xsum,
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xsum,
                                      work->xscale, work->act, work->status, ctas, stream))) return rc;
         if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, work->aq, work->asum,
+        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
                                   work->ascale, out, work->status, ctas, stream);
     }
     if (mma) {
@@ -1745,12 +1745,12 @@ extern "C" int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork
                      qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1);
     const int ctas = sm_count();
     if ((g_tile_path > 0 || (g_tile_path < 0 && (rows > 2048 || !mma))) && g_expert_path != 0 && tile_types(layer)) {
-        if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
+        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
         if ((rc = qw4sh_quantize_rows_pitched(msg, pitch, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, 1, work->xq, work->xsum,
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xsum,
                                      work->xscale, work->act, work->status, ctas, stream))) return rc;
         if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, work->aq, work->asum,
+        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
                                   work->ascale, out, work->status, ctas, stream);
     }
     if (mma) {

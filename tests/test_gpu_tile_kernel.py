@@ -1,4 +1,4 @@
-"""The tile kernels (groups of up to 32 rows per expert on the int8 tensor cores) against the CPU
+"""The tile kernels (groups of up to 16 rows per expert on the int8 tensor cores) against the CPU
 oracle and against the four-row grouped kernels: route ids bit-exact, y within 1e-3 (max abs)."""
 import sys
 from pathlib import Path
@@ -31,8 +31,8 @@ def _forward(gpu, spec, x, tile):
 @pytest.mark.parametrize("routed,shared,tokens,experts,top_k", [
     (12, 12, 5, 64, 10),      # one ragged column tile
     (16, 12, 16, 64, 10),     # IQ2_XXS routed + Q4_K shared
-    (12, 16, 33, 64, 6),      # dense shared groups of 32 + 1
-    (16, 16, 64, 16, 4),      # every expert sees several column tiles; groups split at 32 rows
+    (12, 16, 33, 64, 6),      # dense shared groups of 16 + 16 + 1
+    (16, 16, 64, 16, 4),      # every expert sees several column tiles; groups split at 16 rows
     (16, 12, 100, 64, 10),    # beyond the small-batch dispatch: bitmap dispatch + tile kernels
     (10, 12, 7, 64, 10),      # Q2_K routed: scales folded into the codes, minima through a second MMA
     (10, 10, 40, 32, 6),      # Q2_K everywhere
@@ -73,7 +73,7 @@ def test_tile_kernels_at_config_shapes(gpu):
 
 
 def test_skewed_routing_fills_whole_groups(gpu):
-    """A router that sends every token to the same experts: each list splits into full 32-row groups."""
+    """A router that sends every token to the same experts: each list splits into full 16-row groups."""
     import oracle
     from picoforge_b200 import abi, synth
     spec = synth.make_layer(11, routed_type=abi.IQ2_XXS, shared_type=abi.Q4_K, experts=64, top_k=4)
