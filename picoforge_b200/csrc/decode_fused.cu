@@ -417,7 +417,8 @@ __device__ __forceinline__ float fast_sigmoid(float v) {
 // bits); otherwise it is a warp tree sum.  Returns false (CTA-uniform) when a logit is not
 // finite; the first bad row is recorded.
 __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int norm, uint32_t T, bool exact, uint32_t *ids_s, float *wts_s,
-                                          float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status) {
+                                          float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status,
+                                          unsigned long long *probe) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) *flag = 1;
     __syncthreads();
@@ -442,6 +443,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], m), exp_table);
     }
     __syncthreads();
+    if (probe && tid == 0) probe[0] = clock64();
     if (warp < T) {
         float *p = zs + warp * FMAXE;
         float sum = 0.0f;
@@ -467,6 +469,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
             for (uint32_t e = lane; e < E; e += 32) sum += p[e];
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
+        if (probe && tid == 0) probe[1] = clock64();
         // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
         // The row stays in shared memory; every lane keeps the best two keys of its elements (e = lane,
         // lane + 32, ...), so a round is two warp reductions, and a lane rescans its elements only
@@ -486,6 +489,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         __syncwarp();
         uint32_t b1, e1, b2, e2;
         scan2(b1, e1, b2, e2);
+        if (probe && tid == 0) probe[2] = clock64();
         bool second_valid = true;
         float selected = 0.0f, mine = 0.0f;
 #pragma unroll 1
@@ -544,7 +548,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     const bool clocked = cta == 0 && tid == 0;
 #ifdef QW4_NO_PHASE_CLOCKS
 #define CLOCK(i) do { } while (0)
+#define ROUTE_PROBE nullptr
 #else
+#define ROUTE_PROBE (clocked ? clocks + 13 : nullptr)
 #define CLOCK(i) do { if (clocked) clocks[i] = clock64(); } while (0)
 #endif
     CLOCK(0);
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     if (bulk_logits && alive) alive = fbar_wait(xbar, 1, a.status);            // second use of this barrier: phase parity 1
     __syncthreads();
     CLOCK(5);
-    const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status);
+    const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status, ROUTE_PROBE);
     CLOCK(6);
     if (routed_ok) {
         if (tid < pairs) {
