@@ -417,8 +417,7 @@ __device__ __forceinline__ float fast_sigmoid(float v) {
 // bits); otherwise it is a warp tree sum.  Returns false (CTA-uniform) when a logit is not
 // finite; the first bad row is recorded.
 __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int norm, uint32_t T, bool exact, uint32_t *ids_s, float *wts_s,
-                                          float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status,
-                                          unsigned long long *probe) {
+                                          float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) *flag = 1;
     __syncthreads();
@@ -443,23 +442,28 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], m), exp_table);
     }
     __syncthreads();
-    if (probe && tid == 0) probe[0] = clock64();
     if (warp < T) {
-        float *p = zs + warp * FMAXE;
+        const float *p = zs + warp * FMAXE;
         float sum = 0.0f;
         if (exact) {
             if (lane == 0) {                                               // the reference's serial sum
+                // 32 values per round: the loads of the next round are issued before the 32 dependent adds of this
+                // one, and the loop overhead hides under the add chain (a lone warp issues every other cycle)
                 uint32_t e = 0;
-                // the next eight values are loaded before the eight dependent adds of the current ones
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (E >= 8) { a = *reinterpret_cast<const float4 *>(p); b = *reinterpret_cast<const float4 *>(p + 4); }
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = E >= 32 ? *reinterpret_cast<const float4 *>(p + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-                for (; e + 8 <= E; e += 8) {
-                    float4 na = a, nb = b;
-                    if (e + 16 <= E) { na = *reinterpret_cast<const float4 *>(p + e + 8); nb = *reinterpret_cast<const float4 *>(p + e + 12); }
-                    sum = __fadd_rn(sum, a.x); sum = __fadd_rn(sum, a.y); sum = __fadd_rn(sum, a.z); sum = __fadd_rn(sum, a.w);
-                    sum = __fadd_rn(sum, b.x); sum = __fadd_rn(sum, b.y); sum = __fadd_rn(sum, b.z); sum = __fadd_rn(sum, b.w);
-                    a = na; b = nb;
+                for (; e + 32 <= E; e += 32) {
+                    float4 w[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) w[j] = e + 64 <= E ? *reinterpret_cast<const float4 *>(p + e + 32 + 4 * j) : v[j];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        sum = __fadd_rn(sum, v[j].x); sum = __fadd_rn(sum, v[j].y); sum = __fadd_rn(sum, v[j].z); sum = __fadd_rn(sum, v[j].w);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = w[j];
                 }
                 for (; e < E; e++) sum = __fadd_rn(sum, p[e]);
             }
@@ -469,28 +473,37 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
             for (uint32_t e = lane; e < E; e += 32) sum += p[e];
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        if (probe && tid == 0) probe[1] = clock64();
+        if (lane == 0) scratch[4 + warp] = sum;
+    }
+    __syncthreads();
+    // the divisions are spread over all warps (the routing warps alone would do sixteen each, one after the other)
+#pragma unroll 1
+    for (uint32_t e = tid; e < E; e += FT) {                                   // the tokens' divisions of one column are independent: in flight together
+#pragma unroll
+        for (int r = 0; r < FTOK; r++)
+            if ((uint32_t)r < T) zs[r * FMAXE + e] = __fdiv_rn(zs[r * FMAXE + e], scratch[4 + r]);
+    }
+    __syncthreads();
+    if (warp < T) {
+        float *p = zs + warp * FMAXE;
         // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
-        // The row stays in shared memory; every lane keeps the best two keys of its elements (e = lane,
+        // The row stays in shared memory; every lane keeps the best three keys of its elements (e = lane,
         // lane + 32, ...), so a round is two warp reductions, and a lane rescans its elements only
-        // when it wins a second time after its last scan.
-        auto scan2 = [&](uint32_t &b1, uint32_t &e1, uint32_t &b2, uint32_t &e2) {
-            b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu;
+        // when it wins a third time after its last scan.
+        uint32_t b1, e1, b2, e2, b3, e3;
+        auto scan3 = [&]() {
+            b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu; b3 = 0; e3 = 0xffffffffu;
 #pragma unroll 4
             for (uint32_t e = lane; e < E; e += 32) {                              // ascending e: the lowest id wins among equals
                 const float v = p[e];
                 const uint32_t key = v < 0.0f ? 0u : __float_as_uint(v) + 1u;
-                if (key > b1) { b2 = b1; e2 = e1; b1 = key; e1 = e; }
-                else if (key > b2) { b2 = key; e2 = e; }
+                if (key > b1) { b3 = b2; e3 = e2; b2 = b1; e2 = e1; b1 = key; e1 = e; }
+                else if (key > b2) { b3 = b2; e3 = e2; b2 = key; e2 = e; }
+                else if (key > b3) { b3 = key; e3 = e; }
             }
         };
-#pragma unroll 4
-        for (uint32_t e = lane; e < E; e += 32) p[e] = __fdiv_rn(p[e], sum);
-        __syncwarp();
-        uint32_t b1, e1, b2, e2;
-        scan2(b1, e1, b2, e2);
-        if (probe && tid == 0) probe[2] = clock64();
-        bool second_valid = true;
+        scan3();
+        uint32_t spare = 2;                                                        // valid entries behind the first
         float selected = 0.0f, mine = 0.0f;
 #pragma unroll 1
         for (uint32_t slot = 0; slot < k; slot++) {
@@ -501,8 +514,8 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
             if (slot == lane) mine = value;
             if ((e_win & 31u) == lane) {                                           // only this lane's elements changed
                 p[e_win] = -1.0f;
-                if (second_valid) { b1 = b2; e1 = e2; second_valid = false; }
-                else { scan2(b1, e1, b2, e2); second_valid = true; }
+                if (spare) { b1 = b2; e1 = e2; b2 = b3; e2 = e3; spare--; }
+                else { scan3(); spare = 2; }
             }
             selected = __fadd_rn(selected, value);
         }
@@ -548,27 +561,21 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     const bool clocked = cta == 0 && tid == 0;
 #ifdef QW4_NO_PHASE_CLOCKS
 #define CLOCK(i) do { } while (0)
-#define ROUTE_PROBE nullptr
 #else
-#define ROUTE_PROBE (clocked ? clocks + 13 : nullptr)
 #define CLOCK(i) do { if (clocked) clocks[i] = clock64(); } while (0)
 #endif
     CLOCK(0);
 
-    if (tid == 0) {
-#pragma unroll 1
-        for (uint32_t i = 0; i < FW * FNS; i++) fbar_init(&ringbar[i], 1);
-#pragma unroll 1
-        for (uint32_t i = 0; i < FRCH; i++) fbar_init(&rowbar[i], 1);
-        fbar_init(lutbar, 1);
-        fbar_init(xbar, 1);
+    if (tid < FW * FNS + FRCH + 2) {                                           // the barriers lie one after the other: one thread each
+        fbar_init(&ringbar[tid], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 8) misc_f[tid] = 0.0f;
     unsigned long long *exp_table = reinterpret_cast<unsigned long long *>(smem + p.misc + 256);
-    if (tid < 32) exp_table[tid] = c_exp2_table[tid];
+    const unsigned long long exp_entry = tid < 32 ? c_exp2_table[tid] : 0ull;  // a global load: stored to shared memory once x has arrived
     float4 *xconsts = reinterpret_cast<float4 *>(smem + p.misc + 512);
     __syncthreads();
+    CLOCK(13);
 
     // ================================ phase A ================================
     const uint32_t n_rows = cta <= E ? (E - cta) / grid + 1 : 0;              // router rows cta, cta + grid, ... <= E
@@ -576,40 +583,41 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     uint8_t *rows = region + p.rows;
     const uint32_t chunk_bytes = H;                                            // H * 4 / FRCH
     if (warp == 0) {
+        // x first: it is what every warp waits for next
+        if (lane == 30) fbar_expect(xbar, T * H * 4u);
         if (lane < FRCH) fbar_expect(&rowbar[lane], n_rows * chunk_bytes);
         __syncwarp();
-        if (lane < n_rows * FRCH) {
-            const uint32_t j = lane / FRCH, c = lane % FRCH, r = cta + j * grid;
-            const uint8_t *src = r < E ? a.w[0].data + (uint64_t)r * a.w[0].row_bytes : a.w[7].data;
-            fbulk(rows + j * p.row_pitch + c * chunk_bytes, src + c * chunk_bytes, chunk_bytes, &rowbar[c]);
-        }
+        if (lane < T) fbulk(xf + lane * p.xf_pitch, a.x + (uint64_t)lane * H, H * 4u, xbar);
         if (LUT && lane == 31) {
             fbar_expect(lutbar, F_LUT_BYTES);
             fbulk(smem + p.lut, a.lut, F_LUT_BYTES, lutbar);
         }
-        if (lane == 30) fbar_expect(xbar, T * H * 4u);
-        __syncwarp();
-        if (lane < T) fbulk(xf + lane * p.xf_pitch, a.x + (uint64_t)lane * H, H * 4u, xbar);
-    } else if (warp == 1) {                                                    // the shared expert's tensors -> L2
-#pragma unroll
-        for (uint32_t m = 4; m <= 6; m++) {                                     // shared tensors are far below 4 GB
-            const uint32_t bytes = (uint32_t)a.w[m].expert_bytes & ~15u;
-            const uint32_t sub = ((bytes / (grid * 32u)) + 16u) & ~15u;
-            const uint32_t from = (cta * 32u + lane) * sub;
-            if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
-        }
+    } else if (warp >= 2 && warp < 2 + n_rows && lane < FRCH) {                // router row warp - 2: one request per chunk and lane.  (Requests cost
+        const uint32_t j = warp - 2, c = lane, r = cta + j * grid;             // the issuing warp some 50 cycles each, so they are dealt out; a copy
+        const uint8_t *src = r < E ? a.w[0].data + (uint64_t)r * a.w[0].row_bytes : a.w[7].data;      // may land before warp 0's expect.)
+        fbulk(rows + j * p.row_pitch + c * chunk_bytes, src + c * chunk_bytes, chunk_bytes, &rowbar[c]);
+    } else if (warp == 1 && lane < 3) {                                        // the shared expert's tensors -> L2: one request per tensor
+        const uint32_t m = 4 + lane;                                            // (a warp that issues dozens of them holds the CTA barrier up)
+        const uint32_t bytes = (uint32_t)a.w[m].expert_bytes & ~15u;            // shared tensors are far below 4 GB
+        const uint32_t sub = ((bytes / grid) + 16u) & ~15u;
+        const uint32_t from = cta * sub;
+        if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
     }
     // x -> shared memory (float, one bulk copy per row) with the row maxima, then digits; token rows beyond T stay zero
     bool alive = fbar_wait(xbar, 0, a.status);
+    if (tid < 32) exp_table[tid] = exp_entry;
+    CLOCK(14);
     {
         float m[FTOK] = {0.f, 0.f, 0.f, 0.f};
+        if (alive) {
+#pragma unroll 1
+            for (uint32_t c4 = tid; c4 < (H >> 2); c4 += FT) {                  // the rows' loads of one column are in flight together
 #pragma unroll
-        for (int q = 0; q < FTOK; q++) {
-            if ((uint32_t)q < T && alive) {
-#pragma unroll 2
-                for (uint32_t c4 = tid; c4 < (H >> 2); c4 += FT) {
-                    const float4 v = *reinterpret_cast<const float4 *>(xf + q * p.xf_pitch + c4 * 16);
-                    m[q] = fmaxf(m[q], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                for (int q = 0; q < FTOK; q++) {
+                    if ((uint32_t)q < T) {
+                        const float4 v = *reinterpret_cast<const float4 *>(xf + q * p.xf_pitch + c4 * 16);
+                        m[q] = fmaxf(m[q], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                    }
                 }
             }
         }
@@ -619,6 +627,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
             if (lane == 0 && v > 0.0f) atomicMax(reinterpret_cast<uint32_t *>(misc_f) + q, __float_as_uint(v));
         }
+        CLOCK(15);
 #pragma unroll 1
         for (uint32_t i = tid; i < (FTOK - T) * 2 * (p.kp >> 4); i += FT)       // digit rows of absent tokens
             reinterpret_cast<uint4 *>(xq + 2 * T * p.kp)[i] = make_uint4(0, 0, 0, 0);
@@ -732,7 +741,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     if (bulk_logits && alive) alive = fbar_wait(xbar, 1, a.status);            // second use of this barrier: phase parity 1
     __syncthreads();
     CLOCK(5);
-    const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status, ROUTE_PROBE);
+    const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status);
     CLOCK(6);
     if (routed_ok) {
         if (tid < pairs) {
@@ -813,7 +822,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         // down tiles of this CTA's columns -> L2, ahead of phase C
 #pragma unroll 1
         for (uint32_t tile = cta; tile < (H >> 4); tile += grid)
-            for (uint32_t j = tid; j < n_src; j += FT) {
+            for (uint32_t j = warp * 4 + lane; lane < 4 && j < n_src; j += FW * 4) {      // a few requests per warp: none of them falls behind
                 const Src s = srcs[j];
                 const uint32_t rb = s.shared ? (IS >> 8) * (ST == T_Q4_K ? 144u : 64u) : (I >> 8) * (RT == T_Q4_K ? 144u : 64u);
                 const uint8_t *mat = s.shared ? a.w[6].data : a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes;
@@ -906,12 +915,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             float *stage = reinterpret_cast<float *>(region + p.tiles);
             bool ok = __syncthreads_and(alive);                                    // CTA-uniform from here on: the digitiser meets at CTA barriers
             if (ok) {
-                if (warp == 0) {
+                if (tid == 0) fbar_expect(&rowbar[0], (pairs * I + T * IS) * 4u);
+                if (lane < 4) {                                                   // four requests per warp
                     asm volatile("fence.proxy.async;" ::: "memory");              // the rows were written through the generic proxy
-                    if (lane == 0) fbar_expect(&rowbar[0], (pairs * I + T * IS) * 4u);
-                    __syncwarp();
 #pragma unroll 1
-                    for (uint32_t r = lane; r < rows_c; r += 32) {
+                    for (uint32_t r = warp * 4 + lane; r < rows_c; r += FW * 4) {
                         if (r < pairs) fbulk(stage + r * I, a.act + (uint64_t)r * I, I * 4u, &rowbar[0]);
                         else fbulk(stage + pairs * I + (r - pairs) * IS, a.shared_act + (uint64_t)(r - pairs) * IS, IS * 4u, &rowbar[0]);
                     }
