@@ -447,7 +447,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         float sum = 0.0f;
         if (exact) {
             if (lane == 0) {                                               // the reference's serial sum
-                // 32 values per round: the loads of the next round are issued before the 32 dependent adds of this
+                // 32 values per pass: the loads of the next pass are issued before the 32 dependent adds of this
                 // one, and the loop overhead hides under the add chain (a lone warp issues every other cycle)
                 uint32_t e = 0;
                 float4 v[8];
@@ -488,7 +488,7 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
         float *p = zs + warp * FMAXE;
         // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
         // The row stays in shared memory; every lane keeps the best three keys of its elements (e = lane,
-        // lane + 32, ...), so a round is two warp reductions, and a lane rescans its elements only
+        // lane + 32, ...), so a selection step is two warp reductions, and a lane rescans its elements only
         // when it wins a third time after its last scan.
         uint32_t b1, e1, b2, e2, b3, e3;
         auto scan3 = [&]() {

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const uint32_t *__restric
                                                        uint32_t cap, float *__restrict__ msg, uint32_t pitch, uint32_t hidden,
                                                        uint32_t *__restrict__ slot_of_pair, uint32_t *status) {
     __shared__ uint32_t base[EP_MAX_WORLD];                  // rows placed so far, per destination
-    __shared__ uint32_t wcount[32][EP_MAX_WORLD];            // this round: rows of each warp per destination, then their first position
+    __shared__ uint32_t wcount[32][EP_MAX_WORLD];            // this batch of 1024 pairs: rows of each warp per destination, then their first position
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     uint32_t *words = reinterpret_cast<uint32_t *>(msg);
     for (uint32_t s = tid; s < world * cap; s += 1024) words[(uint64_t)s * pitch + hidden] = 0xffffffffu;

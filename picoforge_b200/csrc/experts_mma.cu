@@ -132,7 +132,8 @@ template <uint32_t TYPE, int MODE>
 __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
     Plan p;
     const uint32_t nb = k_storage / 256;
-    p.unit_rows = MODE == 0 ? 16 : 128;
+    p.unit_rows = MODE == 0 ? 32 : 128;                                 // gate/up: two 16-row tiles per unit, so that the barriers and the
+                                                                         // partial-sum exchange of a unit are paid once per 32 rows
     p.matrices = MODE == 0 ? 2 : 1;
     p.kp = k_storage + 32;
     p.pitch = Fmt<TYPE>::pitch(nb);
@@ -147,7 +148,7 @@ __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
     p.meta = b; b += 64;                                                 // [0..3] pair, [4] count, [8..11] float scale
     p.bslot_bytes = (b + 127) & ~127u;
     p.bslot = at; at += 2 * p.bslot_bytes;
-    p.partial = at; at += 2 * CW * 64 * 4;                               // [parity][warp][64 floats]
+    p.partial = at; at += 2 * CW * 128 * 4;                              // [parity][warp][128 floats] (gate/up: two row tiles; down uses 64)
     at = (at + 127) & ~127u;
     p.dsec = p.unit_rows * p.pitch;                                      // IQ2_XXS: fp16 d after the payload rows
     uint32_t per_matrix = p.unit_rows * p.pitch + (TYPE == T_IQ2_XXS ? ((p.unit_rows * nb * 2 + 15) & ~15u) : 0);
@@ -369,11 +370,14 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
         if (alive && lane == 0) alive = mbar_wait(&full[stage], phase, a.status);
         alive = __shfl_sync(0xffffffffu, alive, 0);
         const uint8_t *st = smem + p.stages + stage * p.stage_bytes;
-        float facc[2] = {0.0f, 0.0f};
-        if (MODE == 0) {                                                 // warp = (matrix, k-slice of 8)
+        float facc[2] = {0.0f, 0.0f}, facc2[2] = {0.0f, 0.0f};
+        if (MODE == 0) {                                                 // warp = (matrix, k-slice of 8), both row tiles of the unit
             const uint32_t m = warp & 1u, ks = warp >> 1;
             if (alive)
-                for (uint32_t h = ks; h < halves; h += 8) Consume<TYPE>::half_block(st + m * p.per_matrix, p, smem + p.lut, act, nb, 0, h, g, t, facc);
+                for (uint32_t h = ks; h < halves; h += 8) {
+                    Consume<TYPE>::half_block(st + m * p.per_matrix, p, smem + p.lut, act, nb, 0, h, g, t, facc);
+                    Consume<TYPE>::half_block(st + m * p.per_matrix, p, smem + p.lut, act, nb, 16, h, g, t, facc2);
+                }
         } else {                                                         // warp = (row tile of 8, k-slice of 2)
             const uint32_t rt = warp & 7u, ks = warp >> 3;
             if (alive)
@@ -382,20 +386,21 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);
         if (++stage == p.n_stages) { stage = 0; phase ^= 1u; }
-        float *mine = partial + (parity * CW + warp) * 64;
+        float *mine = partial + (parity * CW + warp) * 128;
         mine[lane] = facc[0];                                            // (row g, token t) at 4g + t
         mine[32 + lane] = facc[1];                                       // (row g + 8, token t)
+        if (MODE == 0) { mine[64 + lane] = facc2[0]; mine[96 + lane] = facc2[1]; }     // rows 16 + g, 24 + g
         consumer_sync();
-        const float *part = partial + parity * CW * 64;
+        const float *part = partial + parity * CW * 128;
         const uint32_t *meta = reinterpret_cast<const uint32_t *>(act + p.meta);
         const float *tokscale = reinterpret_cast<const float *>(act + p.meta) + 8;
         const uint32_t count = meta[4];
         if (MODE == 0) {
-            if (tid < 64) {                                              // 16 rows x 4 tokens
+            if (tid < 128) {                                             // 32 rows x 4 tokens
                 const uint32_t row = tid >> 2, tok = tid & 3u;
                 float gsum = 0.0f, usum = 0.0f;
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) { gsum += part[(2 * ks) * 64 + tid]; usum += part[(2 * ks + 1) * 64 + tid]; }
+                for (int ks = 0; ks < 8; ks++) { gsum += part[(2 * ks) * 128 + tid]; usum += part[(2 * ks + 1) * 128 + tid]; }
                 if (tok < count) {
                     const float dx = tokscale[tok];
                     gsum *= dx; usum *= dx;
@@ -408,7 +413,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
             }
         } else {                                                         // 128 rows x 4 tokens: every consumer thread
             const uint32_t rt = tid >> 6, within = tid & 63u, tok = within & 3u;
-            const float sum = (part[rt * 64 + within] + part[(8 + rt) * 64 + within]) * tokscale[tok];
+            const float sum = (part[rt * 128 + within] + part[(8 + rt) * 128 + within]) * tokscale[tok];
             if (tok < count) {
                 if ((__float_as_uint(sum) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
                 a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + rt * 16 + (within >> 2)] = sum;
@@ -548,7 +553,7 @@ __global__ void __launch_bounds__(1024) build_groups_kernel(const uint32_t *__re
         uint32_t at = s_base + wsum[warp] + scan - count;
         for (uint32_t r = first; r < end; r += TOK) groups[at++] = VGroup{e, r, min((uint32_t)TOK, end - r), 0};
         __syncthreads();
-        if (tid == 1023) s_base = at;                                // end of the last thread = end of the round
+        if (tid == 1023) s_base = at;                                // end of the last thread = end of this pass
         __syncthreads();
     }
     if (tid == 0) *n_groups = s_base;
@@ -590,7 +595,7 @@ static const uint8_t *lut_image() {
 extern "C" int qw4sh_mma_supported(const QW4ShTensor *w, int mode) {
     if (w->type != T_Q4_K && w->type != T_IQ2_XXS) return 0;
     if (w->k_storage % 256 || w->k_storage > KMAX || w->k_logical != w->k_storage) return 0;
-    if (w->n_out % (mode == 0 ? 16 : 128)) return 0;
+    if (w->n_out % (mode == 0 ? 32 : 128)) return 0;
     return 1;
 }
 

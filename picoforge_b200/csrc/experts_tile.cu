@@ -305,15 +305,15 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
     bool alive = true;
     if (LUT) alive = tbar_wait(lutbar, 0, a.status);                           // also without work: no copy may be in flight when the CTA leaves
     const uint8_t *bl = digits_s + g * kp + 8 * t;                              // digit row g of a column tile, this lane's column phase
-    // A work item is (group, part): with few groups each group's row tiles are dealt to `parts` CTAs, one round of TW
+    // A work item is (group, part): with few groups each group's row tiles are dealt to `parts` CTAs, one pass of TW
     // tiles at a time (every CTA of a group stages the group's digits for itself); with many groups a CTA takes whole
     // groups and stages the digits once for all of the expert's tiles.
     const uint32_t rounds = (tiles + TW - 1) / TW;
-    const uint32_t parts = n_groups < 2 * gridDim.x ? rounds : 1u;             // restaging the digits costs a few percent of a round
+    const uint32_t parts = n_groups < 2 * gridDim.x ? rounds : 1u;             // restaging the digits costs a few percent of a pass
     uint32_t ring_base = 0;                                                     // slices this warp has pushed through its ring
-    uint32_t round = 0;
+    uint32_t turn = 0;                                                          // items this CTA has taken: parity of the digits barrier
 #pragma unroll 1
-    for (uint32_t item = blockIdx.x; item < n_groups * parts; item += gridDim.x, round++) {
+    for (uint32_t item = blockIdx.x; item < n_groups * parts; item += gridDim.x, turn++) {
         const uint32_t gi = item / parts, part = item % parts;
         const uint32_t tile0 = warp + TW * part, tile_step = TW * parts;       // this warp's row tiles: tile0, tile0 + tile_step, ...
         const uint32_t mine = tiles > tile0 ? (tiles - 1 - tile0) / tile_step + 1 : 0;
@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
             const uint32_t row_t = __shfl_sync(0xffffffffu, my_row, (4 * q + t) & 31u);
             xs[q] = 4u * q + t < count ? __ldg(a.scale + row_t) : 0.0f;
         }
-        if (alive) alive = tbar_wait(digitbar, round & 1u, a.status);
+        if (alive) alive = tbar_wait(digitbar, turn & 1u, a.status);
 #pragma unroll 1
         for (uint32_t n = 0; n < slices; n++) {
             const uint32_t s = n % spu, at = ring_base + n;
@@ -483,7 +483,7 @@ __global__ void __launch_bounds__(1024) build_tile_groups_kernel(const uint32_t 
         uint32_t at = s_base + wsum[warp] + scan - count;
         for (uint32_t r = first; r < end; r += TROWS) groups[at++] = TGroup{e, r, min(TROWS, end - r), 0};
         __syncthreads();
-        if (tid == 1023) s_base = at;                                // end of the last thread = end of the round
+        if (tid == 1023) s_base = at;                                // end of the last thread = end of this pass
         __syncthreads();
     }
     if (tid == 0) *n_groups = s_base;

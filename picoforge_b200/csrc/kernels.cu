@@ -811,7 +811,7 @@ __global__ void __launch_bounds__(1024) group_rows_kernel(uint32_t experts, uint
         const uint32_t rank = __popc(same & ((1u << lane) - 1u)), leader = __ffs(same) - 1;
         const uint32_t warps = min(32u, (rows - r0 + 31) / 32);
         uint32_t base = 0;
-        for (uint32_t w = 0; w < warps; w++) {                     // the warps of this round in turn: stable across warps
+        for (uint32_t w = 0; w < warps; w++) {                     // the warps of this batch in turn: stable across warps
             if (warp == w && ok && rank == 0) { base = cursor[e]; cursor[e] = base + __popc(same); }
             __syncthreads();
         }

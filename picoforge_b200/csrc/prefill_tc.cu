@@ -526,7 +526,7 @@ __global__ void __launch_bounds__(1024) build_groups32_kernel(const uint32_t *__
         uint32_t at = s_base + wsum[warp] + scan - count;
         for (uint32_t r = first; r < end; r += PT_TOK) groups[at++] = PGroup{e, r, min(PT_TOK, end - r), 0};
         __syncthreads();
-        if (tid == 1023) s_base = at;                                // inclusive end of the last thread = end of the round
+        if (tid == 1023) s_base = at;                                // inclusive end of the last thread = end of this pass
         __syncthreads();
     }
     if (tid == 0) *n_groups = s_base;
