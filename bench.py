@@ -580,7 +580,7 @@ def main():
         "layer": {"weight_bytes": layer_bytes, "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / hbm_peak,
                   "frac_of_nominal_8tbs": layer_gbs / NOMINAL_HBM_GBS,
                   "stage_us_multi_kernel_path": stage_us, "stage_bytes": bytes_by_stage},
-        "e2e": {"value": e2e_us_per_token, "unit": "us/token", "h2d_bytes_per_step": int(x.nbytes) + 16,
+        "e2e": {"value": e2e_us_per_token, "unit": "us/token", "h2d_bytes_per_step": int(x.nbytes),   # status words: cleared only after an error
                 "d2h_bytes_per_step": int(x.nbytes) + 16, "steps": e2e_steps},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
