@@ -595,7 +595,6 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
                                                                 uint32_t *__restrict__ n_groups, uint32_t *status) {
     __shared__ __align__(16) float p[512];
     __shared__ float wred[16];
-    __shared__ float2 wbest[2][16];
     __shared__ float s_sum;
     __shared__ uint32_t s_bad, s_last, wsum[16];
     extern __shared__ uint32_t sids[];                         // [tokens * k] for the dispatch step
@@ -632,30 +631,47 @@ __global__ void __launch_bounds__(512) route_group_small_kernel(uint32_t experts
         }
         __syncthreads();
         if (e < experts) { value = __fdiv_rn(p[e], s_sum); probs[(uint64_t)t * experts + e] = value; }
-        float selected = 0.0f, mine = 0.0f;
-        for (uint32_t slot = 0; slot < k; slot++) {
-            float best = value;
-            uint32_t best_e = e;
-            for (int o = 16; o; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        // Selection by one warp over the row in shared memory: lane L owns experts L, L + 32, ... and keeps the best
+        // three of them in registers (keys: float bits + 1, a chosen entry becomes -1 = key 0), so a slot costs two
+        // warp reductions; a lane rescans its experts only when it wins a third time after its last scan.  Ties go
+        // to the lower id, the sum of the chosen probabilities runs in slot order (the reference's order).
+        __syncthreads();                                       // every thread has read its exp value out of p
+        p[e] = e < experts ? value : -1.0f;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t b1, e1, b2, e2, b3, e3;
+            auto scan3 = [&]() {
+                b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu; b3 = 0; e3 = 0xffffffffu;
+#pragma unroll 4
+                for (uint32_t i = lane; i < experts; i += 32) {            // ascending ids: the lowest wins among equals
+                    const float v = p[i];
+                    const uint32_t key = v < 0.0f ? 0u : __float_as_uint(v) + 1u;
+                    if (key > b1) { b3 = b2; e3 = e2; b2 = b1; e2 = e1; b1 = key; e1 = i; }
+                    else if (key > b2) { b3 = b2; e3 = e2; b2 = key; e2 = i; }
+                    else if (key > b3) { b3 = key; e3 = i; }
+                }
+            };
+            scan3();
+            uint32_t spare = 2;
+            float selected = 0.0f;
+            for (uint32_t slot = 0; slot < k; slot++) {
+                const uint32_t top = __reduce_max_sync(0xffffffffu, b1);
+                const uint32_t e_win = __reduce_min_sync(0xffffffffu, b1 == top ? e1 : 0xffffffffu);
+                const float best = __uint_as_float(top - 1u);
+                if (lane == 0) { ids[(uint64_t)t * k + slot] = e_win; sids[slot] = top - 1u; }    // sids: free until the dispatch step
+                if ((e_win & 31u) == lane) {
+                    p[e_win] = -1.0f;
+                    if (spare) { b1 = b2; e1 = e2; b2 = b3; e2 = e3; spare--; }
+                    else { scan3(); spare = 2; }
+                }
+                selected = __fadd_rn(selected, best);
             }
-            if (lane == 0) wbest[slot & 1u][warp] = make_float2(best, __uint_as_float(best_e));
-            __syncthreads();
-            best = -2.0f; best_e = 0xffffffffu;
-#pragma unroll
-            for (int w = 0; w < 16; w++) {
-                const float2 c = wbest[slot & 1u][w];
-                const uint32_t ce = __float_as_uint(c.y);
-                if (c.x > best || (c.x == best && ce < best_e)) { best = c.x; best_e = ce; }
+            __syncwarp();
+            for (uint32_t slot = lane; slot < k; slot += 32) {
+                const float raw = __uint_as_float(sids[slot]);
+                weights[(uint64_t)t * k + slot] = norm ? __fdiv_rn(raw, selected) : raw;
             }
-            if (e == best_e) value = -1.0f;                    // probabilities are >= 0: never chosen again
-            if (e == 0) ids[(uint64_t)t * k + slot] = best_e;
-            if (e == slot) mine = best;                        // thread s keeps the weight of slot s (k <= 512)
-            selected = __fadd_rn(selected, best);
         }
-        if (e < k) weights[(uint64_t)t * k + e] = norm ? __fdiv_rn(mine, selected) : mine;
     }
     // ---- the CTA that arrives last does the dispatch for all tokens ----
     __threadfence();
