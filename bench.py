@@ -298,7 +298,7 @@ def run_expert_parallel(args, rank: int, local_rank: int, world: int) -> None:
                        "tokens_per_step": tokens, "layers": n_layers,
                        "parallelism": f"expert parallel, {epr} experts per GPU, router and shared expert replicated, tokens data-parallel",
                        "exchange": "torch.distributed all_to_all_single over NCCL, two per layer (rows with their expert ids, outputs); the shared expert runs on a second stream under the exchange",
-                       "same_workload_on_one_gpu": "python bench.py --workload c4 (no exchange; 180 us per layer measured)",
+                       "same_workload_on_one_gpu": "python bench.py --workload c4 (no exchange; 174 us per layer measured)",
                        "router": args.router, "l2": f"{n_layers} layers of weights per step ({touched / world / 1e6:.0f} MB per GPU), L2 is 126 MB",
                        "distinct_experts_per_layer": distinct / n_layers},
             "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",

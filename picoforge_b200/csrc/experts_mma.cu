@@ -132,8 +132,8 @@ template <uint32_t TYPE, int MODE>
 __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
     Plan p;
     const uint32_t nb = k_storage / 256;
-    p.unit_rows = MODE == 0 ? 32 : 128;                                 // gate/up: two 16-row tiles per unit, so that the barriers and the
-                                                                         // partial-sum exchange of a unit are paid once per 32 rows
+    p.unit_rows = MODE == 0 ? 32 : 256;                                 // two row tiles per warp and unit, so that the barriers and the
+                                                                         // partial-sum exchange of a unit are paid half as often
     p.matrices = MODE == 0 ? 2 : 1;
     p.kp = k_storage + 32;
     p.pitch = Fmt<TYPE>::pitch(nb);
@@ -148,7 +148,7 @@ __host__ __device__ inline Plan make_plan(uint32_t k_storage) {
     p.meta = b; b += 64;                                                 // [0..3] pair, [4] count, [8..11] float scale
     p.bslot_bytes = (b + 127) & ~127u;
     p.bslot = at; at += 2 * p.bslot_bytes;
-    p.partial = at; at += 2 * CW * 128 * 4;                              // [parity][warp][128 floats] (gate/up: two row tiles; down uses 64)
+    p.partial = at; at += 2 * CW * 128 * 4;                              // [parity][warp][128 floats]: two row tiles of 64 values per warp
     at = (at + 127) & ~127u;
     p.dsec = p.unit_rows * p.pitch;                                      // IQ2_XXS: fp16 d after the payload rows
     uint32_t per_matrix = p.unit_rows * p.pitch + (TYPE == T_IQ2_XXS ? ((p.unit_rows * nb * 2 + 15) & ~15u) : 0);
@@ -381,7 +381,10 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
         } else {                                                         // warp = (row tile of 8, k-slice of 2)
             const uint32_t rt = warp & 7u, ks = warp >> 3;
             if (alive)
-                for (uint32_t h = ks; h < halves; h += 2) Consume<TYPE>::half_block(st, p, smem + p.lut, act, nb, rt * 16, h, g, t, facc);
+                for (uint32_t h = ks; h < halves; h += 2) {
+                    Consume<TYPE>::half_block(st, p, smem + p.lut, act, nb, rt * 16, h, g, t, facc);
+                    Consume<TYPE>::half_block(st, p, smem + p.lut, act, nb, 128 + rt * 16, h, g, t, facc2);
+                }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
         float *mine = partial + (parity * CW + warp) * 128;
         mine[lane] = facc[0];                                            // (row g, token t) at 4g + t
         mine[32 + lane] = facc[1];                                       // (row g + 8, token t)
-        if (MODE == 0) { mine[64 + lane] = facc2[0]; mine[96 + lane] = facc2[1]; }     // rows 16 + g, 24 + g
+        mine[64 + lane] = facc2[0]; mine[96 + lane] = facc2[1];          // the second row tile: rows 16 + g, 24 + g (gate/up) or 128 + ... (down)
         consumer_sync();
         const float *part = partial + parity * CW * 128;
         const uint32_t *meta = reinterpret_cast<const uint32_t *>(act + p.meta);
@@ -411,12 +414,15 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
                     a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + row] = v;
                 }
             }
-        } else {                                                         // 128 rows x 4 tokens: every consumer thread
+        } else {                                                         // 256 rows x 4 tokens: two per consumer thread
             const uint32_t rt = tid >> 6, within = tid & 63u, tok = within & 3u;
-            const float sum = (part[rt * 128 + within] + part[(8 + rt) * 128 + within]) * tokscale[tok];
             if (tok < count) {
-                if ((__float_as_uint(sum) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
-                a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + rt * 16 + (within >> 2)] = sum;
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const float sum = (part[rt * 128 + half * 64 + within] + part[(8 + rt) * 128 + half * 64 + within]) * tokscale[tok];
+                    if ((__float_as_uint(sum) & 0x7f800000u) == 0x7f800000u) atomicOr(a.status, QW4SH_ERR_NONFINITE);
+                    a.out[(uint64_t)meta[tok] * a.w0.n_out + row_tile + half * 128 + rt * 16 + (within >> 2)] = sum;
+                }
             }
         }
         parity ^= 1u;
@@ -595,7 +601,7 @@ static const uint8_t *lut_image() {
 extern "C" int qw4sh_mma_supported(const QW4ShTensor *w, int mode) {
     if (w->type != T_Q4_K && w->type != T_IQ2_XXS) return 0;
     if (w->k_storage % 256 || w->k_storage > KMAX || w->k_logical != w->k_storage) return 0;
-    if (w->n_out % (mode == 0 ? 32 : 128)) return 0;
+    if (w->n_out % (mode == 0 ? 32 : 256)) return 0;
     return 1;
 }
 
