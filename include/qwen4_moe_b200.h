@@ -370,20 +370,25 @@ Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *moe, uint32_t tensor, size_t e
 /* Dispatch lists for ids that are already in device memory, computed WITHOUT allocating
  * anything.  This entry point has no counterpart in the reference.  It is for callers that
  * must not allocate while they run: a decode loop that has given all spare HBM to weights and
- * caches (where cudaMalloc can fail and in any case stalls the device), or host code that is
- * inside a stream capture, where cudaMalloc is not allowed.  The caller passes inputs and
- * outputs, all device pointers: ids_dev [tokens, top_k] dense uint32; offsets_dev
+ * caches, where cudaMalloc can fail and in any case stalls the device.  The caller passes
+ * inputs and outputs, all device pointers: ids_dev [tokens, top_k] dense uint32; offsets_dev
  * [experts + 1], pair_to_row_dev and row_to_pair_dev [tokens * top_k] uint32.  The kernel's own
  * working memory is a fixed array built into the library (about 33 KB of every GPU that loads
  * it, until exit), which limits a call to QW4CU_NOALLOC_MAX_EXPERTS experts and
- * QW4CU_NOALLOC_MAX_PAIRS pairs; more returns QW4_CAPACITY with the limit in the message.
+ * QW4CU_NOALLOC_MAX_PAIRS pairs; more returns QW4_CAPACITY with the limit in the message.  One
+ * CTA does the work in `pairs` loop steps, about a millisecond at the pair limit.
  * The first call on each device looks up the array's device address, so make that call before
  * any stream capture begins.  All calls share the array: calls that overlap on the GPU race,
- * so serialise them.  Runs on the default stream and returns when the lists are complete.
+ * so serialise them.
+ * Stream: the kernel is enqueued on the stream the library uses at that moment (the one given
+ * to qw4cu_set_stream, else the library's own stream once a workspace exists on the device,
+ * else the legacy default stream), behind earlier library calls on it, so ids produced by
+ * qw4cu_moe_route_device need no synchronisation in between.  The call then waits for that
+ * stream and returns when the lists are complete.
  * Ids are taken to be distinct within a token (routing produces them so); an id >= experts
  * returns QW4_RANGE and leaves the outputs unspecified. */
 #define QW4CU_NOALLOC_MAX_EXPERTS 4096
-#define QW4CU_NOALLOC_MAX_PAIRS (1 << 22)
+#define QW4CU_NOALLOC_MAX_PAIRS (1 << 18)
 Qwen4Status qw4cu_group_pairs_device_noalloc(uint32_t experts, uint32_t top_k, size_t tokens,
                                              const uint32_t *ids_dev, uint32_t *offsets_dev,
                                              uint32_t *pair_to_row_dev, uint32_t *row_to_pair_dev,
@@ -398,6 +403,8 @@ int qw4cu_upload(void *device_dst, const void *host_src, size_t bytes);
 int qw4cu_download(void *host_dst, const void *device_src, size_t bytes);
 /* Writes `bytes` of a scratch buffer larger than L2 so that the next kernel starts cold. */
 int qw4cu_flush_l2(void);
+/* Free and total bytes of the current device (cudaMemGetInfo); 0 on success. */
+int qw4cu_mem_info(size_t *free_bytes, size_t *total_bytes);
 int qw4cu_device_synchronize(void);
 
 #ifdef __cplusplus

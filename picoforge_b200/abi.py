@@ -231,6 +231,7 @@ class MoeApi:
             "qw4cu_upload": ([P, P, C.c_size_t], C.c_int),
             "qw4cu_download": ([P, P, C.c_size_t], C.c_int),
             "qw4cu_flush_l2": ([], C.c_int),
+            "qw4cu_mem_info": ([C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)], C.c_int),
             "qw4cu_device_synchronize": ([], C.c_int),
         }
         for name, (argtypes, restype) in sig.items():

@@ -190,6 +190,9 @@ int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const 
 /* Caller-provided stream (NULL: back to the library's own).  current_stream returns the one in force. */
 int qw4sh_set_stream(void *stream);
 int qw4sh_current_stream(void **stream);
+/* The stream in force without creating one (NULL: the legacy default stream). */
+int qw4sh_existing_stream(void **stream);
+int qw4sh_mem_info(size_t *free_bytes, size_t *total_bytes);
 
 #ifdef __cplusplus
 }

@@ -1486,8 +1486,13 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
                           uint32_t *ids_out, float *weights_out, int router_mode, bool timed) {
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
-    if (!timed && g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count()))
-        return qw4sh_fused_decode(layer, work, x, y, tokens, ids_out, weights_out, router_mode, sm_count());
+    if (!timed && g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count())) {
+        // a cooperative grid that cannot be resident all at once (another context holds SMs) is refused
+        // at launch: the multi-kernel sequence below does the same work
+        const int fused_rc = qw4sh_fused_decode(layer, work, x, y, tokens, ids_out, weights_out, router_mode, sm_count());
+        if (fused_rc != (int)cudaErrorCooperativeLaunchTooLarge) return fused_rc;
+        (void)cudaGetLastError();
+    }
     const bool tile = tile_path(layer, tokens);
     const bool mma = tile || mma_path(layer, tokens);
     const bool fused_route = mma && T <= 64 && E <= 512 && k <= E && T * k < 4096;
@@ -1820,6 +1825,22 @@ extern "C" int qw4sh_current_stream(void **stream) {
     CU(cudaGetDevice(&device));
     if (device >= 0 && device < 64 && g_user_stream_set[device]) { *stream = g_user_stream[device]; return 0; }
     return qw4sh_shared_stream(stream);
+}
+
+// The stream in force WITHOUT creating one: the caller's (qw4sh_set_stream), else the library's own if a
+// workspace has already made it, else the legacy default stream (nullptr).
+extern "C" int qw4sh_existing_stream(void **stream) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    *stream = nullptr;
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    if (g_user_stream_set[device]) *stream = g_user_stream[device];
+    else if (g_stream[device]) *stream = g_stream[device];
+    return 0;
+}
+extern "C" int qw4sh_mem_info(size_t *free_bytes, size_t *total_bytes) {
+    CU(cudaMemGetInfo(free_bytes, total_bytes));
+    return 0;
 }
 
 extern "C" int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]) {

@@ -8,6 +8,7 @@
 #include "cuda_shim.h"
 
 #include <math.h>
+#include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -45,21 +46,22 @@ struct Qwen4MoeWork {
 typedef struct { uintptr_t first, end; } Span;
 
 /* ---- errors --------------------------------------------------------------------------- */
-static Qwen4Status report(Qwen4Error *err, Qwen4Status code, const char *detail) {
-    if (err) {
-        memset(err, 0, sizeof *err);
-        err->code = code;
-        if (code != QW4_OK) {
-            snprintf(err->subject, sizeof err->subject, "qwen4_moe");
-            snprintf(err->detail, sizeof err->detail, "%s", detail);
-        }
-    }
+/* Fills *err (when given) and hands the code back, so that `return raise(...)` reads as one step. */
+static Qwen4Status raise(Qwen4Error *err, Qwen4Status code, const char *format, ...) {
+    if (!err) return code;
+    memset(err, 0, sizeof *err);
+    err->code = code;
+    if (code == QW4_OK) return code;
+    strncpy(err->subject, "qwen4_moe", sizeof err->subject - 1);
+    va_list args;
+    va_start(args, format);
+    vsnprintf(err->detail, sizeof err->detail, format, args);
+    va_end(args);
     return code;
 }
+#define report(err, code, text) raise((err), (code), "%s", (text))
 static Qwen4Status cuda_failure(Qwen4Error *err, const char *what) {
-    char text[256];
-    snprintf(text, sizeof text, "%s: %s", what, qw4sh_last_error());
-    return report(err, QW4_GPU_ERROR, text);
+    return raise(err, QW4_GPU_ERROR, "%s: %s", what, qw4sh_last_error());
 }
 #define TRY(call) do { Qwen4Status st_ = (call); if (st_ != QW4_OK) return st_; } while (0)
 
@@ -74,45 +76,64 @@ static int current_router_mode(void) {
 void qw4cu_set_router_mode(int mode) { router_mode = mode ? 1 : 0; }
 int qw4cu_get_router_mode(void) { return current_router_mode(); }
 
-/* ---- view checks (status codes as picoforge src/qwen4_moe.c:138-186) ------------------ */
-static Qwen4Status check_config(const Qwen4MoeConfig *c, Qwen4Error *err) {
-    if (!c) return report(err, QW4_INVALID_ARGUMENT, "null config");
-    if (!c->hidden_size || !c->experts || !c->top_k || c->top_k > c->experts || !c->intermediate ||
-        !c->shared_intermediate || c->down_physical < c->intermediate)
-        return report(err, QW4_RANGE, "invalid MoE dimensions");
+/* ---- argument views ---------------------------------------------------------------------
+ * Every caller-owned array an entry point touches is described once as a Region (rows of
+ * `cols` elements, `pitch` bytes apart) and validated by region_span, which also yields the
+ * address range used for the overlap checks.  The status code of each defect and the order in
+ * which defects are reported are the boundary contract (picoforge src/qwen4_moe.c:134-186):
+ * shape, element stride, row-size overflow, row pitch, extent overflow, capacity, null,
+ * alignment, address overflow. */
+typedef struct {
+    const char *name;
+    const void *base;
+    size_t capacity;              /* bytes the caller declares addressable */
+    size_t rows, cols, pitch;     /* pitch in bytes */
+    size_t elem;                  /* bytes per element; also the required alignment of base */
+} Region;
+
+static Qwen4Status region_span(const Region *r, Span *span, Qwen4Error *err) {
+    *span = (Span){0, 0};
+    if (r->cols > SIZE_MAX / r->elem) return raise(err, QW4_OVERFLOW, "%s: a row does not fit size_t", r->name);
+    const size_t row = r->cols * r->elem;
+    if (r->pitch < row || r->pitch % r->elem) return raise(err, QW4_STRIDE, "%s: row pitch %zu cannot hold %zu-byte rows", r->name, r->pitch, row);
+    if (r->rows == 0) return QW4_OK;
+    if (r->rows - 1 > (SIZE_MAX - row) / r->pitch) return raise(err, QW4_OVERFLOW, "%s: extent does not fit size_t", r->name);
+    const size_t extent = (r->rows - 1) * r->pitch + row;
+    if (extent == 0) return QW4_OK;
+    if (r->capacity < extent) return raise(err, QW4_CAPACITY, "%s: %zu bytes declared, %zu needed", r->name, r->capacity, extent);
+    if (r->base == NULL) return raise(err, QW4_INVALID_ARGUMENT, "%s: null data for a nonempty view", r->name);
+    const uintptr_t at = (uintptr_t)r->base;
+    if (at % r->elem) return raise(err, QW4_STRIDE, "%s: data not aligned to %zu bytes", r->name, r->elem);
+    if (extent > UINTPTR_MAX - at) return raise(err, QW4_OVERFLOW, "%s: address range wraps", r->name);
+    *span = (Span){at, at + extent};
     return QW4_OK;
 }
-static Qwen4Status check_memory(const void *data, size_t cap, size_t bytes, size_t alignment, Span *span, Qwen4Error *err) {
-    span->first = span->end = 0;
-    if (!bytes) return QW4_OK;
-    if (cap < bytes) return report(err, QW4_CAPACITY, "view capacity too small");
-    if (!data) return report(err, QW4_INVALID_ARGUMENT, "null nonempty view");
-    const uintptr_t first = (uintptr_t)data;
-    if (first % alignment) return report(err, QW4_STRIDE, "unaligned view");
-    if (bytes > UINTPTR_MAX - first) return report(err, QW4_OVERFLOW, "address extent overflow");
-    span->first = first; span->end = first + bytes;
-    return QW4_OK;
+/* A rank-2 token-major FP32 view [rows, cols] (Qwen4F32 and Qwen4F32Mut share the layout). */
+static Qwen4Status f32_span(const char *name, const float *data, size_t capacity, size_t rank, const size_t *dim, const size_t *stride,
+                            size_t rows, size_t cols, Span *span, Qwen4Error *err) {
+    if (rank != 2 || dim[0] != rows || dim[1] != cols) return raise(err, QW4_SHAPE, "%s: want a [%zu, %zu] matrix", name, rows, cols);
+    if (stride[1] != sizeof(float)) return raise(err, QW4_STRIDE, "%s: last axis must be dense", name);
+    const Region r = {name, data, capacity, rows, cols, stride[0], sizeof(float)};
+    return region_span(&r, span, err);
 }
-static Qwen4Status check_rows(const void *data, size_t cap, size_t rows, size_t cols, size_t pitch, Span *span, Qwen4Error *err) {
-    span->first = span->end = 0;
-    if (cols > SIZE_MAX / 4) return report(err, QW4_OVERFLOW, "row bytes overflow");
-    const size_t row_bytes = cols * 4;
-    if (pitch % 4 || pitch < row_bytes) return report(err, QW4_STRIDE, "row stride must cover contiguous features");
-    if (!rows) return QW4_OK;
-    if (rows - 1 > (SIZE_MAX - row_bytes) / pitch) return report(err, QW4_OVERFLOW, "view extent overflow");
-    return check_memory(data, cap, (rows - 1) * pitch + row_bytes, 4, span, err);
+#define F32_SPAN(name, view, rows, cols, span, err) \
+    f32_span((name), (view).data, (view).capacity_bytes, (view).rank, (view).dim, (view).stride_bytes, (rows), (cols), (span), (err))
+static Qwen4Status u32_span(const char *name, Qwen4U32Mut v, Span *span, Qwen4Error *err) {
+    const Region r = {name, v.data, v.capacity_bytes, v.rows, v.cols, v.row_stride_bytes, sizeof(uint32_t)};
+    return region_span(&r, span, err);
 }
-static Qwen4Status check_f32(const float *data, size_t cap, size_t rank, const size_t *dim, const size_t *stride,
-                             size_t rows, size_t cols, Span *span, Qwen4Error *err) {
-    if (rank != 2 || dim[0] != rows || dim[1] != cols) return report(err, QW4_SHAPE, "expected rank-2 token-major view");
-    if (stride[1] != sizeof(float)) return report(err, QW4_STRIDE, "features must be contiguous");
-    return check_rows(data, cap, rows, cols, stride[0], span, err);
-}
-static Qwen4Status check_disjoint(const Span *spans, size_t n, Qwen4Error *err) {
-    for (size_t i = 0; i < n; i++)
+static bool spans_meet(Span a, Span b) { return a.first < b.end && b.first < a.end; }
+static Qwen4Status all_apart(const Span *spans, size_t n, Qwen4Error *err) {
+    for (size_t i = 1; i < n; i++)
         for (size_t j = 0; j < i; j++)
-            if (spans[i].first < spans[j].end && spans[j].first < spans[i].end)
-                return report(err, QW4_INVALID_ARGUMENT, "overlapping views");
+            if (spans_meet(spans[i], spans[j])) return raise(err, QW4_INVALID_ARGUMENT, "arguments %zu and %zu share memory", j, i);
+    return QW4_OK;
+}
+static Qwen4Status check_config(const Qwen4MoeConfig *c, Qwen4Error *err) {
+    if (!c) return raise(err, QW4_INVALID_ARGUMENT, "config pointer is null");
+    const bool sized = c->hidden_size && c->experts && c->intermediate && c->shared_intermediate;
+    const bool routable = c->top_k >= 1 && c->top_k <= c->experts;
+    if (!sized || !routable || c->down_physical < c->intermediate) return raise(err, QW4_RANGE, "MoE dimensions out of range");
     return QW4_OK;
 }
 
@@ -493,22 +514,19 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
     if (m->local_experts != m->c.experts) return report(err, QW4_BAD_STATE, "sharded handle: use the route/experts/combine calls");
     use_current_stream(w);
     Span spans[4]; size_t ns = 2;
-    TRY(check_f32(x.data, x.capacity_bytes, x.rank, x.dim, x.stride_bytes, t, h, &spans[0], err));
-    TRY(check_f32(y.data, y.capacity_bytes, y.rank, y.dim, y.stride_bytes, t, h, &spans[1], err));
+    TRY(F32_SPAN("x", x, t, h, &spans[0], err));
+    TRY(F32_SPAN("y", y, t, h, &spans[1], err));
     if (routes) {
-        TRY(check_f32(routes->weights.data, routes->weights.capacity_bytes, routes->weights.rank, routes->weights.dim,
-                      routes->weights.stride_bytes, t, k, &spans[2], err));
-        if (routes->ids.rows != t || routes->ids.cols != k) return report(err, QW4_SHAPE, "optional route shape mismatch");
-        TRY(check_rows(routes->ids.data, routes->ids.capacity_bytes, t, k, routes->ids.row_stride_bytes, &spans[3], err));
+        TRY(F32_SPAN("route weights", routes->weights, t, k, &spans[2], err));
+        if (routes->ids.rows != t || routes->ids.cols != k) return raise(err, QW4_SHAPE, "route ids: want a [%zu, %zu] matrix", t, k);
+        TRY(u32_span("route ids", routes->ids, &spans[3], err));
         ns = 4;
     }
-    TRY(check_disjoint(spans, ns, err));
+    TRY(all_apart(spans, ns, err));
     for (size_t a = 0; a < 8; a++) {
         const Span weights = {(uintptr_t)m->host[a].span.data, (uintptr_t)m->host[a].span.data + m->host[a].layout.tensor_bytes};
-        for (size_t b = 0; b < ns; b++) {
-            const Span both[2] = {spans[b], weights};
-            TRY(check_disjoint(both, 2, err));
-        }
+        for (size_t b = 0; b < ns; b++)
+            if (spans_meet(spans[b], weights)) return raise(err, QW4_INVALID_ARGUMENT, "argument %zu overlaps weight tensor %zu", b, a);
     }
     /* Nonfinite input is rejected before any state is touched (src/qwen4_moe.c:411-413). */
     for (size_t row = 0; row < t; row++) {
@@ -592,14 +610,12 @@ Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *c, Qwen4F32 logits, Qwen4MoeRo
     TRY(check_config(c, err));
     const size_t t = logits.dim[0], e = c->experts, k = c->top_k;
     Span spans[4];
-    TRY(check_f32(logits.data, logits.capacity_bytes, logits.rank, logits.dim, logits.stride_bytes, t, e, &spans[0], err));
-    TRY(check_f32(probabilities.data, probabilities.capacity_bytes, probabilities.rank, probabilities.dim,
-                  probabilities.stride_bytes, t, e, &spans[1], err));
-    TRY(check_f32(routes.weights.data, routes.weights.capacity_bytes, routes.weights.rank, routes.weights.dim,
-                  routes.weights.stride_bytes, t, k, &spans[2], err));
-    if (routes.ids.rows != t || routes.ids.cols != k) return report(err, QW4_SHAPE, "route ID shape mismatch");
-    TRY(check_rows(routes.ids.data, routes.ids.capacity_bytes, t, k, routes.ids.row_stride_bytes, &spans[3], err));
-    TRY(check_disjoint(spans, 4, err));
+    TRY(F32_SPAN("logits", logits, t, e, &spans[0], err));
+    TRY(F32_SPAN("probabilities", probabilities, t, e, &spans[1], err));
+    TRY(F32_SPAN("route weights", routes.weights, t, k, &spans[2], err));
+    if (routes.ids.rows != t || routes.ids.cols != k) return raise(err, QW4_SHAPE, "route ids: want a [%zu, %zu] matrix", t, k);
+    TRY(u32_span("route ids", routes.ids, &spans[3], err));
+    TRY(all_apart(spans, 4, err));
     if (!t) return report(err, QW4_OK, "");
     if (t > UINT32_MAX / 2) return report(err, QW4_OVERFLOW, "too many rows");
     const size_t ze = t * e * 4, zk = t * k * 4;
@@ -645,16 +661,19 @@ Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *c, Qwen4U32Mut ids, QW4Moe
     if (ids.rows > SIZE_MAX / k || e == SIZE_MAX) return report(err, QW4_OVERFLOW, "group count overflow");
     const size_t pairs = ids.rows * k;
     Span spans[5];
-    TRY(check_rows(ids.data, ids.capacity_bytes, ids.rows, ids.cols, ids.row_stride_bytes, &spans[0], err));
-    const void *data[4] = {g.offsets, g.cursors, g.pair_to_row, g.row_to_pair};
-    const size_t counts[4] = {e + 1, e, pairs, pairs};
-    const size_t caps[4] = {g.offsets_capacity_bytes, g.cursors_capacity_bytes, g.pair_to_row_capacity_bytes,
-                            g.row_to_pair_capacity_bytes};
+    TRY(u32_span("ids", ids, &spans[0], err));
+    const Region lists[4] = {
+        {"offsets", g.offsets, g.offsets_capacity_bytes, 1, e + 1, 0, sizeof(size_t)},
+        {"cursors", g.cursors, g.cursors_capacity_bytes, 1, e, 0, sizeof(size_t)},
+        {"pair_to_row", g.pair_to_row, g.pair_to_row_capacity_bytes, 1, pairs, 0, sizeof(size_t)},
+        {"row_to_pair", g.row_to_pair, g.row_to_pair_capacity_bytes, 1, pairs, 0, sizeof(size_t)}};
     for (size_t a = 0; a < 4; a++) {
-        if (counts[a] > SIZE_MAX / sizeof(size_t)) return report(err, QW4_OVERFLOW, "group array bytes overflow");
-        TRY(check_memory(data[a], caps[a], counts[a] * sizeof(size_t), _Alignof(size_t), &spans[a + 1], err));
+        Region r = lists[a];
+        if (r.cols > SIZE_MAX / r.elem) return raise(err, QW4_OVERFLOW, "%s: byte count does not fit size_t", r.name);
+        r.pitch = r.cols * r.elem;                          /* one dense row */
+        TRY(region_span(&r, &spans[a + 1], err));
     }
-    TRY(check_disjoint(spans, 5, err));
+    TRY(all_apart(spans, 5, err));
     for (size_t t = 0; t < ids.rows; t++) {
         const uint32_t *row = ids.data + t * (ids.row_stride_bytes / 4);
         for (size_t s = 0; s < k; s++) {
@@ -725,6 +744,7 @@ void qw4cu_host_free(void *p) { qw4sh_host_free(p); }
 int qw4cu_upload(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy(dst, src, bytes, 1); }
 int qw4cu_download(void *dst, const void *src, size_t bytes) { return qw4sh_memcpy(dst, src, bytes, 0); }
 int qw4cu_flush_l2(void) { return qw4sh_flush_l2(); }
+int qw4cu_mem_info(size_t *free_bytes, size_t *total_bytes) { return qw4sh_mem_info(free_bytes, total_bytes); }
 int qw4cu_device_synchronize(void) { return qw4sh_device_sync(); }
 void qw4cu_set_graph_mode(int on) { qw4sh_set_graph_mode(on); }
 int qw4cu_get_graph_mode(void) { return qw4sh_get_graph_mode(); }
