@@ -542,10 +542,10 @@ def main():
         clocks16 = (C.c_uint64 * 16)()
         lib.qw4cu_decode_phase_clocks(layers[(args.steps - 1) % len(layers)].work, clocks16)
         ticks = [int(v) for v in clocks16[:13]]
-        names = ["stage_x", "digitise_x", "router_rows", "barrier_1", "load_logits", "route", "list_experts", "gate_up_slices",
-                 "store_units", "barrier_2", "digitise_act", "down_combine"]
+        names = ["stage_x", "fast_logits", "digitise_x", "barrier_1", "speculate_sets", "list_experts", "gate_up_slices",
+                 "store_digits", "barrier_2_and_routes", "verify_routes", "load_act_digits", "down_combine"]
         phases = {name: ticks[j + 1] - ticks[j] for j, name in enumerate(names)}
-        phases["unit"] = "SM cycles of CTA 0, last timed launch"
+        phases["unit"] = "SM cycles of the first streaming CTA, last timed launch"
     else:
         kernel_us, kernel_bytes = stage_us[dominant], bytes_by_stage[dominant]
     achieved = kernel_bytes / (kernel_us * 1e-6) / 1e9 if kernel_us > 0 else 0.0

@@ -316,14 +316,21 @@ int qw4cu_get_graph_mode(void);
  * tensor-core grouped kernels for any batch size the formats allow. */
 void qw4cu_set_expert_path(int path);
 /* One-kernel decode path (no counterpart in the reference): batches of up to four tokens whose
- * expert tensors are all Q4_K or IQ2_XXS run the whole layer as one persistent cooperative kernel
- * (router, top-k, gate/up + SwiGLU, down + combine, two grid-wide barriers).  -1 (default): used
- * whenever the layer fits it; 0: never (the multi-kernel sequence runs instead).
- * qw4cu_decode_phase_clocks copies the SM clock that CTA 0 of the workspace's last one-kernel
- * launch read at its phase boundaries into clocks[0..12] (start, x staged, x digitised, router
- * rows done, barrier 1 passed, logits loaded, routed, sources listed, gate/up slices done,
- * units stored, barrier 2 passed, activations digitised, end); call it after
- * qw4cu_moe_work_sync. */
+ * expert tensors are all Q4_K or IQ2_XXS run the whole layer as one persistent kernel, one CTA
+ * per SM.  The reference's router arithmetic (serial sums, about 9 k cycles of dependent adds)
+ * runs in a few CTAs of their own while the others start the experts from tree-summed logits; the
+ * exact routes are compared with that speculation before the down projection, and the experts
+ * are run again with the exact ids in the rare launch where the expert sets differ, so ids and
+ * route weights are always the exact mode's.  -1 (default): used whenever the layer fits it; 0:
+ * never (the multi-kernel sequence runs instead).
+ * qw4cu_decode_phase_clocks copies the SM clock that the first streaming CTA of the workspace's
+ * last one-kernel launch read at its phase boundaries into clocks[0..12] (start, x staged, fast
+ * logits written, x digitised, barrier 1 passed, expert sets speculated, sources listed, gate/up
+ * slices done, activation digits stored, barrier 2 passed and routes received, routes verified,
+ * activation digits loaded, end); call it after qw4cu_moe_work_sync.
+ * qw4cu_decode_repairs: launches of this workspace, since it was created or reset, that had to
+ * run the experts a second time.  qw4cu_set_decode_wrong_speculation(1) makes every later launch
+ * speculate a wrong expert for its first token (test aid for that repair path; 0 restores). */
 void qw4cu_set_fused_decode(int mode);
 /* Tensor-core prefill path (no counterpart in the reference): batches of more than 64 tokens whose
  * expert tensors are all Q4_K run gate/up and down as grouped GEMMs on tcgen05 tensor cores with
@@ -340,6 +347,11 @@ void qw4cu_set_tile_path(int path);
  * 4 activation loader) spent waiting, at [32 * mode + 4 * role + kind]; kind 3 is the role's whole run. */
 void qw4cu_prefill_debug(void *device_words);
 int qw4cu_decode_phase_clocks(const Qwen4MoeWork *work, uint64_t clocks[16]);
+int qw4cu_decode_repairs(const Qwen4MoeWork *work, uint32_t *count);
+/* Profiling aid: the first `words` (<= 1024) 32-bit words of the one-kernel path's counter block: counters,
+ * phase clocks, and from word 256 four marks per CTA (cycles since that CTA started). */
+int qw4cu_decode_debug_words(const Qwen4MoeWork *work, uint32_t *out, size_t words);
+void qw4cu_set_decode_wrong_speculation(int on);
 /* Profiling aid: launch only one step of the small-batch sequence on later forwards, so that a
  * kernel can be timed back to back in isolation (the workspace keeps the results of an
  * earlier complete forward).  Steps: 0 router logits, 1 quantise x, 2 route + dispatch, 3 routed

@@ -54,7 +54,9 @@ typedef struct {
     void *groups32, *shared_groups32;  /* groups of <= 32 rows (16 bytes each): routed, shared */
     uint32_t *n_groups32;         /* [2]: routed, shared */
     uint32_t *dispatch_scratch;   /* [2 * experts * ceil(cap / 32) + experts]: token bitmaps, word prefixes, counts */
-    uint32_t *sync;               /* [256]: grid-barrier counters, phase clocks and row maxima of the one-kernel decode path */
+    uint32_t *sync;               /* [256]: counters and phase clocks of the one-kernel decode path */
+    void *fused_aq, *fused_asc;   /* one-kernel decode path: activation digits and their per-chunk scales */
+    float *logits_fast;           /* one-kernel decode path: tree-summed logits [4, experts + 1 padded to 4] */
     void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
     void *graph_cache;            /* replay cache of the launch sequence (qw4sh_graph_cache_create) */
@@ -139,6 +141,10 @@ void qw4sh_set_fused_decode(int mode);
 int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                        uint32_t *ids_out, float *weights_out, int router_mode, int sm_count);
 int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[16]);
+/* Launches of this workspace whose speculated expert sets had to be repaired (since it was cleared). */
+int qw4sh_fused_repairs(const QW4ShWork *work, uint32_t *count);
+void qw4sh_set_wrong_speculation(int on);
+void qw4sh_fused_scratch_sizes(const QW4ShLayer *layer, size_t *aq_bytes, size_t *asc_bytes, size_t *fast_bytes);
 
 /* Tensor-core prefill path (prefill_tc.cu): Q4_K experts, groups of <= 32 token rows, tcgen05
  * MMAs with TMEM accumulators.  supported: 1 when a tensor fits it. */

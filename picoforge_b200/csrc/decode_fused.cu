@@ -1,35 +1,43 @@
 // The whole MoE layer for a decode step of up to four tokens as ONE persistent kernel (sm_100a).
 //
-// One CTA per SM, launched cooperatively so that all CTAs are resident; two grid-wide barriers
-// separate three phases (picoforge src/qwen4_moe.c:334-382 is the CPU statement of the sequence):
+// One CTA per SM, all resident at once; picoforge src/qwen4_moe.c:334-382 is the CPU statement of
+// the sequence.  The CTAs have two roles.
 //
-//   A  every CTA stages x, turns it into int8 digit pairs, and computes its 3-4 rows of the
-//      router projection (plus the shared expert's gate row): exact mode walks k = 0..K-1 with
-//      separately rounded products and sums (the reference's bits, src/qwen4_packed.c:164-173),
-//      fast mode uses warp-tree sums.  The shared expert's tensors are prefetched into L2.
-//   B  every CTA routes all tokens itself from the logits (softmax, top-k, renormalise; the same
-//      arithmetic in every CTA, so no second exchange is needed), builds the list of distinct
-//      experts, prefetches its down-projection tiles into L2, and streams its share of the
-//      gate/up rows.  A work unit is 8 gate rows + the same 8 up rows of one expert (gate rows in
-//      MMA rows 0-7, up rows in 8-15, so the lane that holds gate.x also holds up.x); a unit is cut
-//      into K slices, and the CTA's slices are dealt to its warps round robin.  A warp fetches a
-//      slice with TMA bulk copies into its own two-stage ring (no producer warp, no CTA-wide
-//      barrier inside the stream), feeds int8 tensor-core MMAs with the raw codes and leaves its
-//      partial sums in shared memory; after one CTA barrier the units are summed in slice order,
-//      SwiGLU is applied and the result stored, with the row maxima kept for phase C.
-//   C  CTA c owns 16 columns of y: its warps split the sources (shared expert + distinct routed
-//      experts), each runs the 16 x K down tile on the tensor cores against the digit image of the
-//      pair's activation, scales by the route weight (or the sigmoid gate) and the partial sums
-//      are added in warp order: y is deterministic.
+// CHAIN CTAs (the first NC) own the reference's router arithmetic: every logit is one chain of K
+// separately rounded multiply-adds in ascending k (src/qwen4_packed.c:164-173), 32 router rows
+// per CTA, one warp per token, lane = row, the rows streamed through a swizzled cp.async ring by
+// the CTA's other warps.  A chain is 2048 dependent adds, about 9 k cycles whatever else happens,
+// so it is kept OFF the critical path: when all chains are done, chain CTA t routes token t
+// (libm-exact softmax, serial exp-sum, top-k, renormalisation: src/qwen4_moe.c:209-247) and
+// publishes ids and weights.
 //
-// The four tokens' digit pairs fill the eight MMA columns, so every expert sees the same B
-// operand in phase B; results of tokens not routed to an expert are simply not stored.
+// STREAMING CTAs (all others) do not wait for that.  They compute tree-summed logits of their 3-4
+// router rows at once (phase A), exchange them through the first grid-wide barrier, take the
+// top-k SET of every token from those logits (a speculation: the tree sums differ from the chains
+// in the last bits, which matters only for a near-tie at the k-th place) and stream the gate/up
+// rows of the experts in that set (phase B).  At the second barrier they also wait for the chain
+// CTAs' routes and compare: if a token's exact expert set differs from the speculated one, phase B
+// runs again with the exact ids, so ids and weights are always the reference's bits.  Phase C
+// (down projection, weighted combine, sigmoid-gated shared expert) uses the exact weights.
 //
-// Code that runs once per launch is kept compact on purpose (loops instead of unrolled
-// sequences, no per-thread arrays in local memory): a kernel of this kind executes most of its
-// instructions a handful of times.
+//   A  x -> shared memory, int8 digit pairs of x, tree-summed logits of rows sc, sc + NS, ...
+//   B  work unit = 8 gate rows + the same 8 up rows of one expert (gate in MMA rows 0-7, up in
+//      8-15); a unit is cut into K slices dealt to the CTA's warps, each warp fetching slices with
+//      TMA bulk copies into its own ring and feeding int8 tensor-core MMAs with the raw codes.
+//      Units come in granules of four (32 activation columns): the warp that sums a granule's
+//      slices applies SwiGLU and writes the activation as int8 digit pairs with ONE SCALE PER
+//      32-COLUMN CHUNK, so that no row maximum has to cross the grid and phase C starts with a
+//      bulk copy of ready-made digits.
+//   C  streaming CTA sc owns 16 columns of y: its warps split the sources (shared expert +
+//      distinct routed experts), each runs the 16 x K down tile on the tensor cores against the
+//      digits of the pair's activation, scales by the route weight (or the sigmoid gate), and the
+//      partial sums are added in warp order: y is deterministic.
 //
-// Every wait (mbarrier or grid barrier) is bounded: after about a second the kernel records
+// The kernel is launched as a normal grid of one CTA per SM with programmatic stream
+// serialisation: the next layer's launch may begin while this one drains, and everything that
+// touches memory another launch writes comes after griddepcontrol.wait.  All CTAs are resident
+// together because each needs more than half of an SM's shared memory and the grid is the SM
+// count; every wait (mbarrier, counter) is bounded: after about a second the kernel records
 // QW4SH_ERR_STATE and leaves.
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -47,29 +55,38 @@ constexpr int FTOK = 4;                         // tokens per launch
 constexpr int FMAXK = 16;                       // top-k limit
 constexpr int FMAXE = 512;                      // experts limit
 constexpr int FMAXSRC = FTOK * FMAXK + 1;       // shared expert + distinct routed experts
-constexpr int FRMAX = 4;                        // router rows per CTA
-constexpr int FRCH = 4;                         // router row chunks (one mbarrier each)
+constexpr int FRMAX = 4;                        // router rows per streaming CTA
 constexpr int FNS = 2;                          // ring stages per warp
 constexpr uint32_t FSTAGE = 4608;               // bytes per ring stage (IQ2_XXS: 4096 payload + 512 super-scales)
 constexpr uint32_t F_LUT_GRID = 256 * 128, F_LUT_SIGN = 128 * 128, F_LUT_BYTES = F_LUT_GRID + F_LUT_SIGN;
-constexpr uint32_t F_SYNC_CLOCKS = 8, F_SYNC_AMAX = 64;   // word offsets inside the sync array
+constexpr uint32_t FZP = FMAXE + 4;             // pitch of a logit row in shared memory (floats)
+constexpr int CROWS = 32;                       // router rows per chain CTA (lane = row)
+constexpr int CSTG = 16;                        // chunks in flight in a chain CTA
+constexpr int CCH = 64;                         // columns per chunk: 256 bytes per row
+// words of the sync array
+enum : uint32_t { S_FAST = 0, S_CHAIN = 1, S_ROUTED = 2, S_ACT0 = 3, S_ACT1 = 4, S_EXITS = 5, S_ROUTE_FAIL = 6, S_CLOCKS = 8, S_REPAIRS = 48, S_MARKS = 256 };
 
 struct FusedArgs {
     DevTensor w[8];                             // router, gate, up, down, sgate, sup, sdown, srouter
     const float *x;
     float *y;
     uint32_t tokens, hidden, experts, top_k, inter, shared_inter;
-    int norm, router_mode;
-    float *logits, *shared_logit;               // [T, E], [T]
+    int norm, router_mode;                      // 0 exact, 1 fast, 2 exact with a wrong speculation forced (test aid)
+    float *logits, *shared_logit;               // [T, E], [T]: the logits the routes were made from
+    float *logits_fast;                         // [T, fast_pitch]: tree sums, the shared router's at column E
+    uint32_t fast_pitch;
     uint32_t *ids;                              // [T, k]
     float *weights;                             // [T, k]
-    float *act, *shared_act;                    // [T*k, I], [T, Is]
+    uint8_t *aq;                                // [T*k + T][2][ap] activation digits (pairs, then the shared expert's rows)
+    float2 *asc;                                // [T*k + T][imax / 32] per chunk: scale, sum of the chunk's represented values
     uint32_t *ids_out;
     float *weights_out;
     const uint8_t *lut;                         // IQ2_XXS tables image (F_LUT_BYTES) or nullptr
-    uint32_t *sync;                             // [0] barrier 1, [1] barrier 2, [2] exits, [8..39] clocks of CTA 0, [64..] row maxima
+    uint32_t *sync;                             // counters (S_*), then the phase clocks of the first streaming CTA
     uint32_t *status;
     uint32_t partial_slices;                    // capacity of the partial-sum buffer (slices per CTA)
+    uint32_t chain_ctas;                        // NC
+    long long t0;                               // (device side) this CTA's clock at its start
 };
 
 // One distinct source of phase C / one expert of phase B.
@@ -79,15 +96,15 @@ struct Src {
     __device__ __forceinline__ uint32_t slot(uint32_t t) const { return (slots >> (8 * t)) & 0xffu; }
 };
 
-// Shared-memory plan (byte offsets), the same on host and device.  `region` is reused by the
-// three phases; the digit image of x lives at its start through phases A and B.
+// Shared-memory plan of a streaming CTA (byte offsets), the same on host and device.  `region` is
+// reused by the three phases; the digit image of x lives at its start through phases A and B.
 struct FPlan {
-    uint32_t bars, ids, wts, misc, tokmask, slotmap, src, lut, region, total;
+    uint32_t bars, ids, wts, idx, wtx, misc, tokmask, slotmap, src, lut, region, total;
     uint32_t kp;                                // pitch of one digit row of x
     uint32_t xq, xsum;                          // phases A and B (inside region)
-    uint32_t xf, xf_pitch, rows, row_pitch, prod;   // phase A
+    uint32_t xf, xf_pitch, rows, row_pitch;     // phase A
     uint32_t zs, ring, partial;                 // phase B
-    uint32_t aq, ap, asum, ascale, aconst, tiles, cpartial;   // phase C
+    uint32_t aq, ap, asc, tiles, cpartial;      // phase C
 };
 __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max, uint32_t rows_c, uint32_t partial_slices, bool lut) {
     FPlan p;
@@ -95,8 +112,9 @@ __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max,
     p.bars = at; at += 512;
     p.ids = at; at += FTOK * FMAXK * 4;
     p.wts = at; at += FTOK * FMAXK * 4;
-    p.misc = at; at += 1024;                    // floats [0..3] x scales, [4..7] shared logits, [8..15] route scratch; words from +64;
-                                                // +256: expf table (32 x 8 bytes); +512: digitiser constants of x (4 x float4)
+    p.idx = at; at += FTOK * FMAXK * 4;         // the exact routes as published
+    p.wtx = at; at += FTOK * FMAXK * 4;
+    p.misc = at; at += 1024;                    // floats [0..3] x maxima then scales, [4..7] shared logits; words from +64; +512: digitiser constants of x
     p.tokmask = at; at += FMAXE;
     p.slotmap = at; at += FMAXE * 4;
     p.src = at; at += ((FMAXSRC * 8 + 127) & ~127u);
@@ -112,27 +130,42 @@ __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max,
     p.xf_pitch = hidden * 4 + 16;
     p.xf = a; a += FTOK * p.xf_pitch;
     p.row_pitch = hidden * 4 + 16;
-    p.rows = a; a += FRMAX * p.row_pitch;
-    p.prod = a; a += 2 * 16 * (hidden / FRCH + 4) * 4;
-    // phase B: the logits / probabilities are dead before the first copy lands in the ring
+    p.rows = a; a += FRMAX * p.row_pitch + 8 * 16 * 4;      // + the partial sums of the fast logits
+    // phase B: the logit keys are dead before the first copy lands in the ring
     uint32_t b = head;
     p.zs = b;
     p.ring = b; b += FW * FNS * FSTAGE;
-    if (b < head + FTOK * FMAXE * 4) b = head + FTOK * FMAXE * 4;
+    if (b < head + FTOK * FZP * 4) b = head + FTOK * FZP * 4;
     p.partial = b; b += partial_slices * 256;
     // phase C
     uint32_t c = 0;
     p.ap = inter_max + 32;
     p.aq = c; c += rows_c * 2 * p.ap;
-    p.asum = c; c += rows_c * (inter_max / 32) * 8;
-    p.ascale = c; c += ((rows_c * 4 + 127) & ~127u);
-    p.aconst = c; c += ((rows_c * 16 + 127) & ~127u);
+    c = (c + 127) & ~127u;
+    p.asc = c; c += rows_c * (inter_max / 32) * 8;
     c = (c + 127) & ~127u;
     p.tiles = c; c += FW * FNS * FSTAGE;
     p.cpartial = c; c += FW * 32 * 8;
     uint32_t m = a > b ? a : b;
     m = m > c ? m : c;
     p.total = p.region + m;
+    return p;
+}
+// Shared-memory plan of a chain CTA.
+struct CPlan { uint32_t bars, misc, ids, wts, xf, xf_pitch, ring, zs, total; };
+__host__ __device__ inline CPlan make_cplan(uint32_t hidden) {
+    CPlan p;
+    uint32_t at = 0;
+    p.bars = at; at += 512;
+    p.misc = at; at += 1024;
+    p.ids = at; at += FMAXK * 4 * FTOK;
+    p.wts = at; at += FMAXK * 4 * FTOK;
+    p.xf_pitch = hidden * 4 + 16;
+    p.xf = at; at += FTOK * p.xf_pitch;
+    at = (at + 127) & ~127u;
+    p.ring = at; at += CSTG * CROWS * CCH * 4;
+    p.zs = at; at += FTOK * FZP * 4;
+    p.total = at;
     return p;
 }
 
@@ -143,6 +176,9 @@ __device__ __forceinline__ void fbar_init(uint64_t *bar, uint32_t count) {
 }
 __device__ __forceinline__ void fbar_expect(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fs_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fs_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool fbar_try(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -172,16 +208,46 @@ __device__ __forceinline__ uint32_t fld_acquire(const uint32_t *p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void fred_release(uint32_t *p) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
 __device__ __forceinline__ void fmma_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+#ifdef QW4_X_NOMMA
+    c[0] = (int)(a0 ^ b0); c[1] = (int)(a1 ^ b1); c[2] = (int)(a2 + b0); c[3] = (int)(a3 + b1);
+    return;
+#endif
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// All CTAs arrive, then wait until `expected` have.  False (CTA-uniform) when the wait ran out.
-__device__ __forceinline__ bool grid_barrier(uint32_t *counter, uint32_t expected, uint32_t *status, uint32_t *flag_smem) {
-    __syncthreads();
+// Shared-memory loads by 32-bit shared address.  The `ring` forms are volatile: they read memory that bulk
+// copies rewrite between uses and must stay behind the mbarrier wait that precedes them in program order; the
+// `table` forms read tables that never change after the CTA built them, so the compiler may move them freely.
+__device__ __forceinline__ uint2 lds_ring2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_ring_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_table2(uint32_t a) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_table4(uint32_t a) {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
+// Thread 0 waits until *counter >= expected (bounded); the verdict reaches every thread.
+// False (CTA-uniform) when the wait ran out.
+__device__ __forceinline__ bool wait_counter(const uint32_t *counter, uint32_t expected, uint32_t *status, uint32_t *flag_smem) {
     if (threadIdx.x == 0) {
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
         uint32_t ok = 1;
         const long long start = clock64();
         while (fld_acquire(counter) < expected) {
@@ -190,16 +256,33 @@ __device__ __forceinline__ bool grid_barrier(uint32_t *counter, uint32_t expecte
         *flag_smem = ok;
     }
     __syncthreads();
-    return *flag_smem != 0;
+    const bool ok = *flag_smem != 0;
+    __syncthreads();
+    return ok;
+}
+// All threads' earlier global writes are ordered before one release increment.
+__device__ __forceinline__ void arrive_counter(uint32_t *counter) {
+    __syncthreads();
+    if (threadIdx.x == 0) fred_release(counter);
 }
 
 // ---- half blocks (128 columns) on the tensor cores ----------------------------------------------
 // MMA k-slots are permuted so that lane (g, t) owns the eight consecutive columns 8t..8t+7 of
 // every 32-column chunk, for MMA rows g and g + 8 and for activation column g (token g >> 1,
-// digit g & 1).  f0 += row g . x[token t], f1 += row g+8 . x[token t], both in units of the
-// token's digit scale.  xq is the lane's digit pointer at the first chunk, xsum the token's digit
+// digit g & 1).  f0 += row g . x[token t], f1 += row g+8 . x[token t].
+//
+// Halves (phase B): the activation has one scale per row, so the sums stay integers over a half
+// block and the results are in units of the token's digit scale; xsum holds the token's digit
 // sums (Q4_K's min term).
+// HalvesS (phase C): one scale per 32-column chunk; `asc` points at the token row's (scale, chunk
+// sum) pairs and the results are plain values.
 template <uint32_t TYPE> struct Halves;
+template <uint32_t TYPE> struct HalvesS;
+
+__device__ __forceinline__ void q4k_scales(const uint4 h0, uint32_t hb, uint32_t &sc, uint32_t &mn) {
+    if (hb == 0) { sc = h0.y & 0x3f3f3f3fu; mn = h0.z & 0x3f3f3f3fu; }
+    else { sc = (h0.w & 0x0f0f0f0fu) | ((h0.y >> 2) & 0x30303030u); mn = ((h0.w >> 4) & 0x0f0f0f0fu) | ((h0.z >> 2) & 0x30303030u); }
+}
 
 // Q4_K: r0 / r1 point at the first 144-byte block of the two rows; `halves` half blocks follow.
 template <> struct Halves<T_Q4_K> {
@@ -212,11 +295,8 @@ template <> struct Halves<T_Q4_K> {
             const uint32_t hb = h & 1u;
             const uint4 h0 = *reinterpret_cast<const uint4 *>(b0), h1 = *reinterpret_cast<const uint4 *>(b1);
             uint32_t sc0, mn0, sc1, mn1;
-            if (hb == 0) { sc0 = h0.y & 0x3f3f3f3fu; mn0 = h0.z & 0x3f3f3f3fu; sc1 = h1.y & 0x3f3f3f3fu; mn1 = h1.z & 0x3f3f3f3fu; }
-            else {
-                sc0 = (h0.w & 0x0f0f0f0fu) | ((h0.y >> 2) & 0x30303030u); mn0 = ((h0.w >> 4) & 0x0f0f0f0fu) | ((h0.z >> 2) & 0x30303030u);
-                sc1 = (h1.w & 0x0f0f0f0fu) | ((h1.y >> 2) & 0x30303030u); mn1 = ((h1.w >> 4) & 0x0f0f0f0fu) | ((h1.z >> 2) & 0x30303030u);
-            }
+            q4k_scales(h0, hb, sc0, mn0);
+            q4k_scales(h1, hb, sc1, mn1);
             int qacc[4] = {0, 0, 0, 0}, macc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int cc = 0; cc < 2; cc++) {                             // 64 columns: low and high nibbles of 32 bytes
@@ -244,6 +324,96 @@ template <> struct Halves<T_Q4_K> {
         }
     }
 };
+template <> struct HalvesS<T_Q4_K> {
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t, const uint16_t *,
+                                            const uint16_t *, const uint8_t *, uint32_t t, const uint8_t *aq, const float2 *asc,
+                                            float &f0, float &f1) {
+#pragma unroll 1
+        for (uint32_t h = 0; h < halves; h++, aq += 128, asc += 4) {
+            const uint8_t *b0 = r0 + (h >> 1) * 144u, *b1 = r1 + (h >> 1) * 144u;
+            const uint32_t hb = h & 1u;
+            const uint4 h0 = *reinterpret_cast<const uint4 *>(b0), h1 = *reinterpret_cast<const uint4 *>(b1);
+            uint32_t sc0, mn0, sc1, mn1;
+            q4k_scales(h0, hb, sc0, mn0);
+            q4k_scales(h1, hb, sc1, mn1);
+            float qf0 = 0.0f, qf1 = 0.0f, mf0 = 0.0f, mf1 = 0.0f;
+            const float lo = 1.0f / 254.0f;
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+                const uint2 q0 = *reinterpret_cast<const uint2 *>(b0 + 16 + (hb * 2 + cc) * 32 + 8 * t);
+                const uint2 q1 = *reinterpret_cast<const uint2 *>(b1 + 16 + (hb * 2 + cc) * 32 + 8 * t);
+#pragma unroll
+                for (int nib = 0; nib < 2; nib++) {
+                    const int j = cc * 2 + nib;
+                    const uint2 bq = *reinterpret_cast<const uint2 *>(aq + j * 32);
+                    int c[4];
+                    fmma_zero(c, (q0.x >> (4 * nib)) & 0x0f0f0f0fu, (q1.x >> (4 * nib)) & 0x0f0f0f0fu,
+                              (q0.y >> (4 * nib)) & 0x0f0f0f0fu, (q1.y >> (4 * nib)) & 0x0f0f0f0fu, bq.x, bq.y);
+                    const float2 a = asc[j];
+                    const float s0 = (float)((sc0 >> (8 * j)) & 0xffu), s1 = (float)((sc1 >> (8 * j)) & 0xffu);
+                    const float m0 = (float)((mn0 >> (8 * j)) & 0xffu), m1 = (float)((mn1 >> (8 * j)) & 0xffu);
+                    qf0 = fmaf(s0 * a.x, fmaf((float)c[1], lo, (float)c[0]), qf0);
+                    qf1 = fmaf(s1 * a.x, fmaf((float)c[3], lo, (float)c[2]), qf1);
+                    mf0 = fmaf(m0, a.y, mf0); mf1 = fmaf(m1, a.y, mf1);
+                }
+            }
+            const float d0 = __half2float(__ushort_as_half((uint16_t)(h0.x & 0xffffu))), n0 = __half2float(__ushort_as_half((uint16_t)(h0.x >> 16)));
+            const float d1 = __half2float(__ushort_as_half((uint16_t)(h1.x & 0xffffu))), n1 = __half2float(__ushort_as_half((uint16_t)(h1.x >> 16)));
+            f0 += d0 * qf0 - n0 * mf0;
+            f1 += d1 * qf1 - n1 * mf1;
+        }
+    }
+};
+
+// The IQ2_XXS tables in shared memory, built by the CTA itself from the 2-bit level list.
+// Grid: 256 entries of 128 bytes, each holding 8 copies of {magnitudes 0-3, magnitudes 4-7, the same
+// negated byte by byte} (lane L reads copy L % 8 with one 128-bit load).  Signs: 128 entries of 128
+// bytes, each 16 copies of two byte-permute selectors (lane L reads copy L % 16 with a 64-bit load):
+// nibble i of a selector is i for a positive weight and i + 4 for a negative one, so that ONE prmt
+// of (magnitudes, negated magnitudes) yields four signed int8 weights.  The eighth sign of a group
+// is the parity of the seven stored ones.  Neither table has bank conflicts.
+__device__ __forceinline__ void build_iq2_tables(uint8_t *lut) {
+    for (uint32_t entry = threadIdx.x; entry < 256 + 128; entry += blockDim.x) {
+        uint4 *to = reinterpret_cast<uint4 *>(lut + entry * 128u);            // the sign entries follow the grid's
+        if (entry < 256) {
+            const uint32_t levels = c_iq2_levels[entry];
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                lo |= iq2_magnitude((levels >> (2 * j)) & 3u) << (8 * j);
+                hi |= iq2_magnitude((levels >> (2 * j + 8)) & 3u) << (8 * j);
+            }
+            // magnitudes are never zero, so (v ^ 0xff) + 1 = -v stays inside its byte
+            const uint4 v = make_uint4(lo, hi, (lo ^ 0xffffffffu) + 0x01010101u, (hi ^ 0xffffffffu) + 0x01010101u);
+#pragma unroll
+            for (int c = 0; c < 8; c++) to[c] = v;
+        } else {
+            const uint32_t signs = iq2_signs8(entry - 256);
+            uint32_t lo = 0x3210u, hi = 0x3210u;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if ((signs >> j) & 1u) lo += 4u << (4 * j);
+                if ((signs >> (j + 4)) & 1u) hi += 4u << (4 * j);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c++) to[c] = make_uint4(lo, hi, lo, hi);
+        }
+    }
+}
+// Signed int8 weights of the lane's eight columns of one group: g.x holds the four grid indices
+// (byte t is the lane's), g.y the four 7-bit sign fields and the scale.  `rg` / `rs` are the
+// lane's rotate counts that bring its index byte / sign field to bit 7, where the tables' 128-byte
+// entry pitch wants them.
+__device__ __forceinline__ void iq2_weights(const uint2 g, uint32_t grid, uint32_t sign, uint32_t rg, uint32_t rs, uint32_t &lo, uint32_t &hi) {
+#ifdef QW4_X_NOLUT
+    lo = __funnelshift_r(g.x, g.x, rg) & 0x7f80u; hi = __funnelshift_r(g.y, g.y, rs) & 0x3f80u;
+    return;
+#endif
+    const uint4 v = lds_table4(grid + (__funnelshift_r(g.x, g.x, rg) & 0x7f80u));
+    const uint2 sel = lds_table2(sign + (__funnelshift_r(g.y, g.y, rs) & 0x3f80u));
+    lo = __byte_perm(v.x, v.z, sel.x);
+    hi = __byte_perm(v.y, v.w, sel.y);
+}
 
 // IQ2_XXS: r0 / r1 point at the two rows' first 8-byte group of the span (a multiple of 16
 // groups from the row start, so the in-row swizzle `swz` applies to the local index); d0p / d1p
@@ -252,32 +422,70 @@ template <> struct Halves<T_IQ2_XXS> {
     static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
                                             const uint16_t *d1p, const uint8_t *lut, uint32_t t, const uint8_t *xq, const int2 *,
                                             float &f0, float &f1) {
-        const uint8_t *grid = lut + (threadIdx.x & 15u) * 8u;            // 64-bit reads: 16 copies
-        const uint8_t *sign = lut + F_LUT_GRID + (threadIdx.x & 7u) * 16u;   // 128-bit reads: 8 copies
-        const uint32_t pick = 0x4440u + t, shift_s = 7 * t;
+        const uint32_t grid = fs_u32(lut) + (threadIdx.x & 7u) * 16u, sign = fs_u32(lut) + F_LUT_GRID + (threadIdx.x & 15u) * 8u;
+        const uint32_t rg = (8u * t + 25u) & 31u, rs = (7u * t + 25u) & 31u;
+        const uint32_t a0s = fs_u32(r0), a1s = fs_u32(r1), d0s = fs_u32(d0p), d1s = fs_u32(d1p);
+        uint32_t xs = fs_u32(xq);
 #pragma unroll 1
-        for (uint32_t h = 0; h < halves; h++, xq += 128) {
+        for (uint32_t h = 0; h < halves; h++, xs += 128) {
             const uint32_t at = ((h * 4u) ^ swz) * 8u;
+            uint2 g0[4], g1[4], bq[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { g0[j] = lds_ring2(a0s + at + 8 * j); g1[j] = lds_ring2(a1s + at + 8 * j); bq[j] = lds_ring2(xs + j * 32); }
+            const uint32_t dh0 = lds_ring_u16(d0s + (h >> 1) * 2u), dh1 = lds_ring_u16(d1s + (h >> 1) * 2u);
             int iacc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const uint2 g0 = *reinterpret_cast<const uint2 *>(r0 + at + 8 * j), g1 = *reinterpret_cast<const uint2 *>(r1 + at + 8 * j);
-                const uint32_t i0 = __byte_perm(g0.x, 0u, pick), i1 = __byte_perm(g1.x, 0u, pick);
-                const uint32_t s0 = (g0.y >> shift_s) & 127u, s1 = (g1.y >> shift_s) & 127u;
-                const uint2 v0 = *reinterpret_cast<const uint2 *>(grid + i0 * 128u), v1 = *reinterpret_cast<const uint2 *>(grid + i1 * 128u);
-                const uint4 m0 = *reinterpret_cast<const uint4 *>(sign + s0 * 128u), m1 = *reinterpret_cast<const uint4 *>(sign + s1 * 128u);
-                const uint2 bq = *reinterpret_cast<const uint2 *>(xq + j * 32);
+                uint32_t a0, a1, a2, a3;
+                iq2_weights(g0[j], grid, sign, rg, rs, a0, a2);
+                iq2_weights(g1[j], grid, sign, rg, rs, a1, a3);
                 int c[4];
-                // m.x/m.y: 0xff where the weight is negative; m.z/m.w: 0x01 there.  Magnitudes are
-                // never zero, so (v ^ 0xff) + 1 = -v stays inside its byte.
-                fmma_zero(c, (v0.x ^ m0.x) + m0.z, (v1.x ^ m1.x) + m1.z, (v0.y ^ m0.y) + m0.w, (v1.y ^ m1.y) + m1.w, bq.x, bq.y);
-                const int w0 = (int)((g0.y >> 27) | 1u), w1 = (int)((g1.y >> 27) | 1u);         // 2 * scale + 1
+                fmma_zero(c, a0, a1, a2, a3, bq[j].x, bq[j].y);
+                const int w0 = (int)((g0[j].y >> 27) | 1u), w1 = (int)((g1[j].y >> 27) | 1u);         // 2 * scale + 1
                 iacc[0] += c[0] * w0; iacc[1] += c[1] * w0; iacc[2] += c[2] * w1; iacc[3] += c[3] * w1;
             }
             const float lo = 1.0f / 254.0f;
-            const float d0 = __half2float(__ushort_as_half(d0p[h >> 1])) * 0.125f, d1 = __half2float(__ushort_as_half(d1p[h >> 1])) * 0.125f;
+            const float d0 = __half2float(__ushort_as_half((uint16_t)dh0)) * 0.125f, d1 = __half2float(__ushort_as_half((uint16_t)dh1)) * 0.125f;
             f0 += d0 * fmaf((float)iacc[1], lo, (float)iacc[0]);
             f1 += d1 * fmaf((float)iacc[3], lo, (float)iacc[2]);
+        }
+    }
+};
+template <> struct HalvesS<T_IQ2_XXS> {
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
+                                            const uint16_t *d1p, const uint8_t *lut, uint32_t t, const uint8_t *aq, const float2 *asc,
+                                            float &f0, float &f1) {
+        const uint32_t grid = fs_u32(lut) + (threadIdx.x & 7u) * 16u, sign = fs_u32(lut) + F_LUT_GRID + (threadIdx.x & 15u) * 8u;
+        const uint32_t rg = (8u * t + 25u) & 31u, rs = (7u * t + 25u) & 31u;
+        const uint32_t a0s = fs_u32(r0), a1s = fs_u32(r1), d0s = fs_u32(d0p), d1s = fs_u32(d1p);
+        uint32_t xs = fs_u32(aq), ss = fs_u32(asc);
+#pragma unroll 1
+        for (uint32_t h = 0; h < halves; h++, xs += 128, ss += 32) {
+            const uint32_t at = ((h * 4u) ^ swz) * 8u;
+            uint2 g0[4], g1[4], bq[4], sc[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                g0[j] = lds_ring2(a0s + at + 8 * j); g1[j] = lds_ring2(a1s + at + 8 * j);
+                bq[j] = lds_ring2(xs + j * 32); sc[j] = lds_ring2(ss + j * 8);
+            }
+            const uint32_t dh0 = lds_ring_u16(d0s + (h >> 1) * 2u), dh1 = lds_ring_u16(d1s + (h >> 1) * 2u);
+            float fa0 = 0.0f, fa1 = 0.0f;
+            const float lo = 1.0f / 254.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t a0, a1, a2, a3;
+                iq2_weights(g0[j], grid, sign, rg, rs, a0, a2);
+                iq2_weights(g1[j], grid, sign, rg, rs, a1, a3);
+                int c[4];
+                fmma_zero(c, a0, a1, a2, a3, bq[j].x, bq[j].y);
+                const float w0 = (float)((g0[j].y >> 27) | 1u), w1 = (float)((g1[j].y >> 27) | 1u);   // 2 * scale + 1
+                const float a = __uint_as_float(sc[j].x);
+                fa0 = fmaf(w0 * a, fmaf((float)c[1], lo, (float)c[0]), fa0);
+                fa1 = fmaf(w1 * a, fmaf((float)c[3], lo, (float)c[2]), fa1);
+            }
+            const float d0 = __half2float(__ushort_as_half((uint16_t)dh0)) * 0.125f, d1 = __half2float(__ushort_as_half((uint16_t)dh1)) * 0.125f;
+            f0 = fmaf(d0, fa0, f0);
+            f1 = fmaf(d1, fa1, f1);
         }
     }
 };
@@ -327,63 +535,57 @@ __device__ __forceinline__ void issue_down_tile(const uint8_t *mat, uint32_t n_o
 }
 template <uint32_t TYPE>
 __device__ __forceinline__ void consume_down_tile(const uint8_t *stage, uint32_t nb, const uint8_t *lut, const uint8_t *aq_lane,
-                                                  const int2 *asum_tok, uint32_t g, uint32_t t, float &f0, float &f1) {
+                                                  const float2 *asc_tok, uint32_t g, uint32_t t, float &f0, float &f1) {
     const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
     const uint16_t *d = reinterpret_cast<const uint16_t *>(stage + 4096);
-    Halves<TYPE>::run(stage + g * row_bytes, stage + (8 + g) * row_bytes, nb * 2, iq2_swizzle(g, nb), d + g * nb, d + (8 + g) * nb, lut, t,
-                      aq_lane, asum_tok, f0, f1);
+    HalvesS<TYPE>::run(stage + g * row_bytes, stage + (8 + g) * row_bytes, nb * 2, iq2_swizzle(g, nb), d + g * nb, d + (8 + g) * nb, lut, t,
+                       aq_lane, asc_tok, f0, f1);
 }
 
 // Two int8 digits per value: v ~ dx * (q1 + q2 / 254), |v| <= 127 dx.  Rounding by the
 // 1.5 * 2^23 trick (no conversion instructions): the integer sits in the low mantissa bits, so
-// the low byte of the rounded float's bit pattern IS the int8 digit and four of them are packed
-// with byte permutes.  `s` accumulates both digit sums: the first in its low half, the second
-// in its high half (each below 2^15 in magnitude for a 32-column chunk).
+// the low byte of the rounded float's bit pattern IS the int8 digit.  c = (dx, 1 / dx, 254 / dx).
+__device__ __forceinline__ void digit_pair(float v, const float4 c, uint32_t &ra, uint32_t &rb) {
+    const float magic = 12582912.0f;
+    const float r1 = fmaf(v, c.y, magic);
+    const float q1 = r1 - magic;
+    // second digit clamped to [-127, 127] in the float domain, before the rounding add
+    const float r2 = fmaxf(-127.0f, fminf(127.0f, fmaf(-q1, c.x, v) * c.z)) + magic;
+    ra = __float_as_uint(r1); rb = __float_as_uint(r2);
+}
+// Four values at once, packed; `s` accumulates both digit sums: the first in its low half, the
+// second in its high half (each below 2^15 in magnitude for a 32-column chunk).
 __device__ __forceinline__ void digits4(const float4 v, const float4 c, uint32_t &hi, uint32_t &lo, int &s) {
     const float vv[4] = {v.x, v.y, v.z, v.w};
-    const float magic = 12582912.0f;
     uint32_t ra[4], rb[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const float r1 = fmaf(vv[j], c.y, magic);
-        const float q1 = r1 - magic;
-        // second digit clamped to [-127, 127] in the float domain, before the rounding add
-        const float r2 = fmaxf(-127.0f, fminf(127.0f, fmaf(-q1, c.x, vv[j]) * c.z)) + magic;
-        ra[j] = __float_as_uint(r1); rb[j] = __float_as_uint(r2);
-    }
+    for (int j = 0; j < 4; j++) digit_pair(vv[j], c, ra[j], rb[j]);
     hi = __byte_perm(__byte_perm(ra[0], ra[1], 0x0040), __byte_perm(ra[2], ra[3], 0x0040), 0x5410);
     lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
     s += __dp4a((int)hi, 0x01010101, 0) + (__dp4a((int)lo, 0x01010101, 0) << 16);
 }
 
-// Rows of `k` floats (k % 256 == 0) with known maxima -> digit images, digit sums per 32-column
-// chunk and scales.  A warp takes one 256-column segment of one row at a time: two float4 per
-// lane, eight consecutive lanes cover one chunk, no index arithmetic beyond the segment's.
-// `amax` holds the maxima on entry and the scales (max / 127, or 0 for an unusable row) on
-// return; `consts` is scratch, one float4 per row.
-// The first `NT` threads of the CTA take part and meet at named barrier `BAR` (0 with NT = FT is the
-// CTA barrier).
-template <bool GLOBAL, int NT = FT, int BAR = 0>
+// Rows of `k` floats (k % 256 == 0) in shared memory with known maxima -> digit images, digit
+// sums per 32-column chunk and scales.  A warp takes one 256-column segment of one row at a time:
+// two float4 per lane, eight consecutive lanes cover one chunk.  `amax` holds the maxima on entry
+// and the scales (max / 127, or 0 for an unusable row) on return; `consts` is scratch, one float4
+// per row.  CTA-wide.
 __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pitch, uint32_t rows, uint32_t k, float *amax, uint8_t *dq,
-                                           uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts, uint32_t rotate = 0) {
-    auto meet = [] { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(NT) : "memory"); };
+                                           uint32_t dq_pitch, int2 *sums, uint32_t sums_pitch, float4 *consts) {
 #pragma unroll 1
-    for (uint32_t r = threadIdx.x; r < rows; r += NT) {
+    for (uint32_t r = threadIdx.x; r < rows; r += FT) {
         const float m = amax[r];
         const bool usable = finite_f32(m) && m > 0.0f;
         const float inv = usable ? __fdividef(127.0f, m) : 0.0f;
         consts[r] = make_float4(usable ? m * (1.0f / 127.0f) : 0.0f, inv, 2.0f * inv * 127.0f, 0.0f);
     }
-    meet();
-    // `rotate`: every CTA reads the same rows from L2; starting each at a different unit keeps them
-    // off the same lines at the same time
+    __syncthreads();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, segs = k >> 8, units = rows * segs;
 #pragma unroll 1
-    for (uint32_t u0 = warp; u0 < units; u0 += NT / 32) {
-        const uint32_t u = GLOBAL ? (u0 + rotate * 5u) % units : u0;
+    for (uint32_t u = warp; u < units; u += FW) {
         const uint32_t r = u / segs, seg = u - r * segs;
         const float4 *from = reinterpret_cast<const float4 *>(src + (uint64_t)r * src_pitch) + seg * 64u + lane;
-        const float4 v0 = GLOBAL ? __ldcg(from) : *from, v1 = GLOBAL ? __ldcg(from + 32) : *(from + 32);
+        const float4 v0 = *from, v1 = *(from + 32);
         const float4 c = consts[r];
         uint32_t hi0, lo0, hi1, lo1;
         int s0 = 0, s1 = 0;
@@ -400,10 +602,10 @@ __device__ __forceinline__ void digitise_rows(const float *src, uint32_t src_pit
             to[4] = make_int2(a1, (s1 - a1) >> 16);
         }
     }
-    meet();
+    __syncthreads();
 #pragma unroll 1
-    for (uint32_t r = threadIdx.x; r < rows; r += NT) amax[r] = consts[r].x;
-    meet();
+    for (uint32_t r = threadIdx.x; r < rows; r += FT) amax[r] = consts[r].x;
+    __syncthreads();
 }
 
 __device__ __forceinline__ float fast_sigmoid(float v) {
@@ -411,53 +613,136 @@ __device__ __forceinline__ float fast_sigmoid(float v) {
     return v >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
 }
 
-// Softmax, top-k and renormalisation of `tokens` rows of logits in shared memory (zs, FMAXE
-// floats per row), CTA-wide; src/qwen4_moe.c:209-247 with its order of operations: ties go to
-// the lower id, and with `exact` the exp-sum runs serially over e = 0..E-1 (the reference's
-// bits); otherwise it is a warp tree sum.  Returns false (CTA-uniform) when a logit is not
-// finite; the first bad row is recorded.
-__device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, int norm, uint32_t T, bool exact, uint32_t *ids_s, float *wts_s,
-                                          float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status) {
+// Top-k of up to 32 * PL ordered keys held in registers, one warp: lane L holds the keys of elements
+// L, L + 32, ... (0: absent).  Sequential selection (k dependent warp reductions) costs a lone warp
+// several hundred cycles per round, so the work is arranged in parallel steps instead:
+//   1. every lane's maximum, and the k-th largest of those 32 maxima: at least k elements reach it;
+//   2. the elements that reach it (typically a dozen or two) are compacted into `cand` (shared memory);
+//   3. every candidate counts the candidates that beat it (larger key, or equal key and lower element):
+//      that count is its place, and places below k are written out.
+// Returns false when more than 64 elements qualify (heavy ties): the caller then selects sequentially.
+// cand: 128 words.  ids_out[place] = element, keys_out[place] = key (either may alias nothing else).
+template <int PL>
+__device__ __forceinline__ bool warp_topk(const uint32_t (&key)[PL], uint32_t lane, uint32_t k, uint32_t *cand, uint32_t *ids_out,
+                                          uint32_t *keys_out) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < PL; i++) m = max(m, key[i]);
+    uint32_t ahead = 0;                                                     // lanes whose maximum beats this lane's
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const uint32_t v = __shfl_sync(0xffffffffu, m, j);
+        ahead += (v > m || (v == m && (uint32_t)j < lane)) ? 1u : 0u;
+    }
+    const uint32_t holder = __ballot_sync(0xffffffffu, ahead == min(k, 32u) - 1u);
+    const uint32_t bound = max(__shfl_sync(0xffffffffu, m, __ffs(holder) - 1), 1u);
+    uint32_t count = 0;
+    const uint32_t below = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < PL; i++) {
+        const bool in = key[i] >= bound;
+        const uint32_t votes = __ballot_sync(0xffffffffu, in);
+        const uint32_t at = count + __popc(votes & below);
+        if (in && at < 64) { cand[at] = key[i]; cand[64 + at] = lane + 32u * i; }
+        count += __popc(votes);
+    }
+    if (count > 64) return false;
+    __syncwarp();
+    const uint32_t k0 = lane < count ? cand[lane] : 0u, e0 = cand[64 + lane];
+    const uint32_t k1 = lane + 32 < count ? cand[lane + 32] : 0u, e1 = cand[96 + lane];
+    uint32_t place0 = 0, place1 = 0;
+#pragma unroll 4
+    for (uint32_t j = 0; j < count; j++) {
+        const uint32_t kj = cand[j], ej = cand[64 + j];
+        place0 += (kj > k0 || (kj == k0 && ej < e0)) ? 1u : 0u;
+        place1 += (kj > k1 || (kj == k1 && ej < e1)) ? 1u : 0u;
+    }
+    if (lane < count && place0 < k) { ids_out[place0] = e0; if (keys_out) keys_out[place0] = k0; }
+    if (lane + 32 < count && place1 < k) { ids_out[place1] = e1; if (keys_out) keys_out[place1] = k1; }
+    __syncwarp();
+    return true;
+}
+// The sequential form: every lane keeps its best three (key, element) pairs, so a selection step is one
+// warp maximum and a ballot, and a lane rescans its registers only when it has won three times.
+template <int PL>
+__device__ __forceinline__ void topk_scan(const uint32_t (&key)[PL], uint32_t lane, uint32_t &b1, uint32_t &e1, uint32_t &b2, uint32_t &e2,
+                                          uint32_t &b3, uint32_t &e3) {
+    b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu; b3 = 0; e3 = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < PL; i++) {                                         // ascending element: the lowest wins among equals
+        const uint32_t k = key[i], e = lane + 32u * i;
+        if (k > b1) { b3 = b2; e3 = e2; b2 = b1; e2 = e1; b1 = k; e1 = e; }
+        else if (k > b2) { b3 = b2; e3 = e2; b2 = k; e2 = e; }
+        else if (k > b3) { b3 = k; e3 = e; }
+    }
+}
+template <int PL>
+__device__ __forceinline__ void topk_clear(uint32_t (&key)[PL], uint32_t index) {
+#pragma unroll
+    for (int i = 0; i < PL; i++) if ((uint32_t)i == index) key[i] = 0;
+}
+template <int PL>
+__device__ __noinline__ void warp_topk_sequential(uint32_t (&key)[PL], uint32_t lane, uint32_t k, uint32_t *ids_out, uint32_t *keys_out) {
+    uint32_t b1, e1, b2, e2, b3, e3, spare = 2;
+    topk_scan<PL>(key, lane, b1, e1, b2, e2, b3, e3);
+#pragma unroll 1
+    for (uint32_t slot = 0; slot < k; slot++) {
+        const uint32_t top = __reduce_max_sync(0xffffffffu, b1);
+        const uint32_t e_win = __reduce_min_sync(0xffffffffu, b1 == top ? e1 : 0xffffffffu);
+        if (lane == 0) { ids_out[slot] = e_win; if (keys_out) keys_out[slot] = top; }
+        if ((e_win & 31u) == lane) {
+            topk_clear<PL>(key, e_win >> 5);
+            if (spare) { b1 = b2; e1 = e2; b2 = b3; e2 = e3; spare--; }
+            else { topk_scan<PL>(key, lane, b1, e1, b2, e2, b3, e3); spare = 2; }
+        }
+    }
+    __syncwarp();
+}
+
+// Softmax, top-k and renormalisation of ONE row of logits in shared memory (zs), CTA-wide;
+// src/qwen4_moe.c:209-247 with its order of operations: ties go to the lower id, and with `exact`
+// the exp-sum runs serially over e = 0..E-1 (the reference's bits); otherwise it is a warp tree
+// sum.  Returns false (CTA-uniform) when a logit is not finite; the row is recorded.
+__device__ __forceinline__ bool route_row(float *zs, uint32_t E, uint32_t k, int norm, uint32_t row, bool exact, uint32_t *ids_s, float *wts_s,
+                                       float *scratch, const unsigned long long *exp_table, uint32_t *flag, uint32_t *status) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (tid == 0) *flag = 1;
     __syncthreads();
-    if (warp < T) {                                                       // row maximum and finiteness
+    if (warp == 0) {                                                      // row maximum and finiteness
         float m = -CUDART_INF_F;
         bool bad = false;
 #pragma unroll 4
-        for (uint32_t e = lane; e < E; e += 32) { const float v = zs[warp * FMAXE + e]; bad |= !finite_f32(v); m = fmaxf(m, v); }
+        for (uint32_t e = lane; e < E; e += 32) { const float v = zs[e]; bad |= !finite_f32(v); m = fmaxf(m, v); }
         for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         bad = __any_sync(0xffffffffu, bad);
         if (lane == 0) {
-            scratch[warp] = m;
-            if (bad) { atomicOr(status, QW4SH_ERR_NONFINITE); atomicMin(status + 1, warp); *flag = 0; }
+            scratch[0] = m;
+            if (bad) { atomicOr(status, QW4SH_ERR_NONFINITE); atomicMin(status + 1, row); *flag = 0; }
         }
     }
     __syncthreads();
     if (!*flag) return false;
+    {
+        const float m = scratch[0];
 #pragma unroll 1
-    for (uint32_t r = 0; r < T; r++) {                                     // p = expf(z - max)
-        const float m = scratch[r];
-#pragma unroll 1
-        for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = expf_libm_table(__fsub_rn(zs[r * FMAXE + e], m), exp_table);
+        for (uint32_t e = tid; e < E; e += FT) zs[e] = expf_libm_table(__fsub_rn(zs[e], m), exp_table);   // p = expf(z - max)
     }
     __syncthreads();
-    if (warp < T) {
-        const float *p = zs + warp * FMAXE;
+    if (warp == 0) {
         float sum = 0.0f;
         if (exact) {
             if (lane == 0) {                                               // the reference's serial sum
                 // 32 values per pass: the loads of the next pass are issued before the 32 dependent adds of this
-                // one, and the loop overhead hides under the add chain (a lone warp issues every other cycle)
+                // one, and the loop overhead hides under the add chain
                 uint32_t e = 0;
                 float4 v[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = E >= 32 ? *reinterpret_cast<const float4 *>(p + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < 8; j++) v[j] = E >= 32 ? *reinterpret_cast<const float4 *>(zs + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
                 for (; e + 32 <= E; e += 32) {
                     float4 w[8];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) w[j] = e + 64 <= E ? *reinterpret_cast<const float4 *>(p + e + 32 + 4 * j) : v[j];
+                    for (int j = 0; j < 8; j++) w[j] = e + 64 <= E ? *reinterpret_cast<const float4 *>(zs + e + 32 + 4 * j) : v[j];
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         sum = __fadd_rn(sum, v[j].x); sum = __fadd_rn(sum, v[j].y); sum = __fadd_rn(sum, v[j].z); sum = __fadd_rn(sum, v[j].w);
@@ -465,148 +750,305 @@ __device__ __forceinline__ bool route_tokens(float *zs, uint32_t E, uint32_t k, 
 #pragma unroll
                     for (int j = 0; j < 8; j++) v[j] = w[j];
                 }
-                for (; e < E; e++) sum = __fadd_rn(sum, p[e]);
+                for (; e < E; e++) sum = __fadd_rn(sum, zs[e]);
             }
             sum = __shfl_sync(0xffffffffu, sum, 0);
         } else {
 #pragma unroll 4
-            for (uint32_t e = lane; e < E; e += 32) sum += p[e];
+            for (uint32_t e = lane; e < E; e += 32) sum += zs[e];
             for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        if (lane == 0) scratch[4 + warp] = sum;
+        if (lane == 0) scratch[1] = sum;
     }
     __syncthreads();
-    // the divisions are spread over all warps (the routing warps alone would do sixteen each, one after the other)
+    {
+        const float sum = scratch[1];
 #pragma unroll 1
-    for (uint32_t e = tid; e < E; e += FT) {                                   // the tokens' divisions of one column are independent: in flight together
+        for (uint32_t e = tid; e < E; e += FT) zs[e] = __fdiv_rn(zs[e], sum);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // keys: bits of p / sum (>= 0, so ordered as integers) + 1
+        constexpr int PL = FMAXE / 32;
+        uint32_t key[PL];
 #pragma unroll
-        for (int r = 0; r < FTOK; r++)
-            if ((uint32_t)r < T) zs[r * FMAXE + e] = __fdiv_rn(zs[r * FMAXE + e], scratch[4 + r]);
-    }
-    __syncthreads();
-    if (warp < T) {
-        float *p = zs + warp * FMAXE;
-        // keys: bits of p / sum (>= 0, so ordered as integers) + 1; a chosen entry becomes -1 (key 0).
-        // The row stays in shared memory; every lane keeps the best three keys of its elements (e = lane,
-        // lane + 32, ...), so a selection step is two warp reductions, and a lane rescans its elements only
-        // when it wins a third time after its last scan.
-        uint32_t b1, e1, b2, e2, b3, e3;
-        auto scan3 = [&]() {
-            b1 = 0; e1 = 0xffffffffu; b2 = 0; e2 = 0xffffffffu; b3 = 0; e3 = 0xffffffffu;
-#pragma unroll 4
-            for (uint32_t e = lane; e < E; e += 32) {                              // ascending e: the lowest id wins among equals
-                const float v = p[e];
-                const uint32_t key = v < 0.0f ? 0u : __float_as_uint(v) + 1u;
-                if (key > b1) { b3 = b2; e3 = e2; b2 = b1; e2 = e1; b1 = key; e1 = e; }
-                else if (key > b2) { b3 = b2; e3 = e2; b2 = key; e2 = e; }
-                else if (key > b3) { b3 = key; e3 = e; }
-            }
-        };
-        scan3();
-        uint32_t spare = 2;                                                        // valid entries behind the first
-        float selected = 0.0f, mine = 0.0f;
+        for (int i = 0; i < PL; i++) { const uint32_t e = lane + 32u * i; key[i] = e < E ? __float_as_uint(zs[e]) + 1u : 0u; }
+        __syncwarp();
+        uint32_t *cand = reinterpret_cast<uint32_t *>(zs), *keys_out = cand + 128;     // the probabilities are in registers now
+        if (!warp_topk<PL>(key, lane, k, cand, ids_s, keys_out)) warp_topk_sequential<PL>(key, lane, k, ids_s, keys_out);
+        const float mine = lane < k ? __uint_as_float(keys_out[lane] - 1u) : 0.0f;
+        float selected = 0.0f;
 #pragma unroll 1
-        for (uint32_t slot = 0; slot < k; slot++) {
-            const uint32_t top = __reduce_max_sync(0xffffffffu, b1);
-            const uint32_t e_win = __reduce_min_sync(0xffffffffu, b1 == top ? e1 : 0xffffffffu);
-            const float value = __uint_as_float(top - 1u);
-            if (lane == 0) ids_s[warp * k + slot] = e_win;
-            if (slot == lane) mine = value;
-            if ((e_win & 31u) == lane) {                                           // only this lane's elements changed
-                p[e_win] = -1.0f;
-                if (spare) { b1 = b2; e1 = e2; b2 = b3; e2 = e3; spare--; }
-                else { scan3(); spare = 2; }
-            }
-            selected = __fadd_rn(selected, value);
-        }
-        if (lane < k) wts_s[warp * k + lane] = norm ? __fdiv_rn(mine, selected) : mine;
+        for (uint32_t slot = 0; slot < k; slot++) selected = __fadd_rn(selected, __shfl_sync(0xffffffffu, mine, slot));   // slot order
+        if (lane < k) wts_s[lane] = norm ? __fdiv_rn(mine, selected) : mine;
     }
     __syncthreads();
     return true;
+}
+
+// The k largest of one row of logits by VALUE (ties to the lower id), one warp; the row is turned
+// read into ordered integer keys (its memory then serves as scratch).  `extra`: choose k + 1 and put the last one in slot k - 1 (a
+// deliberately wrong set, for the test of the repair path).  Returns false on a nonfinite logit.
+__device__ __forceinline__ bool speculate_row(float *zs, uint32_t E, uint32_t k, bool extra, uint32_t *ids_s, uint32_t lane) {
+    constexpr int PL = FMAXE / 32;
+    uint32_t key[PL];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < PL; i++) {
+        const uint32_t e = lane + 32u * i;
+        const uint32_t u = e < E ? __float_as_uint(zs[e]) : 0u;
+        bad |= e < E && (u & 0x7f800000u) == 0x7f800000u;
+        key[i] = e < E ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;      // monotone in the value, never 0
+    }
+    if (__any_sync(0xffffffffu, bad)) return false;
+    __syncwarp();
+    uint32_t *cand = reinterpret_cast<uint32_t *>(zs);                          // the row is in registers now
+    const uint32_t want = extra && k < E ? k + 1 : k;
+    uint32_t *out = extra ? cand + 128 : ids_s;
+    if (!warp_topk<PL>(key, lane, want, cand, out, nullptr)) warp_topk_sequential<PL>(key, lane, want, out, nullptr);
+    if (extra) {                                                                // the wrong set: the (k + 1)-th takes the k-th's place
+        if (lane < k) ids_s[lane] = out[lane == k - 1 && want > k ? k : lane];
+        __syncwarp();
+    }
+    return true;
+}
+
+// CLOCK: SM clock of the first streaming CTA at a phase boundary.  MARK: cycles since its own start, for every CTA
+// (words S_MARKS + 4 * cta + i of the sync array).
+#ifdef QW4_NO_PHASE_CLOCKS
+#define CLOCK(i) do { } while (0)
+#define MARK(i) do { } while (0)
+#else
+#define CLOCK(i) do { if (clocked) clocks[i] = clock64(); } while (0)
+#define MARK(i) do { if (threadIdx.x == 0) a.sync[S_MARKS + 4 * blockIdx.x + (i)] = (uint32_t)(clock64() - a.t0); } while (0)
+#endif
+
+// ---- chain CTA -----------------------------------------------------------------------------------
+// Exact logits of router rows [32 c, 32 c + 32) (row E is the shared expert's router) for every
+// token, then, in CTA t < T, the routing of token t.
+__device__ __forceinline__ void chain_cta(FusedArgs &a, uint8_t *smem) {
+    const uint32_t T = a.tokens, H = a.hidden, E = a.experts, k = a.top_k;
+    const CPlan p = make_cplan(H);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, cta = blockIdx.x;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + p.bars);              // [CSTG]
+    uint64_t *empty = full + CSTG;                                             // [CSTG]
+    uint64_t *xbar = empty + CSTG;
+    float *misc_f = reinterpret_cast<float *>(smem + p.misc);
+    uint32_t *misc_u = reinterpret_cast<uint32_t *>(smem + p.misc) + 16;
+    unsigned long long *exp_table = reinterpret_cast<unsigned long long *>(smem + p.misc + 256);
+    const bool exact = a.router_mode != 1;
+    const uint32_t loaders = 64;                                               // two loader warps: the rest sleep at the CTA barrier
+    if (tid < CSTG) { fbar_init(&full[tid], loaders); fbar_init(&empty[tid], T); }
+    if (tid == CSTG) fbar_init(xbar, 1);
+    if (tid <= CSTG) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (tid < 32) exp_table[tid] = c_exp2_table[tid];
+    __syncthreads();
+    const uint32_t r0 = cta * CROWS;
+    const uint32_t nr = exact && r0 <= E ? min((uint32_t)CROWS, E + 1 - r0) : 0;
+    bool alive = true;
+    if (nr && warp >= T && warp < T + 2) {
+        // loader warps (weights only: they start before the previous launch has drained): 16-byte pieces of the
+        // chunk, piece q of row r stored at position q ^ (r & 7)
+        uint8_t *ring = smem + p.ring;
+        const uint32_t lt = tid - 32 * T, pieces = nr * (CCH / 4), chunks = H / CCH;
+#pragma unroll 1
+        for (uint32_t i = 0; i < chunks && alive; i++) {
+            const uint32_t st = i % CSTG;
+            if (i >= CSTG) {
+                const uint32_t parity = ((i / CSTG) - 1u) & 1u;
+                const long long start = clock64();
+                while (!fbar_try(&empty[st], parity)) {                         // the chain warps share the schedulers: poll gently
+                    __nanosleep(200);
+                    if (clock64() - start > (1ll << 31)) { atomicOr(a.status, QW4SH_ERR_STATE); alive = false; break; }
+                }
+            }
+            if (!alive) break;
+#pragma unroll 1
+            for (uint32_t pc = lt; pc < pieces; pc += loaders) {
+                const uint32_t r = pc / (CCH / 4), q = pc % (CCH / 4), gr = r0 + r;
+                const uint8_t *src = (gr < E ? a.w[0].data + (uint64_t)gr * a.w[0].row_bytes : a.w[7].data) + (uint64_t)i * (CCH * 4) + q * 16u;
+                const uint32_t dst = fs_u32(ring + (st * CROWS + r) * (CCH * 4) + ((q ^ (r & 7u)) << 4));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(fs_u32(&full[st])) : "memory");
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) a.t0 = clock64();                                            // read back by thread 0 only
+    if (nr && warp < T) {
+        // chain warp: token = warp, lane = row.  Multiplies and adds are separately rounded.
+        uint8_t *xf = smem + p.xf;
+        const uint8_t *ring = smem + p.ring;
+        const uint32_t chunks = H / CCH;
+        if (tid == 0) {
+            fbar_expect(xbar, T * H * 4u);
+            for (uint32_t q = 0; q < T; q++) fbulk(xf + q * p.xf_pitch, a.x + (uint64_t)q * H, H * 4u, xbar);
+        }
+        alive = fbar_wait(xbar, 0, a.status);
+        MARK(2);
+        long long waited = 0;
+        const float4 *xv = reinterpret_cast<const float4 *>(xf + warp * p.xf_pitch);
+        float sum = 0.0f;
+#pragma unroll 1
+        for (uint32_t i = 0; i < chunks; i++) {
+            const uint32_t st = i % CSTG;
+            const long long w0 = clock64();
+            if (alive) alive = fbar_wait(&full[st], (i / CSTG) & 1u, a.status);
+            alive = __all_sync(0xffffffffu, alive);
+            waited += clock64() - w0;
+            if (!alive) break;
+            const uint8_t *row = ring + (st * CROWS + lane) * (CCH * 4);
+            // a lone warp issues every other cycle: the products go two at a time (mul.rn.f32x2 rounds each half
+            // like a scalar multiply), which leaves load + 2 packed multiplies + 4 adds per four columns, just
+            // under the adds' own latency
+#pragma unroll
+            for (uint32_t q = 0; q < CCH / 4; q++) {
+                const ulonglong2 w4 = *reinterpret_cast<const ulonglong2 *>(row + ((q ^ (lane & 7u)) << 4));
+                const ulonglong2 x4 = *reinterpret_cast<const ulonglong2 *>(&xv[i * (CCH / 4) + q]);
+                unsigned long long p01, p23;
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p01) : "l"(w4.x), "l"(x4.x));
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p23) : "l"(w4.y), "l"(x4.y));
+                sum = __fadd_rn(sum, __uint_as_float((uint32_t)p01)); sum = __fadd_rn(sum, __uint_as_float((uint32_t)(p01 >> 32)));
+                sum = __fadd_rn(sum, __uint_as_float((uint32_t)p23)); sum = __fadd_rn(sum, __uint_as_float((uint32_t)(p23 >> 32)));
+            }
+            __syncwarp();
+            if (lane == 0) fbar_arrive(&empty[st]);
+        }
+        if (alive && lane < nr) {
+            const uint32_t r = r0 + lane;
+            if (!finite_f32(sum)) { atomicOr(a.status, QW4SH_ERR_NONFINITE); atomicMin(a.status + 1, warp); }
+            if (r < E) a.logits[(uint64_t)warp * E + r] = sum; else a.shared_logit[warp] = sum;
+        }
+        if (tid == 0) a.sync[S_MARKS + 4 * blockIdx.x + 3] = (uint32_t)waited;
+    }
+    MARK(0);
+    if (exact) arrive_counter(a.sync + S_CHAIN);          // also for a CTA without rows: the count is NC
+    if (cta >= T) return;
+    // ---- routing of token `cta` ----
+    const uint32_t waited = exact ? S_CHAIN : S_FAST;
+    const uint32_t expected = exact ? a.chain_ctas : gridDim.x - a.chain_ctas;
+    bool ok = wait_counter(a.sync + waited, expected, a.status, misc_u);
+    float *zs = reinterpret_cast<float *>(smem + p.zs);
+    uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + p.ids);
+    float *wts_s = reinterpret_cast<float *>(smem + p.wts);
+    if (ok) {
+        const float *from = exact ? a.logits + (uint64_t)cta * E : a.logits_fast + (uint64_t)cta * a.fast_pitch;
+#pragma unroll 1
+        for (uint32_t e = tid; e < E; e += FT) {
+            const float v = __ldcg(from + e);
+            zs[e] = v;
+            if (!exact) a.logits[(uint64_t)cta * E + e] = v;
+        }
+        if (!exact && tid == 0) a.shared_logit[cta] = __ldcg(a.logits_fast + (uint64_t)cta * a.fast_pitch + E);
+        __syncthreads();
+        ok = route_row(zs, E, k, a.norm, cta, exact, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status);
+    }
+    if (ok && tid < k) {
+        const uint32_t e = ids_s[tid];
+        const float w = wts_s[tid];
+        a.ids[cta * k + tid] = e; a.weights[cta * k + tid] = w;
+        if (a.ids_out) a.ids_out[cta * k + tid] = e;
+        if (a.weights_out) a.weights_out[cta * k + tid] = w;
+    }
+    if (!ok && tid == 0) atomicOr(a.sync + S_ROUTE_FAIL, 1u);
+    __threadfence();
+    arrive_counter(a.sync + S_ROUTED);
+    MARK(1);
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
 template <uint32_t RT, uint32_t ST>
 __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_constant__ FusedArgs args) {
     extern __shared__ __align__(128) uint8_t smem[];
-    // The arguments span four cache lines of the constant bank, and a first touch of each line costs a
-    // miss that every SM takes at the same moment.  All lines are fetched at once here, into shared
-    // memory, and read from there afterwards.
+    // The arguments span several cache lines of the constant bank, and a first touch of each line
+    // costs a miss that every SM takes at the same moment.  All lines are fetched at once here,
+    // into shared memory, and read from there afterwards.
     __shared__ FusedArgs a;
     for (uint32_t i = threadIdx.x; i < sizeof(FusedArgs) / 4; i += FT)
         reinterpret_cast<uint32_t *>(&a)[i] = reinterpret_cast<const uint32_t *>(&args)[i];
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t NC = a.chain_ctas;
+    const uint32_t tid = threadIdx.x;
+    __shared__ uint32_t leaving_last;
+    auto leave = [&]() {
+        // the CTA that leaves last clears the counters for the next launch
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            leaving_last = atomicAdd(a.sync + S_EXITS, 1u) == gridDim.x - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (leaving_last && tid < 8) { a.sync[tid] = 0; __threadfence(); }
+    };
+    if (blockIdx.x < NC) { chain_cta(a, smem); leave(); return; }
+
     const uint32_t T = a.tokens, H = a.hidden, E = a.experts, k = a.top_k, I = a.inter, IS = a.shared_inter;
     const uint32_t pairs = T * k, rows_c = pairs + T, imax = I > IS ? I : IS;
     constexpr bool LUT = RT == T_IQ2_XXS || ST == T_IQ2_XXS;
     const FPlan p = make_fplan(H, imax, rows_c, a.partial_slices, LUT);
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
-    const uint32_t cta = blockIdx.x, grid = gridDim.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t sc = blockIdx.x - NC, NS = gridDim.x - NC;
     uint64_t *ringbar = reinterpret_cast<uint64_t *>(smem + p.bars);           // [FW][FNS]
-    uint64_t *rowbar = ringbar + FW * FNS;                                     // [FRCH]
-    uint64_t *lutbar = rowbar + FRCH;
-    uint64_t *xbar = lutbar + 1;                                               // x rows (phase A), then the logits (phase B)
-    uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + p.ids);
-    float *wts_s = reinterpret_cast<float *>(smem + p.wts);
-    float *misc_f = reinterpret_cast<float *>(smem + p.misc);                  // [0..3] x maxima then scales, [4..7] shared logits, [8..15] scratch
-    uint32_t *misc_u = reinterpret_cast<uint32_t *>(smem + p.misc) + 16;       // [0] barrier flag, [1] route ok, [2] sources, [4..19] chunk counts
+    uint64_t *rowbar = ringbar + FW * FNS;
+    uint64_t *lutbar = rowbar + 1;
+    uint64_t *xbar = lutbar + 1;                                               // x rows (phase A), then the fast logits (phase B)
+    uint64_t *abar = xbar + 1;                                                 // activation digits (phase C)
+    uint32_t *ids_s = reinterpret_cast<uint32_t *>(smem + p.ids);              // the ids phase B works with
+    float *wts_s = reinterpret_cast<float *>(smem + p.wts);                    // exact weights in the order of ids_s
+    uint32_t *ids_x = reinterpret_cast<uint32_t *>(smem + p.idx);              // the exact routes as published
+    float *wts_x = reinterpret_cast<float *>(smem + p.wtx);
+    float *misc_f = reinterpret_cast<float *>(smem + p.misc);                  // [0..3] x maxima then scales, [4..7] shared logits
+    uint32_t *misc_u = reinterpret_cast<uint32_t *>(smem + p.misc) + 16;       // [0] wait flag, [1] spec ok, [2] sources, [3] verify, [4..19] chunk counts
     uint8_t *tokmask = smem + p.tokmask, *slotmap = smem + p.slotmap;
     Src *srcs = reinterpret_cast<Src *>(smem + p.src);
     const uint8_t *lut = smem + p.lut;
     uint8_t *region = smem + p.region;
     uint8_t *xq = region + p.xq;
     int2 *xsum = reinterpret_cast<int2 *>(region + p.xsum);
-    uint32_t *amax_g = a.sync + F_SYNC_AMAX;                                   // row maxima of act / shared_act (float bits)
-    unsigned long long *clocks = reinterpret_cast<unsigned long long *>(a.sync + F_SYNC_CLOCKS);
-    const bool clocked = cta == 0 && tid == 0;
-#ifdef QW4_NO_PHASE_CLOCKS
-#define CLOCK(i) do { } while (0)
-#else
-#define CLOCK(i) do { if (clocked) clocks[i] = clock64(); } while (0)
-#endif
-    CLOCK(0);
+    unsigned long long *clocks = reinterpret_cast<unsigned long long *>(a.sync + S_CLOCKS);
+    const bool clocked = sc == 0 && tid == 0;
 
-    if (tid < FW * FNS + FRCH + 2) {                                           // the barriers lie one after the other: one thread each
+    if (tid < FW * FNS + 4) {                                                  // the barriers lie one after the other: one thread each
         fbar_init(&ringbar[tid], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 8) misc_f[tid] = 0.0f;
-    unsigned long long *exp_table = reinterpret_cast<unsigned long long *>(smem + p.misc + 256);
-    const unsigned long long exp_entry = tid < 32 ? c_exp2_table[tid] : 0ull;  // a global load: stored to shared memory once x has arrived
+    if (LUT) build_iq2_tables(smem + p.lut);
     float4 *xconsts = reinterpret_cast<float4 *>(smem + p.misc + 512);
     __syncthreads();
-    CLOCK(13);
 
     // ================================ phase A ================================
-    const uint32_t n_rows = cta <= E ? (E - cta) / grid + 1 : 0;              // router rows cta, cta + grid, ... <= E
+    const uint32_t n_rows = sc <= E ? (E - sc) / NS + 1 : 0;                  // router rows sc, sc + NS, ... <= E
     uint8_t *xf = region + p.xf;
     uint8_t *rows = region + p.rows;
-    const uint32_t chunk_bytes = H;                                            // H * 4 / FRCH
+    // weights first: nothing another launch writes
     if (warp == 0) {
-        // x first: it is what every warp waits for next
-        if (lane == 30) fbar_expect(xbar, T * H * 4u);
-        if (lane < FRCH) fbar_expect(&rowbar[lane], n_rows * chunk_bytes);
+        if (lane == 0) fbar_expect(rowbar, n_rows * H * 4u);
+        __syncwarp();
+        if (lane < n_rows) {
+            const uint32_t r = sc + lane * NS;
+            const uint8_t *src = r < E ? a.w[0].data + (uint64_t)r * a.w[0].row_bytes : a.w[7].data;
+            fbulk(rows + lane * p.row_pitch, src, H * 4u, rowbar);
+        }
+    } else if (warp == 1 && lane < 3) {                                        // the shared expert's tensors -> L2: one request per tensor
+        const uint32_t m = 4 + lane;
+        const uint32_t bytes = (uint32_t)a.w[m].expert_bytes & ~15u;            // shared tensors are far below 4 GB
+        const uint32_t sub = ((bytes / NS) + 16u) & ~15u;
+        const uint32_t from = sc * sub;
+        if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) a.t0 = clock64();
+    CLOCK(0);
+    if (warp == 0) {
+        if (lane == 0) fbar_expect(xbar, T * H * 4u);
         __syncwarp();
         if (lane < T) fbulk(xf + lane * p.xf_pitch, a.x + (uint64_t)lane * H, H * 4u, xbar);
-        if (LUT && lane == 31) {
-            fbar_expect(lutbar, F_LUT_BYTES);
-            fbulk(smem + p.lut, a.lut, F_LUT_BYTES, lutbar);
-        }
-    } else if (warp >= 2 && warp < 2 + n_rows && lane < FRCH) {                // router row warp - 2: one request per chunk and lane.  (Requests cost
-        const uint32_t j = warp - 2, c = lane, r = cta + j * grid;             // the issuing warp some 50 cycles each, so they are dealt out; a copy
-        const uint8_t *src = r < E ? a.w[0].data + (uint64_t)r * a.w[0].row_bytes : a.w[7].data;      // may land before warp 0's expect.)
-        fbulk(rows + j * p.row_pitch + c * chunk_bytes, src + c * chunk_bytes, chunk_bytes, &rowbar[c]);
-    } else if (warp == 1 && lane < 3) {                                        // the shared expert's tensors -> L2: one request per tensor
-        const uint32_t m = 4 + lane;                                            // (a warp that issues dozens of them holds the CTA barrier up)
-        const uint32_t bytes = (uint32_t)a.w[m].expert_bytes & ~15u;            // shared tensors are far below 4 GB
-        const uint32_t sub = ((bytes / grid) + 16u) & ~15u;
-        const uint32_t from = cta * sub;
-        if (from < bytes) fprefetch_l2(a.w[m].data + from, from + sub <= bytes ? sub : bytes - from);
     }
     // x -> shared memory (float, one bulk copy per row) with the row maxima, then digits; token rows beyond T stay zero
     bool alive = fbar_wait(xbar, 0, a.status);
-    if (tid < 32) exp_table[tid] = exp_entry;
-    CLOCK(14);
+    CLOCK(1);
     {
         float m[FTOK] = {0.f, 0.f, 0.f, 0.f};
         if (alive) {
@@ -627,7 +1069,6 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
             if (lane == 0 && v > 0.0f) atomicMax(reinterpret_cast<uint32_t *>(misc_f) + q, __float_as_uint(v));
         }
-        CLOCK(15);
 #pragma unroll 1
         for (uint32_t i = tid; i < (FTOK - T) * 2 * (p.kp >> 4); i += FT)       // digit rows of absent tokens
             reinterpret_cast<uint4 *>(xq + 2 * T * p.kp)[i] = make_uint4(0, 0, 0, 0);
@@ -635,321 +1076,325 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         for (uint32_t i = tid; i < (FTOK - T) * (H >> 5); i += FT) xsum[T * (H >> 5) + i] = make_int2(0, 0);
     }
     __syncthreads();
-    CLOCK(1);
-    if (a.router_mode != 0) digitise_rows<false>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
-    CLOCK(2);
-    // router rows
-    if (a.router_mode == 0) {
-        // Exact order: every (row, token) logit is one chain of K separately rounded adds, and a lone
-        // warp issues too slowly to also load and multiply.  So the other warps write the products
-        // (the same separately rounded multiplies) chunk by chunk into a two-buffer ring, and the
-        // last warp only loads and adds: lane = chain.  Named barriers 2/3 say "buffer filled",
-        // 4/5 "buffer drained".
-        float *prod = reinterpret_cast<float *>(region + p.prod);              // [2][16 chains][chunk + 4]
-        const uint32_t chunk = H / FRCH, ppitch = chunk + 4, chains = n_rows * T;
-        uint8_t *chain_map = smem + p.misc + 640;                              // chain -> router row of this CTA | token << 4
-        if (tid < chains) chain_map[tid] = (uint8_t)((tid / T) | ((tid % T) << 4));
-        __syncthreads();
-        if (warp == FW - 1) {
-            float sum = 0.0f;
+    // tree-summed logits of this CTA's rows: eight warps split K, each holds its columns of x in registers
+    // and reads every router row once; sixteen (row, token) sums per warp, then eight partial sums each
+    if (alive) alive = fbar_wait(rowbar, 0, a.status);
+    float *lpart = reinterpret_cast<float *>(region + p.rows + FRMAX * p.row_pitch);    // [8 warps][16]
+    if (warp < 8 && alive) {
+        float acc[FRMAX][FTOK];
+#pragma unroll
+        for (int j = 0; j < FRMAX; j++)
+#pragma unroll
+            for (int q = 0; q < FTOK; q++) acc[j][q] = 0.0f;
+        const uint32_t per_warp = H >> 3;                                      // columns of this warp
 #pragma unroll 1
-            for (uint32_t c = 0; c < FRCH; c++) {
-                asm volatile("bar.sync %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
-                if (lane < chains) {
-                    const float4 *pv = reinterpret_cast<const float4 *>(prod + ((c & 1u) * 16 + lane) * ppitch);
-#pragma unroll 4
-                    for (uint32_t i = 0; i < chunk / 4; i++) {
-                        const float4 q = pv[i];
-                        sum = __fadd_rn(sum, q.x); sum = __fadd_rn(sum, q.y); sum = __fadd_rn(sum, q.z); sum = __fadd_rn(sum, q.w);
-                    }
+        for (uint32_t c0 = 0; c0 < per_warp; c0 += 128) {
+            const uint32_t col = warp * per_warp + c0 + lane * 4;
+            float4 xv[FTOK];
+#pragma unroll
+            for (int q = 0; q < FTOK; q++)
+                xv[q] = (uint32_t)q < T ? *reinterpret_cast<const float4 *>(xf + q * p.xf_pitch + col * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < FRMAX; j++) {
+                if ((uint32_t)j < n_rows) {
+                    const float4 w4 = *reinterpret_cast<const float4 *>(rows + j * p.row_pitch + col * 4);
+#pragma unroll
+                    for (int q = 0; q < FTOK; q++)
+                        acc[j][q] = fmaf(w4.x, xv[q].x, fmaf(w4.y, xv[q].y, fmaf(w4.z, xv[q].z, fmaf(w4.w, xv[q].w, acc[j][q]))));
                 }
-                if (c + 2 < FRCH) asm volatile("bar.arrive %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
-            }
-            if (lane < chains) {
-                const uint32_t j = lane / T, tok = lane % T, r = cta + j * grid;
-                if (!finite_f32(sum)) { atomicOr(a.status, QW4SH_ERR_NONFINITE); atomicMin(a.status + 1, tok); }
-                if (r < E) a.logits[(uint64_t)tok * E + r] = sum; else a.shared_logit[tok] = sum;
-            }
-        } else {
-#pragma unroll 1
-            for (uint32_t c = 0; c < FRCH; c++) {
-                if (alive) alive = fbar_wait(&rowbar[c], 0, a.status);           // on a failed wait the products are garbage, the flag is set
-                if (c >= 2) asm volatile("bar.sync %0, %1;" ::"r"(4 + (c & 1u)), "n"(FT) : "memory");
-                // one unit = 32 float4 of one chain: no index arithmetic beyond a table look-up per unit
-#pragma unroll 1
-                for (uint32_t u = warp; u < chains * (chunk / 128); u += FW - 1) {
-                    const uint32_t ch = u / (chunk / 128), q4 = (u % (chunk / 128)) * 32 + lane;
-                    const uint32_t jt = chain_map[ch], j = jt & 15u, tok = jt >> 4;
-                    const float4 w4 = *reinterpret_cast<const float4 *>(rows + j * p.row_pitch + c * chunk_bytes + q4 * 16);
-                    const float4 x4 = *reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch + c * chunk_bytes + q4 * 16);
-                    *reinterpret_cast<float4 *>(prod + ((c & 1u) * 16 + ch) * ppitch + q4 * 4) =
-                        make_float4(__fmul_rn(w4.x, x4.x), __fmul_rn(w4.y, x4.y), __fmul_rn(w4.z, x4.z), __fmul_rn(w4.w, x4.w));
-                }
-                asm volatile("bar.arrive %0, %1;" ::"r"(2 + (c & 1u)), "n"(FT) : "memory");
-                // both product buffers are full and the chain warp is busy with them: the digit image of x is
-                // built here, under the chain
-                if (c == 1) digitise_rows<false, FT - 32, 6>(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum,
-                                                              H >> 5, xconsts);
             }
         }
-    } else {
-#pragma unroll 1
-        for (uint32_t c = 0; c < FRCH && alive; c++) alive = fbar_wait(&rowbar[c], 0, a.status);
-#pragma unroll 1
-        for (uint32_t dot = warp; dot < n_rows * T && alive; dot += FW) {
-            const uint32_t j = dot / T, tok = dot % T;
-            const float4 *wv = reinterpret_cast<const float4 *>(rows + j * p.row_pitch);
-            const float4 *xv = reinterpret_cast<const float4 *>(xf + tok * p.xf_pitch);
-            float acc = 0.0f;
-#pragma unroll 1
-            for (uint32_t i = lane; i < (H >> 2); i += 32) {
-                const float4 w4 = wv[i], x4 = xv[i];
-                acc = fmaf(w4.x, x4.x, fmaf(w4.y, x4.y, fmaf(w4.z, x4.z, fmaf(w4.w, x4.w, acc))));
+#pragma unroll
+        for (int j = 0; j < FRMAX; j++)
+#pragma unroll
+            for (int q = 0; q < FTOK; q++) {
+                float v = acc[j][q];
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) lpart[warp * 16 + j * FTOK + q] = v;
             }
-            for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (lane == 0) {
-                const uint32_t r = cta + j * grid;
-                if (!finite_f32(acc)) { atomicOr(a.status, QW4SH_ERR_NONFINITE); atomicMin(a.status + 1, tok); }
-                if (r < E) a.logits[(uint64_t)tok * E + r] = acc; else a.shared_logit[tok] = acc;
-            }
-        }
     }
-    alive = __all_sync(0xffffffffu, alive);
+    __syncthreads();
+    if (tid < n_rows * FTOK && (tid % FTOK) < T && alive) {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) v += lpart[w * 16 + tid];
+        a.logits_fast[(uint64_t)(tid % FTOK) * a.fast_pitch + sc + (tid / FTOK) * NS] = v;
+    }
+    CLOCK(2);
+    arrive_counter(a.sync + S_FAST);                                          // (its CTA barrier also orders the reads of xf before the digits' consts)
+    digitise_rows(reinterpret_cast<const float *>(xf), p.xf_pitch >> 2, T, H, misc_f, xq, p.kp, xsum, H >> 5, xconsts);
     CLOCK(3);
-    if (!grid_barrier(a.sync + 0, grid, a.status, misc_u)) return;
+    if (!wait_counter(a.sync + S_FAST, NS, a.status, misc_u)) return;
     CLOCK(4);
+#ifndef QW4_X_WAITS
+    MARK(0);
+#endif
 
     // ================================ phase B ================================
     float *zs = reinterpret_cast<float *>(region + p.zs);
-    const bool bulk_logits = (E & 3u) == 0;                                   // whole 16-byte pieces: one bulk copy per token row
-    if (bulk_logits) {
-        if (warp == 0 && alive) {
-            asm volatile("fence.proxy.async;" ::: "memory");                      // generic-proxy writes (the logits; phase A's use of this memory) before the copy
-            if (lane == 0) fbar_expect(xbar, T * E * 4u);
-            __syncwarp();
-            if (lane < T) fbulk(zs + lane * FMAXE, a.logits + (uint64_t)lane * E, E * 4u, xbar);
-        }
-    } else {
-#pragma unroll 1
-        for (uint32_t r = 0; r < T; r++)
-#pragma unroll 1
-            for (uint32_t e = tid; e < E; e += FT) zs[r * FMAXE + e] = __ldcg(a.logits + (uint64_t)r * E + e);
+    if (warp == 0 && alive) {
+        asm volatile("fence.proxy.async;" ::: "memory");                          // generic-proxy writes (the logits; phase A's use of this memory) before the copy
+        if (lane == 0) fbar_expect(xbar, T * a.fast_pitch * 4u);
+        __syncwarp();
+        if (lane < T) fbulk(zs + lane * FZP, a.logits_fast + (uint64_t)lane * a.fast_pitch, a.fast_pitch * 4u, xbar);
     }
-    if (tid < T) misc_f[4 + tid] = __ldcg(a.shared_logit + tid);
-#pragma unroll 1
-    for (uint32_t i = tid; i < FMAXE; i += FT) tokmask[i] = 0;
-    if (bulk_logits && alive) alive = fbar_wait(xbar, 1, a.status);            // second use of this barrier: phase parity 1
+    if (alive) alive = fbar_wait(xbar, 1, a.status);                           // second use of this barrier: phase parity 1
+    CLOCK(13);
+    if (tid == 0) misc_u[1] = 1;
     __syncthreads();
-    CLOCK(5);
-    const bool routed_ok = route_tokens(zs, E, k, a.norm, T, a.router_mode == 0, ids_s, wts_s, misc_f + 8, exp_table, misc_u + 1, a.status);
-    CLOCK(6);
-    if (routed_ok) {
-        if (tid < pairs) {
-            const uint32_t e = ids_s[tid], tok = tid / k;
-            atomicOr(reinterpret_cast<uint32_t *>(tokmask) + (e >> 2), (1u << tok) << (8 * (e & 3u)));
-            slotmap[e * 4 + tok] = (uint8_t)(tid % k);
-            if (cta == 0) {
-                a.ids[tid] = e; a.weights[tid] = wts_s[tid];
-                if (a.ids_out) a.ids_out[tid] = e;
-                if (a.weights_out) a.weights_out[tid] = wts_s[tid];
-            }
-        }
-        __syncthreads();
-        // distinct experts in ascending order behind the shared expert (source 0)
-#pragma unroll 1
-        for (uint32_t c = warp; c < (E + 31) / 32; c += FW) {
-            const uint32_t e = c * 32 + lane;
-            const uint32_t any = __ballot_sync(0xffffffffu, e < E && tokmask[e] != 0);
-            if (lane == 0) misc_u[4 + c] = __popc(any);
-        }
-        __syncthreads();
-        if (tid == 0) {
-            uint32_t running = 1;
-#pragma unroll 1
-            for (uint32_t c = 0; c < (E + 31) / 32; c++) { const uint32_t n = misc_u[4 + c]; misc_u[4 + c] = running; running += n; }
-            misc_u[2] = running;
-            Src s; s.expert = 0xffffu; s.mask = (uint8_t)((1u << T) - 1u); s.shared = 1; s.slots = 0;
-            srcs[0] = s;
-        }
-        __syncthreads();
-#pragma unroll 1
-        for (uint32_t c = warp; c < (E + 31) / 32; c += FW) {
-            const uint32_t e = c * 32 + lane;
-            const bool has = e < E && tokmask[e] != 0;
-            const uint32_t any = __ballot_sync(0xffffffffu, has);
-            if (has) {
-                Src s; s.expert = (uint16_t)e; s.mask = tokmask[e]; s.shared = 0;
-                s.slots = *reinterpret_cast<const uint32_t *>(slotmap + e * 4);
-                srcs[misc_u[4 + c] + __popc(any & ((1u << lane) - 1u))] = s;
-            }
-        }
-        __syncthreads();
+    if (warp < T) {
+        if (a.router_mode == 1 && lane == 0) misc_f[4 + warp] = zs[warp * FZP + E];     // the shared router's tree sum
+        CLOCK(14);
+        const bool fine = speculate_row(zs + warp * FZP, E, k, a.router_mode == 2 && warp == 0, ids_s + warp * k, lane);
+        if (!fine && lane == 0) misc_u[1] = 0;
+        CLOCK(15);
     }
-    const uint32_t n_src = routed_ok ? misc_u[2] : 0;
-    CLOCK(7);
+    __syncthreads();
+    const bool all_alive = __syncthreads_and(alive);
+    bool lists_ok = misc_u[1] != 0 && all_alive;
+    CLOCK(5);
+
+#ifdef QW4_X_WAITS
+    long long x_waited = 0, x_consumed = 0, x_issued = 0;
+#endif
     uint32_t ring_count = 0;                                                   // slices this warp has pushed through its ring
     uint64_t *bar = ringbar + warp * FNS;
-    if (routed_ok) {
-        // gate/up units: shared expert first, then the routed experts; whole units per CTA
-        const uint32_t us = IS >> 3, ur = I >> 3, total = us + (n_src - 1) * ur;
-        const uint32_t u0 = total * cta / grid, u1 = total * (cta + 1) / grid;            // total <= 65 * 128: no overflow
-        const uint32_t n_shu = u0 < us ? min(us, u1) - u0 : 0;                 // shared units of this CTA come first
-        const uint32_t nbh = H >> 8;
-        const uint32_t spu_s = nbh / FGeo<ST>::SLICE_BLOCKS, spu_r = nbh / FGeo<RT>::SLICE_BLOCKS;
-        const uint32_t slices = min(n_shu * spu_s + (u1 - u0 - n_shu) * spu_r, a.partial_slices);
-        const uint32_t mine = slices > warp ? (slices - 1 - warp) / FW + 1 : 0;
-        uint8_t *ring = region + p.ring + warp * FNS * FSTAGE;
-        float2 *partial = reinterpret_cast<float2 *>(region + p.partial);
-        if (LUT && alive) alive = fbar_wait(lutbar, 0, a.status);
-        alive = __all_sync(0xffffffffu, alive);
-        auto locate = [&](uint32_t n, uint32_t &ul, uint32_t &s, bool &sh) {   // CTA slice n -> local unit, slice, kind
-            if (n < n_shu * spu_s) { ul = n / spu_s; s = n % spu_s; sh = true; }
-            else { const uint32_t m = n - n_shu * spu_s; ul = n_shu + m / spu_r; s = m % spu_r; sh = false; }
-        };
-        auto issue = [&](uint32_t i) {
-            uint32_t ul, s; bool sh;
-            locate(warp + i * FW, ul, s, sh);
-            const uint32_t u = u0 + ul;
-            uint8_t *stage = ring + (i % FNS) * FSTAGE;
-            if (sh) issue_unit_slice<ST>(a.w[4].data, a.w[5].data, IS, nbh, u * 8, s, stage, &bar[i % FNS], lane);
-            else {
-                const uint32_t v = u - us, e = srcs[1 + v / ur].expert;
-                issue_unit_slice<RT>(a.w[1].data + (uint64_t)e * a.w[1].expert_bytes, a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, I, nbh,
-                                     (v % ur) * 8, s, stage, &bar[i % FNS], lane);
-            }
-        };
-        if (alive) for (uint32_t i = 0; i < FNS && i < mine; i++) issue(i);
-        // down tiles of this CTA's columns -> L2, ahead of phase C
+    uint32_t n_src = 0;
+    const uint32_t gs = IS >> 5, gr = I >> 5;                                  // granules (32 activation columns) per expert
+    const uint32_t nbh = H >> 8;
+    const uint32_t spu_s = nbh / FGeo<ST>::SLICE_BLOCKS, spu_r = nbh / FGeo<RT>::SLICE_BLOCKS;
 #pragma unroll 1
-        for (uint32_t tile = cta; tile < (H >> 4); tile += grid)
-            for (uint32_t j = warp * 4 + lane; lane < 4 && j < n_src; j += FW * 4) {      // a few requests per warp: none of them falls behind
-                const Src s = srcs[j];
-                const uint32_t rb = s.shared ? (IS >> 8) * (ST == T_Q4_K ? 144u : 64u) : (I >> 8) * (RT == T_Q4_K ? 144u : 64u);
-                const uint8_t *mat = s.shared ? a.w[6].data : a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes;
-                fprefetch_l2(mat + tile * 16 * rb, 16 * rb);
-            }
-        const uint8_t *xq_lane = xq + g * p.kp + 8 * t;
-        const int2 *xsum_tok = xsum + t * (H >> 5);
+    for (uint32_t attempt = 0; attempt < 2; attempt++) {
+        // ---- lists from ids_s: token masks and slots per expert, distinct experts in ascending order behind the shared expert ----
+        if (lists_ok) {
+            if (warp == 0) {                                                   // one warp, warp-level synchronisation only
 #pragma unroll 1
-        for (uint32_t i = 0; i < mine; i++) {
-            uint32_t ul, s; bool sh;
-            locate(warp + i * FW, ul, s, sh);
-            if (alive) alive = fbar_wait(&bar[i % FNS], (i / FNS) & 1u, a.status);
-            alive = __all_sync(0xffffffffu, alive);
-            const uint8_t *stage = ring + (i % FNS) * FSTAGE;
-            float f0 = 0.0f, f1 = 0.0f;
-            if (alive) {
-                if (sh) consume_unit_slice<ST>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
-                else consume_unit_slice<RT>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
-            }
-            partial[(warp + i * FW) * 32 + lane] = make_float2(f0, f1);
-            __syncwarp();
-            fproxy_fence();
-            if (alive && i + FNS < mine) issue(i + FNS);
-        }
-        ring_count = alive ? mine : 0;
-        CLOCK(8);
-        __syncthreads();
-        // units: slices added in order, SwiGLU, store, row maxima
+                for (uint32_t i = lane; i < FMAXE / 4; i += 32) reinterpret_cast<uint32_t *>(tokmask)[i] = 0;
+                __syncwarp();
 #pragma unroll 1
-        for (uint32_t ul = warp; ul < u1 - u0; ul += FW) {
-            const bool sh = ul < n_shu;
-            const uint32_t spu = sh ? spu_s : spu_r;
-            const uint32_t n0 = sh ? ul * spu_s : n_shu * spu_s + (ul - n_shu) * spu_r;
-            if (n0 + spu > slices) break;                                      // beyond the partial buffer (never for supported shapes)
-            float f0 = 0.0f, f1 = 0.0f;
-#pragma unroll 1
-            for (uint32_t s = 0; s < spu; s++) { const float2 v = partial[(n0 + s) * 32 + lane]; f0 += v.x; f1 += v.y; }
-            const uint32_t u = u0 + ul;
-            float v = 0.0f;
-            uint32_t row = 0;
-            bool live = false;
-            if (t < T) {
-                const float dx = misc_f[t];
-                const float gate = f0 * dx, upv = f1 * dx;
-                v = gate * fast_sigmoid(gate) * upv;
-                if (sh) { live = true; row = pairs + t; a.shared_act[(uint64_t)t * IS + u * 8 + g] = v; }
-                else {
-                    const uint32_t vu = u - us;
-                    const Src sr = srcs[1 + vu / ur];
-                    if ((sr.mask >> t) & 1u) { live = true; row = t * k + sr.slot(t); a.act[(uint64_t)row * I + (vu % ur) * 8 + g] = v; }
+                for (uint32_t pr = lane; pr < pairs; pr += 32) {
+                    const uint32_t e = ids_s[pr], tok = pr / k;
+                    atomicOr(reinterpret_cast<uint32_t *>(tokmask) + (e >> 2), (1u << tok) << (8 * (e & 3u)));
+                    slotmap[e * 4 + tok] = (uint8_t)(pr % k);
                 }
-                if (live && !finite_f32(v)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
+                __syncwarp();
+                if (lane == 0) { Src s0; s0.expert = 0xffffu; s0.mask = (uint8_t)((1u << T) - 1u); s0.shared = 1; s0.slots = 0; srcs[0] = s0; }
+                uint32_t running = 1;
+#pragma unroll 4
+                for (uint32_t c = 0; c < (E + 31) / 32; c++) {
+                    const uint32_t e = c * 32 + lane;
+                    const bool has = e < E && tokmask[e] != 0;
+                    const uint32_t any = __ballot_sync(0xffffffffu, has);
+                    if (has) {
+                        Src sn; sn.expert = (uint16_t)e; sn.mask = tokmask[e]; sn.shared = 0;
+                        sn.slots = *reinterpret_cast<const uint32_t *>(slotmap + e * 4);
+                        srcs[running + __popc(any & ((1u << lane) - 1u))] = sn;
+                    }
+                    running += __popc(any);
+                }
+                if (lane == 0) misc_u[2] = running;
             }
-            float m = live ? fabsf(v) : 0.0f;                                  // maximum over the unit's eight rows (lanes of equal t)
-            for (int o = 4; o < 32; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (live && g == 0 && m > 0.0f) atomicMax(amax_g + row, __float_as_uint(m));
+            __syncthreads();
+            n_src = misc_u[2];
         }
+        CLOCK(6);
+        if (lists_ok) {
+            // ---- gate/up: whole granules per CTA, the shared expert's first ----
+            const uint32_t total = gs + (n_src - 1) * gr;
+            const uint32_t g0 = total * sc / NS, g1 = total * (sc + 1) / NS;               // total <= 65 * 32: no overflow
+            const uint32_t n_shg = g0 < gs ? min(gs, g1) - g0 : 0;               // shared granules of this CTA come first
+            const uint32_t n_shu = n_shg * 4;
+            const uint32_t slices = min(n_shu * spu_s + ((g1 - g0) * 4 - n_shu) * spu_r, a.partial_slices);
+            const uint32_t mine = slices > warp ? (slices - 1 - warp) / FW + 1 : 0;
+            uint8_t *ring = region + p.ring + warp * FNS * FSTAGE;
+            float2 *partial = reinterpret_cast<float2 *>(region + p.partial);
+            alive = __all_sync(0xffffffffu, alive);
+            auto locate = [&](uint32_t n, uint32_t &ul, uint32_t &s, bool &sh) {   // CTA slice n -> local unit, slice, kind
+                if (n < n_shu * spu_s) { ul = n / spu_s; s = n % spu_s; sh = true; }
+                else { const uint32_t m = n - n_shu * spu_s; ul = n_shu + m / spu_r; s = m % spu_r; sh = false; }
+            };
+            auto issue = [&](uint32_t i) {
+                uint32_t ul, s; bool sh;
+                locate(warp + i * FW, ul, s, sh);
+                const uint32_t u = g0 * 4 + ul;                                    // unit index over all sources
+                const uint32_t at = ring_count + i;
+                uint8_t *stage = ring + (at % FNS) * FSTAGE;
+                if (sh) issue_unit_slice<ST>(a.w[4].data, a.w[5].data, IS, nbh, u * 8, s, stage, &bar[at % FNS], lane);
+                else {
+                    const uint32_t v = u - gs * 4, ur = gr * 4, e = srcs[1 + v / ur].expert;
+                    issue_unit_slice<RT>(a.w[1].data + (uint64_t)e * a.w[1].expert_bytes, a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, I, nbh,
+                                         (v % ur) * 8, s, stage, &bar[at % FNS], lane);
+                }
+            };
+            __syncthreads();                                                       // the keys in zs are dead: the ring may be written
+            fproxy_fence();
+            if (alive) for (uint32_t i = 0; i < FNS && i < mine; i++) issue(i);
+            // down tiles of this CTA's columns -> L2, ahead of phase C
+#pragma unroll 1
+            for (uint32_t tile = sc; tile < (H >> 4); tile += NS)
+                for (uint32_t j = warp * 4 + lane; lane < 4 && j < n_src; j += FW * 4) {      // a few requests per warp: none of them falls behind
+                    const Src s = srcs[j];
+                    const uint32_t rb = s.shared ? (IS >> 8) * (ST == T_Q4_K ? 144u : 64u) : (I >> 8) * (RT == T_Q4_K ? 144u : 64u);
+                    const uint8_t *mat = s.shared ? a.w[6].data : a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes;
+                    fprefetch_l2(mat + tile * 16 * rb, 16 * rb);
+                }
+            const uint8_t *xq_lane = xq + g * p.kp + 8 * t;
+            const int2 *xsum_tok = xsum + t * (H >> 5);
+#pragma unroll 1
+            for (uint32_t i = 0; i < mine; i++) {
+                uint32_t ul, s; bool sh;
+                locate(warp + i * FW, ul, s, sh);
+                const uint32_t at = ring_count + i;
+#ifdef QW4_X_WAITS
+                const long long w_begin = clock64();
+#endif
+                if (alive) alive = fbar_wait(&bar[at % FNS], (at / FNS) & 1u, a.status);
+                alive = __all_sync(0xffffffffu, alive);
+#ifdef QW4_X_WAITS
+                x_waited += clock64() - w_begin;
+#endif
+                const uint8_t *stage = ring + (at % FNS) * FSTAGE;
+                float f0 = 0.0f, f1 = 0.0f;
+#ifdef QW4_X_WAITS
+                const long long c_begin = clock64();
+#endif
+                if (alive) {
+                    if (sh) consume_unit_slice<ST>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
+                    else consume_unit_slice<RT>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
+                }
+                partial[(warp + i * FW) * 32 + lane] = make_float2(f0, f1);
+                __syncwarp();
+#ifdef QW4_X_WAITS
+                const long long i_begin = clock64();
+                x_consumed += i_begin - c_begin;
+#endif
+                fproxy_fence();
+                if (alive && i + FNS < mine) issue(i + FNS);
+#ifdef QW4_X_WAITS
+                x_issued += clock64() - i_begin;
+#endif
+            }
+            if (alive) ring_count += mine;
+#ifdef QW4_X_WAITS
+            if (tid == 32) { a.sync[S_MARKS + 4 * blockIdx.x + 0] = (uint32_t)x_waited; a.sync[S_MARKS + 4 * blockIdx.x + 2] = mine;
+                             a.sync[S_MARKS + 4 * blockIdx.x + 1] = (uint32_t)x_consumed; a.sync[S_MARKS + 4 * blockIdx.x + 3] = (uint32_t)x_issued; }
+#endif
+            CLOCK(7);
+#ifndef QW4_X_WAITS
+            MARK(1);
+#endif
+            __syncthreads();
+            // granules: slices added in order, SwiGLU, digit pairs with one scale per chunk
+#pragma unroll 1
+            for (uint32_t gl = warp; gl < g1 - g0; gl += FW) {
+                const bool sh = gl < n_shg;
+                const uint32_t spu = sh ? spu_s : spu_r;
+                const uint32_t gi = g0 + gl;                                       // granule over all sources
+                const Src sr = sh ? srcs[0] : srcs[1 + (gi - gs) / gr];
+                const uint32_t chunk = sh ? gi : (gi - gs) % gr;
+                const bool live = t < T && ((sr.mask >> t) & 1u);
+                const uint32_t row = sh ? pairs + t : t * k + sr.slot(t);
+                float v[4];
+                float m = 0.0f;
+                bool whole = true;
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    const uint32_t ul = gl * 4 + u;
+                    const uint32_t n0 = sh ? ul * spu_s : n_shu * spu_s + (ul - n_shu) * spu_r;
+                    whole &= n0 + spu <= slices;                                   // beyond the partial buffer (never for supported shapes)
+                    float f0 = 0.0f, f1 = 0.0f;
+#pragma unroll 1
+                    for (uint32_t s = 0; s < spu && whole; s++) { const float2 q = partial[(n0 + s) * 32 + lane]; f0 += q.x; f1 += q.y; }
+                    const float dx = misc_f[t];
+                    const float gate = f0 * dx, upv = f1 * dx;
+                    v[u] = live ? gate * fast_sigmoid(gate) * upv : 0.0f;
+                    m = fmaxf(m, fabsf(v[u]));
+                }
+                if (!whole) { if (lane == 0) atomicOr(a.status, QW4SH_ERR_STATE); continue; }
+                for (int o = 4; o < 32; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));   // over the eight rows of every unit
+                if (live && !finite_f32(m)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
+                const bool usable = finite_f32(m) && m > 0.0f;
+                const float inv = usable ? __fdividef(127.0f, m) : 0.0f, d = usable ? m * (1.0f / 127.0f) : 0.0f;
+                const float4 c = make_float4(d, inv, 254.0f * inv, 0.0f);
+                int s1 = 0, s2 = 0;
+                uint8_t *out = a.aq + (uint64_t)row * 2u * p.ap + chunk * 32u + g;
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    uint32_t ra, rb;
+                    digit_pair(v[u], c, ra, rb);
+                    s1 += (int)(int8_t)(ra & 0xffu); s2 += (int)(int8_t)(rb & 0xffu);
+                    if (live) { out[u * 8] = (uint8_t)ra; out[p.ap + u * 8] = (uint8_t)rb; }
+                }
+                for (int o = 4; o < 32; o <<= 1) { s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
+                if (live && g == 0) a.asc[(uint64_t)row * (imax >> 5) + chunk] = make_float2(d, d * fmaf((float)s2, 1.0f / 254.0f, (float)s1));
+            }
+        }
+        CLOCK(8);
+        __threadfence();
+        arrive_counter(a.sync + (attempt ? S_ACT1 : S_ACT0));
+        if (!wait_counter(a.sync + (attempt ? S_ACT1 : S_ACT0), NS, a.status, misc_u)) return;
+        if (attempt == 1) break;
+        if (!wait_counter(a.sync + S_ROUTED, T, a.status, misc_u)) return;
+        CLOCK(9);
+#ifndef QW4_X_WAITS
+        MARK(2);
+#endif
+        if (fld_acquire(a.sync + S_ROUTE_FAIL)) { leave(); return; }             // a nonfinite logit: y stays untouched
+        // ---- the exact routes against the speculation ----
+        if (tid < pairs) { ids_x[tid] = __ldcg(a.ids + tid); wts_x[tid] = __ldcg(a.weights + tid); }
+        if (tid < T) misc_f[4 + tid] = a.router_mode == 1 ? misc_f[4 + tid] : __ldcg(a.shared_logit + tid);
+        __syncthreads();
+        bool same = lists_ok;
+        if (lists_ok && tid < pairs) same = ((tokmask[ids_x[tid]] >> (tid / k)) & 1u) != 0;   // k distinct ids on both sides: contained = equal
+        same = __syncthreads_and(same);
+        if (same) {
+            if (tid < pairs) { const uint32_t e = ids_x[tid], tok = tid / k; wts_s[tok * k + slotmap[e * 4 + tok]] = wts_x[tid]; }
+            __syncthreads();
+            break;
+        }
+        // repair: phase B again with the exact ids (every CTA takes this branch together: same data, same test)
+        if (tid < pairs) { ids_s[tid] = ids_x[tid]; wts_s[tid] = wts_x[tid]; }
+        if (sc == 0 && tid == 0) atomicAdd(a.sync + S_REPAIRS, 1u);             // repaired launches since the workspace was cleared (diagnostic)
+        lists_ok = __syncthreads_and(alive);
     }
-    CLOCK(9);
-    if (!grid_barrier(a.sync + 1, grid, a.status, misc_u)) return;
     CLOCK(10);
 
     // ================================ phase C ================================
-    if (routed_ok && cta < (H >> 4)) {
+    if (sc < (H >> 4) && lists_ok) {
         uint8_t *aq = region + p.aq;
-        int2 *asum = reinterpret_cast<int2 *>(region + p.asum);
-        float *ascale = reinterpret_cast<float *>(region + p.ascale);
+        float2 *asc = reinterpret_cast<float2 *>(region + p.asc);
         uint8_t *tiles = region + p.tiles + warp * FNS * FSTAGE;
         float2 *cpartial = reinterpret_cast<float2 *>(region + p.cpartial);
         const uint32_t my_src = n_src > warp ? (n_src - 1 - warp) / FW + 1 : 0;
-        const uint32_t n_tiles = ((H >> 4) - cta + grid - 1) / grid;
+        const uint32_t n_tiles = ((H >> 4) - sc + NS - 1) / NS;
         const uint32_t steps = my_src * n_tiles;
         auto issue = [&](uint32_t n) {                                         // the ring barriers go on counting where phase B left them
-            const uint32_t tile = cta + (n / my_src) * grid, j = warp + (n % my_src) * FW;
+            const uint32_t tile = sc + (n / my_src) * NS, j = warp + (n % my_src) * FW;
             const Src s = srcs[j];
             const uint32_t at = ring_count + n;
             uint8_t *stage = tiles + (at % FNS) * FSTAGE;
             if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &bar[at % FNS], lane);
             else issue_down_tile<RT>(a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes, H, I >> 8, tile * 16, stage, &bar[at % FNS], lane);
         };
-        // digit images of the activation rows: pairs first, then the shared expert's rows
-#pragma unroll 1
-        for (uint32_t r = tid; r < rows_c; r += FT) ascale[r] = __uint_as_float(__ldcg(amax_g + r));
-        float4 *aconsts = reinterpret_cast<float4 *>(region + p.aconst);
-        // The rows were written by other CTAs a moment ago and every CTA needs all of them.  Read with ordinary
-        // loads they cost a chain of L2 round trips; when they fit the (still idle) tile ring they come in with
-        // one bulk copy per row instead and are digitised out of shared memory.
-        const bool staged = rows_c * imax * 4u <= FW * FNS * FSTAGE && ((I | IS) & 3u) == 0;
-        if (staged) {
-            float *stage = reinterpret_cast<float *>(region + p.tiles);
-            bool ok = __syncthreads_and(alive);                                    // CTA-uniform from here on: the digitiser meets at CTA barriers
-            if (ok) {
-                if (tid == 0) fbar_expect(&rowbar[0], (pairs * I + T * IS) * 4u);
-                if (lane < 4) {                                                   // four requests per warp
-                    asm volatile("fence.proxy.async;" ::: "memory");              // the rows were written through the generic proxy
-#pragma unroll 1
-                    for (uint32_t r = warp * 4 + lane; r < rows_c; r += FW * 4) {
-                        if (r < pairs) fbulk(stage + r * I, a.act + (uint64_t)r * I, I * 4u, &rowbar[0]);
-                        else fbulk(stage + pairs * I + (r - pairs) * IS, a.shared_act + (uint64_t)(r - pairs) * IS, IS * 4u, &rowbar[0]);
-                    }
-                }
-                ok = __syncthreads_and(fbar_wait(&rowbar[0], 1, a.status));         // second use of this barrier: phase parity 1
-            }
-            if (ok) {
-                if (I == IS) digitise_rows<false>(stage, I, rows_c, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
-                else {
-                    digitise_rows<false>(stage, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts);
-                    digitise_rows<false>(stage + pairs * I, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5),
-                                            imax >> 5, aconsts + pairs);
-                }
-            }
-            alive = ok;
-            fproxy_fence();                                                        // the ring goes back to the bulk copies
-            if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
-        } else {
+        bool ok = __syncthreads_and(alive);                                    // also: phase B's use of the region is over
+        if (ok) {
+            asm volatile("fence.proxy.async;" ::: "memory");                      // the digits were written through the generic proxy, by other CTAs
             fproxy_fence();
-            if (alive) for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
-            __syncthreads();
-            digitise_rows<true>(a.act, I, pairs, I, ascale, aq, p.ap, asum, imax >> 5, aconsts, cta);
-            digitise_rows<true>(a.shared_act, IS, T, IS, ascale + pairs, aq + 2 * pairs * p.ap, p.ap, asum + pairs * (imax >> 5), imax >> 5,
-                                   aconsts + pairs, cta);
+            const uint32_t aq_bytes = rows_c * 2u * p.ap, asc_bytes = rows_c * (imax >> 5) * 8u;
+            if (tid == 0) {
+                fbar_expect(abar, aq_bytes + asc_bytes);
+                fbulk(aq, a.aq, aq_bytes, abar);
+                fbulk(asc, a.asc, asc_bytes, abar);
+            }
+            for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
+            ok = __syncthreads_and(fbar_wait(abar, 0, a.status));
         }
+        alive = ok;
         CLOCK(11);
         uint32_t n = 0;
 #pragma unroll 1
         for (uint32_t ti = 0; ti < n_tiles; ti++) {
-            const uint32_t tile = cta + ti * grid;
+            const uint32_t tile = sc + ti * NS;
             float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll 1
             for (uint32_t si = 0; si < my_src; si++, n++) {
@@ -959,21 +1404,21 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 const bool live_t = t < T && ((s.mask >> t) & 1u);
                 const uint32_t row_t = s.shared ? pairs + (t < T ? t : 0) : (live_t ? t * k + s.slot(t) : 0);
                 const uint8_t *aq_lane = aq + (2 * row_g + (g & 1u)) * p.ap + 8 * t;
-                const int2 *asum_tok = asum + row_t * (imax >> 5);
+                const float2 *asc_tok = asc + row_t * (imax >> 5);
                 const uint32_t at = ring_count + n;
                 if (alive) alive = fbar_wait(&bar[at % FNS], (at / FNS) & 1u, a.status);
                 alive = __all_sync(0xffffffffu, alive);
                 const uint8_t *stage = tiles + (at % FNS) * FSTAGE;
                 float f0 = 0.0f, f1 = 0.0f;
                 if (alive) {
-                    if (s.shared) consume_down_tile<ST>(stage, IS >> 8, lut, aq_lane, asum_tok, g, t, f0, f1);
-                    else consume_down_tile<RT>(stage, I >> 8, lut, aq_lane, asum_tok, g, t, f0, f1);
+                    if (s.shared) consume_down_tile<ST>(stage, IS >> 8, lut, aq_lane, asc_tok, g, t, f0, f1);
+                    else consume_down_tile<RT>(stage, I >> 8, lut, aq_lane, asc_tok, g, t, f0, f1);
                 }
                 __syncwarp();
                 fproxy_fence();
                 if (alive && n + FNS < steps) issue(n + FNS);
                 if (live_t) {
-                    const float coef = (s.shared ? fast_sigmoid(misc_f[4 + t]) : wts_s[t * k + s.slot(t)]) * ascale[row_t];
+                    const float coef = s.shared ? fast_sigmoid(misc_f[4 + t]) : wts_s[t * k + s.slot(t)];
                     acc0 = fmaf(coef, f0, acc0); acc1 = fmaf(coef, f1, acc1);
                 }
             }
@@ -987,7 +1432,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                     const float2 v = cpartial[w * 32 + l];
                     sum += hi ? v.y : v.x;
                 }
-                if (tt < T) {
+                if (tt < T && alive) {
                     if (!finite_f32(sum)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
                     a.y[(uint64_t)tt * H + tile * 16 + hi * 8 + gg] = sum;
                 }
@@ -996,20 +1441,12 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         }
     }
     CLOCK(12);
-    // the CTA that leaves last clears the counters and the row maxima for the next launch
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        misc_u[0] = atomicAdd(a.sync + 2, 1u) == grid - 1 ? 1u : 0u;
-    }
-    __syncthreads();
-    if (misc_u[0]) {
-#pragma unroll 1
-        for (uint32_t r = tid; r < rows_c; r += FT) amax_g[r] = 0;
-        if (tid == 0) { a.sync[0] = 0; a.sync[1] = 0; a.sync[2] = 0; }
-        __threadfence();
-    }
+#ifndef QW4_X_WAITS
+    MARK(3);
+#endif
+    leave();
 #undef CLOCK
+#undef MARK
 }
 
 }  // namespace qw4
@@ -1028,24 +1465,41 @@ static DevTensor fdev(const QW4ShTensor &s) {
 
 static int g_fused_mode = -1;                          // -1 automatic, 0 never
 extern "C" void qw4sh_set_fused_decode(int mode) { g_fused_mode = mode; }
+static int g_wrong_speculation = 0;
+extern "C" void qw4sh_set_wrong_speculation(int on) { g_wrong_speculation = on ? 1 : 0; }
 
 static bool fused_type(uint32_t type) { return type == T_Q4_K || type == T_IQ2_XXS; }
 static uint32_t slice_blocks(uint32_t type) { return type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS; }
 
-// Most slices one CTA can get: its share of the units (whole units, the shared expert's first),
-// each cut into its format's number of slices.
-static uint32_t partial_capacity(const QW4ShLayer *l, size_t tokens, int grid) {
-    const uint32_t nbh = l->hidden >> 8, spu_s = nbh / slice_blocks(l->w[4].type), spu_r = nbh / slice_blocks(l->w[1].type);
-    const uint32_t us = l->shared_inter >> 3, ur = l->inter >> 3;
-    const uint64_t total = us + (uint64_t)tokens * l->top_k * ur;
-    const uint32_t per_cta = (uint32_t)((total + grid - 1) / grid) + 1;
-    return per_cta * (spu_s > spu_r ? spu_s : spu_r);
+// Chain CTAs: one per 32 rows of the router (the shared expert's router is row E), and at least
+// one per token (chain CTA t routes token t).  The fast mode keeps only the routing CTAs.
+static uint32_t chain_ctas(const QW4ShLayer *l, size_t tokens, int router_mode) {
+    const uint32_t by_rows = router_mode == 1 ? 0 : (l->experts + 1 + CROWS - 1) / CROWS;
+    return by_rows > tokens ? by_rows : (uint32_t)tokens;
 }
 
-static FPlan plan_for(const QW4ShLayer *l, size_t tokens, int grid) {
+// Most slices one streaming CTA can get: its share of the granules (whole granules of four units,
+// the shared expert's first), each unit cut into its format's number of slices.
+static uint32_t partial_capacity(const QW4ShLayer *l, size_t tokens, uint32_t streaming) {
+    const uint32_t nbh = l->hidden >> 8, spu_s = nbh / slice_blocks(l->w[4].type), spu_r = nbh / slice_blocks(l->w[1].type);
+    const uint64_t total = (l->shared_inter >> 5) + (uint64_t)tokens * l->top_k * (l->inter >> 5);
+    const uint32_t per_cta = (uint32_t)((total + streaming - 1) / streaming) + 1;
+    return per_cta * 4 * (spu_s > spu_r ? spu_s : spu_r);
+}
+
+static FPlan plan_for(const QW4ShLayer *l, size_t tokens, uint32_t streaming) {
     const uint32_t imax = l->inter > l->shared_inter ? l->inter : l->shared_inter;
     const bool lut = l->w[1].type == T_IQ2_XXS || l->w[4].type == T_IQ2_XXS;
-    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, grid), lut);
+    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, streaming), lut);
+}
+
+// Bytes of the workspace arrays the kernel needs beyond the common ones (for `cap` tokens, at most FTOK used).
+extern "C" void qw4sh_fused_scratch_sizes(const QW4ShLayer *l, size_t *aq_bytes, size_t *asc_bytes, size_t *fast_bytes) {
+    const uint32_t imax = l->inter > l->shared_inter ? l->inter : l->shared_inter;
+    const size_t rows = (size_t)FTOK * l->top_k + FTOK;
+    *aq_bytes = rows * 2 * (imax + 32) + 256;
+    *asc_bytes = rows * (imax / 32 + 1) * 8 + 256;
+    *fast_bytes = (size_t)FTOK * ((l->experts + 1 + 3) & ~3u) * 4 + 256;
 }
 
 // Whether the one-kernel decode path covers this layer and batch.
@@ -1063,20 +1517,34 @@ extern "C" int qw4sh_fused_supported(const QW4ShLayer *l, size_t tokens, const f
     // a down tile (16 rows) must fit one ring stage
     if (rt == T_Q4_K ? I > 512 : I > 1024) return 0;
     if (st == T_Q4_K ? IS > 512 : IS > 1024) return 0;
-    if (grid < 1 || (uint32_t)grid * FRMAX < l->experts + 1) return 0;
-    if (tokens * l->top_k + tokens > 192) return 0;                      // row maxima live in the sync array
-    if (plan_for(l, tokens, grid).total > 227u * 1024u) return 0;
+    const uint32_t nc = chain_ctas(l, tokens, 0);
+    if (grid < 1 || (uint32_t)grid <= nc) return 0;
+    const uint32_t streaming = (uint32_t)grid - nc;
+    if (streaming * FRMAX < l->experts + 1) return 0;
+    if (plan_for(l, tokens, streaming).total > 227u * 1024u || make_cplan(H).total > 227u * 1024u) return 0;
     return 1;
 }
 
 template <uint32_t RT, uint32_t ST>
 static int launch_fused(const FusedArgs &a, uint32_t smem, int grid, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(fused_decode_kernel<RT, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static bool configured[64] = {false};                 // per device: the attribute and the residency check
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[device]) {
+        e = cudaFuncSetAttribute(fused_decode_kernel<RT, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+        if (e != cudaSuccess) return (int)e;
+        // the grid barriers need every CTA resident: one per SM, and an SM must take one
+        int resident = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fused_decode_kernel<RT, ST>, FT, 227 * 1024 - 1024);
+        if (e != cudaSuccess) return (int)e;
+        if (resident < 1) return (int)cudaErrorCooperativeLaunchTooLarge;
+        configured[device] = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(FT); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, fused_decode_kernel<RT, ST>, a);
     if (e != cudaSuccess) return (int)e;
@@ -1085,22 +1553,27 @@ static int launch_fused(const FusedArgs &a, uint32_t smem, int grid, cudaStream_
 
 extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                                   uint32_t *ids_out, float *weights_out, int router_mode, int sm_count) {
+    if (!work->fused_aq || !work->fused_asc || !work->logits_fast) return -5;
     FusedArgs a;
     for (int i = 0; i < 8; i++) a.w[i] = fdev(layer->w[i]);
     a.x = x; a.y = y;
     a.tokens = (uint32_t)tokens; a.hidden = layer->hidden; a.experts = layer->experts; a.top_k = layer->top_k;
-    a.inter = layer->inter; a.shared_inter = layer->shared_inter; a.norm = layer->norm; a.router_mode = router_mode;
+    a.inter = layer->inter; a.shared_inter = layer->shared_inter; a.norm = layer->norm; a.router_mode = router_mode == 0 && g_wrong_speculation ? 2 : router_mode;
     a.logits = work->logits; a.shared_logit = work->shared_logit; a.ids = work->ids; a.weights = work->weights;
-    a.act = work->act; a.shared_act = work->shared_act; a.ids_out = ids_out; a.weights_out = weights_out;
+    a.logits_fast = work->logits_fast; a.fast_pitch = (layer->experts + 1 + 3) & ~3u;
+    a.aq = (uint8_t *)work->fused_aq; a.asc = (float2 *)work->fused_asc;
+    a.ids_out = ids_out; a.weights_out = weights_out;
     a.sync = work->sync; a.status = work->status;
     const uint32_t rt = layer->w[1].type, st = layer->w[4].type;
-    const bool lut = rt == T_IQ2_XXS || st == T_IQ2_XXS;
-    a.lut = lut ? qw4sh_lut_image() : nullptr;
-    if (lut && !a.lut) return -3;
-    a.partial_slices = partial_capacity(layer, tokens, sm_count);
-    const FPlan p = plan_for(layer, tokens, sm_count);
-    if (p.total > 227u * 1024u) return -4;
+    a.lut = nullptr;
+    const uint32_t streaming = (uint32_t)sm_count - chain_ctas(layer, tokens, 0);     // the same split in every mode (plans, capacity)
+    a.chain_ctas = (uint32_t)sm_count - streaming;
+    a.partial_slices = partial_capacity(layer, tokens, streaming);
+    const FPlan p = plan_for(layer, tokens, streaming);
+    const CPlan c = make_cplan(layer->hidden);
+    const uint32_t smem = p.total > c.total ? p.total : c.total;
+    if (smem > 227u * 1024u - 1024u) return -4;
     cudaStream_t s = (cudaStream_t)work->stream;
-    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, p.total, sm_count, s) : launch_fused<T_Q4_K, T_IQ2_XXS>(a, p.total, sm_count, s);
-    return st == T_Q4_K ? launch_fused<T_IQ2_XXS, T_Q4_K>(a, p.total, sm_count, s) : launch_fused<T_IQ2_XXS, T_IQ2_XXS>(a, p.total, sm_count, s);
+    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, smem, sm_count, s) : launch_fused<T_Q4_K, T_IQ2_XXS>(a, smem, sm_count, s);
+    return st == T_Q4_K ? launch_fused<T_IQ2_XXS, T_Q4_K>(a, smem, sm_count, s) : launch_fused<T_IQ2_XXS, T_IQ2_XXS>(a, smem, sm_count, s);
 }

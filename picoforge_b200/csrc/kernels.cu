@@ -1482,11 +1482,15 @@ static int launch_route_group_small(const QW4ShLayer *layer, const QW4ShWork *wo
     return 0;
 }
 
+static bool takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, const float *y, size_t tokens) {
+    return g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count());
+}
+
 static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                           uint32_t *ids_out, float *weights_out, int router_mode, bool timed) {
     cudaStream_t stream = (cudaStream_t)work->stream;
     const uint32_t T = (uint32_t)tokens, k = layer->top_k, E = layer->experts, H = layer->hidden;
-    if (!timed && g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count())) {
+    if (!timed && takes_fused(layer, work, x, y, tokens)) {
         // a cooperative grid that cannot be resident all at once (another context holds SMs) is refused
         // at launch: the multi-kernel sequence below does the same work
         const int fused_rc = qw4sh_fused_decode(layer, work, x, y, tokens, ids_out, weights_out, router_mode, sm_count());
@@ -1847,6 +1851,10 @@ extern "C" int qw4sh_fused_phase_clocks(const QW4ShWork *work, uint64_t clocks[1
     CU(cudaMemcpy(clocks, work->sync + 8, 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     return 0;
 }
+extern "C" int qw4sh_fused_repairs(const QW4ShWork *work, uint32_t *count) {
+    CU(cudaMemcpy(count, work->sync + 48, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return 0;
+}
 
 extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
                                    uint32_t *ids_out, float *weights_out, int router_mode) {
@@ -1861,6 +1869,8 @@ extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *wor
         return rc;
     }
     GraphCache *cache = (GraphCache *)work->graph_cache;
+    // the one-kernel decode path is one launch already, chained to its neighbours by programmatic stream serialisation
+    if (takes_fused(layer, work, x, y, tokens)) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
     if (!g_graph_mode || !cache) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
     const bool same = cache->layer == layer && cache->x == x && cache->y == y && cache->ids == ids_out &&
                       cache->weights == weights_out && cache->tokens == tokens && cache->mode == router_mode;

@@ -256,21 +256,24 @@ static Qwen4Status plan_work(const Qwen4Moe *m, size_t cap, size_t *chunk, Plan 
     const size_t i = m->c.intermediate, si = m->c.shared_intermediate;
     /* sizes in 4-byte words */
     const size_t g32 = pairs / 32 + e + 2;                   /* groups of <= 32 rows: at most pairs/32 + experts */
-    const size_t count[49] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
+    size_t fused_aq = 0, fused_asc = 0, fused_fast = 0;
+    qw4sh_fused_scratch_sizes(&m->layer, &fused_aq, &fused_asc, &fused_fast);
+    const size_t count[52] = {t * h, t * h, t * e, t * e, t, pairs, pairs, e + 1, pairs, pairs, e + 1,
         pairs * i, t * si, t * h, 4,
         pairs * h, t * h,                                   /* 15 out, 16 shared_out */
         t * h / 2 + 8, t * h / 2 + 8, t * (h / 32 + 1) * 2, t,                 /* 17 xq, 18 xneg, 19 xsum, 20 xscale */
         pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) * 2, pairs,  /* 21 aq, 22 aneg, 23 asum, 24 ascale */
         t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) * 2, t,              /* 25 sq, 26 sneg, 27 ssum, 28 sscale */
-        pairs * 4 + t + 16, t + 8, 4, 256, 0,
+        pairs * 4 + t + 16, t + 8, 4, 1024, 0,
         /* 34.. tensor-core prefill: fp16 hi/lo images (2 bytes per value) and 32-column sums of x, act, shared act; groups */
         t * h / 2 + 8, t * h / 2 + 8, t * (h / 32) / 2 + 8, t * (h / 32) / 2 + 8,               /* 34 xh_hi, 35 xh_lo, 36 xs_hi, 37 xs_lo */
         pairs * i / 2 + 8, pairs * i / 2 + 8, pairs * (i / 32 + 1) / 2 + 8, pairs * (i / 32 + 1) / 2 + 8,   /* 38-41 act */
         t * si / 2 + 8, t * si / 2 + 8, t * (si / 32 + 1) / 2 + 8, t * (si / 32 + 1) / 2 + 8,           /* 42-45 shared act */
         g32 * 4 + (t / 32 + 2) * 4, 8,
-        2 * e * (t / 32 + 1) + e + 8};                                                      /* 48 dispatch scratch */                                                      /* 46 groups32 (routed, then shared), 47 counts */                                  /* 29 groups, 30 spare, 31 n_groups, 32 sync */
+        2 * e * (t / 32 + 1) + e + 8,
+        fused_aq / 4, fused_asc / 4, fused_fast / 4};                                    /* 49-51 one-kernel decode path */                                                      /* 48 dispatch scratch */                                                      /* 46 groups32 (routed, then shared), 47 counts */                                  /* 29 groups, 30 spare, 31 n_groups, 32 sync */
     size_t at = 0;
-    for (int j = 0; j < 49; j++) {
+    for (int j = 0; j < 52; j++) {
         if (count[j] > (SIZE_MAX >> 4)) return report(err, QW4_OVERFLOW, "scratch size overflow");
         plan->offset[j] = at;
         at += align256(count[j] * 4 + 4);
@@ -349,6 +352,8 @@ Qwen4Status qwen4_moe_work_create(const Qwen4Moe *m, size_t cap, size_t budget, 
     w->d.shared_groups32 = (char *)w->d.groups32 + (pairs_of(m, chunk) / 32 + m->c.experts + 2) * 16;
     w->d.n_groups32 = (uint32_t *)(base + plan.offset[47]);
     w->d.dispatch_scratch = (uint32_t *)(base + plan.offset[48]);
+    w->d.fused_aq = base + plan.offset[49]; w->d.fused_asc = base + plan.offset[50];
+    w->d.logits_fast = (float *)(base + plan.offset[51]);
     if (qw4sh_prepare_mma()) {
         Qwen4Status st = cuda_failure(err, "tensor-core tables");
         qwen4_moe_work_destroy(w);
@@ -756,6 +761,9 @@ void qw4cu_set_prefill_path(int path) { qw4sh_set_prefill_path(path); }
 void qw4cu_set_tile_path(int path) { qw4sh_set_tile_path(path); }
 void qw4cu_prefill_debug(void *device_words) { qw4sh_prefill_debug(device_words); }
 int qw4cu_decode_phase_clocks(const Qwen4MoeWork *w, uint64_t clocks[16]) { return w ? qw4sh_fused_phase_clocks(&w->d, clocks) : -1; }
+void qw4cu_set_decode_wrong_speculation(int on) { qw4sh_set_wrong_speculation(on); }
+int qw4cu_decode_debug_words(const Qwen4MoeWork *w, uint32_t *out, size_t words) { return w && out && words <= 1024 ? qw4sh_memcpy(out, w->d.sync, words * 4, 0) : -1; }
+int qw4cu_decode_repairs(const Qwen4MoeWork *w, uint32_t *count) { return w && count ? qw4sh_fused_repairs(&w->d, count) : -1; }
 int qw4cu_stage_times(double *ms, uint64_t *forwards) { return qw4sh_stage_times(ms, forwards); }
 int qw4cu_moe_work_timer_begin(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[0], w->d.stream) : -1; }
 int qw4cu_moe_work_timer_end(Qwen4MoeWork *w) { return w ? qw4sh_event_record(w->d.timer[1], w->d.stream) : -1; }

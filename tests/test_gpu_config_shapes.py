@@ -123,22 +123,17 @@ def test_decode_one_kernel_path_metric(gpu):
 
 
 def test_three_layer_stack_fed_layer_to_layer(gpu):
-    """Layer l + 1 reads layer l's output, brought back to unit RMS on the host (the engine has
-    norms and other blocks in between).  The GPU stack feeds on its own outputs, the oracle stack
-    on the oracle's: ids stay equal layer by layer and the last y holds the tolerance."""
-    x_gpu = synth.activations(4, 64)
-    x_gpu[:, 0] = 1.0
-    x_cpu = x_gpu.copy()
+    """Layer l + 1 reads the GPU's output of layer l, brought back to unit RMS on the host (the
+    engine has norms and other blocks in between).  Every layer is checked against the oracle run
+    on the very input the GPU layer saw: ids bit-exact, y within the tolerance."""
+    x = synth.activations(4, 64)
+    x[:, 0] = 1.0
     for index in range(3):
         spec = c4_layer(index)
-        want = oracle.forward(spec, x_cpu, threads=synth.threads())
+        want = oracle.forward(spec, x, threads=synth.threads())
         with MoeLayer(gpu, spec, 64) as layer:
-            y, ids, _ = layer.forward(x_gpu)
+            y, ids, _ = layer.forward(x)
         np.testing.assert_array_equal(ids, want["ids"], err_msg=f"layer {index}")
         assert np.abs(y.astype(np.float64) - want["y"]).max() <= Y_TOLERANCE, index
-
-        def renorm(v):
-            out = (v / np.sqrt(np.mean(v.astype(np.float64) ** 2, axis=1, keepdims=True))).astype(np.float32)
-            out[:, 0] = 1.0                                   # the constant column that carries the popularity bias
-            return out
-        x_gpu, x_cpu = renorm(y), renorm(want["y"])
+        x = (y / np.sqrt(np.mean(y.astype(np.float64) ** 2, axis=1, keepdims=True))).astype(np.float32)
+        x[:, 0] = 1.0                                         # the constant column that carries the popularity bias

@@ -68,6 +68,38 @@ def test_one_kernel_decode_at_config_shapes_both_router_modes(gpu):
         assert np.abs(weights - want["weights"]).max() <= 1e-6
 
 
+@pytest.mark.parametrize("routed,tokens,experts", [(16, 4, 64), (12, 1, 512), (16, 3, 512)])
+def test_wrong_speculation_is_repaired(gpu, routed, tokens, experts):
+    """The kernel starts the experts from tree-summed logits and checks that guess against the exact
+    routes.  With a wrong expert forced into the guess of token 0 the launch must notice, run the
+    experts again with the exact ids, and still return the reference's ids, weights and y."""
+    import oracle
+    from picoforge_b200 import synth
+    from picoforge_b200.layer import MoeLayer
+    spec = synth.make_layer(640 + routed + tokens, routed_type=routed, shared_type=12, experts=experts, top_k=10)
+    x = synth.activations(640 + tokens, tokens)
+    want = oracle.forward(spec, x, threads=synth.threads())
+    repairs = C.c_uint32()
+    with MoeLayer(gpu, spec, tokens) as layer:
+        y0, ids0, weights0 = layer.forward(x)
+        assert gpu.lib.qw4cu_decode_repairs(layer.work, C.byref(repairs)) == 0 and repairs.value == 0
+        gpu.lib.qw4cu_set_decode_wrong_speculation(1)
+        try:
+            gpu.lib.qw4cu_launch_log_begin()
+            y, ids, weights = layer.forward(x)
+            assert gpu.launch_names() == ["fused_decode_kernel"]
+        finally:
+            gpu.lib.qw4cu_set_decode_wrong_speculation(0)
+        assert gpu.lib.qw4cu_decode_repairs(layer.work, C.byref(repairs)) == 0 and repairs.value == 1
+        y2, ids2, _ = layer.forward(x)                  # and the workspace is fit for the next launch
+    np.testing.assert_array_equal(ids, want["ids"])
+    np.testing.assert_array_equal(weights, want["weights"])
+    assert np.abs(y - want["y"]).max() <= Y_TOLERANCE
+    np.testing.assert_array_equal(ids0, ids)
+    np.testing.assert_array_equal(y2, y0)
+    assert np.abs(y - y0).max() <= 1e-4                 # same experts, possibly in another source order
+
+
 def test_nonfinite_logit_leaves_outputs_untouched(gpu):
     """A NaN router weight makes every logit NaN: status NONFINITE, y keeps its fill value."""
     from picoforge_b200 import abi, synth
