@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the B200 Qwen4 MoE layer.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2|c3|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c0|c1|c2|c3|c4] [--sharded c4,c3] [--impl reference]
 
 A step is one pass of the MoE layer over one batch of synthetic tokens.  The default workload
 (N = 1) is the 4-token decode / multi-token-verify batch with IQ2_XXS routed experts and a
@@ -17,9 +17,15 @@ One JSON line is printed by rank 0:
   cpu_baseline  the reference's own CPU MoE path timed here on the host cores
 `--impl reference` times only that CPU path and prints the same line shape.
 
-With N > 1 (torchrun, one rank per GPU) the workload is the sharded one: batched decode of 64
-sequences through 48 Q4_K layers with the 512 experts cut into N blocks (expert parallel), rows
-exchanged by all-to-all over NCCL; `--workload c4` runs the same batch on one GPU for comparison.
+With N > 1 (torchrun, one rank per GPU) every rank runs its own replica of that batch (single-token
+decode stays on one GPU: independent replicas, no collective on the data path, weak scaling).
+
+The two sharded configurations are measured beside it at every N, N = 1 included, through the
+library's expert-parallel step (`qw4cu_moe_ep_forward_device`: experts in N contiguous blocks, one
+all-gather and one reduce-scatter per layer over NCCL), and reported under "sharded": c4 (64
+streams x 1 token through 48 Q4_K layers, Zipf expert popularity) and c3 (8 chunks of 1024 tokens
+through 48 layers, Q2_K routed + Q4_K shared), each with the parity of its first layer against the
+CPU oracle.  `--workload c3|c4` runs one of them alone; `--sharded ""` leaves them out.
 """
 from __future__ import annotations
 
@@ -40,12 +46,11 @@ sys.path.insert(0, str(ROOT))
 from picoforge_b200 import abi, synth  # noqa: E402
 from picoforge_b200.layer import MoeLayer  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarised in profiles/ (ncu's replay adds cache write-backs to the write part; the read part equals
-# the algorithmic bytes).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel.  ncu cannot run inside a timed
+# benchmark, so the figure comes from the capture summarised in the named file (same command, same workload) and
+# is reported with that source; a workload without a capture of its current kernel reports null.
 TRAFFIC = {
-    "c1:fused_decode_kernel": 32.91e6 + 12.29e6,
-    "c2:gate_up_routed": 144.26e6 + 17.5e6,
+    "c1:fused_decode_kernel": {"bytes": 32.07e6 + 0.02e6, "source": "profiles/decode_c1_fused_decode_kernel.md"},
 }
 
 STAGES = ("router_logits", "route", "group", "gate_up_routed", "gate_up_shared", "down_routed", "down_shared", "combine")
@@ -81,11 +86,11 @@ def workload(name: str, layers: int):
         x = synth.activations(2, 1024)
         x[:, 0] = 1.0
         desc = "c2: 1024-token prefill chunk, Q4_K, Zipf(1.1) expert popularity"
-    elif name == "c3":
+    elif name == "c3-layer":
         specs = [synth.make_layer(3, layer=l, routed_type=abi.Q2_K, shared_type=abi.Q4_K) for l in range(layers)]
         x = synth.activations(3, 1024)
         desc = "c3 (one GPU): 1024-token prefill chunk, Q2_K routed + Q4_K shared, uniform routing"
-    elif name == "c4":
+    elif name == "c4-layer":
         specs = []
         for l in range(layers):
             spec = synth.make_layer(4, layer=l, routed_type=abi.Q4_K, shared_type=abi.Q4_K)
@@ -201,134 +206,171 @@ def cpu_reference_step(specs, x, repeats: int, warmup: int):
     return seconds, threads, kind
 
 
-# ---- main --------------------------------------------------------------------------------------
-# ---- expert-parallel batched decode (C4) ------------------------------------------------------------
-def run_expert_parallel(args, rank: int, local_rank: int, world: int) -> None:
-    """64 concurrent sequences, one token each, through `--ep-layers` Q4_K layers with Zipf(1.1) expert
-    popularity; the 512 experts are cut into `world` contiguous blocks, tokens are data-parallel, and
-    rows travel to the experts' owners and back by all-to-all over NCCL (picoforge_b200/expert_parallel.py).
-    Total work is fixed as N grows ("strong" scaling).  Time: CUDA events on the stream everything is
-    enqueued on, maximum over ranks."""
-    import torch
-    import torch.distributed as dist
-    from picoforge_b200.expert_parallel import EpLayer, TorchExchange
+# ---- sharded workloads (expert parallel over the ranks of this job, world 1 included) -----------------
+SHARDED = {
+    # name: (routed type, shared type, tokens per chunk, chunks, Zipf-skewed router, seed, description)
+    "c4": (abi.Q4_K, abi.Q4_K, 64, 1, True, 4, "c4: batched decode, 64 sequences x 1 token through {layers} Q4_K layers, Zipf(1.1) expert popularity"),
+    "c3": (abi.Q2_K, abi.Q4_K, 1024, 8, False, 3, "c3: 8192-token prefill (8 chunks of 1024) through {layers} layers, Q2_K routed + Q4_K shared, uniform routing"),
+}
 
-    torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    api = abi.product()
+
+def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
+    """One sharded workload through qw4cu_moe_ep_forward_device: experts in `world` contiguous blocks, tokens
+    data-parallel, one all-gather and one reduce-scatter per layer issued by the library over NCCL.  The same
+    code path runs at world 1 (the collectives become copies), so the numbers of all N are one curve.  Layer 0
+    holds quantised Gaussian weights and is checked against the CPU oracle on a token sample; the other layers
+    hold fabricated blocks (same shapes and byte counts).  Every layer reads the same resident chunk of
+    activations (in the engine the MoE input comes from the layer's own mixer, not from the previous MoE)."""
+    from picoforge_b200.expert_parallel import Communicator, EpLayer
     lib = api.lib
-    if lib.qw4cu_set_device(local_rank) != 0:
-        raise SystemExit(lib.qw4cu_last_error().decode())
-    lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
-    lib.qw4cu_set_tile_path(args.tile_path)
-    tokens, n_layers = 64, args.ep_layers
-    per, epr = tokens // world, 512 // world
-    x_all = synth.activations(4, tokens)
-    x_all[:, 0] = 1.0
-    specs, layers = [], []
+    routed, shared, chunk_tokens, chunks, skewed, seed, text = SHARDED[name]
+    n_layers = args.ep_layers
+    per, epr = chunk_tokens // world, 512 // world
+    broadcast = None
+    if world > 1:
+        def broadcast(payload):
+            box = [payload]
+            control.broadcast_object_list(box, src=0)
+            return box[0]
+    comm = Communicator(api, rank, world, broadcast)
+    x_all = synth.activations(seed, chunk_tokens * chunks)
+    if skewed:
+        x_all[:, 0] = 1.0
+    layers, spec = [], None
     for l in range(n_layers):
-        spec = synth.make_layer(4, layer=l, routed_type=abi.Q4_K, shared_type=abi.Q4_K, shard=(rank * epr, epr))
-        synth.zipf_router_bias(spec, 4 + l)
-        specs.append(spec)
-        layers.append(EpLayer(api, spec, per, world, rank, TorchExchange()))
-        spec.tensors = []                                        # resident in HBM now: keep one layer of host bytes at a time
-    stream = torch.cuda.Stream()
-    pinned_x = torch.from_numpy(x_all[rank * per:(rank + 1) * per].copy()).pin_memory()
-    pinned_y = torch.empty_like(pinned_x).pin_memory()
-    with torch.cuda.stream(stream):
-        x = pinned_x.cuda(non_blocking=True)
+        spec = synth.make_layer(seed, layer=l, routed_type=routed, shared_type=shared, shard=(rank * epr, epr) if world > 1 else None,
+                                fabricated=l > 0, reuse=spec if l > 1 else None)
+        if skewed:
+            synth.zipf_router_bias(spec, seed + l)
+        layers.append(EpLayer(api, spec, per, world, rank))
+    layouts = spec.layouts()
+    expert_bytes = layouts[1].expert_bytes + layouts[2].expert_bytes + layouts[3].expert_bytes
+    replicated = layouts[0].tensor_bytes + layouts[7].tensor_bytes + sum(layouts[i].tensor_bytes for i in (4, 5, 6))
+    spec.tensors = []
+    hidden = 2048
+    x_dev = []
+    for c in range(chunks):
+        rows = np.ascontiguousarray(x_all[c * chunk_tokens + rank * per:c * chunk_tokens + (rank + 1) * per])
+        pointer = lib.qw4cu_malloc(rows.nbytes)
+        assert lib.qw4cu_upload(pointer, rows.ctypes.data, rows.nbytes) == 0
+        x_dev.append(pointer)
+    y_dev = lib.qw4cu_malloc(per * hidden * 4)
 
-        def step():
-            y = None
+    def barrier():
+        if world > 1:
+            control.barrier()
+
+    # ---- parity of layer 0 on this rank's first tokens of chunk 0 (rank 0 reports) ----
+    layers[0].forward(comm, x_dev[0], y_dev)
+    layers[0].sync()
+    parity = None
+    if rank == 0:
+        import oracle
+        sample = min(8, per)
+        y0 = np.empty((per, hidden), np.float32)
+        assert lib.qw4cu_download(y0.ctypes.data, y_dev, y0.nbytes) == 0
+        ids0, _ = layers[0].routes()
+        full = synth.make_layer(seed, layer=0, routed_type=routed, shared_type=shared)
+        if skewed:
+            synth.zipf_router_bias(full, seed)
+        want = oracle.forward(full, x_all[:sample], threads=synth.threads())
+        parity = {"tokens": sample, "max_abs": float(np.abs(y0[:sample] - want["y"]).max()),
+                  "ids_equal": bool(np.array_equal(ids0[:sample], want["ids"]))}
+        del full
+
+    def step():
+        for c in range(chunks):
             for layer in layers:
-                y = layer.forward(x)
-            return y
+                layer.forward(comm, x_dev[c], y_dev)
 
-        for _ in range(max(args.warmup, 3)):
-            step()
-        stream.synchronize()
+    def sync_all():
         for layer in layers:
             layer.sync()
-        dist.barrier()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            before = lib.qw4cu_launch_count()
-            begin.record(stream)
-            for _ in range(args.steps):
-                y = step()
-            end.record(stream)
-            stream.synchronize()
-            launches = lib.qw4cu_launch_count() - before
-        for layer in layers:
-            layer.sync()                                                      # error words of every layer
-        dist.barrier()
-        elapsed = torch.tensor([begin.elapsed_time(end)], device="cuda")
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        ms_per_step = float(elapsed.item()) / args.steps
-        assert bool(torch.isfinite(y).all())
-        # end to end: pinned host x in, y back out, every step
-        e2e_steps = max(1, min(args.steps, 50))
-        dist.barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            x.copy_(pinned_x, non_blocking=True)
-            y = step()
-            pinned_y.copy_(y, non_blocking=True)
-            stream.synchronize()
-        e2e = torch.tensor([time.perf_counter() - t0], device="cuda")
-        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
-        # distinct experts per layer over all ranks (weight bytes actually touched)
-        ids = torch.stack([layer.ids for layer in layers]).to(torch.int64)        # [L, per, k]
-        gathered = [torch.empty_like(ids) for _ in range(world)]
-        dist.all_gather(gathered, ids)
-        distinct = float(sum(len(torch.unique(torch.cat([g[l] for g in gathered]))) for l in range(n_layers)))
-    if rank == 0:
-        hbm_peak, peak_kind = peaks()
-        layouts = specs[0].layouts()
-        expert_bytes = layouts[1].expert_bytes + layouts[2].expert_bytes + layouts[3].expert_bytes
-        replicated = layouts[0].tensor_bytes + layouts[7].tensor_bytes + sum(layouts[i].tensor_bytes for i in (4, 5, 6))
-        touched = distinct * expert_bytes + n_layers * world * replicated
-        us = ms_per_step * 1e3 / (tokens * n_layers)
-        achieved = touched / (ms_per_step * 1e-3) / 1e9
-        print(json.dumps({
-            "metric": "moe_layer_us_per_token_decode", "value": us, "unit": "us/token", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"c4: batched decode, 64 sequences x 1 token through {n_layers} Q4_K layers, Zipf(1.1) expert popularity",
-                       "tokens_per_step": tokens, "layers": n_layers,
-                       "parallelism": f"expert parallel, {epr} experts per GPU, router and shared expert replicated, tokens data-parallel",
-                       "exchange": "torch.distributed all_to_all_single over NCCL, two per layer (rows with their expert ids, outputs); the shared expert runs on a second stream under the exchange",
-                       "same_workload_on_one_gpu": "python bench.py --workload c4 (no exchange; 174 us per layer measured)",
-                       "router": args.router, "l2": f"{n_layers} layers of weights per step ({touched / world / 1e6:.0f} MB per GPU), L2 is 126 MB",
-                       "distinct_experts_per_layer": distinct / n_layers},
-            "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
-                         "frac": achieved / (hbm_peak * world), "peak_kind": peak_kind, "traffic": None, "algorithmic_bytes": touched,
-                         "kernel_us": ms_per_step * 1e3},
-            "e2e": {"value": float(e2e.item()) / e2e_steps * 1e6 / (tokens * n_layers), "unit": "us/token",
-                    "h2d_bytes_per_step": int(pinned_x.numel() * 4 * world), "d2h_bytes_per_step": int(pinned_y.numel() * 4 * world),
-                    "steps": e2e_steps},
-            "gpu_launches": int(launches), "clocks": clocks.summary(), "cpu_baseline": None,
-        }))
+
+    for _ in range(max(1, args.ep_warmup)):
+        step()
+    sync_all()
+    barrier()
+    work0 = layers[0].layer.work
+    before = lib.qw4cu_launch_count()
+    lib.qw4cu_moe_work_timer_begin(work0)
+    for _ in range(args.ep_steps):
+        step()
+    lib.qw4cu_moe_work_timer_end(work0)
+    elapsed_ms = lib.qw4cu_moe_work_timer_elapsed_ms(work0)
+    sync_all()
+    launches = lib.qw4cu_launch_count() - before
+    barrier()
+    distinct = None
+    if chunks == 1:                                                                   # decode: the experts actually touched, over all ranks
+        ids_local = np.stack([layer.routes()[0] for layer in layers])                 # [L, per, k]
+        gathered = [ids_local]
+        if world > 1:
+            gathered = [None] * world
+            control.all_gather_object(gathered, ids_local)
+        distinct = float(sum(len(np.unique(np.concatenate([g[l] for g in gathered]))) for l in range(n_layers)))
+    if world > 1:
+        import torch
+        t = torch.tensor([elapsed_ms], dtype=torch.float64)
+        control.all_reduce(t, op=control.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
     for layer in layers:
         layer.close()
-    lib.qw4cu_set_stream(None)
-    dist.destroy_process_group()
+    comm.close()
+    for pointer in x_dev + [y_dev]:
+        lib.qw4cu_free(pointer)
+    if rank != 0:
+        return None
+    ms_per_step = elapsed_ms / args.ep_steps
+    tokens = chunk_tokens * chunks
+    passes = chunks * n_layers                                                        # chunk-layers per step
+    if distinct is None:
+        touched = passes * (512 * expert_bytes + world * replicated)                  # prefill: every expert of every layer, per chunk
+    else:
+        touched = distinct * expert_bytes + n_layers * world * replicated
+    achieved = touched / (ms_per_step * 1e-3) / 1e9
+    out = {
+        "workload": text.format(layers=n_layers), "n_gpus": world, "steps": args.ep_steps, "warmup": max(1, args.ep_warmup),
+        "ms_per_step": ms_per_step, "us_per_token_layer": ms_per_step * 1e3 / (tokens * n_layers),
+        "us_per_chunk_layer": ms_per_step * 1e3 / passes, "tokens_per_s": tokens / (ms_per_step * 1e-3), "scaling": "strong",
+        "parallelism": f"expert parallel over {world} GPU(s): {epr} experts each, router and shared expert replicated, tokens data-parallel; "
+                       "per layer one all-gather of token rows and one reduce-scatter of partial sums, issued by the library (NCCL)",
+        "weights": "layer 0: quantised Gaussian masters (checked against the CPU oracle); other layers: fabricated blocks of the same formats",
+        "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
+                     "frac": achieved / (hbm_peak * world), "peak_kind": peak_kind, "algorithmic_bytes": touched, "traffic": None},
+        "parity": parity, "gpu_launches": int(launches),
+    }
+    if distinct is not None:
+        out["distinct_experts_per_layer"] = distinct / n_layers
+    else:
+        flops = passes * (2.0 * chunk_tokens * 10 * 3 * 2048 * 512 + 2.0 * chunk_tokens * 3 * 2048 * 512 + 2.0 * chunk_tokens * 2048 * 513)
+        peak_tf = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops_sustained", 1422.1) \
+            if (ROOT / "MEASURED_PEAKS.json").exists() else 1400.0
+        out["roofline_tensor"] = {"bound": "tensor", "achieved": flops / (ms_per_step * 1e-3) / 1e12, "peak": peak_tf * world, "unit": "TFLOP/s",
+                                  "frac": flops / (ms_per_step * 1e-3) / 1e12 / (peak_tf * world),
+                                  "note": "against the sustained dense bf16 rate; at about 20 rows per expert the binding roof is HBM"}
+    return out
 
 
+# ---- main --------------------------------------------------------------------------------------
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=400)
-    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--workload", default="c1")
+    parser.add_argument("--workload", default="c1", help="c0 | c1 | c2 | c3-layer | c4-layer (one layer, every rank runs its own replica); c3 | c4: only that sharded workload")
     parser.add_argument("--layers", type=int, default=8, help="rotating weight sets (L2 hygiene)")
     parser.add_argument("--router", default="exact", choices=["exact", "fast"])
+    parser.add_argument("--repeats", type=int, default=25, help="timed regions of --steps steps each; the value is their median")
     parser.add_argument("--no-graph", action="store_true")
     parser.add_argument("--expert-path", type=int, default=-1, help="-1 auto, 0 CUDA-core kernels, 1 tensor-core grouped kernels")
     parser.add_argument("--tile-path", type=int, default=-1, help="-1 auto, 0 never, 1 tile kernels for every batch of more than four rows")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
-    parser.add_argument("--ep-layers", type=int, default=48, help="layers of the expert-parallel workload (N > 1)")
+    parser.add_argument("--sharded", default="c4,c3", help="sharded workloads measured beside the headline (comma list, '' for none)")
+    parser.add_argument("--ep-layers", type=int, default=48, help="layers of the sharded workloads")
+    parser.add_argument("--ep-steps", type=int, default=3)
+    parser.add_argument("--ep-warmup", type=int, default=1)
     parser.add_argument("--profile", action="store_true",
                         help="only W + K directly launched steps (the command to run under ncu); prints no bench line")
     args = parser.parse_args()
@@ -342,21 +384,18 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        # N > 1 runs the sharded batched-decode workload (c4): the CPU arm times the same 64-token batch through one of
-        # its layers on the host cores (a bounded sample: every layer costs the same)
-        name = "c4" if world > 1 and args.workload == "c1" else args.workload
+        name = args.workload if args.workload in ("c0", "c1", "c2") else "c1"
         desc, tokens, specs, x = workload(name, 1)
-        if name == "c4":
-            desc = "c4: batched decode, 64 sequences x 1 token through Q4_K layers, Zipf(1.1) expert popularity (CPU: one layer sampled)"
         per_step = 0.6 * tokens / max(1, min(tokens, len(os.sched_getaffinity(0))))
         steps = max(1, min(args.steps, int(120 / max(per_step, 1e-3))))
         seconds, threads, kind = cpu_reference_step(specs, x, steps, min(args.warmup, 3))
         us_per_token = seconds * 1e6 / tokens
         unit = "us/token"
         print(json.dumps({
-            "impl": "reference", "metric": "moe_layer_us_per_token_decode", "value": us_per_token, "unit": unit,
+            "impl": "reference", "metric": "moe_layer_us_per_token_decode" if name != "c2" else "moe_layer_us_per_token_prefill",
+            "value": us_per_token, "unit": unit,
             "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": seconds * 1e3,
-            "higher_is_better": False, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": desc, "tokens_per_step": tokens},
             "cpu_baseline": {"value": us_per_token, "unit": unit, "cores": threads, "kind": kind,
                              "sample": f"{steps} steps of the full {tokens}-token batch through one layer"},
@@ -364,25 +403,52 @@ def main():
         }))
         return
 
-    if world > 1:
-        return run_expert_parallel(args, rank, local_rank, world)
-
     api = abi.product()
     lib = api.lib
     if lib.qw4cu_device_count() <= 0:
         raise SystemExit(f"no CUDA device: {lib.qw4cu_last_error().decode()}")
     if lib.qw4cu_set_device(local_rank) != 0:
         raise SystemExit(lib.qw4cu_last_error().decode())
-    dist = None
+    control = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import torch.distributed as control                                         # gloo: the control plane only (ids, barriers, maxima)
+        control.init_process_group("gloo")
 
     lib.qw4cu_set_router_mode(1 if args.router == "fast" else 0)
     lib.qw4cu_set_tile_path(args.tile_path)
     lib.qw4cu_set_expert_path(args.expert_path)
+    sharded_names = [n for n in args.sharded.split(",") if n]
+    if args.workload in SHARDED:
+        sharded_names, headline = [args.workload], None
+    else:
+        headline = decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind)
+    if args.profile:
+        return
+    sharded = {}
+    for name in sharded_names:
+        result = run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind)
+        if rank == 0:
+            sharded[name] = result
+    if control is not None:
+        control.barrier()
+        control.destroy_process_group()
+    if rank != 0:
+        return
+    if headline is None:                                                             # a sharded workload on its own
+        only = sharded[sharded_names[0]]
+        headline = {"metric": "moe_layer_us_per_token_" + ("decode" if sharded_names[0] == "c4" else "prefill"),
+                    "value": only["us_per_token_layer"], "unit": "us/token", "n_gpus": world, "steps": only["steps"], "warmup": only["warmup"],
+                    "ms_per_step": only["ms_per_step"], "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic", "config": {"workload": only["workload"], "parallelism": only["parallelism"]},
+                    "roofline": only["roofline"], "e2e": None, "gpu_launches": only["gpu_launches"], "cpu_baseline": None}
+    headline["sharded"] = sharded
+    print(json.dumps(headline))
+
+
+def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind):
+    """The single-layer workloads (c0, c1, c2): every rank runs its own replica of the batch on its GPU (independent
+    layers, no collective on the data path: weak scaling); rank 0 returns the JSON line, the others None."""
+    lib = api.lib
     desc, tokens, specs, x = workload(args.workload, args.layers)
     layers = [MoeLayer(api, spec, tokens) for spec in specs]
     err = abi.Qwen4Error()
@@ -403,8 +469,16 @@ def main():
                 raise abi.MoeError(st, err)
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
+        if control is not None:
+            control.barrier()
+
+    def max_over_ranks(value):
+        if control is None:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64)
+        control.all_reduce(t, op=control.ReduceOp.MAX)
+        return float(t.item())
 
     if args.profile:
         lib.qw4cu_set_graph_mode(0)
@@ -413,7 +487,7 @@ def main():
         sync_all()
         print(json.dumps({"profile_steps": args.steps, "warmup": args.warmup,
                           "launches": int(lib.qw4cu_launch_count())}))
-        return
+        return None
 
     # routes of every layer (for byte counts) and a first correctness-preserving pass
     ids_per_layer = []
@@ -461,30 +535,24 @@ def main():
     sync_all()
     barrier()
     first = layers[0]
+    region_ms = []
     with ClockSampler(local_rank) as clocks:
         launches_before = lib.qw4cu_launch_count()
-        lib.qw4cu_moe_work_timer_begin(first.work)
-        for j in range(args.steps):
-            device_step(j)
-        lib.qw4cu_moe_work_timer_end(first.work)
-        elapsed_ms = lib.qw4cu_moe_work_timer_elapsed_ms(first.work)
+        for _ in range(max(1, args.repeats)):                     # the reference's protocol: repeated regions, median and spread
+            lib.qw4cu_moe_work_timer_begin(first.work)
+            for j in range(args.steps):
+                device_step(j)
+            lib.qw4cu_moe_work_timer_end(first.work)
+            region_ms.append(lib.qw4cu_moe_work_timer_elapsed_ms(first.work))
         sync_all()
-        launches = lib.qw4cu_launch_count() - launches_before
-        # keep the GPU loaded a little longer so that short timed regions still get clock samples
-        extra_until = time.perf_counter() + 0.05
-        j = 0
-        while time.perf_counter() < extra_until:
-            device_step(j)
-            j += 1
-        sync_all()
+        launches = (lib.qw4cu_launch_count() - launches_before) // max(1, args.repeats)
     barrier()
-    if dist is not None:
-        import torch
-        t = torch.tensor([elapsed_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    region_ms = sorted(region_ms)
+    elapsed_ms = max_over_ranks(float(np.median(region_ms)))
     ms_per_step = elapsed_ms / args.steps
     us_per_token = ms_per_step * 1e3 / (tokens * world)          # whole job: world replicas of the batch
+    spread = {"regions": len(region_ms), "steps_per_region": args.steps,
+              "p10_ms_per_step": region_ms[len(region_ms) // 10] / args.steps, "p90_ms_per_step": region_ms[(len(region_ms) * 9) // 10] / args.steps}
 
     # ---- end to end through the reference-facing host API ------------------------------------------
     lib.qw4cu_set_graph_mode(0)
@@ -508,17 +576,16 @@ def main():
     start = time.perf_counter()
     for i in range(e2e_steps):
         host_step(i)
-    e2e_seconds = time.perf_counter() - start
+    e2e_seconds = max_over_ranks(time.perf_counter() - start)
     barrier()
-    if dist is not None:
-        import torch
-        t = torch.tensor([e2e_seconds], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_seconds = float(t.item())
     e2e_us_per_token = e2e_seconds / e2e_steps * 1e6 / (tokens * world)
 
+    for layer in layers:
+        layer.close()
+    for pointer in [x_dev] + y_dev:
+        lib.qw4cu_free(pointer)
     if rank != 0:
-        return
+        return None
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------------
     cpu = None
@@ -550,7 +617,7 @@ def main():
         kernel_us, kernel_bytes = stage_us[dominant], bytes_by_stage[dominant]
     achieved = kernel_bytes / (kernel_us * 1e-6) / 1e9 if kernel_us > 0 else 0.0
     tensor = None
-    if args.workload in ("c2", "c3"):
+    if args.workload in ("c2", "c3-layer"):
         # FLOPs of the chunk (routed 2 * pairs * 3 * H * I, shared, router) against the measured dense bf16 rate
         spec0 = specs[0]
         pairs = tokens * spec0.top_k
@@ -562,18 +629,22 @@ def main():
                   "unit": "TFLOP/s", "frac": flops / (ms_per_step * 1e-3) / 1e12 / peak_tf,
                   "note": "whole step against the sustained dense bf16 rate; at about 20 rows per expert the binding roof is HBM"}
     traffic = TRAFFIC.get(f"{args.workload}:{dominant}")
+    clock_summary = clocks.summary()
     line = {
-        "metric": "moe_layer_us_per_token_decode" if args.workload not in ("c2", "c3") else "moe_layer_us_per_token_prefill",
+        "metric": "moe_layer_us_per_token_decode" if args.workload not in ("c2", "c3-layer") else "moe_layer_us_per_token_prefill",
         "value": us_per_token, "unit": "us/token", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": desc, "tokens_per_step": tokens, "parallelism": "single GPU" if world == 1 else f"{world} replicas",
+        "config": {"workload": desc, "tokens_per_step": tokens, "parallelism": "single GPU" if world == 1 else f"{world} GPUs, one independent replica of the batch each (no collective on the data path)",
                    "router": args.router, "launch": "one persistent kernel per layer" if phases else ("direct" if args.no_graph else "cuda-graph replay per layer"),
                    "l2": f"rotating {len(layers)} weight sets ({layer_bytes * len(layers) / 1e6:.0f} MB touched between reuse of a set; L2 is 126 MB)",
                    "distinct_experts_per_step": distinct, "spinup_ms": 300},
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": traffic,
+                     "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": traffic["bytes"] if traffic else None,
+                     "traffic_source": traffic["source"] if traffic else None,
                      "algorithmic_bytes": kernel_bytes, "kernel_us": kernel_us},
+        "timing": dict(spread, median_ms_per_step=ms_per_step,
+                       ms_per_step_x_sm_mhz=ms_per_step * clock_summary["sm_mhz"] if clock_summary["sm_mhz"] else None),
         "roofline_tensor": tensor,
         "phases": phases,
         "tokens_per_s": tokens * world / (ms_per_step * 1e-3),
@@ -583,10 +654,10 @@ def main():
         "e2e": {"value": e2e_us_per_token, "unit": "us/token", "h2d_bytes_per_step": int(x.nbytes),   # status words: cleared only after an error
                 "d2h_bytes_per_step": int(x.nbytes) + 16, "steps": e2e_steps},
         "gpu_launches": int(launches),
-        "clocks": clocks.summary(),
+        "clocks": clock_summary,
         "cpu_baseline": cpu,
     }
-    print(json.dumps(line))
+    return line
 
 
 if __name__ == "__main__":

@@ -251,52 +251,57 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *moe, const float *x_dev, fl
 Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
 
 /* Expert parallelism (no counterpart in the reference, which is a single-device engine).
- * A sharded handle holds experts [first_expert, first_expert + local_experts) of the layer:
- * weights->gate/up/down carry local_experts experts, the router and the shared expert are
- * complete.  The layer is then run in three device-pointer pieces, between which the caller
- * exchanges rows with the other ranks (all-to-all):
- *   route     x [tokens, hidden] -> ids, weights [tokens, k] (global expert ids), kept in the
- *             workspace for the combine and optionally copied out;
- *   experts   rows [rows, hidden] gathered from all ranks, local_ids [rows] = expert index
- *             inside this shard or 0xffffffff for an unused row -> out [rows, hidden], the
- *             expert's SwiGLU output per row (unused rows are not meaningful);
- *   combine   pair_out [tokens * k, hidden] in pair order (token * k + slot) -> y = slot-order
- *             weighted sum + sigmoid-gated shared expert, with the weights of the route call.
- * All three enqueue on the stream in force and return without waiting. */
+ * Experts are cut into equal contiguous blocks, one per rank; the router and the shared expert
+ * are replicated; tokens are data-parallel, the same number on every rank.  A sharded handle
+ * holds experts [first_expert, first_expert + local_experts): weights->gate/up/down carry
+ * local_experts experts, the router and the shared expert are complete.
+ *
+ * One layer step moves one exchange row per TOKEN (qw4cu_ep_row_floats(moe) floats: the token's
+ * activations, its k route ids, its k route weights) to every rank with an all-gather, lets every
+ * rank run its own experts on the tokens routed to them and form per-token partial sums (its
+ * experts' weighted outputs, plus the sigmoid-gated shared expert for its own tokens), and ends
+ * with a reduce-scatter (sum) that hands every rank the finished rows of its own tokens.  The sum
+ * over a token's experts therefore runs per rank and then over ranks, not in slot order: y agrees
+ * with the one-device layer within the layer tolerance, ids and route weights bit for bit.
+ *
+ * qw4cu_moe_ep_forward_device does the whole step, collectives included, through NCCL (taken from
+ * the process at run time: libnccl.so.2, or the file named by QW4CU_NCCL_LIBRARY).  A C host makes
+ * the communicator itself: rank 0 calls qw4cu_ep_unique_id and hands the 128 bytes to the other
+ * ranks by any means, then every rank calls qw4cu_ep_create with its device current (world 1 needs
+ * no NCCL and no id).  The workspace must have capacity for (world + 1) * tokens_local tokens.
+ * Every rank must make the same sequence of calls; all of them enqueue on the stream in force and
+ * return without waiting (the exchange buffers grow on the first call of a size: make that call
+ * outside any stream capture).
+ *
+ * The two compute pieces are also callable on their own, for a caller with an exchange of its
+ * own (or one process that plays several ranks):
+ *   begin    routes x [tokens_local, hidden], writes this rank's exchange rows to rows_local_dev
+ *            [tokens_local, row floats] (and ids / weights [tokens_local, k] if not NULL) and starts
+ *            the shared expert of these tokens on a second stream;
+ *   experts  rows_all_dev: the rows of all ranks in rank order [tokens_total, row floats]; own_first:
+ *            index of this rank's first token in it; partial_dev [tokens_total, hidden] receives the
+ *            partial sums.  y of a token = sum over ranks of its partial rows. */
+typedef struct QW4CuEp QW4CuEp;
 Qwen4Status qw4cu_moe_create_sharded(const Qwen4MoeConfig *config, const Qwen4MoeWeights *weights,
                                      uint32_t first_expert, uint32_t local_experts, Qwen4Moe **out,
                                      Qwen4Error *err);
+int qw4cu_ep_unique_id(unsigned char id[128]);
+Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW4CuEp **out, Qwen4Error *err);
+void qw4cu_ep_destroy(QW4CuEp *ep);
+size_t qw4cu_ep_row_floats(const Qwen4Moe *moe);
+Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *moe, QW4CuEp *ep, const float *x_dev, float *y_dev, size_t tokens_local,
+                                        uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work, Qwen4Error *err);
+Qwen4Status qw4cu_moe_ep_begin_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens_local, float *rows_local_dev,
+                                      uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work, Qwen4Error *err);
+Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *moe, const float *rows_all_dev, size_t tokens_total, size_t own_first,
+                                        float *partial_dev, Qwen4MoeWork *work, Qwen4Error *err);
+/* Router and routes only: x [tokens, hidden] -> ids, weights [tokens, k] (device pointers, either may be NULL). */
 Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
                                    uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work,
                                    Qwen4Error *err);
-Qwen4Status qw4cu_moe_experts_device(const Qwen4Moe *moe, const float *rows_dev, size_t rows,
-                                     const uint32_t *local_ids_dev, float *out_dev,
-                                     Qwen4MoeWork *work, Qwen4Error *err);
-Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
-                                     const float *pair_out_dev, float *y_dev, Qwen4MoeWork *work,
-                                     Qwen4Error *err);
-/* The same step with packed exchange messages, for an all-to-all of equal blocks.  A message has one block per
- * rank of `slots_per_rank` slots; a slot is qw4cu_ep_slot_floats(moe) floats: the token's activations, one word
- * with the expert's index inside the destination's shard (0xffffffff: unused slot), padding.
- *   route_pack  routes the rank's tokens, writes msg_dev (pairs in pair order inside each block) and the slot of
- *               every pair into slots_dev [tokens * k] (and the global expert ids into ids_dev [tokens, k] if
- *               not NULL), and starts the shared expert on a second stream so that it runs under the exchange
- *   experts     rows slots as received -> out_dev [rows, hidden], row r for slot r
- *   combine     back_dev [ranks * slots_per_rank, hidden]: the outputs returned for this rank's message;
- *               gathers them into pair order, joins the shared expert, writes y
- * slots_per_rank >= tokens * k.  The workspace must hold ranks * slots_per_rank rows; with tokens more rows
- * than that the shared expert never has to wait for the routed experts' buffers. */
-size_t qw4cu_ep_slot_floats(const Qwen4Moe *moe);
-Qwen4Status qw4cu_moe_ep_route_pack_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens, size_t slots_per_rank,
-                                           float *msg_dev, uint32_t *slots_dev, uint32_t *ids_dev, Qwen4MoeWork *work,
-                                           Qwen4Error *err);
-Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *moe, const float *msg_dev, size_t rows, float *out_dev,
-                                        Qwen4MoeWork *work, Qwen4Error *err);
-Qwen4Status qw4cu_moe_ep_combine_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens, const float *back_dev,
-                                        const uint32_t *slots_dev, float *y_dev, Qwen4MoeWork *work, Qwen4Error *err);
 /* Makes every later call on this device enqueue on the caller's CUDA stream (a cudaStream_t
  * passed as void *), so that the library's kernels order with the caller's own work, e.g. the
- * NCCL all-to-all of an expert-parallel step.  NULL restores the library's own stream; the legacy
+ * collectives of an expert-parallel step.  NULL restores the library's own stream; the legacy
  * default stream is named by its handle cudaStreamLegacy ((cudaStream_t)1), not by 0. */
 int qw4cu_set_stream(void *cuda_stream);
 

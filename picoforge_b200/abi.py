@@ -198,12 +198,13 @@ class MoeApi:
             "qw4cu_moe_work_sync": ([P, E], C.c_int),
             "qw4cu_moe_create_sharded": ([C.POINTER(Qwen4MoeConfig), C.POINTER(Qwen4MoeWeights), C.c_uint32, C.c_uint32, C.POINTER(P), E], C.c_int),
             "qw4cu_moe_route_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
-            "qw4cu_moe_experts_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
-            "qw4cu_moe_combine_device": ([P, P, C.c_size_t, P, P, P, E], C.c_int),
-            "qw4cu_ep_slot_floats": ([P], C.c_size_t),
-            "qw4cu_moe_ep_route_pack_device": ([P, P, C.c_size_t, C.c_size_t, P, P, P, P, E], C.c_int),
-            "qw4cu_moe_ep_experts_device": ([P, P, C.c_size_t, P, P, E], C.c_int),
-            "qw4cu_moe_ep_combine_device": ([P, P, C.c_size_t, P, P, P, P, E], C.c_int),
+            "qw4cu_ep_unique_id": ([C.c_char_p], C.c_int),
+            "qw4cu_ep_create": ([C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_void_p), E], C.c_int),
+            "qw4cu_ep_destroy": ([P], None),
+            "qw4cu_ep_row_floats": ([P], C.c_size_t),
+            "qw4cu_moe_ep_forward_device": ([P, P, P, P, C.c_size_t, P, P, P, E], C.c_int),
+            "qw4cu_moe_ep_begin_device": ([P, P, C.c_size_t, P, P, P, P, E], C.c_int),
+            "qw4cu_moe_ep_experts_device": ([P, P, C.c_size_t, C.c_size_t, P, P, E], C.c_int),
             "qw4cu_set_stream": ([P], C.c_int),
             "qw4cu_moe_work_timer_begin": ([P], C.c_int),
             "qw4cu_moe_work_timer_end": ([P], C.c_int),

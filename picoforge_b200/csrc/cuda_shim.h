@@ -151,17 +151,23 @@ void qw4sh_fused_scratch_sizes(const QW4ShLayer *layer, size_t *aq_bytes, size_t
 /* Stable per-expert lists of plain rows (one id per row; 0xffffffff: none), one CTA. */
 int qw4sh_group_rows(uint32_t experts, size_t rows, const uint32_t *ids, uint32_t *offsets, uint32_t *pair_to_row,
                      uint32_t *row_to_pair, uint32_t *active, uint32_t *status, void *stream);
-/* Expert-parallel exchange messages (ep_exchange.cu) and the pieces that use them. */
-uint32_t qw4sh_ep_pitch(uint32_t hidden);
-int qw4sh_ep_pack(const float *x, uint32_t tokens, uint32_t k, uint32_t hidden, const uint32_t *ids, uint32_t experts_per_rank,
-                  uint32_t world, uint32_t cap, float *msg, uint32_t *slot_of_pair, uint32_t *status, void *stream);
-int qw4sh_ep_ids(const float *msg, uint32_t hidden, uint32_t rows, uint32_t *ids, void *stream);
-int qw4sh_ep_gather(const float *back, uint32_t hidden, const uint32_t *slot_of_pair, uint32_t pairs, float *pair_out, void *stream);
-int qw4sh_ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens);
-int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg, size_t rows, uint32_t local_experts,
-                             float *out, size_t shared_tokens);
-int qw4sh_ep_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *back,
-                             const uint32_t *slots, float *y, int shared_started);
+/* Expert parallelism (ep_nccl.cu, kernels.cu): exchange rows of hidden + 2 * (k padded to 4) floats per token. */
+typedef struct QW4ShEp QW4ShEp;
+uint32_t qw4sh_ep_row_floats(uint32_t hidden, uint32_t k);
+int qw4sh_ep_unique_id(unsigned char id[128]);
+int qw4sh_ep_create(const unsigned char id[128], int rank, int world, QW4ShEp **out);
+void qw4sh_ep_destroy(QW4ShEp *ep);
+int qw4sh_ep_rank(const QW4ShEp *ep);
+int qw4sh_ep_world(const QW4ShEp *ep);
+int qw4sh_ep_reserve(QW4ShEp *ep, uint32_t hidden, uint32_t k, size_t tokens_local);
+float *qw4sh_ep_msg_local(QW4ShEp *ep);
+float *qw4sh_ep_msg_all(QW4ShEp *ep);
+float *qw4sh_ep_partial_buffer(QW4ShEp *ep);
+int qw4sh_ep_all_gather(QW4ShEp *ep, size_t floats_per_rank, void *stream);
+int qw4sh_ep_reduce_scatter(QW4ShEp *ep, float *y, size_t floats_per_rank, void *stream);
+int qw4sh_ep_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, float *msg_local, int router_mode);
+int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg_all, size_t total, size_t own_first, size_t own,
+                     uint32_t first_expert, uint32_t local_experts, float *partial);
 int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum,
                                 float *xscale, void *stream);
 void qw4sh_launch_log_begin(void);
@@ -187,12 +193,7 @@ int qw4sh_prefill_tc(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, con
                      const void *sum_lo, void *out_hi, void *out_lo, void *osum_hi, void *osum_lo, float *out, uint32_t *status,
                      int ctas, void *stream);
 
-/* Expert-parallel pieces of the layer (see include/qwen4_moe_b200.h). */
 int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode);
-int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *rows_x, size_t rows,
-                          const uint32_t *local_ids, uint32_t local_experts, float *out);
-int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens,
-                          const float *pair_out, float *y);
 /* Caller-provided stream (NULL: back to the library's own).  current_stream returns the one in force. */
 int qw4sh_set_stream(void *stream);
 int qw4sh_current_stream(void **stream);

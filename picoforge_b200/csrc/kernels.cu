@@ -31,6 +31,10 @@ static int fail(cudaError_t e, const char *where) {
 }
 #define CU(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(e_, #call); } while (0)
 // Names of the kernels launched since qw4sh_launch_log_begin (string literals; the first LOG_CAP are kept).
+extern "C" int qw4sh_fail_text(const char *text) {
+    snprintf(g_error, sizeof g_error, "%s", text);
+    return -1;
+}
 static const unsigned LOG_CAP = 512;
 static const char *g_log[LOG_CAP];
 static unsigned g_log_n = LOG_CAP;                // full: logging off until the first begin
@@ -1622,8 +1626,7 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
 }
 
 // ------------------------------------------------------------------------------------
-// Expert-parallel pieces: route only / experts only (rows already gathered from all ranks,
-// ids local to this rank's shard, 0xffffffff = no expert) / shared expert + combine.
+// Pieces of the layer that run on their own.
 // ------------------------------------------------------------------------------------
 extern "C" int qw4sh_group_rows(uint32_t experts, size_t rows, const uint32_t *ids, uint32_t *offsets, uint32_t *pair_to_row,
                                 uint32_t *row_to_pair, uint32_t *active, uint32_t *status, void *stream) {
@@ -1644,81 +1647,34 @@ extern "C" int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *wor
                        work->weights, work->status, stream);
 }
 
-extern "C" int qw4sh_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *rows_x, size_t rows,
-                                     const uint32_t *local_ids, uint32_t local_experts, float *out) {
-    if (!rows) return 0;
-    if (ensure_constants()) return -1;
-    cudaStream_t stream = (cudaStream_t)work->stream;
-    const uint32_t R = (uint32_t)rows, H = layer->hidden;
-    int rc;
-    if (local_experts <= 1024) {
-        if ((rc = qw4sh_group_rows(local_experts, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status,
-                                   stream))) return rc;
-    } else if (rows > 64 && work->dispatch_scratch) {
-        if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
-                                    work->dispatch_scratch, work->status, stream))) return rc;
-    } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
-    const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
-                     qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1) && (g_expert_path == 1 || rows <= 2048);
-    if ((g_tile_path > 0 ? rows > 4 : g_tile_path < 0 && (rows > 2048 || !mma)) && g_expert_path != 0 && tile_types(layer)) {
-        const int ctas = sm_count();
-        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(rows_x, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xsum,
-                                     work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
-                                  work->ascale, out, work->status, ctas, stream);
-    }
-    if (mma) {
-        const int ctas = sm_count();
-        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(rows_x, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xneg,
-                                    work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
-                                 work->asum, work->ascale, out, work->status, ctas, stream);
-    }
-    const uint32_t groups = R < local_experts ? R : local_experts;
-    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), rows_x, H, work->offsets, work->row_to_pair, work->active, 1, R,
-                             groups, work->act, work->status, stream))) return rc;
-    return launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, nullptr, local_ids, nullptr, nullptr, 1, R, out, nullptr,
-                       work->status, stream);
+// ---- expert parallelism (ep_nccl.cu holds the exchange) -------------------------------------------------
+extern "C" uint32_t qw4sh_ep_row_floats(uint32_t hidden, uint32_t k);
+extern "C" int qw4sh_ep_pack_rows(const float *x, const uint32_t *ids, const float *weights, uint32_t tokens, uint32_t hidden, uint32_t k,
+                                  float *msg, void *stream);
+extern "C" int qw4sh_ep_local_ids(const float *msg, uint32_t hidden, uint32_t k, uint32_t tokens, uint32_t experts, uint32_t first,
+                                  uint32_t count, uint32_t *local, uint32_t *status, void *stream);
+extern "C" int qw4sh_ep_partial(const float *msg, uint32_t hidden, uint32_t k, uint32_t tokens, const uint32_t *local, const float *out,
+                                const float *shared_out, const float *shared_logit, uint32_t own_first, uint32_t own, float *partial,
+                                uint32_t *status, void *stream);
+extern "C" int qw4sh_quantize_rows_listed(const float *x, uint32_t pitch, uint32_t max_rows, uint32_t k, const uint32_t *row_list,
+                                          const uint32_t *row_count, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream);
+
+static bool shared_on_mma(const QW4ShLayer *layer) {
+    return layer->w[4].type == layer->w[5].type && qw4sh_mma_supported(&layer->w[4], 0) && qw4sh_mma_supported(&layer->w[5], 0) &&
+           qw4sh_mma_supported(&layer->w[6], 1);
+}
+static bool shared_on_tiles(const QW4ShLayer *layer) {
+    return layer->w[4].type == layer->w[5].type && qw4sh_tile_supported(&layer->w[4], 0) && qw4sh_tile_supported(&layer->w[5], 0) &&
+           qw4sh_tile_supported(&layer->w[6], 1);
 }
 
-extern "C" int qw4sh_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *pair_out,
-                                     float *y) {
+// The shared expert of `tokens` own tokens, on the side stream: it needs only x, so it runs under the exchange.
+// Its x digits live in the LAST rows of the quantisation buffers (rows 0 .. total-1 belong to the gathered rows).
+static int ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens) {
     if (!tokens) return 0;
-    if (ensure_constants()) return -1;
-    cudaStream_t stream = (cudaStream_t)work->stream;
-    const uint32_t T = (uint32_t)tokens, H = layer->hidden;
-    if (layer->w[4].type != layer->w[5].type || !qw4sh_mma_supported(&layer->w[4], 0) || !qw4sh_mma_supported(&layer->w[5], 0) ||
-        !qw4sh_mma_supported(&layer->w[6], 1))
-        return fail(cudaErrorNotSupported, "expert-parallel combine needs a Q4_K or IQ2_XXS shared expert");
-    const int ctas = sm_count();
-    uint8_t *shared_groups = (uint8_t *)work->groups + (size_t)T * layer->top_k * 16;
-    int rc;
-    if ((rc = qw4sh_build_dense_groups(T, shared_groups, work->n_groups + 1, stream))) return rc;
-    if ((rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-    if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], shared_groups, work->n_groups + 1, nullptr, 1, work->xq, work->xneg, work->xsum,
-                                work->xscale, work->shared_act, work->status, ctas, stream))) return rc;
-    if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, stream))) return rc;
-    if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, shared_groups, work->n_groups + 1, nullptr, 1, work->sq, work->sneg, work->ssum,
-                                work->sscale, work->shared_out, work->status, ctas, stream))) return rc;
-    return qw4sh_combine(pair_out, work->shared_out, work->weights, work->shared_logit, layer->top_k, H, T, y, nullptr, work->status, stream);
-}
-
-// ---- expert-parallel pieces with packed messages (ep_exchange.cu) and the shared expert under the exchange ----
-// The shared expert needs only x.  Started here on the side stream, right after the routing, it runs while the
-// rows travel; its x digits live in the LAST rows of the quantisation buffers, which the routed experts (rows
-// 0 .. R-1 of the same buffers) leave alone as long as R + tokens <= capacity.
-extern "C" int qw4sh_ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens) {
-    if (!tokens) return 0;
-    if (tokens > work->cap) return fail(cudaErrorInvalidValue, "token count beyond the workspace");
-    if (layer->w[4].type != layer->w[5].type || !qw4sh_mma_supported(&layer->w[4], 0) || !qw4sh_mma_supported(&layer->w[5], 0) ||
-        !qw4sh_mma_supported(&layer->w[6], 1))
-        return fail(cudaErrorNotSupported, "expert-parallel combine needs a Q4_K or IQ2_XXS shared expert");
+    const bool tiles = tokens > MMA_MAX_TOKENS || !shared_on_mma(layer);
+    if (tiles ? !shared_on_tiles(layer) : !shared_on_mma(layer))
+        return fail(cudaErrorNotSupported, "expert-parallel step needs a Q4_K, IQ2_XXS or Q2_K shared expert");
     cudaStream_t stream = (cudaStream_t)work->stream, side;
     cudaEvent_t *ev;
     int rc;
@@ -1731,85 +1687,81 @@ extern "C" int qw4sh_ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *w
     const int ctas = sm_count();
     CU(cudaEventRecord(ev[0], stream));
     CU(cudaStreamWaitEvent(side, ev[0], 0));
-    if ((rc = qw4sh_build_dense_groups(T, work->shared_groups, work->n_groups + 3, side))) return rc;
     if ((rc = qw4sh_quantize_rows(x, T, H, xq, xneg, xsum, xscale, side))) return rc;
-    if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 3, nullptr, 1, xq, xneg, xsum, xscale,
-                                work->shared_act, work->status, ctas, side))) return rc;
-    if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
-    if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 3, nullptr, 1, work->sq, work->sneg, work->ssum,
-                                work->sscale, work->shared_out, work->status, ctas, side))) return rc;
+    if (tiles) {
+        if ((rc = qw4sh_build_dense_tile_groups(T, work->shared_groups, work->n_groups + 3, side))) return rc;
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 3, nullptr, 1, xq, xsum, xscale,
+                                     work->shared_act, work->status, ctas, side))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
+        if ((rc = qw4sh_expert_tiles(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 3, nullptr, 1, work->sq, work->ssum,
+                                     work->sscale, work->shared_out, work->status, ctas, side))) return rc;
+    } else {
+        if ((rc = qw4sh_build_dense_groups(T, work->shared_groups, work->n_groups + 3, side))) return rc;
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[4], &layer->w[5], work->shared_groups, work->n_groups + 3, nullptr, 1, xq, xneg, xsum, xscale,
+                                    work->shared_act, work->status, ctas, side))) return rc;
+        if ((rc = qw4sh_quantize_rows(work->shared_act, T, layer->shared_inter, work->sq, work->sneg, work->ssum, work->sscale, side))) return rc;
+        if ((rc = qw4sh_grouped_mma(1, &layer->w[6], nullptr, work->shared_groups, work->n_groups + 3, nullptr, 1, work->sq, work->sneg, work->ssum,
+                                    work->sscale, work->shared_out, work->status, ctas, side))) return rc;
+    }
     CU(cudaEventRecord(ev[3], side));
     return 0;
 }
 
-// Rows as they arrived: `rows` message slots (hidden floats, the local expert id, padding).  `shared_tokens` > 0: a
-// shared-expert branch of that many tokens may still be running on the side stream.
-extern "C" int qw4sh_ep_experts_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg, size_t rows, uint32_t local_experts,
-                                        float *out, size_t shared_tokens) {
-    if (!rows) return 0;
-    if (ensure_constants()) return -1;
-    if (rows > work->cap) return fail(cudaErrorInvalidValue, "more rows than the workspace holds");
-    cudaStream_t stream = (cudaStream_t)work->stream;
-    const uint32_t R = (uint32_t)rows, H = layer->hidden, pitch = qw4sh_ep_pitch(H);
+// Step 1 of an expert-parallel layer on this rank: router and routes of its own tokens, the exchange rows
+// packed into msg_local, the shared expert started beside.
+extern "C" int qw4sh_ep_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, float *msg_local, int router_mode) {
+    if (!tokens) return 0;
     int rc;
-    if (shared_tokens && rows + shared_tokens > work->cap) {              // the tail rows are in use: let the shared expert finish first
+    if ((rc = qw4sh_route_forward(layer, work, x, tokens, router_mode))) return rc;
+    if ((rc = qw4sh_ep_pack_rows(x, work->ids, work->weights, (uint32_t)tokens, layer->hidden, layer->top_k, msg_local, work->stream))) return rc;
+    return ep_shared_begin(layer, work, x, tokens);
+}
+
+// Step 3: this rank's experts (global ids first_expert .. + local_experts) over the gathered rows of `total` tokens,
+// then the per-token partial sums; tokens [own_first, own_first + own) are this rank's (they get the shared expert).
+extern "C" int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg_all, size_t total, size_t own_first, size_t own,
+                                uint32_t first_expert, uint32_t local_experts, float *partial) {
+    if (!total) return 0;
+    if (ensure_constants()) return -1;
+    if (total + own > work->cap) return fail(cudaErrorInvalidValue, "workspace too small: capacity must cover all ranks' tokens plus its own");
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    const uint32_t T = (uint32_t)total, H = layer->hidden, k = layer->top_k, pitch = qw4sh_ep_row_floats(H, k);
+    uint32_t *local = work->ids + own * k;                                  // behind this rank's own routes
+    int rc;
+    if ((rc = qw4sh_ep_local_ids(msg_all, H, k, T, layer->experts, first_expert, local_experts, local, work->status, stream))) return rc;
+    if ((rc = qw4sh_group_rows(local_experts, (size_t)T * k, local, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                               work->status, stream))) return rc;
+    const bool mma_types = layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) && qw4sh_mma_supported(&layer->w[2], 0) &&
+                           qw4sh_mma_supported(&layer->w[3], 1);
+    const bool tiles = g_tile_path != 0 && tile_types(layer) && (g_tile_path > 0 || !mma_types || total > MMA_MAX_TOKENS);
+    if (!tiles && !mma_types) return fail(cudaErrorNotSupported, "expert-parallel step needs Q4_K, IQ2_XXS or Q2_K expert tensors");
+    const int ctas = sm_count();
+    const uint32_t *n_local = work->offsets + local_experts;               // rows this rank's experts received
+    if ((rc = qw4sh_quantize_rows_pitched(msg_all, pitch, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+    if (tiles) {
+        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq, work->xsum,
+                                     work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, n_local, work->aq, work->aneg,
+                                             work->asum, work->ascale, stream))) return rc;
+        if ((rc = qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
+                                     work->ascale, work->out, work->status, ctas, stream))) return rc;
+    } else {
+        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq, work->xneg,
+                                    work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, n_local, work->aq, work->aneg,
+                                             work->asum, work->ascale, stream))) return rc;
+        if ((rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
+                                    work->asum, work->ascale, work->out, work->status, ctas, stream))) return rc;
+    }
+    if (own) {
         cudaStream_t side; cudaEvent_t *ev;
         if ((rc = side_stream(&side, &ev))) return rc;
         CU(cudaStreamWaitEvent(stream, ev[3], 0));
     }
-    uint32_t *local_ids = work->ids;
-    if ((rc = qw4sh_ep_ids(msg, H, R, local_ids, stream))) return rc;
-    if (local_experts <= 1024) {
-        if ((rc = qw4sh_group_rows(local_experts, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status,
-                                   stream))) return rc;
-    } else if (rows > 64 && work->dispatch_scratch) {
-        if ((rc = qw4sh_group_large(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
-                                    work->dispatch_scratch, work->status, stream))) return rc;
-    } else if ((rc = qw4sh_group(local_experts, 1, rows, local_ids, work->offsets, work->pair_to_row, work->row_to_pair, work->active, work->status, stream))) return rc;
-    const bool mma = g_expert_path != 0 && layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) &&
-                     qw4sh_mma_supported(&layer->w[2], 0) && qw4sh_mma_supported(&layer->w[3], 1);
-    const int ctas = sm_count();
-    if ((g_tile_path > 0 || (g_tile_path < 0 && (rows > 2048 || !mma))) && g_expert_path != 0 && tile_types(layer)) {
-        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows_pitched(msg, pitch, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xsum,
-                                     work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
-                                  work->ascale, out, work->status, ctas, stream);
-    }
-    if (mma) {
-        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows_pitched(msg, pitch, R, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
-        if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, 1, work->xq, work->xneg,
-                                    work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows(work->act, R, layer->inter, work->aq, work->aneg, work->asum, work->ascale, stream))) return rc;
-        return qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
-                                 work->asum, work->ascale, out, work->status, ctas, stream);
-    }
-    // any other format: rows made contiguous in the staging buffer, CUDA-core kernels
-    CU(cudaMemcpy2DAsync(work->x, (size_t)H * 4, msg, (size_t)pitch * 4, (size_t)H * 4, R, cudaMemcpyDeviceToDevice, stream));
-    const uint32_t groups = R < local_experts ? R : local_experts;
-    if ((rc = launch_gate_up(as_dev(layer->w[1]), as_dev(layer->w[2]), work->x, H, work->offsets, work->row_to_pair, work->active, 1, R,
-                             groups, work->act, work->status, stream))) return rc;
-    return launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, nullptr, local_ids, nullptr, nullptr, 1, R, out, nullptr,
-                       work->status, stream);
-}
-
-// back: the returned outputs, one row of `hidden` floats per slot this rank sent; slots: slot of every pair.
-extern "C" int qw4sh_ep_combine_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, const float *back,
-                                        const uint32_t *slots, float *y, int shared_started) {
-    if (!tokens) return 0;
-    if (ensure_constants()) return -1;
-    cudaStream_t stream = (cudaStream_t)work->stream;
-    const uint32_t T = (uint32_t)tokens, H = layer->hidden;
-    int rc;
-    if (!shared_started && (rc = qw4sh_ep_shared_begin(layer, work, x, tokens))) return rc;
-    if ((rc = qw4sh_ep_gather(back, H, slots, T * layer->top_k, work->out, stream))) return rc;
-    cudaStream_t side; cudaEvent_t *ev;
-    if ((rc = side_stream(&side, &ev))) return rc;
-    CU(cudaStreamWaitEvent(stream, ev[3], 0));
-    return qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, layer->top_k, H, T, y, nullptr, work->status, stream);
+    return qw4sh_ep_partial(msg_all, H, k, T, local, work->out, work->shared_out, work->shared_logit, (uint32_t)own_first, (uint32_t)own, partial,
+                            work->status, stream);
 }
 
 // The stream every workspace created afterwards (and every existing one, through

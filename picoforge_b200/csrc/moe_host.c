@@ -96,7 +96,7 @@ static Qwen4Status region_span(const Region *r, Span *span, Qwen4Error *err) {
     if (r->cols > SIZE_MAX / r->elem) return raise(err, QW4_OVERFLOW, "%s: a row does not fit size_t", r->name);
     const size_t row = r->cols * r->elem;
     if (r->pitch < row || r->pitch % r->elem) return raise(err, QW4_STRIDE, "%s: row pitch %zu cannot hold %zu-byte rows", r->name, r->pitch, row);
-    if (r->rows == 0) return QW4_OK;
+    if (r->rows == 0 || row == 0) return QW4_OK;              /* nothing to address */
     if (r->rows - 1 > (SIZE_MAX - row) / r->pitch) return raise(err, QW4_OVERFLOW, "%s: extent does not fit size_t", r->name);
     const size_t extent = (r->rows - 1) * r->pitch + row;
     if (extent == 0) return QW4_OK;
@@ -428,7 +428,7 @@ static Qwen4Status piece_checks(const Qwen4Moe *m, Qwen4MoeWork *w, size_t rows,
     if (w->owner != m) return report(err, QW4_OWNER, "workspace belongs to another MoE");
     if (!m->alive || w->failed) return report(err, QW4_BAD_STATE, "inactive MoE/workspace; reset required");
     if (w->busy) return report(err, QW4_BUSY, "workspace executing");
-    if (rows > w->chunk) return report(err, QW4_CAPACITY, "batch exceeds the workspace (cap and 2048-row chunk)");
+    if (rows > w->chunk || rows > w->cap) return report(err, QW4_CAPACITY, "batch exceeds the workspace (capacity, 2048 rows at most)");
     use_current_stream(w);
     w->status_clean = false;
     return QW4_OK;
@@ -443,55 +443,68 @@ Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *m, const float *x_dev, size_t
     if (tokens && weights_dev && qw4sh_memcpy2d_async(weights_dev, bytes, w->d.weights, bytes, bytes, 1, 2, w->d.stream)) return cuda_failure(err, "weights copy");
     return report(err, QW4_OK, "");
 }
-Qwen4Status qw4cu_moe_experts_device(const Qwen4Moe *m, const float *rows_dev, size_t rows, const uint32_t *local_ids_dev,
-                                     float *out_dev, Qwen4MoeWork *w, Qwen4Error *err) {
-    TRY(piece_checks(m, w, rows, err));
-    if (rows && (!rows_dev || !local_ids_dev || !out_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
-    if (qw4sh_experts_forward(&m->layer, &w->d, rows_dev, rows, local_ids_dev, m->local_experts, out_dev)) return cuda_failure(err, "experts launch");
+/* ---- expert parallelism ------------------------------------------------------------------ */
+struct QW4CuEp { QW4ShEp *shim; };
+
+int qw4cu_ep_unique_id(unsigned char id[128]) { return id ? qw4sh_ep_unique_id(id) : -1; }
+Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW4CuEp **out, Qwen4Error *err) {
+    if (out) *out = NULL;
+    if (!out || (world > 1 && !id)) return report(err, QW4_INVALID_ARGUMENT, "null communicator argument");
+    if (world < 1 || rank < 0 || rank >= world) return report(err, QW4_RANGE, "rank outside the world");
+    static const unsigned char none[128] = {0};
+    QW4CuEp *ep = calloc(1, sizeof *ep);
+    if (!ep) return report(err, QW4_OOM, "communicator");
+    if (qw4sh_ep_create(id ? id : none, rank, world, &ep->shim)) { free(ep); return cuda_failure(err, "communicator"); }
+    *out = ep;
     return report(err, QW4_OK, "");
 }
-Qwen4Status qw4cu_moe_combine_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, const float *pair_out_dev, float *y_dev,
-                                     Qwen4MoeWork *w, Qwen4Error *err) {
-    TRY(piece_checks(m, w, tokens, err));
-    if (tokens && (!x_dev || !pair_out_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
-    if (qw4sh_combine_forward(&m->layer, &w->d, x_dev, tokens, pair_out_dev, y_dev)) return cuda_failure(err, "combine launch");
+void qw4cu_ep_destroy(QW4CuEp *ep) { if (ep) { qw4sh_ep_destroy(ep->shim); free(ep); } }
+size_t qw4cu_ep_row_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_row_floats((uint32_t)m->c.hidden_size, (uint32_t)m->c.top_k) : 0; }
+
+static Qwen4Status ep_shard(const Qwen4Moe *m, size_t world, size_t rank, Qwen4Error *err) {
+    if (!m->local_experts || m->c.experts % m->local_experts || m->c.experts / m->local_experts != world ||
+        m->first_expert != rank * m->local_experts)
+        return report(err, QW4_BAD_STATE, "the handle must hold this rank's block of experts (equal contiguous blocks, rank-th block)");
+    return QW4_OK;
+}
+Qwen4Status qw4cu_moe_ep_begin_device(const Qwen4Moe *m, const float *x_dev, size_t tokens_local, float *rows_local_dev, uint32_t *ids_dev,
+                                      float *weights_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens_local, err));
+    if (tokens_local && (!x_dev || !rows_local_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (qw4sh_ep_begin(&m->layer, &w->d, x_dev, tokens_local, rows_local_dev, current_router_mode())) return cuda_failure(err, "route and pack");
+    const size_t bytes = tokens_local * m->c.top_k * 4;
+    if (tokens_local && ids_dev && qw4sh_memcpy2d_async(ids_dev, bytes, w->d.ids, bytes, bytes, 1, 2, w->d.stream)) return cuda_failure(err, "ids copy");
+    if (tokens_local && weights_dev && qw4sh_memcpy2d_async(weights_dev, bytes, w->d.weights, bytes, bytes, 1, 2, w->d.stream)) return cuda_failure(err, "weights copy");
+    w->shared_tokens = tokens_local;
     return report(err, QW4_OK, "");
 }
-/* The same three steps with packed exchange messages and the shared expert under the exchange. */
-size_t qw4cu_ep_slot_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_pitch((uint32_t)m->c.hidden_size) : 0; }
-Qwen4Status qw4cu_moe_ep_route_pack_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, size_t slots_per_rank, float *msg_dev,
-                                           uint32_t *slots_dev, uint32_t *ids_dev, Qwen4MoeWork *w, Qwen4Error *err) {
-    TRY(piece_checks(m, w, tokens, err));
-    if (tokens && (!x_dev || !msg_dev || !slots_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
-    if (!m->local_experts || m->c.experts % m->local_experts) return report(err, QW4_BAD_STATE, "expert shards must be equal blocks");
-    const uint32_t world = (uint32_t)(m->c.experts / m->local_experts);
-    if (world > 64) return report(err, QW4_INVALID_ARGUMENT, "more than 64 ranks");
-    if (slots_per_rank < tokens * m->c.top_k) return report(err, QW4_CAPACITY, "a destination block must hold every pair of this rank");
-    if (qw4sh_route_forward(&m->layer, &w->d, x_dev, tokens, current_router_mode())) return cuda_failure(err, "route launch");
-    if (qw4sh_ep_pack(x_dev, (uint32_t)tokens, (uint32_t)m->c.top_k, (uint32_t)m->c.hidden_size, w->d.ids, m->local_experts, world,
-                      (uint32_t)slots_per_rank, msg_dev, slots_dev, w->d.status, w->d.stream)) return cuda_failure(err, "pack launch");
-    const size_t id_bytes = tokens * m->c.top_k * 4;
-    if (tokens && ids_dev && qw4sh_memcpy2d_async(ids_dev, id_bytes, w->d.ids, id_bytes, id_bytes, 1, 2, w->d.stream)) return cuda_failure(err, "ids copy");
+Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *m, const float *rows_all_dev, size_t tokens_total, size_t own_first, float *partial_dev,
+                                        Qwen4MoeWork *w, Qwen4Error *err) {
+    TRY(piece_checks(m, w, tokens_total, err));
+    if (tokens_total && (!rows_all_dev || !partial_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    const size_t own = w->shared_tokens;
     w->shared_tokens = 0;
-    if (qw4sh_ep_shared_begin(&m->layer, &w->d, x_dev, tokens)) return cuda_failure(err, "shared expert launch");
-    w->shared_tokens = tokens;
-    return report(err, QW4_OK, "");
-}
-Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *m, const float *msg_dev, size_t rows, float *out_dev, Qwen4MoeWork *w,
-                                        Qwen4Error *err) {
-    TRY(piece_checks(m, w, rows, err));
-    if (rows && (!msg_dev || !out_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
-    if (qw4sh_ep_experts_forward(&m->layer, &w->d, msg_dev, rows, m->local_experts, out_dev, w->shared_tokens))
+    if (own_first > tokens_total || own > tokens_total - own_first) return report(err, QW4_RANGE, "own tokens outside the gathered batch");
+    if (tokens_total + own > w->cap) return report(err, QW4_CAPACITY, "workspace capacity must cover all ranks' tokens plus this rank's own");
+    if (qw4sh_ep_experts(&m->layer, &w->d, rows_all_dev, tokens_total, own_first, own, m->first_expert, m->local_experts, partial_dev))
         return cuda_failure(err, "experts launch");
     return report(err, QW4_OK, "");
 }
-Qwen4Status qw4cu_moe_ep_combine_device(const Qwen4Moe *m, const float *x_dev, size_t tokens, const float *back_dev,
-                                        const uint32_t *slots_dev, float *y_dev, Qwen4MoeWork *w, Qwen4Error *err) {
-    TRY(piece_checks(m, w, tokens, err));
-    if (tokens && (!x_dev || !back_dev || !slots_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
-    const int started = w->shared_tokens == tokens && tokens != 0;
-    w->shared_tokens = 0;
-    if (qw4sh_ep_combine_forward(&m->layer, &w->d, x_dev, tokens, back_dev, slots_dev, y_dev, started)) return cuda_failure(err, "combine launch");
+Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *m, QW4CuEp *ep, const float *x_dev, float *y_dev, size_t tokens_local, uint32_t *ids_dev,
+                                        float *weights_dev, Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!ep) return report(err, QW4_INVALID_ARGUMENT, "null communicator");
+    if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
+    const size_t world = (size_t)qw4sh_ep_world(ep->shim), rank = (size_t)qw4sh_ep_rank(ep->shim);
+    TRY(ep_shard(m, world, rank, err));
+    if (tokens_local && (!x_dev || !y_dev)) return report(err, QW4_INVALID_ARGUMENT, "null device view");
+    if (tokens_local > (w->cap) / (world + 1)) return report(err, QW4_CAPACITY, "workspace capacity must cover all ranks' tokens plus this rank's own");
+    if (!tokens_local) return report(err, QW4_OK, "");
+    const uint32_t h = (uint32_t)m->c.hidden_size, k = (uint32_t)m->c.top_k;
+    if (qw4sh_ep_reserve(ep->shim, h, k, tokens_local)) return cuda_failure(err, "exchange buffers");
+    TRY(qw4cu_moe_ep_begin_device(m, x_dev, tokens_local, qw4sh_ep_msg_local(ep->shim), ids_dev, weights_dev, w, err));
+    if (qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.stream)) return cuda_failure(err, "all-gather");
+    TRY(qw4cu_moe_ep_experts_device(m, qw4sh_ep_msg_all(ep->shim), tokens_local * world, rank * tokens_local, qw4sh_ep_partial_buffer(ep->shim), w, err));
+    if (qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.stream)) return cuda_failure(err, "reduce-scatter");
     return report(err, QW4_OK, "");
 }
 int qw4cu_set_stream(void *cuda_stream) { return qw4sh_set_stream(cuda_stream); }

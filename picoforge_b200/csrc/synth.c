@@ -216,12 +216,41 @@ int qw4s_encode_rows(uint32_t type, const float *src, size_t rows, size_t k, uin
     return 0;
 }
 
+/* A row of fabricated blocks: random code, scale and sign bytes with fp16 super-scales chosen so that the decoded
+ * weights have a spread of about 0.02 around zero (the reference's own kernel tests fabricate block bytes the same
+ * way: it has no quantiser).  Far cheaper than drawing and encoding Gaussians; any such bytes are valid blocks. */
+static void fabricated_row(uint32_t type, uint64_t seed, uint64_t stream, uint64_t row, uint8_t *out, size_t k) {
+    Stream s = stream_for(seed, stream ^ 0xfab0000000000000ull, row);
+    const size_t bytes = block_bytes(type), blocks = k / 256;
+    const float base = type == 12 ? 1.1e-4f : type == 10 ? 2.0e-3f : 3.0e-4f, min_ratio = type == 12 ? 7.5f : 1.5f;
+    uint16_t d[16], dmin[16];                                   /* sixteen super-scales, 0.75 .. 1.25 of the base */
+    for (int j = 0; j < 16; j++) {
+        const float scale = base * (0.75f + 0.5f * (float)j / 15.0f);
+        d[j] = float_to_half(scale); dmin[j] = float_to_half(scale * min_ratio);
+    }
+    for (size_t b = 0; b < blocks; b++) {
+        uint8_t *p = out + b * bytes;
+        size_t i = 0;
+        uint64_t v = 0;
+        for (; i + 8 <= bytes; i += 8) { v = next64(&s); memcpy(p + i, &v, 8); }
+        if (i < bytes) { v = next64(&s); memcpy(p + i, &v, bytes - i); }
+        const int pick = (int)(v >> 60);
+        if (type == 12) { put16(p, d[pick]); put16(p + 2, dmin[pick]); }
+        else if (type == 10) { put16(p + 80, d[pick]); put16(p + 82, dmin[pick]); }
+        else put16(p, d[pick]);
+    }
+}
+
 typedef struct {
     uint32_t type; uint64_t seed, stream; float sigma; size_t rows, k, first, last, row0; uint8_t *out; int status;
 } Slice;
 static void *slice_worker(void *arg) {
     Slice *s = arg;
     const size_t bytes = s->type == 0 ? s->k * 4 : s->k / 256 * block_bytes(s->type);
+    if (s->sigma < 0.0f && s->type != 0) {                     /* fabricated blocks */
+        for (size_t r = s->first; r < s->last; r++) fabricated_row(s->type, s->seed, s->stream, r + s->row0, s->out + r * bytes, s->k);
+        return NULL;
+    }
     float *row = malloc(s->k * sizeof *row);
     if (!row) { s->status = -1; return NULL; }
     for (size_t r = s->first; r < s->last; r++) {
@@ -241,7 +270,8 @@ int qw4s_tensor(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size
     return qw4s_tensor_rows(type, seed, stream, sigma, 0, rows, k, out, threads);
 }
 /* Rows [row0, row0 + rows) of the same tensor (an expert shard): identical bytes to the
- * corresponding slice of the whole tensor. */
+ * corresponding slice of the whole tensor.  sigma < 0 (block formats): fabricated blocks instead of
+ * encoded Gaussians. */
 int qw4s_tensor_rows(uint32_t type, uint64_t seed, uint64_t stream, float sigma, size_t row0, size_t rows, size_t k,
                      uint8_t *out, int threads) {
     if (type != 0 && (!block_bytes(type) || k % 256)) return -1;

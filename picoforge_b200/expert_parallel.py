@@ -1,185 +1,164 @@
-"""Expert-parallel execution of the MoE layer over the ranks of one node.
+"""Expert-parallel execution of the MoE layer over the ranks of one node (ctypes plumbing).
 
-The reference is a single-device engine; this module is new design.  The 512 experts are cut
-into contiguous blocks, one per rank; the router and the shared expert are replicated; tokens
-are data-parallel.  One layer step on a rank:
+The reference is a single-device engine; expert parallelism is new design and lives in the C
+library (csrc/ep_nccl.cu, `qw4cu_moe_ep_forward_device`): experts in equal contiguous blocks, one
+per rank; router and shared expert replicated; tokens data-parallel.  One layer step:
 
-    route (own tokens)  ->  dispatch all-to-all (x rows + local expert ids to the owners)
-    ->  experts (rows received from every rank)  ->  combine all-to-all (outputs back)
-    ->  slot-order weighted sum + shared expert (own tokens)
+    route own tokens, pack one row per token (x | ids | weights)     [this rank]
+    all-gather of the rows                                            [NCCL, in the library]
+    own experts on the tokens routed to them, per-token partial sums  [this rank]
+    reduce-scatter (sum) of the partial rows                          [NCCL, in the library]
 
-The three compute pieces are the library's; this file owns the buffers (torch tensors) and calls
-`torch.distributed` all-to-all over NCCL/NVLink between them.  Exchange buffers have a fixed capacity per
-destination (every pair could go to one rank), so no step needs a host round trip for sizes; unused
-slots carry the id 0xffffffff.
-
-Two forms of the same step:
-  packed (default)  `qw4cu_moe_ep_{route_pack,experts,combine}_device`: the library plans and packs the message
-                    itself (rows and ids in one message: two all-to-alls per layer) and runs the shared expert
-                    on a second stream under the exchange
-  plain             `qw4cu_moe_{route,experts,combine}_device` with the plan in torch ops and separate row / id
-                    messages (three all-to-alls); kept as the cross-check of the packed form
+This module holds what a Python caller needs around that: the NCCL unique id handed from rank 0
+to the others over any `torch.distributed` group, a per-rank layer object that owns its device
+buffers through the library's allocator, a loop that plays several ranks inside ONE process with
+the two compute pieces (for boxes with one GPU), and the same scheme in NumPy for CPU ranks.
 """
 from __future__ import annotations
 
 import ctypes as C
 
-import torch
+import numpy as np
 
 from . import abi
 from .layer import LayerSpec, MoeLayer
 
-NO_EXPERT = -1      # 0xffffffff as int32
+
+def owner_of(ids: np.ndarray, experts: int, world: int) -> np.ndarray:
+    """Rank that owns each expert id (equal contiguous blocks)."""
+    return np.asarray(ids) // (experts // world)
 
 
-def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int):
-    """ids [T, k] (global expert ids, any integer dtype).  Returns, per pair in pair order
-    (token * k + slot): destination rank, position inside that rank's buffer (stable: pairs keep
-    their order), and the expert index inside the destination's shard."""
-    flat = ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    order = torch.argsort(dest, stable=True)
-    counts = torch.bincount(dest, minlength=world)
-    starts = torch.cumsum(counts, 0) - counts
-    pos = torch.empty_like(flat)
-    pos[order] = torch.arange(flat.numel(), device=flat.device) - starts[dest[order]]
-    return dest, pos, flat - dest * experts_per_rank, counts
+class Communicator:
+    """The library's NCCL communicator of this rank.  `group_broadcast(bytes_or_None) -> bytes` moves the
+    unique id from rank 0 to everybody (e.g. over a gloo or nccl torch.distributed group)."""
+
+    def __init__(self, api: abi.MoeApi, rank: int, world: int, group_broadcast=None):
+        self.api, self.rank, self.world = api, rank, world
+        self.handle = C.c_void_p()
+        ident = None
+        if world > 1:
+            buffer = C.create_string_buffer(128)
+            if rank == 0 and api.lib.qw4cu_ep_unique_id(buffer) != 0:
+                raise RuntimeError(api.lib.qw4cu_last_error().decode())
+            ident = group_broadcast(buffer.raw if rank == 0 else None)
+            assert len(ident) == 128
+        err = abi.Qwen4Error()
+        st = api.lib.qw4cu_ep_create(ident, rank, world, C.byref(self.handle), C.byref(err))
+        if st:
+            raise abi.MoeError(st, err)
+
+    def close(self):
+        if self.handle:
+            self.api.lib.qw4cu_ep_destroy(self.handle)
+            self.handle = C.c_void_p()
 
 
-class TorchExchange:
-    """all-to-all of equally sized per-destination blocks through torch.distributed."""
+def torch_broadcast(group=None):
+    """A `group_broadcast` over torch.distributed (object broadcast from rank 0)."""
+    import torch.distributed as dist
 
-    def __init__(self, group=None):
-        import torch.distributed as dist
-        self.dist, self.group = dist, group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-
-    def all_to_all(self, send: torch.Tensor) -> torch.Tensor:
-        recv = torch.empty_like(send)
-        self.dist.all_to_all_single(recv, send, group=self.group)
-        return recv
+    def broadcast(payload):
+        box = [payload]
+        dist.broadcast_object_list(box, src=0, group=group)
+        return box[0]
+    return broadcast
 
 
 class EpLayer:
-    """One rank's share of one layer."""
+    """One rank's shard of one layer: the sharded MoE handle, a workspace for (world + 1) * tokens tokens,
+    and the ids / weights of the last step in device memory."""
 
-    def __init__(self, api: abi.MoeApi, spec: LayerSpec, tokens_local: int, world: int, rank: int, exchange, packed: bool = True):
-        assert spec.experts % world == 0
-        self.api, self.world, self.rank, self.exchange, self.packed = api, world, rank, exchange, packed
-        self.epr = spec.experts // world
-        assert spec.local_experts == self.epr and spec.first_expert == rank * self.epr
-        self.spec, self.tokens, self.k, self.hidden = spec, tokens_local, spec.top_k, spec.hidden
-        self.cap = tokens_local * spec.top_k                 # rows one source may send to one destination
-        # tokens_local rows beyond the exchange capacity: room for the shared expert's x digits beside the routed rows
-        self.layer = MoeLayer(api, spec, world * self.cap + tokens_local)
-        dev = torch.device("cuda", torch.cuda.current_device())
-        self.slot_floats = api.lib.qw4cu_ep_slot_floats(self.layer.moe)
-        self.msg = torch.zeros((world, self.cap, self.slot_floats), dtype=torch.float32, device=dev)
-        self.slots = torch.empty((tokens_local * self.k,), dtype=torch.int32, device=dev)
-        self.ids = torch.empty((tokens_local, self.k), dtype=torch.int32, device=dev)
-        self.send_rows = torch.zeros((world, self.cap, self.hidden), dtype=torch.float32, device=dev)
-        self.send_ids = torch.empty((world, self.cap), dtype=torch.int32, device=dev)
-        self.out_rows = torch.zeros((world * self.cap, self.hidden), dtype=torch.float32, device=dev)
-        self.y = torch.empty((tokens_local, self.hidden), dtype=torch.float32, device=dev)
-        self.err = abi.Qwen4Error()
+    def __init__(self, api: abi.MoeApi, spec: LayerSpec, tokens_local: int, world: int, rank: int):
+        assert spec.sharded or world == 1
+        self.api, self.spec, self.tokens, self.world, self.rank = api, spec, tokens_local, world, rank
+        self.layer = MoeLayer(api, spec, (world + 1) * tokens_local)
+        self.ids_dev = api.lib.qw4cu_malloc(max(4, tokens_local * spec.top_k * 4))
+        self.weights_dev = api.lib.qw4cu_malloc(max(4, tokens_local * spec.top_k * 4))
+
+    def _check(self, status, err):
+        if status:
+            raise abi.MoeError(status, err)
+
+    def forward(self, comm: Communicator, x_dev, y_dev):
+        """x_dev, y_dev: device pointers [tokens_local, hidden].  Enqueues the whole step (collectives included)."""
+        err = abi.Qwen4Error()
+        self._check(self.api.lib.qw4cu_moe_ep_forward_device(self.layer.moe, comm.handle, x_dev, y_dev, self.tokens, self.ids_dev,
+                                                             self.weights_dev, self.layer.work, C.byref(err)), err)
+
+    def begin(self, x_dev, rows_local_dev):
+        err = abi.Qwen4Error()
+        self._check(self.api.lib.qw4cu_moe_ep_begin_device(self.layer.moe, x_dev, self.tokens, rows_local_dev, self.ids_dev, self.weights_dev,
+                                                           self.layer.work, C.byref(err)), err)
+
+    def experts(self, rows_all_dev, tokens_total, own_first, partial_dev):
+        err = abi.Qwen4Error()
+        self._check(self.api.lib.qw4cu_moe_ep_experts_device(self.layer.moe, rows_all_dev, tokens_total, own_first, partial_dev,
+                                                             self.layer.work, C.byref(err)), err)
+
+    def sync(self):
+        err = abi.Qwen4Error()
+        self._check(self.api.lib.qw4cu_moe_work_sync(self.layer.work, C.byref(err)), err)
+
+    def routes(self):
+        ids = np.empty((self.tokens, self.spec.top_k), np.uint32)
+        weights = np.empty((self.tokens, self.spec.top_k), np.float32)
+        assert self.api.lib.qw4cu_download(ids.ctypes.data, self.ids_dev, ids.nbytes) == 0
+        assert self.api.lib.qw4cu_download(weights.ctypes.data, self.weights_dev, weights.nbytes) == 0
+        return ids, weights
 
     def close(self):
         self.layer.close()
-
-    def _check(self, status):
-        if status:
-            raise abi.MoeError(status, self.err)
-
-    def _use_torch_stream(self):
-        # torch's default stream has handle 0, which the library reads as "back to my own stream":
-        # name it by CUDA's legacy-default-stream handle (1) instead.
-        self.api.lib.qw4cu_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream or 1))
-
-    def phase_route(self, x: torch.Tensor):
-        """Routes this rank's tokens and fills the per-destination send buffers."""
-        lib, layer = self.api.lib, self.layer
-        assert x.is_contiguous() and x.shape == (self.tokens, self.hidden)
-        self._use_torch_stream()
-        self._check(lib.qw4cu_moe_route_device(layer.moe, x.data_ptr(), self.tokens, self.ids.data_ptr(), None, layer.work,
-                                               C.byref(self.err)))
-        self.dest, self.pos, local, _ = dispatch_plan(self.ids, self.epr, self.world)
-        token = torch.arange(self.tokens * self.k, device=x.device) // self.k
-        self.send_ids.fill_(NO_EXPERT)
-        self.send_ids[self.dest, self.pos] = local.to(torch.int32)
-        self.send_rows[self.dest, self.pos] = x[token]
-        return self.send_rows, self.send_ids
-
-    def phase_experts(self, recv_rows: torch.Tensor, recv_ids: torch.Tensor) -> torch.Tensor:
-        """Runs this rank's experts on the rows received from every rank."""
-        self._use_torch_stream()
-        self._check(self.api.lib.qw4cu_moe_experts_device(self.layer.moe, recv_rows.data_ptr(), self.world * self.cap,
-                                                          recv_ids.data_ptr(), self.out_rows.data_ptr(), self.layer.work,
-                                                          C.byref(self.err)))
-        return self.out_rows.view(self.world, self.cap, self.hidden)
-
-    def phase_combine(self, x: torch.Tensor, back: torch.Tensor) -> torch.Tensor:
-        """back [world, cap, hidden]: block d holds the outputs of the rows sent to rank d."""
-        self._use_torch_stream()
-        pair_out = back[self.dest, self.pos].contiguous()
-        self._check(self.api.lib.qw4cu_moe_combine_device(self.layer.moe, x.data_ptr(), self.tokens, pair_out.data_ptr(),
-                                                          self.y.data_ptr(), self.layer.work, C.byref(self.err)))
-        return self.y
-
-    # ---- packed form ----
-    def packed_route(self, x: torch.Tensor) -> torch.Tensor:
-        assert x.is_contiguous() and x.shape == (self.tokens, self.hidden)
-        self._use_torch_stream()
-        self._check(self.api.lib.qw4cu_moe_ep_route_pack_device(self.layer.moe, x.data_ptr(), self.tokens, self.cap, self.msg.data_ptr(),
-                                                                self.slots.data_ptr(), self.ids.data_ptr(), self.layer.work,
-                                                                C.byref(self.err)))
-        return self.msg
-
-    def packed_experts(self, recv: torch.Tensor) -> torch.Tensor:
-        self._use_torch_stream()
-        self._check(self.api.lib.qw4cu_moe_ep_experts_device(self.layer.moe, recv.data_ptr(), self.world * self.cap, self.out_rows.data_ptr(),
-                                                             self.layer.work, C.byref(self.err)))
-        return self.out_rows.view(self.world, self.cap, self.hidden)
-
-    def packed_combine(self, x: torch.Tensor, back: torch.Tensor) -> torch.Tensor:
-        self._use_torch_stream()
-        self._check(self.api.lib.qw4cu_moe_ep_combine_device(self.layer.moe, x.data_ptr(), self.tokens, back.data_ptr(), self.slots.data_ptr(),
-                                                             self.y.data_ptr(), self.layer.work, C.byref(self.err)))
-        return self.y
-
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [tokens_local, hidden] float32 on this rank's GPU.  Work is enqueued on torch's current
-        stream (the library is pointed at it), so it orders with the NCCL all-to-alls."""
-        if self.packed:
-            recv = self.exchange.all_to_all(self.packed_route(x))
-            back = self.exchange.all_to_all(self.packed_experts(recv))
-            return self.packed_combine(x, back)
-        send_rows, send_ids = self.phase_route(x)
-        recv_rows = self.exchange.all_to_all(send_rows)
-        recv_ids = self.exchange.all_to_all(send_ids)
-        out = self.phase_experts(recv_rows, recv_ids)
-        back = self.exchange.all_to_all(out)
-        return self.phase_combine(x, back)
-
-    def sync(self):
-        self._check(self.api.lib.qw4cu_moe_work_sync(self.layer.work, C.byref(self.err)))
+        for pointer in (self.ids_dev, self.weights_dev):
+            if pointer:
+                self.api.lib.qw4cu_free(pointer)
+        self.ids_dev = self.weights_dev = None
 
 
-def transpose_blocks(sends):
-    """What an all-to-all does, for `world` ranks emulated in one process (tests on one GPU or on
-    the CPU): sends[r] = [world, cap, ...] of rank r -> result[r][s] = sends[s][r]."""
-    stacked = torch.stack(list(sends))                        # [src, dst, cap, ...]
-    return [stacked[:, r].contiguous() for r in range(stacked.shape[1])]
+def forward_emulated(api: abi.MoeApi, layers: list[EpLayer], xs: list[np.ndarray]) -> list[np.ndarray]:
+    """Plays len(layers) ranks on ONE device with the library's two compute pieces; the all-gather is a
+    concatenation and the reduce-scatter a sum, both done here on the host.  Returns y per rank."""
+    lib = api.lib
+    world, per = len(layers), xs[0].shape[0]
+    hidden = layers[0].spec.hidden
+    pitch = lib.qw4cu_ep_row_floats(layers[0].layer.moe)
+    rows_all = np.empty((world * per, pitch), np.float32)
+    d_x, d_rows = lib.qw4cu_malloc(per * hidden * 4), lib.qw4cu_malloc(per * pitch * 4)
+    d_all, d_partial = lib.qw4cu_malloc(world * per * pitch * 4), lib.qw4cu_malloc(world * per * hidden * 4)
+    try:
+        # every rank's begin (and with it the start of its shared expert) comes before any rank's experts
+        for r, layer in enumerate(layers):
+            x = np.ascontiguousarray(xs[r], np.float32)
+            assert lib.qw4cu_upload(d_x, x.ctypes.data, x.nbytes) == 0
+            layer.begin(d_x, d_rows)
+            layer.sync()
+            block = rows_all[r * per:(r + 1) * per]
+            assert lib.qw4cu_download(block.ctypes.data, d_rows, block.nbytes) == 0
+        assert lib.qw4cu_upload(d_all, rows_all.ctypes.data, rows_all.nbytes) == 0
+        total = np.zeros((world * per, hidden), np.float64)
+        partial = np.empty((world * per, hidden), np.float32)
+        for r, layer in enumerate(layers):
+            layer.experts(d_all, world * per, r * per, d_partial)
+            layer.sync()
+            assert lib.qw4cu_download(partial.ctypes.data, d_partial, partial.nbytes) == 0
+            total += partial
+        return [total[r * per:(r + 1) * per].astype(np.float32) for r in range(world)]
+    finally:
+        for pointer in (d_x, d_rows, d_all, d_partial):
+            lib.qw4cu_free(pointer)
 
 
-def forward_emulated(layers, xs):
-    """Runs the ranks of `layers` (EpLayer objects sharing one GPU) in lockstep."""
-    if layers[0].packed:
-        recvs = transpose_blocks([layer.packed_route(x) for layer, x in zip(layers, xs)])
-        backs = transpose_blocks([layer.packed_experts(r) for layer, r in zip(layers, recvs)])
-        return [layer.packed_combine(x, b.contiguous()).clone() for layer, x, b in zip(layers, xs, backs)]
-    sends = [layer.phase_route(x) for layer, x in zip(layers, xs)]
-    recv_rows = transpose_blocks([s[0] for s in sends])
-    recv_ids = transpose_blocks([s[1] for s in sends])
-    outs = [layer.phase_experts(r, i) for layer, r, i in zip(layers, recv_rows, recv_ids)]
-    backs = transpose_blocks(outs)
-    return [layer.phase_combine(x, b).clone() for layer, x, b in zip(layers, xs, backs)]
+def partial_sums_reference(expert_outputs, ids: np.ndarray, weights: np.ndarray, first: int, count: int) -> np.ndarray:
+    """The per-token partial sums of one rank, in NumPy: expert_outputs(token, expert) -> row [hidden] for the
+    experts [first, first + count) this rank owns.  Used with CPU ranks to check the scheme itself."""
+    tokens = ids.shape[0]
+    out = None
+    for t in range(tokens):
+        for s in range(ids.shape[1]):
+            e = int(ids[t, s])
+            if first <= e < first + count:
+                row = np.asarray(expert_outputs(t, e), np.float64) * float(weights[t, s])
+                if out is None:
+                    out = np.zeros((tokens, row.shape[0]), np.float64)
+                out[t] += row
+    return out

@@ -42,10 +42,15 @@ def threads() -> int:
     return max(1, min(64, len(os.sched_getaffinity(0))))
 
 
-def tensor(gguf_type: int, seed: int, stream: int, rows: int, k: int, sigma: float = 0.02, row0: int = 0) -> np.ndarray:
+def tensor(gguf_type: int, seed: int, stream: int, rows: int, k: int, sigma: float = 0.02, row0: int = 0,
+           out: np.ndarray | None = None) -> np.ndarray:
     """Rows [row0, row0 + rows) of a tensor of k-weight rows ~ N(0, sigma) encoded as gguf_type;
-    returns the packed bytes (a shard has the same bytes as that slice of the whole tensor)."""
-    out = np.empty(rows * abi.row_bytes(gguf_type, k), np.uint8)
+    returns the packed bytes (a shard has the same bytes as that slice of the whole tensor).  `out`: an
+    array of the right size to write into (first-touch page faults of a fresh one can cost more than
+    the generation)."""
+    size = rows * abi.row_bytes(gguf_type, k)
+    if out is None or out.size != size or out.dtype != np.uint8:
+        out = np.empty(size, np.uint8)
     if _lib().qw4s_tensor_rows(gguf_type, seed, stream, sigma, row0, rows, k, out.ctypes.data, threads()):
         raise ValueError(f"cannot synthesise type {gguf_type} with k={k}")
     return out
@@ -69,9 +74,13 @@ def normal(seed: int, stream: int, rows: int, k: int, sigma: float = 1.0) -> np.
 def make_layer(seed: int, layer: int = 0, routed_type: int = abi.Q4_K, shared_type: int = abi.Q4_K,
                hidden: int = 2048, experts: int = 512, top_k: int = 10, inter: int = 512,
                shared_inter: int = 512, down_type: int | None = None, norm: bool = True,
-               shard: tuple | None = None) -> LayerSpec:
+               shard: tuple | None = None, fabricated: bool = False, reuse: LayerSpec | None = None) -> LayerSpec:
     """One synthetic layer.  Stream ids: layer * 8 + tensor index.  shard = (first_expert,
-    local_experts) generates only that slice of the routed expert tensors."""
+    local_experts) generates only that slice of the routed expert tensors.  fabricated: the
+    quantised tensors are random valid blocks with scales set for a spread of about 0.02 (as the
+    reference's kernel tests make theirs) instead of encoded Gaussians: some twenty times
+    faster to make, for stacks of many layers.  reuse: a spec of the same shapes whose arrays are
+    overwritten and returned in the new spec (the old spec must not be used afterwards)."""
     down_type = routed_type if down_type is None else down_type
     types = (abi.F32, routed_type, routed_type, down_type, shared_type, shared_type, shared_type, abi.F32)
     spec = LayerSpec(hidden, experts, top_k, inter, shared_inter, inter, norm, types)
@@ -80,7 +89,9 @@ def make_layer(seed: int, layer: int = 0, routed_type: int = abi.Q4_K, shared_ty
     tensors = []
     for index, (gguf_type, (k_storage, _, n_out, n_experts)) in enumerate(zip(types, spec.shapes())):
         row0 = spec.first_expert * n_out if 1 <= index <= 3 else 0
-        tensors.append(tensor(gguf_type, seed, layer * 8 + index, n_out * n_experts, k_storage, row0=row0))
+        sigma = -1.0 if fabricated and gguf_type != abi.F32 else 0.02
+        old = reuse.tensors[index] if reuse is not None and len(reuse.tensors) == 8 else None
+        tensors.append(tensor(gguf_type, seed, layer * 8 + index, n_out * n_experts, k_storage, sigma=sigma, row0=row0, out=old))
     spec.tensors = tensors
     return spec
 

@@ -128,3 +128,13 @@ def test_group_rejects_bad_ids_before_the_device(product):
 def test_empty_route_needs_no_device(product):
     probs, ids, weights = route(product, np.zeros((0, 4), np.float32), 2)
     assert probs.shape == (0, 4) and ids.shape == (0, 2) and weights.shape == (0, 2)
+
+
+def test_empty_group_views_are_checked_without_dividing_by_their_pitch(product):
+    """No tokens: the pair arrays are empty (zero bytes per row).  The view checks must pass them
+    (picoforge tests/test_qwen4_moe.c:90-93 runs the empty batch) and only the device step may fail here."""
+    try:
+        offsets, p2r, r2p = group_pairs(product, np.zeros((0, 2), np.uint32), 4)
+        assert (offsets == 0).all() and p2r.size == 0 and r2p.size == 0
+    except abi.MoeError as error:                       # no GPU on this machine
+        assert error.status == abi.GPU_ERROR

@@ -1,7 +1,10 @@
-"""Expert parallelism: the dispatch plan and exchange on CPU ranks (gloo, world size 2), and the
-whole sharded layer against the oracle with the ranks emulated on one GPU."""
+"""Expert parallelism: the exchange scheme (one row per token out by all-gather, per-token partial
+sums back by a summed reduce-scatter) among CPU ranks over gloo, a rank that leaves between steps,
+and the library's sharded layer against the oracle: ranks played inside one process on one GPU, and
+one process per GPU with the collectives issued by the library through NCCL."""
 import os
 import sys
+from datetime import timedelta
 from pathlib import Path
 
 import numpy as np
@@ -10,103 +13,92 @@ import pytest
 sys.path.insert(0, str(Path(__file__).parent))
 
 
-def _plan_worker(rank, world, port, results):
+def _routes(seed, tokens, experts, k):
+    rng = np.random.default_rng(seed)
+    ids = np.stack([rng.permutation(experts)[:k] for _ in range(tokens)]).astype(np.uint32)
+    weights = rng.random((tokens, k)).astype(np.float32)
+    return ids, weights / weights.sum(axis=1, keepdims=True)
+
+
+def _scheme_worker(rank, world, port, results):
     import torch
     import torch.distributed as dist
-    from picoforge_b200.expert_parallel import NO_EXPERT, dispatch_plan
+    from picoforge_b200.expert_parallel import owner_of, partial_sums_reference
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        experts, k, tokens, hidden = 8, 3, 5, 4
-        epr, cap = experts // world, tokens * k
-        rng = np.random.default_rng(100 + rank)
-        ids = torch.tensor(np.stack([rng.permutation(experts)[:k] for _ in range(tokens)]), dtype=torch.int32)
-        x = torch.arange(tokens * hidden, dtype=torch.float32).reshape(tokens, hidden) + 1000 * rank
-        dest, pos, local, counts = dispatch_plan(ids, epr, world)
-        send_rows = torch.zeros(world, cap, hidden)
-        send_ids = torch.full((world, cap), NO_EXPERT, dtype=torch.int32)
-        token = torch.arange(tokens * k) // k
-        send_rows[dest, pos] = x[token]
-        send_ids[dest, pos] = local.to(torch.int32)
-        recv_rows, recv_ids = torch.empty_like(send_rows), torch.empty_like(send_ids)
-        dist.all_to_all_single(recv_rows, send_rows)
-        dist.all_to_all_single(recv_ids, send_ids)
-        # every received id belongs to this rank's shard; pretend expert output = row * (1 + local id)
-        valid = recv_ids != NO_EXPERT
-        assert bool(((recv_ids[valid] >= 0) & (recv_ids[valid] < epr)).all())
-        out = recv_rows * (1 + recv_ids.clamp(min=0)).unsqueeze(-1).float()
-        back = torch.empty_like(out)
-        dist.all_to_all_single(back, out)
-        pair_out = back[dest, pos]
-        want = x[token] * (1 + (ids.reshape(-1).to(torch.int64) % epr)).unsqueeze(-1).float()
-        assert torch.equal(pair_out, want)
-        # stable order inside a destination, counts add up
-        for d in range(world):
-            assert torch.equal(pos[dest == d], torch.arange(int(counts[d])))
-        gathered = [None] * world
-        dist.all_gather_object(gathered, int(valid.sum()))
-        results[rank] = (int(counts.sum()), gathered)
+        experts, k, per, hidden = 8, 3, 5, 4
+        epr = experts // world
+        x = np.arange(per * hidden, dtype=np.float32).reshape(per, hidden) + 1000 * rank
+        ids, weights = _routes(100 + rank, per, experts, k)
+        # one row per token: x | ids | weights
+        row = torch.tensor(np.concatenate([x, ids.view(np.float32), weights], axis=1))
+        gathered = [torch.empty_like(row) for _ in range(world)]
+        dist.all_gather(gathered, row)
+        rows_all = torch.cat(gathered).numpy()
+        x_all = rows_all[:, :hidden]
+        ids_all = np.ascontiguousarray(rows_all[:, hidden:hidden + k]).view(np.uint32)
+        w_all = rows_all[:, hidden + k:]
+        assert (owner_of(ids_all, experts, world) < world).all()
+        expert = lambda t, e: x_all[t] * (1.0 + e)                              # noqa: E731  a stand-in for the expert's SwiGLU
+        partial = partial_sums_reference(expert, ids_all, w_all, rank * epr, epr)
+        total = torch.tensor(partial if partial is not None else np.zeros((world * per, hidden)))
+        dist.all_reduce(total)                                                   # gloo has no reduce-scatter: sum, then keep the own rows
+        mine = total.numpy()[rank * per:(rank + 1) * per]
+        want = sum(weights[:, s:s + 1] * x * (1.0 + ids[:, s:s + 1]) for s in range(k))
+        np.testing.assert_allclose(mine, want, rtol=1e-6)
+        results[rank] = int((owner_of(ids_all, experts, world) == rank).sum())
     finally:
         dist.destroy_process_group()
 
 
-def test_dispatch_plan_and_exchange_on_two_cpu_ranks():
+def test_exchange_scheme_on_two_cpu_ranks():
     import torch.multiprocessing as mp
     world = 2
-    manager = mp.Manager()
-    results = manager.dict()
-    mp.spawn(_plan_worker, args=(world, 29500 + os.getpid() % 1000, results), nprocs=world, join=True)
-    assert len(results) == world
-    sent = sum(results[r][0] for r in range(world))
-    received = sum(results[0][1])
-    assert sent == received == world * 5 * 3
+    results = mp.Manager().dict()
+    mp.spawn(_scheme_worker, args=(world, 29500 + os.getpid() % 1000, results), nprocs=world, join=True)
+    assert sum(results[r] for r in range(world)) == world * 5 * 3              # every pair has exactly one owner
 
 
-def test_dispatch_plan_matches_the_oracle_grouping():
+def _leaving_worker(rank, world, port, results):
     import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=5))
+    value = torch.ones(4)
+    dist.all_reduce(value)                                                       # step 1: everybody is there
+    if rank == 1:
+        results[rank] = "left between steps"
+        os._exit(0)                                                              # a rank that dies between two steps, nothing in flight
+    try:
+        dist.all_reduce(value)                                                   # step 2: the peer is gone
+        results[rank] = "no error"
+    except Exception as error:                                                   # noqa: BLE001
+        results[rank] = "error: " + type(error).__name__
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_collective_with_an_error():
+    """Failure detection on the host: the survivor's next collective fails (connection closed or timeout)
+    instead of hanging, so its caller can stop issuing layer steps."""
+    import torch.multiprocessing as mp
+    results = mp.Manager().dict()
+    context = mp.spawn(_leaving_worker, args=(2, 30500 + os.getpid() % 1000, results), nprocs=2, join=False)
+    for process in context.processes:
+        process.join(60)
+        assert not process.is_alive()
+    assert results[1] == "left between steps"
+    assert results[0].startswith("error"), results[0]
+
+
+def test_owners_match_the_oracle_grouping():
     import oracle
-    from picoforge_b200.expert_parallel import dispatch_plan
+    from picoforge_b200.expert_parallel import owner_of
     rng = np.random.default_rng(7)
     ids = np.stack([rng.permutation(64)[:6] for _ in range(40)]).astype(np.uint32)
-    dest, pos, local, counts = dispatch_plan(torch.tensor(ids.astype(np.int64)), 16, 4)
-    offsets, p2r, r2p = oracle.group(ids, 64)
-    # rows of one destination rank are the oracle's rows of its experts, as a set
-    for d in range(4):
-        assert int(counts[d]) == int(offsets[16 * (d + 1)] - offsets[16 * d])
-    assert torch.equal(local, torch.tensor(ids.reshape(-1).astype(np.int64) % 16))
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("packed", [True, False])
-@pytest.mark.parametrize("routed,world,tokens", [(12, 4, 16), (16, 2, 6), (10, 4, 32)])
-def test_sharded_layer_matches_the_oracle_with_emulated_ranks(gpu, routed, world, tokens, packed):
-    """`world` ranks share one GPU; the all-to-all is a block transpose.  Q4_K and IQ2_XXS shards
-    take the tensor-core grouped kernels, Q2_K the CUDA-core kernels.  Both forms of the step: packed
-    messages planned by the library (shared expert on a second stream), and the plan in torch ops."""
-    import torch
-    import oracle
-    from picoforge_b200 import abi, synth
-    from picoforge_b200.expert_parallel import EpLayer, forward_emulated
-    spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4)
-    x = synth.activations(300 + world, tokens)
-    want = oracle.forward(spec, x, threads=synth.threads())
-    per = tokens // world
-    epr = spec.experts // world
-    torch.cuda.set_device(0)
-    layers = [EpLayer(gpu, spec.shard(r * epr, epr), per, world, r, None, packed) for r in range(world)]
-    try:
-        xs = [torch.tensor(x[r * per:(r + 1) * per]).cuda().contiguous() for r in range(world)]
-        ys = forward_emulated(layers, xs)
-        for layer in layers:
-            layer.sync()
-        y = torch.cat(ys).cpu().numpy()
-        ids = torch.cat([layer.ids for layer in layers]).cpu().numpy().astype(np.uint32)
-    finally:
-        for layer in layers:
-            layer.close()
-        gpu.lib.qw4cu_set_stream(None)
-    np.testing.assert_array_equal(ids, want["ids"])
-    assert np.abs(y - want["y"]).max() <= 1e-3
+    owners = owner_of(ids, 64, 4)
+    offsets, _, _ = oracle.group(ids, 64)
+    for rank in range(4):                                                        # a rank's rows are the oracle's rows of its experts
+        assert int((owners == rank).sum()) == int(offsets[16 * (rank + 1)] - offsets[16 * rank])
 
 
 def test_shard_bytes_equal_the_slice_of_the_whole_tensor():
@@ -120,41 +112,74 @@ def test_shard_bytes_equal_the_slice_of_the_whole_tensor():
         np.testing.assert_array_equal(a, b)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("routed,world,tokens", [(12, 4, 16), (16, 2, 6), (10, 4, 32), (10, 2, 160), (12, 1, 24)])
+def test_sharded_layer_matches_the_oracle_with_the_ranks_played_in_one_process(gpu, routed, world, tokens):
+    """`world` ranks share one GPU; the all-gather is a concatenation and the reduce-scatter a sum on the host.
+    Q4_K and IQ2_XXS shards take the four-row grouped kernels, Q2_K (and more than 64 tokens) the tile kernels;
+    80 own tokens per rank put the shared expert on the tile kernels too."""
+    import oracle
+    from picoforge_b200 import abi, synth
+    from picoforge_b200.expert_parallel import EpLayer, forward_emulated
+    spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4)
+    x = synth.activations(300 + world, tokens)
+    want = oracle.forward(spec, x, threads=synth.threads())
+    per, epr = tokens // world, spec.experts // world
+    layers = [EpLayer(gpu, spec.shard(r * epr, epr) if world > 1 else spec, per, world, r) for r in range(world)]
+    try:
+        ys = forward_emulated(gpu, layers, [x[r * per:(r + 1) * per] for r in range(world)])
+        routes = [layer.routes() for layer in layers]
+    finally:
+        for layer in layers:
+            layer.close()
+    y = np.concatenate(ys)
+    np.testing.assert_array_equal(np.concatenate([r[0] for r in routes]), want["ids"])
+    np.testing.assert_array_equal(np.concatenate([r[1] for r in routes]).view(np.uint32), want["weights"].view(np.uint32))
+    assert np.abs(y - want["y"]).max() <= 1e-3
+
+
 def _nccl_worker(rank, world, port, routed, tokens, results):
-    import torch
+    import ctypes as C
     import torch.distributed as dist
     from picoforge_b200 import abi, synth
-    from picoforge_b200.expert_parallel import EpLayer, TorchExchange
+    from picoforge_b200.expert_parallel import Communicator, EpLayer, torch_broadcast
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)                 # only to hand the NCCL id round
     try:
         api = abi.product()
-        assert api.lib.qw4cu_set_device(rank) == 0
+        lib = api.lib
+        assert lib.qw4cu_set_device(rank) == 0
         per, epr = tokens // world, 32 // world
         spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4, shard=(rank * epr, epr))
-        x = synth.activations(300 + world, tokens)[rank * per:(rank + 1) * per]
-        stream = torch.cuda.Stream()
-        with torch.cuda.stream(stream):
-            layer = EpLayer(api, spec, per, world, rank, TorchExchange())
-            y = layer.forward(torch.tensor(x).cuda().contiguous())
-            layer.sync()
-            results[rank] = (y.cpu().numpy(), layer.ids.cpu().numpy().astype(np.uint32))
-            layer.close()
-        api.lib.qw4cu_set_stream(None)
+        x = np.ascontiguousarray(synth.activations(300 + world, tokens)[rank * per:(rank + 1) * per])
+        comm = Communicator(api, rank, world, torch_broadcast())
+        layer = EpLayer(api, spec, per, world, rank)
+        d_x, d_y = lib.qw4cu_malloc(x.nbytes), lib.qw4cu_malloc(x.nbytes)
+        assert lib.qw4cu_upload(d_x, x.ctypes.data, x.nbytes) == 0
+        for _ in range(2):                                                       # twice: the buffers and counters are reusable
+            layer.forward(comm, d_x, d_y)
+        layer.sync()
+        y = np.empty_like(x)
+        assert lib.qw4cu_download(y.ctypes.data, d_y, y.nbytes) == 0
+        results[rank] = (y, layer.routes()[0])
+        dist.barrier()
+        layer.close()
+        comm.close()
+        lib.qw4cu_free(d_x); lib.qw4cu_free(d_y)
+        del C
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("routed", [12, 16])
+@pytest.mark.parametrize("routed", [12, 10])
 def test_sharded_layer_over_nccl_on_two_gpus(gpu, routed):
-    """One process per GPU, rows exchanged by NCCL all-to-all; skipped on a one-GPU box."""
-    import torch
+    """One process per GPU, the library's own all-gather and reduce-scatter over NCCL; skipped on a one-GPU box."""
     import torch.multiprocessing as mp
     import oracle
     from picoforge_b200 import abi, synth
-    if torch.cuda.device_count() < 2:
+    if gpu.lib.qw4cu_device_count() < 2:
         pytest.skip("needs two GPUs")
     world, tokens = 2, 12
     spec = synth.make_layer(300 + routed, routed_type=routed, shared_type=abi.Q4_K, experts=32, top_k=4)
