@@ -301,6 +301,16 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
     sync_all()
     launches = lib.qw4cu_launch_count() - before
     barrier()
+    # one more, untimed, step with an event at every stage boundary (it synchronises per layer: a profile, not a timing)
+    lib.qw4cu_ep_trace(1)
+    step()
+    stage_ms = (C.c_double * 10)()
+    traced = lib.qw4cu_ep_trace_read(stage_ms, 10)
+    lib.qw4cu_ep_trace(0)
+    stage_names = ["router_logits", "route_pack", "all_gather", "local_ids_lists", "digits_x", "gate_up", "digits_act", "down",
+                   "shared_join_partial_sums", "reduce_scatter"]
+    stages_us = {n: stage_ms[i] * 1e3 / max(traced, 1) for i, n in enumerate(stage_names)}
+    barrier()
     distinct = None
     if chunks == 1:                                                                   # decode: the experts actually touched, over all ranks
         ids_local = np.stack([layer.routes()[0] for layer in layers])                 # [L, per, k]
@@ -339,6 +349,7 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
                      "frac": achieved / (hbm_peak * world), "peak_kind": peak_kind, "algorithmic_bytes": touched, "traffic": None},
         "parity": parity, "gpu_launches": int(launches),
+        "stages_us_per_chunk_layer_rank0": stages_us,
     }
     if distinct is not None:
         out["distinct_experts_per_layer"] = distinct / n_layers

@@ -295,6 +295,13 @@ Qwen4Status qw4cu_moe_ep_begin_device(const Qwen4Moe *moe, const float *x_dev, s
                                       uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work, Qwen4Error *err);
 Qwen4Status qw4cu_moe_ep_experts_device(const Qwen4Moe *moe, const float *rows_all_dev, size_t tokens_total, size_t own_first,
                                         float *partial_dev, Qwen4MoeWork *work, Qwen4Error *err);
+/* Profiling aid of qw4cu_moe_ep_forward_device.  qw4cu_ep_trace(1) makes every later step record an event at its
+ * ten stage boundaries and end with a synchronisation that adds the stage times up (0 switches it off; both clear
+ * the sums).  qw4cu_ep_trace_read copies the summed milliseconds of stages 0-9 (router logits; routing and packing;
+ * all-gather; local ids and lists; digits of x; gate/up; digits of the activations; down; shared-expert join and
+ * partial sums; reduce-scatter) and returns the number of steps summed. */
+void qw4cu_ep_trace(int on);
+uint64_t qw4cu_ep_trace_read(double *ms, int n);
 /* Router and routes only: x [tokens, hidden] -> ids, weights [tokens, k] (device pointers, either may be NULL). */
 Qwen4Status qw4cu_moe_route_device(const Qwen4Moe *moe, const float *x_dev, size_t tokens,
                                    uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work,

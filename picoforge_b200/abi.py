@@ -202,6 +202,8 @@ class MoeApi:
             "qw4cu_ep_create": ([C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_void_p), E], C.c_int),
             "qw4cu_ep_destroy": ([P], None),
             "qw4cu_ep_row_floats": ([P], C.c_size_t),
+            "qw4cu_ep_trace": ([C.c_int], None),
+            "qw4cu_ep_trace_read": ([C.POINTER(C.c_double), C.c_int], C.c_uint64),
             "qw4cu_moe_ep_forward_device": ([P, P, P, P, C.c_size_t, P, P, P, E], C.c_int),
             "qw4cu_moe_ep_begin_device": ([P, P, C.c_size_t, P, P, P, P, E], C.c_int),
             "qw4cu_moe_ep_experts_device": ([P, P, C.c_size_t, C.c_size_t, P, P, E], C.c_int),

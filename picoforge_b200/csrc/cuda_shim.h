@@ -165,6 +165,10 @@ float *qw4sh_ep_msg_all(QW4ShEp *ep);
 float *qw4sh_ep_partial_buffer(QW4ShEp *ep);
 int qw4sh_ep_all_gather(QW4ShEp *ep, size_t floats_per_rank, void *stream);
 int qw4sh_ep_reduce_scatter(QW4ShEp *ep, float *y, size_t floats_per_rank, void *stream);
+void qw4sh_ep_trace(int on);
+int qw4sh_ep_trace_mark(int index, void *stream);
+int qw4sh_ep_trace_collect(void);
+uint64_t qw4sh_ep_trace_read(double *ms, int n);
 int qw4sh_ep_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, float *msg_local, int router_mode);
 int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, const float *msg_all, size_t total, size_t own_first, size_t own,
                      uint32_t first_expert, uint32_t local_experts, float *partial);

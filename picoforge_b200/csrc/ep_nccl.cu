@@ -91,6 +91,26 @@ __global__ void __launch_bounds__(256) ep_partial_kernel(const float *__restrict
     *reinterpret_cast<float4 *>(partial + (uint64_t)t * hidden + c) = sum;
 }
 
+// The non-empty experts of the block [first, first + count) out of the ascending list of all non-empty experts
+// (active[0] entries from active[1]), as indices inside the block: active_local[0] = how many, then the indices.
+__global__ void __launch_bounds__(1024) ep_active_slice_kernel(const uint32_t *__restrict__ active, uint32_t first, uint32_t count,
+                                                               uint32_t *__restrict__ active_local) {
+    const uint32_t n = active[0];
+    __shared__ uint32_t below, inside;
+    if (threadIdx.x == 0) { below = 0; inside = 0; }
+    __syncthreads();
+    uint32_t b = 0, in = 0;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t e = active[1 + i];
+        b += e < first ? 1u : 0u;
+        in += e >= first && e - first < count ? 1u : 0u;
+    }
+    atomicAdd(&below, b); atomicAdd(&inside, in);
+    __syncthreads();
+    if (threadIdx.x == 0) active_local[0] = inside;
+    for (uint32_t i = threadIdx.x; i < inside; i += blockDim.x) active_local[1 + i] = active[1 + below + i] - first;   // ascending: the block is contiguous
+}
+
 }  // namespace qw4
 
 using namespace qw4;
@@ -112,6 +132,10 @@ extern "C" int qw4sh_ep_local_ids(const float *msg, uint32_t hidden, uint32_t k,
     ep_local_ids_kernel<<<(pairs + 255) / 256, 256, 0, (cudaStream_t)stream>>>(msg, qw4sh_ep_row_floats(hidden, k), hidden, k, pairs, experts, first,
                                                                               count, local, status);
     return qw4sh_note_launch("ep_local_ids_kernel");
+}
+extern "C" int qw4sh_ep_active_slice(const uint32_t *active, uint32_t first, uint32_t count, uint32_t *active_local, void *stream) {
+    ep_active_slice_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(active, first, count, active_local);
+    return qw4sh_note_launch("ep_active_slice_kernel");
 }
 extern "C" int qw4sh_ep_partial(const float *msg, uint32_t hidden, uint32_t k, uint32_t tokens, const uint32_t *local, const float *out,
                                 const float *shared_out, const float *shared_logit, uint32_t own_first, uint32_t own, float *partial,

@@ -437,14 +437,17 @@ __global__ void __launch_bounds__(NT, 1) grouped_mma_kernel(const GroupedArgs a)
 // 1.5 * 2^23 rounding trick (the low byte of the rounded float's bit pattern is the digit), four digits packed
 // with byte permutes, chunk sums by dp4a and three shuffles (eight consecutive lanes hold one 32-column chunk;
 // both sums travel in one register, the second in the high half).  k % 32 == 0.
-// row_list (optional): CTA b handles row row_list[b], and only CTAs below *row_count work (the rows an expert-parallel
-// rank's experts actually received, out of a launch sized for the most there can be).
+// row_list (optional): CTA b handles row row_list[*row_begin + b] (row_begin null: 0), and only while that index is
+// below *row_end (the rows an expert-parallel rank's experts actually received, out of a launch sized for the most
+// there can be).
 __global__ void __launch_bounds__(128) quantize_rows_kernel(const float *__restrict__ x, uint32_t pitch, uint32_t k, int8_t *__restrict__ xq,
                                                             int8_t *__restrict__ xneg, int *__restrict__ xsum, float *__restrict__ xscale,
-                                                            const uint32_t *__restrict__ row_list, const uint32_t *__restrict__ row_count) {
+                                                            const uint32_t *__restrict__ row_list, const uint32_t *__restrict__ row_begin,
+                                                            const uint32_t *__restrict__ row_end) {
     __shared__ float red[4];
-    if (row_list && blockIdx.x >= *row_count) return;
-    const uint32_t row = row_list ? row_list[blockIdx.x] : blockIdx.x;
+    const uint32_t listed = row_list ? (row_begin ? *row_begin : 0u) + blockIdx.x : 0u;
+    if (row_list && listed >= *row_end) return;
+    const uint32_t row = row_list ? row_list[listed] : blockIdx.x;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, items = k >> 2;
     const float4 *src = reinterpret_cast<const float4 *>(x + (uint64_t)row * pitch);
     float amax = 0.0f;
@@ -643,13 +646,14 @@ extern "C" const uint8_t *qw4sh_lut_image(void) { return lut_image(); }
 extern "C" int qw4sh_quantize_rows_pitched(const float *x, uint32_t pitch, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum,
                                            float *xscale, void *stream) {
     if (!rows) return 0;
-    quantize_rows_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale, nullptr, nullptr);
+    quantize_rows_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale, nullptr, nullptr, nullptr);
     return qw4sh_note_launch("quantize_rows_kernel");
 }
 extern "C" int qw4sh_quantize_rows_listed(const float *x, uint32_t pitch, uint32_t max_rows, uint32_t k, const uint32_t *row_list,
-                                          const uint32_t *row_count, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {
+                                          const uint32_t *row_begin, const uint32_t *row_end, int8_t *xq, int8_t *xneg, int *xsum, float *xscale,
+                                          void *stream) {
     if (!max_rows) return 0;
-    quantize_rows_kernel<<<max_rows, 128, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale, row_list, row_count);
+    quantize_rows_kernel<<<max_rows, 128, 0, (cudaStream_t)stream>>>(x, pitch, k, xq, xneg, xsum, xscale, row_list, row_begin, row_end);
     return qw4sh_note_launch("quantize_rows_kernel");
 }
 extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream) {

@@ -451,31 +451,36 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
 // separately rounded multiply and add when EXACT (the reference's order and bits,
 // src/qwen4_packed.c:164-173); outputs are independent chains, so sixteen of them interleave in
 // each thread.  Row `experts` is the shared expert's gate.
-template <bool EXACT>
+// TI x TJ outputs per thread (tokens x router rows): a CTA of 256 threads covers 16 TI tokens x 16 TJ rows.  Every
+// output is one chain of K dependent adds, so small batches need SMALL tiles: enough CTAs to fill the SMs and
+// enough warps per SM to hide the adds' latency.
+template <bool EXACT, int TI, int TJ>
 __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
-    constexpr int BM = 64, BN = 64, BK = 16;
+    constexpr int BM = 16 * TI, BN = 16 * TJ, BK = 16;
     __shared__ __align__(16) float xs[2][BK][BM + 4], ws[2][BK][BN + 4];
     const uint32_t experts = router.n_out, K = router.k_logical;
     const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
     const uint32_t t0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
-    // loader: thread -> (row tid / 4, float4 tid % 4) of each 64 x 16 tile
+    // loader: thread -> (row tid / 4, float4 tid % 4) of each (up to 64) x 16 tile
     const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4;
     const uint32_t gt = t0 + lr, ge = e0 + lr;
-    const float *xrow = gt < tokens ? x + (uint64_t)gt * K : nullptr;
-    const float *wrow = ge < experts ? (const float *)(router.data + (uint64_t)ge * router.row_bytes) : (ge == experts ? (const float *)srouter.data : nullptr);
-    float acc[4][4];
+    const bool load_x = lr < BM, load_w = lr < BN;
+    const float *xrow = load_x && gt < tokens ? x + (uint64_t)gt * K : nullptr;
+    const float *wrow = !load_w ? nullptr : ge < experts ? (const float *)(router.data + (uint64_t)ge * router.row_bytes)
+                                                          : (ge == experts ? (const float *)srouter.data : nullptr);
+    float acc[TI][TJ];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < TI; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+        for (int j = 0; j < TJ; j++) acc[i][j] = 0.0f;
     float4 xa = xrow ? *reinterpret_cast<const float4 *>(xrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 wa = wrow ? *reinterpret_cast<const float4 *>(wrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
     const uint32_t steps = K / BK;
     for (uint32_t s = 0; s < steps; s++) {
         const uint32_t b = s & 1u;
-        xs[b][lc][lr] = xa.x; xs[b][lc + 1][lr] = xa.y; xs[b][lc + 2][lr] = xa.z; xs[b][lc + 3][lr] = xa.w;
-        ws[b][lc][lr] = wa.x; ws[b][lc + 1][lr] = wa.y; ws[b][lc + 2][lr] = wa.z; ws[b][lc + 3][lr] = wa.w;
+        if (load_x) { xs[b][lc][lr] = xa.x; xs[b][lc + 1][lr] = xa.y; xs[b][lc + 2][lr] = xa.z; xs[b][lc + 3][lr] = xa.w; }
+        if (load_w) { ws[b][lc][lr] = wa.x; ws[b][lc + 1][lr] = wa.y; ws[b][lc + 2][lr] = wa.z; ws[b][lc + 3][lr] = wa.w; }
         __syncthreads();
         if (s + 1 < steps) {
             xa = xrow ? *reinterpret_cast<const float4 *>(xrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -483,22 +488,25 @@ __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevT
         }
 #pragma unroll
         for (int kk = 0; kk < BK; kk++) {
-            const float4 a4 = *reinterpret_cast<const float4 *>(&xs[b][kk][ty * 4]), b4 = *reinterpret_cast<const float4 *>(&ws[b][kk][tx * 4]);
-            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+            float av[TI], bv[TJ];
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int i = 0; i < TI; i++) av[i] = xs[b][kk][ty * TI + i];
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = EXACT ? __fadd_rn(acc[i][j], __fmul_rn(bv[j], av[i])) : fmaf(bv[j], av[i], acc[i][j]);
+            for (int j = 0; j < TJ; j++) bv[j] = ws[b][kk][tx * TJ + j];
+#pragma unroll
+            for (int i = 0; i < TI; i++)
+#pragma unroll
+                for (int j = 0; j < TJ; j++) acc[i][j] = EXACT ? __fadd_rn(acc[i][j], __fmul_rn(bv[j], av[i])) : fmaf(bv[j], av[i], acc[i][j]);
         }
     }
     bool bad = false;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t t = t0 + ty * 4 + i;
+    for (int i = 0; i < TI; i++) {
+        const uint32_t t = t0 + ty * TI + i;
         if (t >= tokens) continue;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t e = e0 + tx * 4 + j;
+        for (int j = 0; j < TJ; j++) {
+            const uint32_t e = e0 + tx * TJ + j;
             if (e > experts) continue;
             bad |= !finite_f32(acc[i][j]);
             if (e < experts) logits[(uint64_t)t * experts + e] = acc[i][j];
@@ -1267,7 +1275,7 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
                          uint32_t *status, int mode, cudaStream_t stream) {
     const DevTensor router = as_dev(layer->w[0]), srouter = as_dev(layer->w[7]);
     const uint32_t rows = layer->experts + 1;
-    if (mode == 0 && tokens > 4 && tokens <= 128 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
+    if (mode == 0 && tokens > 4 && tokens <= 16 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
                ((uintptr_t)router.data & 15u) == 0 && ((uintptr_t)srouter.data & 15u) == 0) {
         if (allow_smem(router_chain_kernel, RC_SMEM)) return -1;
         router_chain_kernel<<<dim3((rows + RC_ROWS - 1) / RC_ROWS, (unsigned)((tokens + RC_TOK - 1) / RC_TOK)), RC_THREADS, RC_SMEM, stream>>>(
@@ -1278,10 +1286,18 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (allow_smem(router_exact_small_kernel, smem)) return -1;
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
         LAUNCHED("router_exact_small_kernel");
-    } else if (tokens > 128 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {   // enough tiles to fill the GPU
-        const dim3 grid((unsigned)((tokens + 63) / 64), (rows + 63) / 64);
-        if (mode == 0) router_gemm_kernel<true><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
-        else router_gemm_kernel<false><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status);
+    } else if (tokens > 16 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
+        // tile per thread by batch size: about one CTA per SM or more at every size from 17 tokens up
+#define ROUTER_GEMM(TI, TJ) do { \
+        const dim3 grid((unsigned)((tokens + 16 * TI - 1) / (16 * TI)), (rows + 16 * TJ - 1) / (16 * TJ)); \
+        if (mode == 0) router_gemm_kernel<true, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); \
+        else router_gemm_kernel<false, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); } while (0)
+        if (tokens >= 768) ROUTER_GEMM(4, 4);
+        else if (tokens >= 384) ROUTER_GEMM(2, 4);
+        else if (tokens >= 192) ROUTER_GEMM(1, 4);
+        else if (tokens >= 96) ROUTER_GEMM(1, 2);
+        else ROUTER_GEMM(1, 1);
+#undef ROUTER_GEMM
         LAUNCHED("router_gemm_kernel");
     } else if (mode == 0) {
         if (tokens <= 1) {
@@ -1657,7 +1673,43 @@ extern "C" int qw4sh_ep_partial(const float *msg, uint32_t hidden, uint32_t k, u
                                 const float *shared_out, const float *shared_logit, uint32_t own_first, uint32_t own, float *partial,
                                 uint32_t *status, void *stream);
 extern "C" int qw4sh_quantize_rows_listed(const float *x, uint32_t pitch, uint32_t max_rows, uint32_t k, const uint32_t *row_list,
-                                          const uint32_t *row_count, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream);
+                                          const uint32_t *row_begin, const uint32_t *row_end, int8_t *xq, int8_t *xneg, int *xsum, float *xscale,
+                                          void *stream);
+extern "C" int qw4sh_ep_active_slice(const uint32_t *active, uint32_t first, uint32_t count, uint32_t *active_local, void *stream);
+
+// Per-stage timing of the expert-parallel step (profiling aid): with the trace on, an event is recorded at every
+// stage boundary and the step ends with a synchronisation that adds the stage times up.
+enum { EP_STAGES = 10 };
+static int g_ep_trace = 0;
+static cudaEvent_t g_ep_event[EP_STAGES + 1] = {nullptr};
+static double g_ep_ms[EP_STAGES] = {0};
+static uint64_t g_ep_steps = 0;
+extern "C" void qw4sh_ep_trace(int on) {
+    g_ep_trace = on ? 1 : 0;
+    for (int i = 0; i < EP_STAGES; i++) g_ep_ms[i] = 0;
+    g_ep_steps = 0;
+}
+extern "C" int qw4sh_ep_trace_mark(int index, void *stream) {
+    if (!g_ep_trace || index < 0 || index > EP_STAGES) return 0;
+    if (!g_ep_event[index]) CU(cudaEventCreate(&g_ep_event[index]));
+    CU(cudaEventRecord(g_ep_event[index], (cudaStream_t)stream));
+    return 0;
+}
+// After the last mark of a step: waits and accumulates (stage i = mark i .. mark i + 1).
+extern "C" int qw4sh_ep_trace_collect(void) {
+    if (!g_ep_trace) return 0;
+    CU(cudaEventSynchronize(g_ep_event[EP_STAGES]));
+    for (int i = 0; i < EP_STAGES; i++) {
+        float ms = 0.0f;
+        if (g_ep_event[i] && g_ep_event[i + 1] && cudaEventElapsedTime(&ms, g_ep_event[i], g_ep_event[i + 1]) == cudaSuccess) g_ep_ms[i] += ms;
+    }
+    g_ep_steps++;
+    return 0;
+}
+extern "C" uint64_t qw4sh_ep_trace_read(double *ms, int n) {
+    for (int i = 0; i < n && i < EP_STAGES; i++) ms[i] = g_ep_ms[i];
+    return g_ep_steps;
+}
 
 static bool shared_on_mma(const QW4ShLayer *layer) {
     return layer->w[4].type == layer->w[5].type && qw4sh_mma_supported(&layer->w[4], 0) && qw4sh_mma_supported(&layer->w[5], 0) &&
@@ -1712,8 +1764,13 @@ static int ep_shared_begin(const QW4ShLayer *layer, const QW4ShWork *work, const
 extern "C" int qw4sh_ep_begin(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, float *msg_local, int router_mode) {
     if (!tokens) return 0;
     int rc;
-    if ((rc = qw4sh_route_forward(layer, work, x, tokens, router_mode))) return rc;
+    if ((rc = qw4sh_ep_trace_mark(0, work->stream))) return rc;
+    if ((rc = launch_router(layer, x, tokens, work->logits, work->shared_logit, work->status, router_mode, (cudaStream_t)work->stream))) return rc;
+    if ((rc = qw4sh_ep_trace_mark(1, work->stream))) return rc;
+    if ((rc = qw4sh_route(layer->experts, layer->top_k, layer->norm, work->logits, layer->experts, tokens, work->probs, work->ids, work->weights,
+                          work->status, work->stream))) return rc;
     if ((rc = qw4sh_ep_pack_rows(x, work->ids, work->weights, (uint32_t)tokens, layer->hidden, layer->top_k, msg_local, work->stream))) return rc;
+    if ((rc = qw4sh_ep_trace_mark(2, work->stream))) return rc;
     return ep_shared_begin(layer, work, x, tokens);
 }
 
@@ -1728,40 +1785,64 @@ extern "C" int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, 
     const uint32_t T = (uint32_t)total, H = layer->hidden, k = layer->top_k, pitch = qw4sh_ep_row_floats(H, k);
     uint32_t *local = work->ids + own * k;                                  // behind this rank's own routes
     int rc;
-    if ((rc = qw4sh_ep_local_ids(msg_all, H, k, T, layer->experts, first_expert, local_experts, local, work->status, stream))) return rc;
-    if ((rc = qw4sh_group_rows(local_experts, (size_t)T * k, local, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
-                               work->status, stream))) return rc;
+    if ((rc = qw4sh_ep_trace_mark(3, stream))) return rc;                   // stage 2 was the all-gather
+    // Lists.  Small batches: the foreign ids are masked out and one CTA sorts the rest.  Large batches: the bitmap
+    // dispatch sorts ALL pairs by global expert (a token meets an expert at most once), and this rank's experts are a
+    // contiguous slice of that order: its offsets start at offsets[first_expert], its rows at row_to_pair[that].
+    const bool sliced = (size_t)T * k > 2048 && work->dispatch_scratch && first_expert + local_experts <= layer->experts;
+    const uint32_t *offsets = work->offsets, *active = work->active, *row_begin = nullptr;
+    if (sliced) {
+        if ((rc = qw4sh_ep_local_ids(msg_all, H, k, T, layer->experts, 0, layer->experts, local, work->status, stream))) return rc;   // global ids, dense
+        if ((rc = qw4sh_group_large(layer->experts, k, T, local, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                                    work->dispatch_scratch, work->status, stream))) return rc;
+        uint32_t *active_local = work->dispatch_scratch;                     // the bitmaps are dead after the placement
+        if ((rc = qw4sh_ep_active_slice(work->active, first_expert, local_experts, active_local, stream))) return rc;
+        offsets = work->offsets + first_expert; active = active_local; row_begin = offsets;
+        if ((rc = qw4sh_ep_local_ids(msg_all, H, k, T, layer->experts, first_expert, local_experts, local, work->status, stream))) return rc;
+    } else {
+        if ((rc = qw4sh_ep_local_ids(msg_all, H, k, T, layer->experts, first_expert, local_experts, local, work->status, stream))) return rc;
+        if ((rc = qw4sh_group_rows(local_experts, (size_t)T * k, local, work->offsets, work->pair_to_row, work->row_to_pair, work->active,
+                                   work->status, stream))) return rc;
+    }
     const bool mma_types = layer->w[1].type == layer->w[2].type && qw4sh_mma_supported(&layer->w[1], 0) && qw4sh_mma_supported(&layer->w[2], 0) &&
                            qw4sh_mma_supported(&layer->w[3], 1);
     const bool tiles = g_tile_path != 0 && tile_types(layer) && (g_tile_path > 0 || !mma_types || total > MMA_MAX_TOKENS);
     if (!tiles && !mma_types) return fail(cudaErrorNotSupported, "expert-parallel step needs Q4_K, IQ2_XXS or Q2_K expert tensors");
     const int ctas = sm_count();
-    const uint32_t *n_local = work->offsets + local_experts;               // rows this rank's experts received
+    const uint32_t *row_end = offsets + local_experts;                      // rows of this rank's experts: [*row_begin (or 0), *row_end)
+    if ((rc = qw4sh_ep_trace_mark(4, stream))) return rc;
     if ((rc = qw4sh_quantize_rows_pitched(msg_all, pitch, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+    if ((rc = qw4sh_ep_trace_mark(5, stream))) return rc;
     if (tiles) {
-        if ((rc = qw4sh_build_tile_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_build_tile_groups(offsets, active, work->groups, work->n_groups, stream))) return rc;
         if ((rc = qw4sh_expert_tiles(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq, work->xsum,
                                      work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, n_local, work->aq, work->aneg,
+        if ((rc = qw4sh_ep_trace_mark(6, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, row_begin, row_end, work->aq, work->aneg,
                                              work->asum, work->ascale, stream))) return rc;
+        if ((rc = qw4sh_ep_trace_mark(7, stream))) return rc;
         if ((rc = qw4sh_expert_tiles(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->asum,
                                      work->ascale, work->out, work->status, ctas, stream))) return rc;
     } else {
-        if ((rc = qw4sh_build_groups(work->offsets, work->active, work->groups, work->n_groups, stream))) return rc;
+        if ((rc = qw4sh_build_groups(offsets, active, work->groups, work->n_groups, stream))) return rc;
         if ((rc = qw4sh_grouped_mma(0, &layer->w[1], &layer->w[2], work->groups, work->n_groups, work->row_to_pair, k, work->xq, work->xneg,
                                     work->xsum, work->xscale, work->act, work->status, ctas, stream))) return rc;
-        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, n_local, work->aq, work->aneg,
+        if ((rc = qw4sh_ep_trace_mark(6, stream))) return rc;
+        if ((rc = qw4sh_quantize_rows_listed(work->act, layer->inter, T * k, layer->inter, work->row_to_pair, row_begin, row_end, work->aq, work->aneg,
                                              work->asum, work->ascale, stream))) return rc;
+        if ((rc = qw4sh_ep_trace_mark(7, stream))) return rc;
         if ((rc = qw4sh_grouped_mma(1, &layer->w[3], nullptr, work->groups, work->n_groups, work->row_to_pair, 1, work->aq, work->aneg,
                                     work->asum, work->ascale, work->out, work->status, ctas, stream))) return rc;
     }
+    if ((rc = qw4sh_ep_trace_mark(8, stream))) return rc;
     if (own) {
         cudaStream_t side; cudaEvent_t *ev;
         if ((rc = side_stream(&side, &ev))) return rc;
         CU(cudaStreamWaitEvent(stream, ev[3], 0));
     }
-    return qw4sh_ep_partial(msg_all, H, k, T, local, work->out, work->shared_out, work->shared_logit, (uint32_t)own_first, (uint32_t)own, partial,
-                            work->status, stream);
+    if ((rc = qw4sh_ep_partial(msg_all, H, k, T, local, work->out, work->shared_out, work->shared_logit, (uint32_t)own_first, (uint32_t)own, partial,
+                               work->status, stream))) return rc;
+    return qw4sh_ep_trace_mark(9, stream);                                  // stage 9 is the reduce-scatter
 }
 
 // The stream every workspace created afterwards (and every existing one, through

@@ -458,6 +458,8 @@ Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW
     *out = ep;
     return report(err, QW4_OK, "");
 }
+void qw4cu_ep_trace(int on) { qw4sh_ep_trace(on); }
+uint64_t qw4cu_ep_trace_read(double *ms, int n) { return ms ? qw4sh_ep_trace_read(ms, n) : 0; }
 void qw4cu_ep_destroy(QW4CuEp *ep) { if (ep) { qw4sh_ep_destroy(ep->shim); free(ep); } }
 size_t qw4cu_ep_row_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_row_floats((uint32_t)m->c.hidden_size, (uint32_t)m->c.top_k) : 0; }
 
@@ -505,6 +507,7 @@ Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *m, QW4CuEp *ep, const fl
     if (qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.stream)) return cuda_failure(err, "all-gather");
     TRY(qw4cu_moe_ep_experts_device(m, qw4sh_ep_msg_all(ep->shim), tokens_local * world, rank * tokens_local, qw4sh_ep_partial_buffer(ep->shim), w, err));
     if (qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.stream)) return cuda_failure(err, "reduce-scatter");
+    if (qw4sh_ep_trace_mark(10, w->d.stream) || qw4sh_ep_trace_collect()) return cuda_failure(err, "stage trace");
     return report(err, QW4_OK, "");
 }
 int qw4cu_set_stream(void *cuda_stream) { return qw4sh_set_stream(cuda_stream); }

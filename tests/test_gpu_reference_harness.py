@@ -1,0 +1,107 @@
+"""The reference's own MoE test harness (picoforge tests/test_qwen4_moe.c) built with the
+reference's MoE object left out and the CUDA library linked in its place
+(oracle/_ref/test_moe_b200, made by oracle/Makefile where the reference sources are mounted).
+The same stdin is given to that binary and to the harness built entirely from the reference
+(oracle/_ref/test_moe): the reference's code on both sides of the boundary, two libraries behind it.
+
+Bars: --route and --group outputs byte for byte; --forward ids and route weights byte for byte, y
+within 1e-3; the built-in unit and grouping tests pass; the lifecycle test runs up to the ONE
+assertion that cannot hold by design (tests/test_qwen4_moe.c:262-264 edits host weight bytes after
+create and expects the next forward to see them: the CUDA library reads weights at create, when it
+uploads them to HBM).
+"""
+import struct
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, str(Path(__file__).parent))
+import cases  # noqa: E402
+from picoforge_b200 import abi, synth  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+REF = Path(__file__).resolve().parent.parent / "oracle" / "_ref"
+OURS, THEIRS = REF / "test_moe_b200", REF / "test_moe"
+
+
+def run(binary, args, payload=b""):
+    return subprocess.run([str(binary), *args], input=payload, capture_output=True, timeout=300)
+
+
+@pytest.fixture(scope="module")
+def harness(gpu):
+    if not OURS.exists() or not THEIRS.exists():
+        pytest.skip("the reference harness has not been built (oracle/Makefile needs the reference sources)")
+    return OURS, THEIRS
+
+
+def test_built_in_tests_up_to_the_by_design_assertion(harness):
+    ours, _ = harness
+    done = run(ours, [])
+    out, err = done.stdout.decode(), done.stderr.decode()
+    assert out.count("OK") >= 2, (out, err)                 # routing and grouping suites finished
+    assert done.returncode != 0                             # the lifecycle suite stops at its weights-edited-after-create line
+    assert "QW4_NONFINITE" in err and "lifecycle_tests" in err, err
+    assert err.count("Assertion") == 1
+
+
+def test_route_stream_is_byte_identical(harness):
+    ours, theirs = harness
+    rng = np.random.default_rng(3811)
+    for (t, e, k, norm) in [(33, 512, 10, 1), (1024, 17, 5, 0), (7, 2048, 32, 1)]:
+        logits = (rng.standard_normal((t, e)) * 3).astype(np.float32)
+        logits[::5, :2] = logits[::5, :1]                   # ties
+        payload = struct.pack("<4I", t, e, k, norm) + logits.tobytes()
+        a, b = run(ours, ["--route"], payload), run(theirs, ["--route"], payload)
+        assert a.returncode == 0 and b.returncode == 0, (a.stderr, b.stderr)
+        assert a.stdout == b.stdout and len(a.stdout) == 4 + 4 * t * (e + 2 * k)
+    bad = np.zeros((2, 4), np.float32)
+    bad[1, 2] = np.nan
+    payload = struct.pack("<4I", 2, 4, 2, 1) + bad.tobytes()
+    a, b = run(ours, ["--route"], payload), run(theirs, ["--route"], payload)
+    assert a.stdout == b.stdout == struct.pack("<I", abi.NONFINITE)
+
+
+def test_group_stream_is_byte_identical(harness):
+    ours, theirs = harness
+    rng = np.random.default_rng(3812)
+    for (t, e, k) in [(3, 4, 2), (1024, 512, 10), (100, 2048, 7)]:
+        ids = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.uint32)
+        payload = struct.pack("<3I", t, e, k) + ids.tobytes()
+        a, b = run(ours, ["--group"], payload), run(theirs, ["--group"], payload)
+        assert a.returncode == 0 and b.returncode == 0, (a.stderr, b.stderr)
+        assert a.stdout == b.stdout
+    dup = struct.pack("<3I", 1, 4, 2) + np.array([[1, 1]], np.uint32).tobytes()
+    a, b = run(ours, ["--group"], dup), run(theirs, ["--group"], dup)
+    assert a.stdout == b.stdout == struct.pack("<I", abi.INVALID_ARGUMENT)
+
+
+@pytest.mark.parametrize("routed,shared,tokens", [(abi.Q4_K, abi.Q4_K, 4), (abi.IQ2_XXS, abi.Q4_K, 37), (abi.Q2_K, abi.Q2_K, 70)])
+def test_forward_stream_matches(harness, routed, shared, tokens):
+    ours, theirs = harness
+    spec = cases.small_layer(700 + routed, routed, shared, experts=16, top_k=4, hidden=512, inter=256, shared_inter=256)
+    x = synth.activations(700 + tokens, tokens, spec.hidden)
+    payload = struct.pack("<9I", spec.hidden, spec.experts, spec.top_k, spec.inter, spec.shared_inter, spec.down_physical, 1, tokens, 0)
+    for gguf_type, (k_storage, _, n_out, n_experts), data in zip(spec.types, spec.shapes(), spec.tensors):
+        payload += struct.pack("<4I", gguf_type, k_storage, n_out, n_experts) + data.tobytes()
+    payload += x.tobytes()
+    a, b = run(ours, ["--forward"], payload), run(theirs, ["--forward"], payload)
+    assert a.returncode == 0 and b.returncode == 0, (a.stderr[-400:], b.stderr[-400:])
+
+    def parse(blob):
+        marker, status, budget = struct.unpack("<3Q", blob[:24])
+        assert marker == 2**64 - 1 and status == abi.OK and budget <= 32 << 20
+        h, k = spec.hidden, spec.top_k
+        y = np.frombuffer(blob, np.float32, tokens * h, 24).reshape(tokens, h)
+        ids = np.frombuffer(blob, np.uint32, tokens * k, 24 + 4 * tokens * h).reshape(tokens, k)
+        weights = np.frombuffer(blob, np.uint32, tokens * k, 24 + 4 * tokens * (h + k)).reshape(tokens, k)
+        assert len(blob) == 24 + 4 * tokens * (h + 2 * k)
+        return y, ids, weights
+    y, ids, weights = parse(a.stdout)
+    y_ref, ids_ref, weights_ref = parse(b.stdout)
+    np.testing.assert_array_equal(ids, ids_ref)
+    np.testing.assert_array_equal(weights, weights_ref)
+    assert np.abs(y - y_ref).max() <= 1e-3
