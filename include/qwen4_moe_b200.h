@@ -211,10 +211,11 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *moe, Qwen4F32 x, Qwen4F32Mut y,
 Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *config, Qwen4U32Mut ids,
                                 QW4MoeGrouping grouping, Qwen4Error *err);
 
-/* Replaces qw4_moe_observe (src/qwen4_moe_internal.h:9-15, src/qwen4_moe.c:134-136).  When
- * set, forward copies stage buffers back and calls the observer for stage 0 (router
- * logits), 11 (routed sum) and 12 (y); the per-expert stages 1-10 are not materialised by
- * the fused kernels and are not reported. */
+/* Replaces qw4_moe_observe (src/qwen4_moe_internal.h:9-15, src/qwen4_moe.c:134-136).  While an
+ * observer is set, qwen4_moe_forward runs the layer stage by stage in the reference's order (32-token
+ * microbatches, one plain kernel per stage, sums in ascending k) instead of the fused kernels, and
+ * reports every stage the reference reports, with its stage / expert / token arguments: projections
+ * 0-7, 8 SiLU, 9 product, 10 sigmoid, 11 routed sum, 12 y.  A diagnostic path: slow by design. */
 void qw4_moe_observe(Qwen4MoeWork *work, QW4MoeObserver observer, void *ctx);
 
 /* ------------------------------------------------------------------------------------

@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "../../include/qwen4_moe_b200.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -197,6 +199,10 @@ int qw4sh_prefill_tc(int mode, const QW4ShTensor *w0, const QW4ShTensor *w1, con
                      const void *sum_lo, void *out_hi, void *out_lo, void *osum_hi, void *osum_lo, float *out, uint32_t *status,
                      int ctas, void *stream);
 
+/* The layer stage by stage in the reference's order, every stage copied back and shown to `observer`
+ * (observed_forward.cu).  The observer has the signature of QW4MoeObserver. */
+int qw4sh_observed_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens, const float *x_host,
+                           size_t x_host_pitch, size_t token0, QW4MoeObserver observer, void *ctx);
 int qw4sh_route_forward(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, size_t tokens, int router_mode);
 /* Caller-provided stream (NULL: back to the library's own).  current_stream returns the one in force. */
 int qw4sh_set_stream(void *stream);

@@ -574,7 +574,9 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
             for (size_t row = 0; row < n; row++) memcpy(pin_x + row * h, xs + row * (x.stride_bytes[0] / 4), h * 4);
             rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, pin_x, h * 4, h * 4, n, 1, w->d.stream);
         } else rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, xs, x.stride_bytes[0], h * 4, n, 1, w->d.stream);
-        if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, w->d.y, n, NULL, NULL, current_router_mode());
+        if (!rc && observe)                    /* stage by stage in the reference's order, every stage shown to the observer */
+            rc = qw4sh_observed_forward(&m->layer, &w->d, w->d.x, w->d.y, n, xs, x.stride_bytes[0] / 4, start, w->observer, w->observer_ctx);
+        else if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, w->d.y, n, NULL, NULL, current_router_mode());
         if (!rc) rc = qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream);
         if (!rc && small) {
             rc = qw4sh_memcpy2d_async(pin_y, h * 4, w->d.y, h * 4, h * 4, n, 0, w->d.stream);
@@ -605,19 +607,6 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
             }
             if (!rc) rc = qw4sh_stream_sync(w->d.stream);
             if (rc) { st = cuda_failure(err, "result copy"); break; }
-        }
-        if (observe) {                         /* stage 0: router logits; stage 12: y */
-            float *logits = malloc(n * m->c.experts * 4);
-            if (logits && !qw4sh_memcpy(logits, w->d.logits, n * m->c.experts * 4, 0)) {
-                Qwen4F32 in = x; in.data = xs; in.dim[0] = n;
-                Qwen4F32 lo = {.data = logits, .capacity_bytes = n * m->c.experts * 4, .rank = 2,
-                    .dim = {n, m->c.experts, 1, 1}, .stride_bytes = {m->c.experts * 4, 4, 0, 0}};
-                w->observer(w->observer_ctx, 0, 0, start, in, lo);
-                Qwen4F32 yo = {.data = ys, .capacity_bytes = y.capacity_bytes, .rank = 2, .dim = {n, h, 1, 1},
-                    .stride_bytes = {y.stride_bytes[0], 4, 0, 0}};
-                w->observer(w->observer_ctx, 12, SIZE_MAX, start, in, yo);
-            }
-            free(logits);
         }
     }
     w->busy = false;

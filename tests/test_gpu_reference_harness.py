@@ -105,3 +105,42 @@ def test_forward_stream_matches(harness, routed, shared, tokens):
     np.testing.assert_array_equal(ids, ids_ref)
     np.testing.assert_array_equal(weights, weights_ref)
     assert np.abs(y - y_ref).max() <= 1e-3
+
+
+def test_forward_stream_with_the_observer_reports_the_reference_stages(harness):
+    """Trace mode of the harness sets an observer (src/qwen4_moe_internal.h:9-15): both builds must emit the same
+    sequence of (stage, expert, token, shapes) records; the matrices agree to rounding (the observed path keeps
+    the reference's order of operations, so nearly all values are equal bit for bit)."""
+    ours, theirs = harness
+    spec = cases.small_layer(811, abi.Q4_K, abi.Q2_K, experts=8, top_k=3, hidden=256, inter=256, shared_inter=256)
+    tokens = 37                                              # two microbatches of the reference: 32 + 5
+    x = synth.activations(811, tokens, spec.hidden)
+    payload = struct.pack("<9I", spec.hidden, spec.experts, spec.top_k, spec.inter, spec.shared_inter, spec.down_physical, 1, tokens, 1)
+    for gguf_type, (k_storage, _, n_out, n_experts), data in zip(spec.types, spec.shapes(), spec.tensors):
+        payload += struct.pack("<4I", gguf_type, k_storage, n_out, n_experts) + data.tobytes()
+    payload += x.tobytes()
+    a, b = run(ours, ["--forward"], payload), run(theirs, ["--forward"], payload)
+    assert a.returncode == 0 and b.returncode == 0, (a.stderr[-400:], b.stderr[-400:])
+
+    def records(blob):
+        out, at = [], 0
+        while True:
+            head = struct.unpack_from("<6Q", blob, at)
+            if head[0] == 2**64 - 1:                         # the end marker of the forward proper
+                return out, blob[at:]
+            stage, expert, token, rows, cols_in, cols_out = head
+            at += 48
+            data = np.frombuffer(blob, np.float32, rows * (cols_in + cols_out), at)
+            at += 4 * rows * (cols_in + cols_out)
+            out.append(((stage, expert, token, rows, cols_in, cols_out), data))
+    mine, tail_a = records(a.stdout)
+    want, tail_b = records(b.stdout)
+    assert [r[0] for r in mine] == [r[0] for r in want]
+    assert {r[0][0] for r in mine} == set(range(13))         # every stage of the reference, 0 to 12
+    same = total = 0
+    for (_, got), (head, ref) in zip(mine, want):
+        np.testing.assert_allclose(got, ref, rtol=2e-5, atol=2e-6, err_msg=str(head))
+        same += int((got.view(np.uint32) == ref.view(np.uint32)).sum()); total += got.size
+    print(f"\n[observer] {len(mine)} records, {same} of {total} values bit-equal to the reference's")
+    assert same >= 0.999 * total
+    assert len(tail_a) == len(tail_b)
