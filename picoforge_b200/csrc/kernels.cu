@@ -451,9 +451,9 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
 // separately rounded multiply and add when EXACT (the reference's order and bits,
 // src/qwen4_packed.c:164-173); outputs are independent chains, so sixteen of them interleave in
 // each thread.  Row `experts` is the shared expert's gate.
-// TI x TJ outputs per thread (tokens x router rows): a CTA of 256 threads covers 16 TI tokens x 16 TJ rows.  Every
-// output is one chain of K dependent adds, so small batches need SMALL tiles: enough CTAs to fill the SMs and
-// enough warps per SM to hide the adds' latency.
+// TI x TJ outputs per thread (tokens x router rows): a CTA of 256 threads covers 16 TI tokens x 16 TJ rows.  The kernel
+// is bound by shared-memory reads and issue slots (two instructions per multiply-add in the exact mode), so the tile
+// per thread stays as large as the batch allows while the grid still covers the SMs.
 template <bool EXACT, int TI, int TJ>
 __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
@@ -1275,7 +1275,7 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
                          uint32_t *status, int mode, cudaStream_t stream) {
     const DevTensor router = as_dev(layer->w[0]), srouter = as_dev(layer->w[7]);
     const uint32_t rows = layer->experts + 1;
-    if (mode == 0 && tokens > 4 && tokens <= 16 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
+    if (mode == 0 && tokens > 4 && tokens <= 128 && router.k_logical % RC_K == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0 &&
                ((uintptr_t)router.data & 15u) == 0 && ((uintptr_t)srouter.data & 15u) == 0) {
         if (allow_smem(router_chain_kernel, RC_SMEM)) return -1;
         router_chain_kernel<<<dim3((rows + RC_ROWS - 1) / RC_ROWS, (unsigned)((tokens + RC_TOK - 1) / RC_TOK)), RC_THREADS, RC_SMEM, stream>>>(
@@ -1287,16 +1287,15 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
         LAUNCHED("router_exact_small_kernel");
     } else if (tokens > 16 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
-        // tile per thread by batch size: about one CTA per SM or more at every size from 17 tokens up
 #define ROUTER_GEMM(TI, TJ) do { \
         const dim3 grid((unsigned)((tokens + 16 * TI - 1) / (16 * TI)), (rows + 16 * TJ - 1) / (16 * TJ)); \
         if (mode == 0) router_gemm_kernel<true, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); \
         else router_gemm_kernel<false, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); } while (0)
+        // four tokens per thread always (one 128-bit read serves four chains); fewer router rows per thread for
+        // smaller batches, so that the grid still covers the SMs
         if (tokens >= 768) ROUTER_GEMM(4, 4);
-        else if (tokens >= 384) ROUTER_GEMM(2, 4);
-        else if (tokens >= 192) ROUTER_GEMM(1, 4);
-        else if (tokens >= 96) ROUTER_GEMM(1, 2);
-        else ROUTER_GEMM(1, 1);
+        else if (tokens >= 384) ROUTER_GEMM(4, 2);
+        else ROUTER_GEMM(4, 1);
 #undef ROUTER_GEMM
         LAUNCHED("router_gemm_kernel");
     } else if (mode == 0) {

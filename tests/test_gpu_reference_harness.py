@@ -39,13 +39,17 @@ def harness(gpu):
 
 
 def test_built_in_tests_up_to_the_by_design_assertion(harness):
-    ours, _ = harness
+    """No arguments: the harness runs its routing, grouping and lifecycle suites in that order and aborts at the first
+    assertion that does not hold.  Against the CUDA library it must get through the first two suites and through the
+    lifecycle suite up to the line that edits host weight bytes after create (its stdout is lost with the abort: the
+    place of the one failed assertion is the evidence)."""
+    ours, theirs = harness
+    assert run(theirs, []).returncode == 0                  # the all-reference build passes everything
     done = run(ours, [])
-    out, err = done.stdout.decode(), done.stderr.decode()
-    assert out.count("OK") >= 2, (out, err)                 # routing and grouping suites finished
-    assert done.returncode != 0                             # the lifecycle suite stops at its weights-edited-after-create line
-    assert "QW4_NONFINITE" in err and "lifecycle_tests" in err, err
-    assert err.count("Assertion") == 1
+    err = done.stderr.decode()
+    assert done.returncode != 0
+    assert err.count("Assertion") == 1, err
+    assert "lifecycle_tests" in err and "QW4_NONFINITE" in err, err
 
 
 def test_route_stream_is_byte_identical(harness):
