@@ -287,7 +287,8 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         for layer in layers:
             layer.sync()
 
-    for _ in range(max(1, args.ep_warmup)):
+    lib.qw4cu_set_graph_mode(0 if args.no_graph else 1)                              # per layer and chunk: captured at its second step, replayed after
+    for _ in range(max(2, args.ep_warmup)):
         step()
     sync_all()
     barrier()
@@ -302,6 +303,7 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
     launches = lib.qw4cu_launch_count() - before
     barrier()
     # one more, untimed, step with an event at every stage boundary (it synchronises per layer: a profile, not a timing)
+    lib.qw4cu_set_graph_mode(0)
     lib.qw4cu_ep_trace(1)
     step()
     stage_ms = (C.c_double * 10)()
@@ -340,7 +342,7 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         touched = distinct * expert_bytes + n_layers * world * replicated
     achieved = touched / (ms_per_step * 1e-3) / 1e9
     out = {
-        "workload": text.format(layers=n_layers), "n_gpus": world, "steps": args.ep_steps, "warmup": max(1, args.ep_warmup),
+        "workload": text.format(layers=n_layers), "n_gpus": world, "steps": args.ep_steps, "warmup": max(2, args.ep_warmup), "launch": "direct" if args.no_graph else "cuda-graph replay per layer and chunk (collectives captured)",
         "ms_per_step": ms_per_step, "us_per_token_layer": ms_per_step * 1e3 / (tokens * n_layers),
         "us_per_chunk_layer": ms_per_step * 1e3 / passes, "tokens_per_s": tokens / (ms_per_step * 1e-3), "scaling": "strong",
         "parallelism": f"expert parallel over {world} GPU(s): {epr} experts each, router and shared expert replicated, tokens data-parallel; "

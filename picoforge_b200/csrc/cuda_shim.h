@@ -25,6 +25,10 @@ typedef struct {
     uint32_t hidden, experts, top_k, inter, shared_inter, down_physical;
     int norm;
     QW4ShTensor w[8];             /* router, gate, up, down, sgate, sup, sdown, srouter */
+    /* one-kernel decode path: tensor maps (CUtensorMap, 128 bytes each) of gate, up, shared gate, shared up, made by
+     * qw4sh_fused_prepare once the images are resident; ready = 0 when the layer does not fit that path */
+    unsigned char fused_maps[4][128];
+    int fused_maps_ready;
 } QW4ShLayer;
 
 /* Device scratch of one workspace, sized for `cap` tokens. */
@@ -138,6 +142,7 @@ int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const fl
  * supported: 1 when the layer, batch and pointers fit it.  set_fused_decode: -1 automatic
  * (default), 0 never.  fused_decode launches it; phase_clocks copies CTA 0's SM clock at its
  * phase boundaries of the workspace's last launch (after a synchronise). */
+int qw4sh_fused_prepare(QW4ShLayer *layer);
 int qw4sh_fused_supported(const QW4ShLayer *layer, size_t tokens, const float *x, const float *y, int sm_count);
 void qw4sh_set_fused_decode(int mode);
 int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
@@ -167,6 +172,10 @@ float *qw4sh_ep_msg_all(QW4ShEp *ep);
 float *qw4sh_ep_partial_buffer(QW4ShEp *ep);
 int qw4sh_ep_all_gather(QW4ShEp *ep, size_t floats_per_rank, void *stream);
 int qw4sh_ep_reduce_scatter(QW4ShEp *ep, float *y, size_t floats_per_rank, void *stream);
+int qw4sh_graph_try(const QW4ShWork *work, const void *layer, const void *x, const void *y, const void *ids, const void *weights,
+                    size_t tokens, int mode);
+int qw4sh_graph_finish(const QW4ShWork *work, int enqueue_failed);
+int qw4sh_ep_trace_on(void);
 void qw4sh_ep_trace(int on);
 int qw4sh_ep_trace_mark(int index, void *stream);
 int qw4sh_ep_trace_collect(void);

@@ -39,9 +39,11 @@
 // together because each needs more than half of an SM's shared memory and the grid is the SM
 // count; every wait (mbarrier, counter) is bounded: after about a second the kernel records
 // QW4SH_ERR_STATE and leaves.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "cuda_shim.h"
 #include "formats.cuh"
@@ -198,6 +200,12 @@ __device__ __forceinline__ bool fbar_wait(uint64_t *bar, uint32_t parity, uint32
 __device__ __forceinline__ void fbulk(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(fs_u32(dst_smem)), "l"(src), "r"(bytes), "r"(fs_u32(bar)) : "memory");
+}
+// Rows [y, y + 8) of expert z, 32-bit words [x, x + box) of each, through a 3-D tensor map {words per row, rows per
+// expert, experts}: one request for the eight row pieces of a unit slice, which lie a row apart in memory.
+__device__ __forceinline__ void ftma_rows(void *dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t z, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(fs_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(fs_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void fprefetch_l2(const void *src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
@@ -495,21 +503,20 @@ template <uint32_t TYPE> struct FGeo;
 template <> struct FGeo<T_Q4_K> { static constexpr uint32_t SLICE_BLOCKS = 2, BLOCK_BYTES = 144; };      // 512 columns, 288 B per row
 template <> struct FGeo<T_IQ2_XXS> { static constexpr uint32_t SLICE_BLOCKS = 4, BLOCK_BYTES = 64; };    // 1024 columns, 256 B per row
 
-// Copies of slice `s` of a gate/up unit (8 gate rows + 8 up rows from row `row0`) into `stage`:
-// row r at r * slice bytes; IQ2_XXS also gets the unit's super-scales behind the rows.
+// Copies of slice `s` of a gate/up unit (8 gate rows + 8 up rows from row `row0` of expert `expert`) into `stage`:
+// row r at r * slice bytes; IQ2_XXS also gets the unit's super-scales behind the rows.  The eight row pieces of a
+// matrix are ONE tensor-map request (issuing a request costs the warp about a hundred cycles whatever its size).
 template <uint32_t TYPE>
-__device__ __forceinline__ void issue_unit_slice(const uint8_t *gate_mat, const uint8_t *up_mat, uint32_t n_out, uint32_t nb, uint32_t row0,
-                                              uint32_t s, uint8_t *stage, uint64_t *bar, uint32_t lane) {
-    const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
+__device__ __forceinline__ void issue_unit_slice(const CUtensorMap *gate_map, const CUtensorMap *up_map, const uint8_t *gate_mat,
+                                              const uint8_t *up_mat, uint32_t expert, uint32_t n_out, uint32_t nb, uint32_t row0, uint32_t s,
+                                              uint8_t *stage, uint64_t *bar, uint32_t lane) {
     constexpr uint32_t slice_bytes = FGeo<TYPE>::SLICE_BLOCKS * FGeo<TYPE>::BLOCK_BYTES;
     if (lane == 0) fbar_expect(bar, 16 * slice_bytes + (TYPE == T_IQ2_XXS ? 2 * 8 * nb * 2 : 0));
     __syncwarp();
-    if (lane < 16) {
-        const uint8_t *mat = lane < 8 ? gate_mat : up_mat;
-        fbulk(stage + lane * slice_bytes, mat + (row0 + (lane & 7u)) * row_bytes + s * slice_bytes, slice_bytes, bar);
-    } else if (TYPE == T_IQ2_XXS && lane < 18) {
-        const uint8_t *mat = lane == 16 ? gate_mat : up_mat;
-        fbulk(stage + 16 * slice_bytes + (lane - 16) * 8 * nb * 2, mat + n_out * nb * 64u + row0 * nb * 2u, 8 * nb * 2, bar);
+    if (lane < 2) ftma_rows(stage + lane * 8 * slice_bytes, lane ? up_map : gate_map, s * (slice_bytes / 4), row0, expert, bar);
+    else if (TYPE == T_IQ2_XXS && lane < 4) {
+        const uint8_t *mat = lane == 2 ? gate_mat : up_mat;                 // the matrix of this expert
+        fbulk(stage + 16 * slice_bytes + (lane - 2) * 8 * nb * 2, mat + n_out * nb * 64u + row0 * nb * 2u, 8 * nb * 2, bar);
     }
 }
 template <uint32_t TYPE>
@@ -958,7 +965,9 @@ __device__ __forceinline__ void chain_cta(FusedArgs &a, uint8_t *smem) {
 
 // ---- the kernel ---------------------------------------------------------------------------------
 template <uint32_t RT, uint32_t ST>
-__global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_constant__ FusedArgs args) {
+__global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_constant__ FusedArgs args, const __grid_constant__ CUtensorMap map_g,
+                                                             const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_sg,
+                                                             const __grid_constant__ CUtensorMap map_su) {
     extern __shared__ __align__(128) uint8_t smem[];
     // The arguments span several cache lines of the constant bank, and a first touch of each line
     // costs a miss that every SM takes at the same moment.  All lines are fetched at once here,
@@ -1219,11 +1228,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 const uint32_t u = g0 * 4 + ul;                                    // unit index over all sources
                 const uint32_t at = ring_count + i;
                 uint8_t *stage = ring + (at % FNS) * FSTAGE;
-                if (sh) issue_unit_slice<ST>(a.w[4].data, a.w[5].data, IS, nbh, u * 8, s, stage, &bar[at % FNS], lane);
+                if (sh) issue_unit_slice<ST>(&map_sg, &map_su, a.w[4].data, a.w[5].data, 0, IS, nbh, u * 8, s, stage, &bar[at % FNS], lane);
                 else {
                     const uint32_t v = u - gs * 4, ur = gr * 4, e = srcs[1 + v / ur].expert;
-                    issue_unit_slice<RT>(a.w[1].data + (uint64_t)e * a.w[1].expert_bytes, a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, I, nbh,
-                                         (v % ur) * 8, s, stage, &bar[at % FNS], lane);
+                    issue_unit_slice<RT>(&map_g, &map_u, a.w[1].data + (uint64_t)e * a.w[1].expert_bytes,
+                                         a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, e, I, nbh, (v % ur) * 8, s, stage, &bar[at % FNS], lane);
                 }
             };
             __syncthreads();                                                       // the keys in zs are dead: the ring may be written
@@ -1502,9 +1511,53 @@ extern "C" void qw4sh_fused_scratch_sizes(const QW4ShLayer *l, size_t *aq_bytes,
     *fast_bytes = (size_t)FTOK * ((l->experts + 1 + 3) & ~3u) * 4 + 256;
 }
 
+// ---- tensor maps of the gate / up matrices ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// {32-bit words of a row's packed payload, rows of an expert, experts}; box = one slice of eight rows.
+static int rows_map(const QW4ShTensor *t, CUtensorMap *map) {
+    static EncodeTiled encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess || !fn) return -1;
+        encode = (EncodeTiled)fn;
+    }
+    const uint32_t nb = t->k_storage >> 8;
+    const uint32_t block = t->type == T_Q4_K ? FGeo<T_Q4_K>::BLOCK_BYTES : FGeo<T_IQ2_XXS>::BLOCK_BYTES;
+    const uint32_t slice = (t->type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS) * block;
+    const cuuint64_t dims[3] = {(cuuint64_t)nb * block / 4, t->n_out, t->n_experts};
+    const cuuint64_t strides[2] = {(cuuint64_t)nb * block, t->expert_bytes};
+    const cuuint32_t box[3] = {slice / 4, 8, 1}, elem[3] = {1, 1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void *)t->data, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -2;
+}
+static bool fused_type(uint32_t type);
+// Called once the images are resident.  A layer the path cannot take simply gets no maps; 0 unless encoding failed.
+extern "C" int qw4sh_fused_prepare(QW4ShLayer *l) {
+    l->fused_maps_ready = 0;
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    const int which[4] = {1, 2, 4, 5};
+    for (int i = 0; i < 4; i++) {
+        const QW4ShTensor *t = &l->w[which[i]];
+        const uint32_t slice_blocks = t->type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS;
+        if (!fused_type(t->type) || t->k_storage % (256 * slice_blocks) || t->k_logical != t->k_storage || t->n_out % 32 ||
+            ((uintptr_t)t->data & 15u) || t->expert_bytes % 16) return 0;
+    }
+    for (int i = 0; i < 4; i++) {
+        alignas(64) CUtensorMap map;
+        if (rows_map(&l->w[which[i]], &map)) return -1;
+        memcpy(l->fused_maps[i], &map, sizeof map);
+    }
+    l->fused_maps_ready = 1;
+    return 0;
+}
+
 // Whether the one-kernel decode path covers this layer and batch.
 extern "C" int qw4sh_fused_supported(const QW4ShLayer *l, size_t tokens, const float *x, const float *y, int grid) {
-    if (g_fused_mode == 0) return 0;
+    if (g_fused_mode == 0 || !l->fused_maps_ready) return 0;
     if (!tokens || tokens > FTOK || l->top_k > FMAXK || l->experts > FMAXE || l->top_k > l->experts) return 0;
     const uint32_t H = l->hidden, I = l->inter, IS = l->shared_inter;
     if (H % 1024 || H > 4096 || I % 256 || IS % 256 || !I || !IS) return 0;
@@ -1526,7 +1579,7 @@ extern "C" int qw4sh_fused_supported(const QW4ShLayer *l, size_t tokens, const f
 }
 
 template <uint32_t RT, uint32_t ST>
-static int launch_fused(const FusedArgs &a, uint32_t smem, int grid, cudaStream_t stream) {
+static int launch_fused(const FusedArgs &a, const QW4ShLayer *layer, uint32_t smem, int grid, cudaStream_t stream) {
     static bool configured[64] = {false};                 // per device: the attribute and the residency check
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
@@ -1546,7 +1599,9 @@ static int launch_fused(const FusedArgs &a, uint32_t smem, int grid, cudaStream_
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, fused_decode_kernel<RT, ST>, a);
+    alignas(64) CUtensorMap maps[4];
+    memcpy(maps, layer->fused_maps, sizeof maps);
+    e = cudaLaunchKernelEx(&cfg, fused_decode_kernel<RT, ST>, a, maps[0], maps[1], maps[2], maps[3]);
     if (e != cudaSuccess) return (int)e;
     return qw4sh_note_launch("fused_decode_kernel");
 }
@@ -1574,6 +1629,6 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
     const uint32_t smem = p.total > c.total ? p.total : c.total;
     if (smem > 227u * 1024u - 1024u) return -4;
     cudaStream_t s = (cudaStream_t)work->stream;
-    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, smem, sm_count, s) : launch_fused<T_Q4_K, T_IQ2_XXS>(a, smem, sm_count, s);
-    return st == T_Q4_K ? launch_fused<T_IQ2_XXS, T_Q4_K>(a, smem, sm_count, s) : launch_fused<T_IQ2_XXS, T_IQ2_XXS>(a, smem, sm_count, s);
+    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_Q4_K, T_IQ2_XXS>(a, layer, smem, sm_count, s);
+    return st == T_Q4_K ? launch_fused<T_IQ2_XXS, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_IQ2_XXS, T_IQ2_XXS>(a, layer, smem, sm_count, s);
 }

@@ -1389,8 +1389,52 @@ extern "C" void qw4sh_graph_cache_destroy(void *cache) {
     delete c;
 }
 static int g_graph_mode = 0, g_stage_timing = 0;
+static unsigned long long g_capture_launches_before = 0;
 extern "C" void qw4sh_set_graph_mode(int on) { g_graph_mode = on ? 1 : 0; }
 extern "C" int qw4sh_get_graph_mode(void) { return g_graph_mode; }
+// Replay cache for a launch sequence the caller enqueues itself (the expert-parallel step).  try: 0 = enqueue
+// directly (graphs off, or first sight of this key: the direct run also settles allocations and kernel attributes),
+// 1 = an earlier capture was replayed: nothing left to do, 2 = capture has begun: enqueue, then call finish.
+extern "C" int qw4sh_graph_try(const QW4ShWork *work, const void *layer, const void *x, const void *y, const void *ids, const void *weights,
+                               size_t tokens, int mode) {
+    GraphCache *cache = (GraphCache *)work->graph_cache;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    if (!g_graph_mode || !cache) return 0;
+    const bool same = cache->layer == layer && cache->x == x && cache->y == y && cache->ids == ids && cache->weights == weights &&
+                      cache->tokens == tokens && cache->mode == mode;
+    if (same && cache->exec) {
+        if (cudaGraphLaunch(cache->exec, stream) != cudaSuccess) return fail(cudaGetLastError(), "graph launch") ? -1 : -1;
+        __sync_fetch_and_add(&g_launches, (unsigned long long)cache->seen);
+        return 1;
+    }
+    if (!same) {
+        if (cache->exec) { cudaGraphExecDestroy(cache->exec); cache->exec = nullptr; }
+        cache->layer = layer; cache->x = x; cache->y = y; cache->ids = ids; cache->weights = weights; cache->tokens = tokens; cache->mode = mode;
+        return 0;
+    }
+    g_capture_launches_before = g_launches;
+    if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { fail(cudaGetLastError(), "begin capture"); return -1; }
+    return 2;
+}
+extern "C" int qw4sh_graph_finish(const QW4ShWork *work, int enqueue_failed) {
+    GraphCache *cache = (GraphCache *)work->graph_cache;
+    cudaStream_t stream = (cudaStream_t)work->stream;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(stream, &graph);
+    cache->seen = (int)(g_launches - g_capture_launches_before);
+    g_launches = g_capture_launches_before;
+    if (enqueue_failed || e != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        cache->layer = nullptr;
+        return enqueue_failed ? -1 : fail(e, "graph capture");
+    }
+    e = cudaGraphInstantiate(&cache->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { cache->exec = nullptr; cache->layer = nullptr; return fail(e, "graph instantiate"); }
+    CU(cudaGraphLaunch(cache->exec, stream));
+    __sync_fetch_and_add(&g_launches, (unsigned long long)cache->seen);
+    return 0;
+}
 
 static cudaEvent_t g_stage_event[QW4SH_STAGES + 1] = {nullptr};
 static bool g_stage_pending = false;
@@ -1688,6 +1732,7 @@ extern "C" void qw4sh_ep_trace(int on) {
     for (int i = 0; i < EP_STAGES; i++) g_ep_ms[i] = 0;
     g_ep_steps = 0;
 }
+extern "C" int qw4sh_ep_trace_on(void) { return g_ep_trace; }
 extern "C" int qw4sh_ep_trace_mark(int index, void *stream) {
     if (!g_ep_trace || index < 0 || index > EP_STAGES) return 0;
     if (!g_ep_event[index]) CU(cudaEventCreate(&g_ep_event[index]));

@@ -216,6 +216,7 @@ static Qwen4Status create_shard(const Qwen4MoeConfig *c, const Qwen4MoeWeights *
             .k_logical = (uint32_t)l->k_logical, .n_out = (uint32_t)l->n_out, .n_experts = (uint32_t)l->n_experts,
             .row_bytes = (uint32_t)l->row_bytes, .expert_bytes = l->expert_bytes};
     }
+    if (qw4sh_fused_prepare(&m->layer)) { release(m); return cuda_failure(err, "tensor maps"); }
     *out = m;
     return report(err, QW4_OK, "");
 }
@@ -503,10 +504,19 @@ Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *m, QW4CuEp *ep, const fl
     if (!tokens_local) return report(err, QW4_OK, "");
     const uint32_t h = (uint32_t)m->c.hidden_size, k = (uint32_t)m->c.top_k;
     if (qw4sh_ep_reserve(ep->shim, h, k, tokens_local)) return cuda_failure(err, "exchange buffers");
-    TRY(qw4cu_moe_ep_begin_device(m, x_dev, tokens_local, qw4sh_ep_msg_local(ep->shim), ids_dev, weights_dev, w, err));
-    if (qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.stream)) return cuda_failure(err, "all-gather");
-    TRY(qw4cu_moe_ep_experts_device(m, qw4sh_ep_msg_all(ep->shim), tokens_local * world, rank * tokens_local, qw4sh_ep_partial_buffer(ep->shim), w, err));
-    if (qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.stream)) return cuda_failure(err, "reduce-scatter");
+    TRY(piece_checks(m, w, tokens_local, err));
+    /* graph mode: the second identical step on this workspace is captured (collectives included), later ones replay it */
+    const int graph = qw4sh_ep_trace_on() ? 0 : qw4sh_graph_try(&w->d, ep, x_dev, y_dev, ids_dev, weights_dev, tokens_local, 1000 + (int)world);
+    if (graph < 0) return cuda_failure(err, "graph replay");
+    if (graph == 1) return report(err, QW4_OK, "");
+    Qwen4Status st = qw4cu_moe_ep_begin_device(m, x_dev, tokens_local, qw4sh_ep_msg_local(ep->shim), ids_dev, weights_dev, w, err);
+    if (st == QW4_OK && qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.stream)) st = cuda_failure(err, "all-gather");
+    if (st == QW4_OK)
+        st = qw4cu_moe_ep_experts_device(m, qw4sh_ep_msg_all(ep->shim), tokens_local * world, rank * tokens_local,
+                                         qw4sh_ep_partial_buffer(ep->shim), w, err);
+    if (st == QW4_OK && qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.stream)) st = cuda_failure(err, "reduce-scatter");
+    if (graph == 2 && qw4sh_graph_finish(&w->d, st != QW4_OK) && st == QW4_OK) st = cuda_failure(err, "graph capture");
+    if (st != QW4_OK) return st;
     if (qw4sh_ep_trace_mark(10, w->d.stream) || qw4sh_ep_trace_collect()) return cuda_failure(err, "stage trace");
     return report(err, QW4_OK, "");
 }
