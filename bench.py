@@ -435,6 +435,14 @@ def main():
         sharded_names, headline = [args.workload], None
     else:
         headline = decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind)
+        if not args.profile and args.workload == "c1" and world == 1:
+            # the single-token figure rides on the same line (five regions are enough for a side figure; no CPU pass)
+            import copy
+            side = copy.copy(args)
+            side.workload, side.repeats, side.cpu_seconds = "c0", 5, 0.0
+            c0 = decode_line(side, api, rank, local_rank, world, control, hbm_peak, peak_kind)
+            headline["c0"] = {"workload": c0["config"]["workload"], "us_per_layer": c0["ms_per_step"] * 1e3, "roofline": c0["roofline"],
+                              "e2e": c0["e2e"], "timing": c0["timing"], "gpu_launches": c0["gpu_launches"]}
     if args.profile:
         return
     sharded = {}
@@ -593,6 +601,8 @@ def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind
     barrier()
     e2e_us_per_token = e2e_seconds / e2e_steps * 1e6 / (tokens * world)
 
+    clocks16 = (C.c_uint64 * 16)()
+    lib.qw4cu_decode_phase_clocks(layers[(args.steps - 1) % len(layers)].work, clocks16)
     for layer in layers:
         layer.close()
     for pointer in [x_dev] + y_dev:
@@ -602,7 +612,7 @@ def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------------
     cpu = None
-    if world == 1:
+    if world == 1 and args.cpu_seconds > 0:
         guess = 0.6 * tokens / max(1, min(tokens, len(os.sched_getaffinity(0))))
         repeats = max(1, int(args.cpu_seconds / max(guess, 1e-3)))
         seconds, threads, kind = cpu_reference_step(specs, x, repeats, 1)
@@ -619,8 +629,6 @@ def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind
         # bytes are every weight byte the step must read once.
         dominant = "fused_decode_kernel"
         kernel_us, kernel_bytes = ms_per_step * 1e3, layer_bytes
-        clocks16 = (C.c_uint64 * 16)()
-        lib.qw4cu_decode_phase_clocks(layers[(args.steps - 1) % len(layers)].work, clocks16)
         ticks = [int(v) for v in clocks16[:13]]
         names = ["stage_x", "fast_logits", "digitise_x", "barrier_1", "speculate_sets", "list_experts", "gate_up_slices",
                  "store_digits", "barrier_2_and_routes", "verify_routes", "load_act_digits", "down_combine"]

@@ -419,6 +419,40 @@ Qwen4Status qw4cu_group_pairs_device_noalloc(uint32_t experts, uint32_t top_k, s
                                              uint32_t *pair_to_row_dev, uint32_t *row_to_pair_dev,
                                              Qwen4Error *err);
 
+/* ------------------------------------------------------------------------------------
+ * One layer's MoE tensors straight from a GGUF v3 file (csrc/gguf_slice.c).
+ *
+ * picoforge reaches them through its model-wide loader: container parse src/gguf.c:31-106,
+ * role table src/qwen4_weights.c:91-99, packed layouts src/qwen4_packed.c:8-32, dimensions
+ * src/qwen4_config.c:170-172,200-211; its harness prints the same facts with --describe
+ * (tests/test_qwen4_moe.c:376-396).  Tensor order everywhere below: router, gate, up, down,
+ * shared gate, shared up, shared down, shared router (the order of Qwen4MoeWeights).
+ * Names: blk.<layer>.ffn_gate_inp / ffn_{gate,up,down}_exps / ffn_{gate,up,down}_shexp /
+ * ffn_gate_inp_shexp (.weight); keys: qwen4exp.embedding_length, .expert_count,
+ * .expert_used_count, .expert_feed_forward_length, .expert_shared_feed_forward_length and the
+ * optional ds4.qwen4.down.{logical,physical}_input.  A malformed file yields a status
+ * (QW4_IO, QW4_FORMAT, QW4_MISSING, QW4_TYPE, QW4_SHAPE, QW4_UNSUPPORTED), never an abort.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+    char name[128];
+    uint32_t type, rank;                   /* GGUF tensor type id; 1..3 dimensions */
+    uint64_t shape[4];                     /* shape[0] is the contiguous (K) axis */
+    uint64_t file_offset, bytes;           /* absolute offset of the payload in the file */
+} QW4CuGgufTensor;
+
+typedef struct {
+    Qwen4MoeConfig config;                 /* trunk_type = the gate / up / down types of THIS layer */
+    QW4CuGgufTensor tensor[8];
+    QW4PackedLayout layout[8];
+    uint64_t data_offset, file_bytes;
+} QW4CuGgufSlice;
+
+/* Header walk only: no payload byte is read and no device is touched. */
+Qwen4Status qw4cu_gguf_slice_describe(const char *path, uint32_t layer, QW4CuGgufSlice *out, Qwen4Error *err);
+/* describe + qwen4_moe_create on a read-only mapping of the file, released before returning (the resident
+ * image is the only copy afterwards).  `slice` may be NULL. */
+Qwen4Status qw4cu_moe_create_from_gguf(const char *path, uint32_t layer, Qwen4Moe **out, QW4CuGgufSlice *slice, Qwen4Error *err);
+
 /* Raw device memory and transfers for callers that keep activations in HBM. */
 void *qw4cu_malloc(size_t bytes);
 void qw4cu_free(void *device_pointer);

@@ -75,6 +75,16 @@ class QW4PackedCpuView(C.Structure):
     _fields_ = [("span", Qwen4CpuSpan), ("layout", QW4PackedLayout)]
 
 
+class QW4CuGgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("type", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_uint64 * 4),
+                ("file_offset", C.c_uint64), ("bytes", C.c_uint64)]
+
+
+class QW4CuGgufSlice(C.Structure):
+    _fields_ = [("config", Qwen4MoeConfig), ("tensor", QW4CuGgufTensor * 8), ("layout", QW4PackedLayout * 8),
+                ("data_offset", C.c_uint64), ("file_bytes", C.c_uint64)]
+
+
 class Qwen4MoeWeights(C.Structure):
     _fields_ = [(name, QW4PackedCpuView) for name in
                 ("router", "gate", "up", "down", "shared_gate", "shared_up", "shared_down",
@@ -238,6 +248,8 @@ class MoeApi:
             "qw4cu_download": ([P, P, C.c_size_t], C.c_int),
             "qw4cu_flush_l2": ([], C.c_int),
             "qw4cu_mem_info": ([C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)], C.c_int),
+            "qw4cu_gguf_slice_describe": ([C.c_char_p, C.c_uint32, C.POINTER(QW4CuGgufSlice), C.POINTER(Qwen4Error)], C.c_int),
+            "qw4cu_moe_create_from_gguf": ([C.c_char_p, C.c_uint32, C.POINTER(P), C.POINTER(QW4CuGgufSlice), C.POINTER(Qwen4Error)], C.c_int),
             "qw4cu_device_synchronize": ([], C.c_int),
         }
         for name, (argtypes, restype) in sig.items():

@@ -48,10 +48,12 @@ def build_product(force: bool = False) -> Path:
         if force or _stale(obj, [src] + headers):
             _run([NVCC, *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-c", src, "-o", obj])
         objects.append(obj)
-    host_obj = build_dir / "moe_host.o"
-    if force or _stale(host_obj, [host] + headers):
-        _run([GCC, "-std=c11", "-O2", "-fPIC", "-Wall", "-Wextra", "-fvisibility=default", "-c", host, "-o", host_obj])
-    objects.append(host_obj)
+    for host in (host, CSRC / "gguf_slice.c"):
+        host_obj = build_dir / (host.stem + ".o")
+        if force or _stale(host_obj, [host] + headers):
+            _run([GCC, "-std=c11", "-O2", "-fPIC", "-Wall", "-Wextra", "-fvisibility=default", "-D_DEFAULT_SOURCE", f"-I{ROOT / 'include'}",
+                  "-c", host, "-o", host_obj])
+        objects.append(host_obj)
     if force or _stale(out, objects):
         _run([NVCC, *ARCH, "-shared", "-Xlinker", "-Bsymbolic", "-o", out, *objects, "-lm"])
     return out

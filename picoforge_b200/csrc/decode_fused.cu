@@ -220,10 +220,6 @@ __device__ __forceinline__ void fred_release(uint32_t *p) {
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }
 __device__ __forceinline__ void fmma_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-#ifdef QW4_X_NOMMA
-    c[0] = (int)(a0 ^ b0); c[1] = (int)(a1 ^ b1); c[2] = (int)(a2 + b0); c[3] = (int)(a3 + b1);
-    return;
-#endif
     asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
@@ -413,10 +409,6 @@ __device__ __forceinline__ void build_iq2_tables(uint8_t *lut) {
 // lane's rotate counts that bring its index byte / sign field to bit 7, where the tables' 128-byte
 // entry pitch wants them.
 __device__ __forceinline__ void iq2_weights(const uint2 g, uint32_t grid, uint32_t sign, uint32_t rg, uint32_t rs, uint32_t &lo, uint32_t &hi) {
-#ifdef QW4_X_NOLUT
-    lo = __funnelshift_r(g.x, g.x, rg) & 0x7f80u; hi = __funnelshift_r(g.y, g.y, rs) & 0x3f80u;
-    return;
-#endif
     const uint4 v = lds_table4(grid + (__funnelshift_r(g.x, g.x, rg) & 0x7f80u));
     const uint2 sel = lds_table2(sign + (__funnelshift_r(g.y, g.y, rs) & 0x3f80u));
     lo = __byte_perm(v.x, v.z, sel.x);
@@ -1135,9 +1127,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     CLOCK(3);
     if (!wait_counter(a.sync + S_FAST, NS, a.status, misc_u)) return;
     CLOCK(4);
-#ifndef QW4_X_WAITS
     MARK(0);
-#endif
 
     // ================================ phase B ================================
     float *zs = reinterpret_cast<float *>(region + p.zs);
@@ -1163,9 +1153,6 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     bool lists_ok = misc_u[1] != 0 && all_alive;
     CLOCK(5);
 
-#ifdef QW4_X_WAITS
-    long long x_waited = 0, x_consumed = 0, x_issued = 0;
-#endif
     uint32_t ring_count = 0;                                                   // slices this warp has pushed through its ring
     uint64_t *bar = ringbar + warp * FNS;
     uint32_t n_src = 0;
@@ -1254,44 +1241,22 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 uint32_t ul, s; bool sh;
                 locate(warp + i * FW, ul, s, sh);
                 const uint32_t at = ring_count + i;
-#ifdef QW4_X_WAITS
-                const long long w_begin = clock64();
-#endif
                 if (alive) alive = fbar_wait(&bar[at % FNS], (at / FNS) & 1u, a.status);
                 alive = __all_sync(0xffffffffu, alive);
-#ifdef QW4_X_WAITS
-                x_waited += clock64() - w_begin;
-#endif
                 const uint8_t *stage = ring + (at % FNS) * FSTAGE;
                 float f0 = 0.0f, f1 = 0.0f;
-#ifdef QW4_X_WAITS
-                const long long c_begin = clock64();
-#endif
                 if (alive) {
                     if (sh) consume_unit_slice<ST>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
                     else consume_unit_slice<RT>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
                 }
                 partial[(warp + i * FW) * 32 + lane] = make_float2(f0, f1);
                 __syncwarp();
-#ifdef QW4_X_WAITS
-                const long long i_begin = clock64();
-                x_consumed += i_begin - c_begin;
-#endif
                 fproxy_fence();
                 if (alive && i + FNS < mine) issue(i + FNS);
-#ifdef QW4_X_WAITS
-                x_issued += clock64() - i_begin;
-#endif
             }
             if (alive) ring_count += mine;
-#ifdef QW4_X_WAITS
-            if (tid == 32) { a.sync[S_MARKS + 4 * blockIdx.x + 0] = (uint32_t)x_waited; a.sync[S_MARKS + 4 * blockIdx.x + 2] = mine;
-                             a.sync[S_MARKS + 4 * blockIdx.x + 1] = (uint32_t)x_consumed; a.sync[S_MARKS + 4 * blockIdx.x + 3] = (uint32_t)x_issued; }
-#endif
             CLOCK(7);
-#ifndef QW4_X_WAITS
             MARK(1);
-#endif
             __syncthreads();
             // granules: slices added in order, SwiGLU, digit pairs with one scale per chunk
 #pragma unroll 1
@@ -1345,9 +1310,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         if (attempt == 1) break;
         if (!wait_counter(a.sync + S_ROUTED, T, a.status, misc_u)) return;
         CLOCK(9);
-#ifndef QW4_X_WAITS
         MARK(2);
-#endif
         if (fld_acquire(a.sync + S_ROUTE_FAIL)) { leave(); return; }             // a nonfinite logit: y stays untouched
         // ---- the exact routes against the speculation ----
         if (tid < pairs) { ids_x[tid] = __ldcg(a.ids + tid); wts_x[tid] = __ldcg(a.weights + tid); }
@@ -1450,9 +1413,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         }
     }
     CLOCK(12);
-#ifndef QW4_X_WAITS
     MARK(3);
-#endif
     leave();
 #undef CLOCK
 #undef MARK

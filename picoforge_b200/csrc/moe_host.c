@@ -221,6 +221,12 @@ static Qwen4Status create_shard(const Qwen4MoeConfig *c, const Qwen4MoeWeights *
     return report(err, QW4_OK, "");
 }
 
+/* For a creator that owned the host bytes only for the duration of create (the GGUF slice reader): the handle
+ * stops remembering their addresses. */
+void qw4cu_moe_forget_host_weights(Qwen4Moe *m) {
+    if (m) for (size_t a = 0; a < 8; a++) m->host[a].span = (Qwen4CpuSpan){NULL, 0};
+}
+
 Qwen4Status qwen4_moe_create(const Qwen4MoeConfig *c, const Qwen4MoeWeights *weights, Qwen4Moe **out, Qwen4Error *err) {
     return create_shard(c, weights, 0, c ? c->experts : 0, out, err);
 }
@@ -555,6 +561,7 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
     }
     TRY(all_apart(spans, ns, err));
     for (size_t a = 0; a < 8; a++) {
+        if (!m->host[a].span.data) continue;                        /* created from a file: no host bytes are borrowed */
         const Span weights = {(uintptr_t)m->host[a].span.data, (uintptr_t)m->host[a].span.data + m->host[a].layout.tensor_bytes};
         for (size_t b = 0; b < ns; b++)
             if (spans_meet(spans[b], weights)) return raise(err, QW4_INVALID_ARGUMENT, "argument %zu overlaps weight tensor %zu", b, a);

@@ -75,16 +75,20 @@ class LayerSpec:
 
 
 class MoeLayer:
-    def __init__(self, api: abi.MoeApi, spec: LayerSpec, token_cap: int):
+    def __init__(self, api: abi.MoeApi, spec: LayerSpec, token_cap: int, moe=None):
+        """`moe`: an existing handle (e.g. from qw4cu_moe_create_from_gguf) that this object takes over."""
         self.api, self.spec, self.token_cap = api, spec, token_cap
         self.moe = C.c_void_p()
         self.work = C.c_void_p()
         err = abi.Qwen4Error()
-        cfg, weights = spec.config(), spec.weights()
-        if spec.sharded:
+        if moe is not None:
+            self.moe, st = moe, 0
+        elif spec.sharded:
+            cfg, weights = spec.config(), spec.weights()
             st = api.lib.qw4cu_moe_create_sharded(C.byref(cfg), C.byref(weights), spec.first_expert, spec.local_experts,
                                                   C.byref(self.moe), C.byref(err))
         else:
+            cfg, weights = spec.config(), spec.weights()
             st = api.lib.qwen4_moe_create(C.byref(cfg), C.byref(weights), C.byref(self.moe), C.byref(err))
         if st:
             raise abi.MoeError(st, err)

@@ -74,16 +74,18 @@ def normal(seed: int, stream: int, rows: int, k: int, sigma: float = 1.0) -> np.
 def make_layer(seed: int, layer: int = 0, routed_type: int = abi.Q4_K, shared_type: int = abi.Q4_K,
                hidden: int = 2048, experts: int = 512, top_k: int = 10, inter: int = 512,
                shared_inter: int = 512, down_type: int | None = None, norm: bool = True,
-               shard: tuple | None = None, fabricated: bool = False, reuse: LayerSpec | None = None) -> LayerSpec:
+               shard: tuple | None = None, fabricated: bool = False, reuse: LayerSpec | None = None,
+               down_physical: int | None = None) -> LayerSpec:
     """One synthetic layer.  Stream ids: layer * 8 + tensor index.  shard = (first_expert,
     local_experts) generates only that slice of the routed expert tensors.  fabricated: the
     quantised tensors are random valid blocks with scales set for a spread of about 0.02 (as the
     reference's kernel tests make theirs) instead of encoded Gaussians: some twenty times
     faster to make, for stacks of many layers.  reuse: a spec of the same shapes whose arrays are
-    overwritten and returned in the new spec (the old spec must not be used afterwards)."""
+    overwritten and returned in the new spec (the old spec must not be used afterwards).
+    down_physical: stored K of the routed down projection when it is padded beyond `inter`."""
     down_type = routed_type if down_type is None else down_type
     types = (abi.F32, routed_type, routed_type, down_type, shared_type, shared_type, shared_type, abi.F32)
-    spec = LayerSpec(hidden, experts, top_k, inter, shared_inter, inter, norm, types)
+    spec = LayerSpec(hidden, experts, top_k, inter, shared_inter, down_physical or inter, norm, types)
     if shard is not None:
         spec.first_expert, spec.local_experts = shard
     tensors = []
