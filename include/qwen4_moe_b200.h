@@ -247,6 +247,19 @@ size_t qw4cu_moe_work_device_bytes(const Qwen4MoeWork *work);
 Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *moe, const float *x_dev, float *y_dev,
                                      size_t tokens, uint32_t *ids_dev, float *weights_dev,
                                      Qwen4MoeWork *work, Qwen4Error *err);
+
+/* The same forward followed by the hyper-connection add of its caller, inside the kernel that writes y:
+ *     residual_dev[t, h, c] += inject_dev[t, h] * y[t, c]        for h < streams
+ * with the product and the sum rounded separately (picoforge src/qwen4_base.c:160-176; its forward graph calls
+ * qwen4_hc_add right after the layer, src/qwen4_forward.c:365-367, and its GPU path fuses the add into the down
+ * epilogue, src/qwen4_moe_internal.h:55-58).  residual_dev [tokens, streams, hidden] and inject_dev
+ * [tokens, streams] are dense FP32 in HBM and must not overlap x, y or each other; y_dev is written as usual.
+ * tokens <= 2048.  A nonfinite residual is reported like a nonfinite y, by qw4cu_moe_work_sync.  The one-kernel
+ * decode path and the tensor-core paths apply the add where they write y; the CUDA-core fallback kernels run it
+ * as one more launch. */
+Qwen4Status qw4cu_moe_forward_hc_add_device(const Qwen4Moe *moe, const float *x_dev, float *y_dev, size_t tokens,
+                                            float *residual_dev, const float *inject_dev, size_t streams,
+                                            Qwen4MoeWork *work, Qwen4Error *err);
 /* Waits for the workspace's stream, converts the device error word (bit 1 nonfinite, bit 2
  * bounds, bit 4 state) into a status and latches the workspace on failure. */
 Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);

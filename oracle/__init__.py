@@ -133,6 +133,45 @@ def forward(spec, x: np.ndarray, threads: int = 1):
     return {"y": y, "ids": ids, "weights": weights, "logits": logits, "routed": routed}
 
 
+def hc_add(residual: np.ndarray, block: np.ndarray, inject: np.ndarray) -> np.ndarray:
+    """The hyper-connection add that follows the layer (picoforge src/qwen4_base.c:160-176):
+    residual[t, h, :] + inject[t, h] * block[t, :], product and sum each rounded to FP32 (NumPy's
+    float32 multiply and add round once each and never fuse).  Returns the new residual."""
+    r, y, g = (np.asarray(a, np.float32) for a in (residual, block, inject))
+    assert r.ndim == 3 and y.shape == (r.shape[0], r.shape[2]) and g.shape == r.shape[:2]
+    out = r + g[:, :, None] * y[:, None, :]
+    assert out.dtype == np.float32
+    return out
+
+
+def reference_hc_add(residual: np.ndarray, block: np.ndarray, inject: np.ndarray) -> np.ndarray:
+    """qwen4_hc_add of the reference's own objects on copies of the arguments."""
+    from picoforge_b200 import abi
+
+    class Shape(C.Structure):
+        _fields_ = [("streams", C.c_size_t), ("hidden_size", C.c_size_t), ("low_rank", C.c_size_t), ("rms_eps", C.c_float)]
+
+    class View(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("capacity_bytes", C.c_size_t), ("rank", C.c_size_t), ("dim", C.c_size_t * 4),
+                    ("stride_bytes", C.c_size_t * 4)]
+
+    def view(a):
+        strides = list(a.strides) + [0] * (4 - a.ndim)
+        dims = list(a.shape) + [0] * (4 - a.ndim)
+        return View(a.ctypes.data, a.nbytes, a.ndim, (C.c_size_t * 4)(*dims), (C.c_size_t * 4)(*strides))
+
+    lib = C.CDLL(str(REFERENCE_LIBRARY))
+    r = np.ascontiguousarray(residual, np.float32).copy()
+    y, g = np.ascontiguousarray(block, np.float32), np.ascontiguousarray(inject, np.float32)
+    shape = Shape(r.shape[1], r.shape[2], 1, 1e-6)
+    err = abi.Qwen4Error()
+    lib.qwen4_hc_add.argtypes = [C.POINTER(Shape), View, View, View, C.POINTER(abi.Qwen4Error)]
+    status = lib.qwen4_hc_add(C.byref(shape), view(r), view(y), view(g), C.byref(err))
+    if status:
+        raise OracleError(status)
+    return r
+
+
 def reference_available() -> bool:
     return REFERENCE_LIBRARY.exists()
 

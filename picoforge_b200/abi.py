@@ -247,6 +247,7 @@ class MoeApi:
             "qw4cu_upload": ([P, P, C.c_size_t], C.c_int),
             "qw4cu_download": ([P, P, C.c_size_t], C.c_int),
             "qw4cu_flush_l2": ([], C.c_int),
+            "qw4cu_moe_forward_hc_add_device": ([P, P, P, C.c_size_t, P, P, C.c_size_t, P, C.POINTER(Qwen4Error)], C.c_int),
             "qw4cu_mem_info": ([C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)], C.c_int),
             "qw4cu_gguf_slice_describe": ([C.c_char_p, C.c_uint32, C.POINTER(QW4CuGgufSlice), C.POINTER(Qwen4Error)], C.c_int),
             "qw4cu_moe_create_from_gguf": ([C.c_char_p, C.c_uint32, C.POINTER(P), C.POINTER(QW4CuGgufSlice), C.POINTER(Qwen4Error)], C.c_int),

@@ -66,6 +66,11 @@ typedef struct {
     void *stream;                 /* cudaStream_t: the library's one stream on this device */
     void *timer[2];               /* cudaEvent_t */
     void *graph_cache;            /* replay cache of the launch sequence (qw4sh_graph_cache_create) */
+    /* hyper-connection add fused into whichever kernel writes y (set per call, NULL otherwise):
+     * residual [tokens, streams, hidden] += inject [tokens, streams] * y, multiply and add rounded separately */
+    float *hc_residual;
+    const float *hc_inject;
+    uint32_t hc_streams;
 } QW4ShWork;
 
 enum { QW4SH_ERR_NONFINITE = 1u, QW4SH_ERR_BOUNDS = 2u, QW4SH_ERR_STATE = 4u };

@@ -89,6 +89,7 @@ struct FusedArgs {
     uint32_t partial_slices;                    // capacity of the partial-sum buffer (slices per CTA)
     uint32_t chain_ctas;                        // NC
     long long t0;                               // (device side) this CTA's clock at its start
+    HcAdd hc;                                   // hyper-connection add applied where y is written (residual nullptr: none)
 };
 
 // One distinct source of phase C / one expert of phase B.
@@ -1407,6 +1408,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 if (tt < T && alive) {
                     if (!finite_f32(sum)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
                     a.y[(uint64_t)tt * H + tile * 16 + hi * 8 + gg] = sum;
+                    if (!hc_add(a.hc, tt, tile * 16 + hi * 8 + gg, H, sum)) atomicOr(a.status, QW4SH_ERR_NONFINITE);
                 }
             }
             __syncthreads();
@@ -1573,6 +1575,7 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
     FusedArgs a;
     for (int i = 0; i < 8; i++) a.w[i] = fdev(layer->w[i]);
     a.x = x; a.y = y;
+    a.hc = HcAdd{work->hc_residual, work->hc_inject, work->hc_streams};
     a.tokens = (uint32_t)tokens; a.hidden = layer->hidden; a.experts = layer->experts; a.top_k = layer->top_k;
     a.inter = layer->inter; a.shared_inter = layer->shared_inter; a.norm = layer->norm; a.router_mode = router_mode == 0 && g_wrong_speculation ? 2 : router_mode;
     a.logits = work->logits; a.shared_logit = work->shared_logit; a.ids = work->ids; a.weights = work->weights;

@@ -524,7 +524,7 @@ __global__ void build_lut_kernel(uint8_t *lut) {
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ out, const float *__restrict__ shared_out,
                                                       const float *__restrict__ weights, const float *__restrict__ shared_logit,
                                                       uint32_t k, uint32_t hidden, float *__restrict__ y, float *__restrict__ routed,
-                                                      uint32_t *status) {
+                                                      uint32_t *status, HcAdd hc) {
     const uint32_t t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
     if (c >= hidden) return;
     float sum = 0.0f;
@@ -536,6 +536,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
         atomicOr(status, QW4SH_ERR_NONFINITE);
     if (routed) routed[(uint64_t)t * hidden + c] = sum;
     y[(uint64_t)t * hidden + c] = total;
+    if (!hc_add(hc, t, c, hidden, total)) atomicOr(status, QW4SH_ERR_NONFINITE);
 }
 
 // Groups of at most four rows out of the expert-sorted lists.
@@ -660,8 +661,10 @@ extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, in
     return qw4sh_quantize_rows_pitched(x, k, rows, k, xq, xneg, xsum, xscale, stream);
 }
 extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,
-                             uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, void *stream) {
-    combine_kernel<<<dim3((hidden + 255) / 256, tokens), 256, 0, (cudaStream_t)stream>>>(out, shared_out, weights, shared_logit, k, hidden, y, routed, status);
+                             uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, float *hc_residual,
+                             const float *hc_inject, uint32_t hc_streams, void *stream) {
+    const HcAdd hc = {hc_residual, hc_inject, hc_streams};
+    combine_kernel<<<dim3((hidden + 255) / 256, tokens), 256, 0, (cudaStream_t)stream>>>(out, shared_out, weights, shared_logit, k, hidden, y, routed, status, hc);
     return qw4sh_note_launch("combine_kernel");
 }
 extern "C" int qw4sh_build_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream) {

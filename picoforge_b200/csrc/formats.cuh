@@ -119,4 +119,25 @@ __device__ inline float decode_value(const DevTensor &t, uint32_t expert, uint32
     }
 }
 
+// The hyper-connection add that follows the layer (picoforge src/qwen4_base.c:160-176, fused into the down
+// epilogue by the reference's GPU path, src/qwen4_moe_internal.h:55-58): for each of the `streams` residual
+// streams, residual[t, h, c] += inject[t, h] * y[t, c], the product and the sum rounded separately.  Called by
+// whichever thread writes y[t, c]; returns false when a result is not finite.
+struct HcAdd {
+    float *residual;                    // [tokens, streams, hidden]; nullptr: no add
+    const float *inject;                // [tokens, streams]
+    uint32_t streams;
+};
+__device__ __forceinline__ bool hc_add(const HcAdd &hc, uint32_t t, uint32_t c, uint32_t hidden, float y) {
+    if (!hc.residual) return true;
+    bool ok = true;
+    for (uint32_t h = 0; h < hc.streams; h++) {
+        float *at = hc.residual + ((uint64_t)t * hc.streams + h) * hidden + c;
+        const float r = __fadd_rn(*at, __fmul_rn(hc.inject[(uint64_t)t * hc.streams + h], y));
+        ok &= (__float_as_uint(r) & 0x7f800000u) != 0x7f800000u;
+        *at = r;
+    }
+    return ok;
+}
+
 }  // namespace qw4

@@ -1555,7 +1555,8 @@ extern "C" int qw4sh_grouped_mma(int mode, const QW4ShTensor *w0, const QW4ShTen
                                  const int *sums, const float *scale, float *out, uint32_t *status, int ctas, void *stream);
 extern "C" int qw4sh_quantize_rows(const float *x, uint32_t rows, uint32_t k, int8_t *xq, int8_t *xneg, int *xsum, float *xscale, void *stream);
 extern "C" int qw4sh_combine(const float *out, const float *shared_out, const float *weights, const float *shared_logit, uint32_t k,
-                             uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, void *stream);
+                             uint32_t hidden, uint32_t tokens, float *y, float *routed, uint32_t *status, float *hc_residual,
+                             const float *hc_inject, uint32_t hc_streams, void *stream);
 extern "C" int qw4sh_build_groups(const uint32_t *offsets, const uint32_t *active, void *groups, uint32_t *n_groups, void *stream);
 extern "C" int qw4sh_build_dense_groups(uint32_t tokens, void *groups, uint32_t *n_groups, void *stream);
 
@@ -1635,6 +1636,11 @@ static int launch_route_group_small(const QW4ShLayer *layer, const QW4ShWork *wo
 
 static bool takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, const float *y, size_t tokens) {
     return g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count());
+}
+
+__global__ void __launch_bounds__(256) hc_add_kernel(const float *__restrict__ y, uint32_t hidden, HcAdd hc, uint32_t *status) {
+    const uint32_t t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if (c < hidden && !hc_add(hc, t, c, hidden, y[(uint64_t)t * hidden + c])) atomicOr(status, QW4SH_ERR_NONFINITE);
 }
 
 static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,
@@ -1744,7 +1750,8 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         if (!overlap && (rc = shared_branch(1))) return rc;
         STAGE_MARK();
         if (overlap) CU(cudaStreamWaitEvent(stream, ev[3], 0));
-        if (STEP(9) && (rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
+        if (STEP(9) && (rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, work->hc_residual, work->hc_inject,
+                                             work->hc_streams, stream))) return rc;
         STAGE_MARK();
     } else if (prefill) {
         // groups of <= 32 rows, tcgen05 MMAs on exact integer codes
@@ -1764,7 +1771,8 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
                                                hf[11], nullptr, nullptr, nullptr, nullptr, work->shared_out, work->status, ctas, stream))) return rc;
         STAGE_MARK();
         if (overlap) CU(cudaStreamWaitEvent(stream, ev[3], 0));
-        if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, stream))) return rc;
+        if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, work->hc_residual, work->hc_inject,
+                                             work->hc_streams, stream))) return rc;
         STAGE_MARK();
     } else {
         const uint32_t groups = (uint32_t)(tokens * k < E ? tokens * k : E);
@@ -1776,6 +1784,10 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         STAGE_MARK();
         if ((rc = launch_down(as_dev(layer->w[3]), as_dev(layer->w[6]), work->act, work->shared_act, work->ids, work->weights,
                               work->shared_logit, k, T, y, work->routed, work->status, stream))) return rc;
+        if (work->hc_residual) {                      // the CUDA-core kernels are the fallback for every format: the add follows as a kernel of its own
+            hc_add_kernel<<<dim3((H + 255) / 256, T), 256, 0, stream>>>(y, H, HcAdd{work->hc_residual, work->hc_inject, work->hc_streams}, work->status);
+            LAUNCHED("hc_add_kernel");
+        }
         STAGE_MARK(); STAGE_MARK(); STAGE_MARK();
     }
 #undef STAGE_MARK
@@ -2051,6 +2063,7 @@ extern "C" int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *wor
     // the one-kernel decode path is one launch already, chained to its neighbours by programmatic stream serialisation
     if (takes_fused(layer, work, x, y, tokens)) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
     if (!g_graph_mode || !cache) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);
+    if (work->hc_residual) return layer_launches(layer, work, x, y, tokens, ids_out, weights_out, router_mode, false);   // not replayed
     const bool same = cache->layer == layer && cache->x == x && cache->y == y && cache->ids == ids_out &&
                       cache->weights == weights_out && cache->tokens == tokens && cache->mode == router_mode;
     if (same && cache->exec) {

@@ -429,6 +429,21 @@ Qwen4Status qw4cu_moe_forward_device(const Qwen4Moe *m, const float *x_dev, floa
     return report(err, QW4_OK, "");
 }
 
+/* The layer followed by the hyper-connection add of its caller (picoforge src/qwen4_forward.c:365-367,
+ * src/qwen4_base.c:160-176): residual [tokens, streams, hidden] += inject [tokens, streams] * y, applied by the
+ * kernel that writes y (the reference's GPU path fuses it the same way, src/qwen4_moe_internal.h:55-58). */
+Qwen4Status qw4cu_moe_forward_hc_add_device(const Qwen4Moe *m, const float *x_dev, float *y_dev, size_t tokens, float *residual_dev,
+                                            const float *inject_dev, size_t streams, Qwen4MoeWork *w, Qwen4Error *err) {
+    if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
+    if (tokens && (!residual_dev || !inject_dev)) return report(err, QW4_INVALID_ARGUMENT, "null hyper-connection view");
+    if (!streams || streams > 64) return report(err, QW4_SHAPE, "hyper-connection streams out of range");
+    if (tokens > w->chunk) return report(err, QW4_CAPACITY, "batch exceeds one launch sequence (2048 rows)");
+    w->d.hc_residual = residual_dev; w->d.hc_inject = inject_dev; w->d.hc_streams = (uint32_t)streams;
+    const Qwen4Status st = qw4cu_moe_forward_device(m, x_dev, y_dev, tokens, NULL, NULL, w, err);
+    w->d.hc_residual = NULL; w->d.hc_inject = NULL; w->d.hc_streams = 0;
+    return st;
+}
+
 /* ---- expert-parallel pieces -------------------------------------------------------------- */
 static Qwen4Status piece_checks(const Qwen4Moe *m, Qwen4MoeWork *w, size_t rows, Qwen4Error *err) {
     if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");
