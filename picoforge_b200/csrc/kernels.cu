@@ -453,7 +453,8 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
 // each thread.  Row `experts` is the shared expert's gate.
 // TI x TJ outputs per thread (tokens x router rows): a CTA of 256 threads covers 16 TI tokens x 16 TJ rows.  The kernel
 // is bound by shared-memory reads and issue slots (two instructions per multiply-add in the exact mode), so the tile
-// per thread stays as large as the batch allows while the grid still covers the SMs.
+// per thread stays as large as the batch allows while the grid still covers the SMs.  (Packed mul.rn.f32x2 / add.rn.f32x2
+// on token pairs was 15% faster but its sums were not the scalar ones in the last bit, so the exact mode stays scalar.)
 template <bool EXACT, int TI, int TJ>
 __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
@@ -511,81 +512,6 @@ __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevT
             bad |= !finite_f32(acc[i][j]);
             if (e < experts) logits[(uint64_t)t * experts + e] = acc[i][j];
             else shared_logit[t] = acc[i][j];
-        }
-    }
-    if (bad) atomicOr(status, QW4SH_ERR_NONFINITE);
-}
-
-// The exact-mode GEMM with packed arithmetic: one mul.rn.f32x2 / add.rn.f32x2 pair serves two tokens' chains of a
-// router row, each half rounded on its own exactly like the scalar multiply and add (the reference's bits,
-// src/qwen4_packed.c:164-173), at half the issue slots.  A thread holds 4 tokens x TJ rows.
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
-template <int TJ>
-__global__ void __launch_bounds__(256) router_gemm_pairs_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
-                                                                float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
-    constexpr int TI = 4, BM = 16 * TI, BN = 16 * TJ, BK = 16;
-    __shared__ __align__(16) float xs[2][BK][BM + 4], ws[2][BK][BN + 4];
-    const uint32_t experts = router.n_out, K = router.k_logical;
-    const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
-    const uint32_t t0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
-    const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4;
-    const uint32_t gt = t0 + lr, ge = e0 + lr;
-    const bool load_x = lr < BM, load_w = lr < BN;
-    const float *xrow = load_x && gt < tokens ? x + (uint64_t)gt * K : nullptr;
-    const float *wrow = !load_w ? nullptr : ge < experts ? (const float *)(router.data + (uint64_t)ge * router.row_bytes)
-                                                          : (ge == experts ? (const float *)srouter.data : nullptr);
-    uint64_t acc[2][TJ];
-#pragma unroll
-    for (int i = 0; i < 2; i++)
-#pragma unroll
-        for (int j = 0; j < TJ; j++) acc[i][j] = 0ull;
-    float4 xa = xrow ? *reinterpret_cast<const float4 *>(xrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 wa = wrow ? *reinterpret_cast<const float4 *>(wrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const uint32_t steps = K / BK;
-    for (uint32_t s = 0; s < steps; s++) {
-        const uint32_t b = s & 1u;
-        if (load_x) { xs[b][lc][lr] = xa.x; xs[b][lc + 1][lr] = xa.y; xs[b][lc + 2][lr] = xa.z; xs[b][lc + 3][lr] = xa.w; }
-        if (load_w) { ws[b][lc][lr] = wa.x; ws[b][lc + 1][lr] = wa.y; ws[b][lc + 2][lr] = wa.z; ws[b][lc + 3][lr] = wa.w; }
-        __syncthreads();
-        if (s + 1 < steps) {
-            xa = xrow ? *reinterpret_cast<const float4 *>(xrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-            wa = wrow ? *reinterpret_cast<const float4 *>(wrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int kk = 0; kk < BK; kk++) {
-            const ulonglong2 av = *reinterpret_cast<const ulonglong2 *>(&xs[b][kk][ty * TI]);     // tokens (0, 1) and (2, 3) as pairs
-            float bv[TJ];
-            if (TJ == 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(&ws[b][kk][tx * TJ]);
-                bv[0] = v.x; bv[1 % TJ] = v.y; bv[2 % TJ] = v.z; bv[3 % TJ] = v.w;
-            } else {
-#pragma unroll
-                for (int j = 0; j < TJ; j++) bv[j] = ws[b][kk][tx * TJ + j];
-            }
-#pragma unroll
-            for (int j = 0; j < TJ; j++) {
-                const uint64_t w2 = f2_pack(bv[j], bv[j]);
-                acc[0][j] = f2_add(acc[0][j], f2_mul(w2, av.x));
-                acc[1][j] = f2_add(acc[1][j], f2_mul(w2, av.y));
-            }
-        }
-    }
-    bool bad = false;
-#pragma unroll
-    for (int i = 0; i < TI; i++) {
-        const uint32_t t = t0 + ty * TI + i;
-        if (t >= tokens) continue;
-#pragma unroll
-        for (int j = 0; j < TJ; j++) {
-            const uint32_t e = e0 + tx * TJ + j;
-            if (e > experts) continue;
-            const uint64_t pair = acc[i >> 1][j];
-            const float v = __uint_as_float((uint32_t)(i & 1 ? pair >> 32 : pair));
-            bad |= !finite_f32(v);
-            if (e < experts) logits[(uint64_t)t * experts + e] = v;
-            else shared_logit[t] = v;
         }
     }
     if (bad) atomicOr(status, QW4SH_ERR_NONFINITE);
@@ -1368,19 +1294,6 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         else router_gemm_kernel<false, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); } while (0)
         // four tokens per thread always (one 128-bit read serves four chains); fewer router rows per thread for
         // smaller batches, so that the grid still covers the SMs
-        static int variant = -1;
-        if (variant < 0) { const char *v = getenv("QW4CU_ROUTER_VARIANT"); variant = v ? atoi(v) : 1; }
-        if (mode == 0 && variant == 1) {
-#define ROUTER_PAIRS(TJ) do { \
-        const dim3 grid((unsigned)((tokens + 63) / 64), (rows + 16 * TJ - 1) / (16 * TJ)); \
-        router_gemm_pairs_kernel<TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); } while (0)
-            if (tokens >= 768) ROUTER_PAIRS(4);
-            else if (tokens >= 384) ROUTER_PAIRS(2);
-            else ROUTER_PAIRS(1);
-#undef ROUTER_PAIRS
-            LAUNCHED("router_gemm_pairs_kernel");
-            return 0;
-        }
         if (tokens >= 768) ROUTER_GEMM(4, 4);
         else if (tokens >= 384) ROUTER_GEMM(4, 2);
         else ROUTER_GEMM(4, 1);
@@ -1665,27 +1578,12 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
     // timing stages.)
     cudaStream_t side = stream;
     cudaEvent_t *ev = nullptr;                          // [0] fork, [1] x digits ready, [2] routes ready, [3] shared expert done
-    const bool prefill = !mma && prefill_path(layer, tokens);
-    const bool overlap = (mma || prefill) && !timed;
+    const bool overlap = mma && !timed;
     uint8_t *shared_groups = (uint8_t *)work->groups + (size_t)T * k * 16;      // behind the routed groups
     if (overlap) {
         if ((rc = side_stream(&side, &ev))) return rc;
         CU(cudaEventRecord(ev[0], stream));
         CU(cudaStreamWaitEvent(side, ev[0], 0));
-    }
-    void *const *hf = work->half;
-    if (prefill) {
-        // tensor-core prefill: the fp16 split of x, and with it the whole shared expert, beside router, route and dispatch
-        if ((rc = qw4sh_split_rows(x, T, H, hf[0], hf[1], hf[2], hf[3], side))) return rc;
-        if (overlap) {
-            CU(cudaEventRecord(ev[1], side));
-            if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, side))) return rc;
-            if ((rc = qw4sh_prefill_tc(0, &layer->w[4], &layer->w[5], work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[0], hf[1], hf[2],
-                                       hf[3], hf[8], hf[9], hf[10], hf[11], nullptr, work->status, sm_count(), side))) return rc;
-            if ((rc = qw4sh_prefill_tc(1, &layer->w[6], nullptr, work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[8], hf[9], hf[10],
-                                       hf[11], nullptr, nullptr, nullptr, nullptr, work->shared_out, work->status, sm_count(), side))) return rc;
-            CU(cudaEventRecord(ev[3], side));
-        }
     }
     if (mma) {
         if (STEP(1) && (rc = qw4sh_quantize_rows(x, T, H, work->xq, work->xneg, work->xsum, work->xscale, side))) return rc;
@@ -1753,24 +1651,25 @@ static int layer_launches(const QW4ShLayer *layer, const QW4ShWork *work, const 
         if (STEP(9) && (rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, work->hc_residual, work->hc_inject,
                                              work->hc_streams, stream))) return rc;
         STAGE_MARK();
-    } else if (prefill) {
-        // groups of <= 32 rows, tcgen05 MMAs on exact integer codes
+    } else if (prefill_path(layer, tokens)) {
+        // tensor-core prefill: groups of <= 32 rows, tcgen05 MMAs on exact integer codes.  (The shared expert on a second
+        // stream beside router and dispatch was measured and made the step slower: its persistent CTAs hold every SM.)
+        void *const *hf = work->half;
         if ((rc = qw4sh_build_groups32(work->offsets, work->active, work->groups32, work->n_groups32, stream))) return rc;
-        if (overlap) CU(cudaStreamWaitEvent(stream, ev[1], 0));
-        else if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, stream))) return rc;
+        if ((rc = qw4sh_build_dense_groups32(T, work->shared_groups32, work->n_groups32 + 1, stream))) return rc;
+        if ((rc = qw4sh_split_rows(x, T, H, hf[0], hf[1], hf[2], hf[3], stream))) return rc;
         if ((rc = qw4sh_prefill_tc(0, &layer->w[1], &layer->w[2], work->groups32, work->n_groups32, work->row_to_pair, k, hf[0], hf[1], hf[2],
                                    hf[3], hf[4], hf[5], hf[6], hf[7], nullptr, work->status, ctas, stream))) return rc;
         STAGE_MARK();
-        if (!overlap && (rc = qw4sh_prefill_tc(0, &layer->w[4], &layer->w[5], work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[0], hf[1],
-                                               hf[2], hf[3], hf[8], hf[9], hf[10], hf[11], nullptr, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_prefill_tc(0, &layer->w[4], &layer->w[5], work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[0], hf[1], hf[2],
+                                   hf[3], hf[8], hf[9], hf[10], hf[11], nullptr, work->status, ctas, stream))) return rc;
         STAGE_MARK();
         if ((rc = qw4sh_prefill_tc(1, &layer->w[3], nullptr, work->groups32, work->n_groups32, work->row_to_pair, 1, hf[4], hf[5], hf[6], hf[7],
                                    nullptr, nullptr, nullptr, nullptr, work->out, work->status, ctas, stream))) return rc;
         STAGE_MARK();
-        if (!overlap && (rc = qw4sh_prefill_tc(1, &layer->w[6], nullptr, work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[8], hf[9], hf[10],
-                                               hf[11], nullptr, nullptr, nullptr, nullptr, work->shared_out, work->status, ctas, stream))) return rc;
+        if ((rc = qw4sh_prefill_tc(1, &layer->w[6], nullptr, work->shared_groups32, work->n_groups32 + 1, nullptr, 1, hf[8], hf[9], hf[10],
+                                   hf[11], nullptr, nullptr, nullptr, nullptr, work->shared_out, work->status, ctas, stream))) return rc;
         STAGE_MARK();
-        if (overlap) CU(cudaStreamWaitEvent(stream, ev[3], 0));
         if ((rc = qw4sh_combine(work->out, work->shared_out, work->weights, work->shared_logit, k, H, T, y, work->routed, work->status, work->hc_residual, work->hc_inject,
                                              work->hc_streams, stream))) return rc;
         STAGE_MARK();
