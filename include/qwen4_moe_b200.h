@@ -466,6 +466,31 @@ Qwen4Status qw4cu_gguf_slice_describe(const char *path, uint32_t layer, QW4CuGgu
  * image is the only copy afterwards).  `slice` may be NULL. */
 Qwen4Status qw4cu_moe_create_from_gguf(const char *path, uint32_t layer, Qwen4Moe **out, QW4CuGgufSlice *slice, Qwen4Error *err);
 
+/* ------------------------------------------------------------------------------------
+ * Speculative verify over a stack of layers, with the route log (csrc/verify_stack.c).
+ *
+ * The real caller of the four-token decode batch: picoforge appends one confirmed token plus up to three
+ * drafts as one batch of 1..4 rows and then keeps the first n (qwen4_gpu_forward_verify / _keep,
+ * src/qwen4_forward_gpu.h:55-63).  The MoE layer is stateless across tokens, so verify is a 1..4-row forward
+ * per layer and keep moves the position.  With a log file set, every append writes the reference's record
+ * (src/qwen4_forward_gpu.m:896-899): uint32 {position, rows, layers, top_k}, then ids [layer][row][top_k].
+ * Layer l reads what layer l - 1 wrote (a stand-in for the engine's layer loop, whose attention and
+ * hyper-connection steps lie outside this library).  `layers` are borrowed and must outlive the handle;
+ * all must share `config`'s hidden size and top_k.
+ * ---------------------------------------------------------------------------------- */
+typedef struct QW4CuVerify QW4CuVerify;
+Qwen4Status qw4cu_verify_create(Qwen4Moe *const *layers, size_t n_layers, const Qwen4MoeConfig *config, QW4CuVerify **out, Qwen4Error *err);
+void qw4cu_verify_destroy(QW4CuVerify *verify);
+/* path NULL stops logging; the file is truncated and flushed after every append. */
+Qwen4Status qw4cu_verify_route_log(QW4CuVerify *verify, const char *path, Qwen4Error *err);
+/* x_host, y_host: dense [count, hidden]; ids_host: [layers][count][top_k] or NULL; count 1..4 (QW4_CAPACITY otherwise).
+ * An append while another is pending settles that one first with all its rows kept. */
+Qwen4Status qw4cu_verify_append(QW4CuVerify *verify, const float *x_host, size_t count, float *y_host, uint32_t *ids_host, Qwen4Error *err);
+/* keep 1..rows of the pending append (QW4_RANGE otherwise; QW4_BAD_STATE when nothing is pending). */
+Qwen4Status qw4cu_verify_keep(QW4CuVerify *verify, size_t keep, Qwen4Error *err);
+uint64_t qw4cu_verify_position(const QW4CuVerify *verify);
+size_t qw4cu_verify_pending(const QW4CuVerify *verify);
+
 /* Raw device memory and transfers for callers that keep activations in HBM. */
 void *qw4cu_malloc(size_t bytes);
 void qw4cu_free(void *device_pointer);

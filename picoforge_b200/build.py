@@ -48,7 +48,7 @@ def build_product(force: bool = False) -> Path:
         if force or _stale(obj, [src] + headers):
             _run([NVCC, *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-c", src, "-o", obj])
         objects.append(obj)
-    for host in (host, CSRC / "gguf_slice.c"):
+    for host in (host, CSRC / "gguf_slice.c", CSRC / "verify_stack.c"):
         host_obj = build_dir / (host.stem + ".o")
         if force or _stale(host_obj, [host] + headers):
             _run([GCC, "-std=c11", "-O2", "-fPIC", "-Wall", "-Wextra", "-fvisibility=default", "-D_DEFAULT_SOURCE", f"-I{ROOT / 'include'}",

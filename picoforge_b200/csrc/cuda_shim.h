@@ -77,6 +77,7 @@ enum { QW4SH_ERR_NONFINITE = 1u, QW4SH_ERR_BOUNDS = 2u, QW4SH_ERR_STATE = 4u };
 
 int qw4sh_device_count(void);
 int qw4sh_set_device(int device);
+int qw4sh_current_device(void);           /* -1 when the runtime cannot tell */
 const char *qw4sh_last_error(void);
 uint64_t qw4sh_launch_count(void);
 

@@ -79,6 +79,7 @@ extern "C" int qw4sh_device_count(void) {
     return n;
 }
 extern "C" int qw4sh_set_device(int device) { CU(cudaSetDevice(device)); return ensure_constants(); }
+extern "C" int qw4sh_current_device(void) { int device = -1; return cudaGetDevice(&device) == cudaSuccess ? device : -1; }
 extern "C" const char *qw4sh_last_error(void) { return g_error; }
 extern "C" uint64_t qw4sh_launch_count(void) { return g_launches; }
 

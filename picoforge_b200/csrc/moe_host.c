@@ -10,6 +10,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <pthread.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -647,6 +648,41 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
 }
 
 /* ---- pure routing ---------------------------------------------------------------------- */
+/* Scratch of the two stateless entry points below.  They have no workspace argument, so the library keeps one device
+ * block and one host block per device between calls and only ever grows them (up to SCRATCH_KEEP; a larger request
+ * gets blocks of its own for that call): the reference's seeded route and grouping tests call these thousands of
+ * times, and a device allocation per call costs more than the kernels.  One caller at a time per process: the lock
+ * is held from scratch_take to scratch_give (the calls are synchronous anyway). */
+#define SCRATCH_KEEP ((size_t)256 << 20)
+static pthread_mutex_t g_scratch_lock = PTHREAD_MUTEX_INITIALIZER;
+static struct { char *dev, *host; size_t dev_bytes, host_bytes; } g_scratch[64];
+typedef struct { char *dev, *host; bool own; } Scratch;
+static Scratch scratch_take(size_t dev_bytes, size_t host_bytes) {
+    Scratch s = {NULL, NULL, false};
+    const int device = qw4sh_current_device();
+    if (device < 0 || device >= 64 || dev_bytes > SCRATCH_KEEP || host_bytes > SCRATCH_KEEP) {
+        s.own = true; s.dev = qw4sh_malloc(dev_bytes); s.host = malloc(host_bytes);
+        return s;
+    }
+    pthread_mutex_lock(&g_scratch_lock);
+    if (g_scratch[device].dev_bytes < dev_bytes) {
+        qw4sh_free(g_scratch[device].dev);
+        g_scratch[device].dev = qw4sh_malloc(dev_bytes);
+        g_scratch[device].dev_bytes = g_scratch[device].dev ? dev_bytes : 0;
+    }
+    if (g_scratch[device].host_bytes < host_bytes) {
+        free(g_scratch[device].host);
+        g_scratch[device].host = malloc(host_bytes);
+        g_scratch[device].host_bytes = g_scratch[device].host ? host_bytes : 0;
+    }
+    s.dev = g_scratch[device].dev; s.host = g_scratch[device].host;
+    return s;
+}
+static void scratch_give(Scratch s) {
+    if (s.own) { qw4sh_free(s.dev); free(s.host); }
+    else pthread_mutex_unlock(&g_scratch_lock);
+}
+
 Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *c, Qwen4F32 logits, Qwen4MoeRoutes routes, Qwen4F32Mut probabilities,
                             Qwen4Error *err) {
     TRY(check_config(c, err));
@@ -661,8 +697,8 @@ Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *c, Qwen4F32 logits, Qwen4MoeRo
     if (!t) return report(err, QW4_OK, "");
     if (t > UINT32_MAX / 2) return report(err, QW4_OVERFLOW, "too many rows");
     const size_t ze = t * e * 4, zk = t * k * 4;
-    char *dev = qw4sh_malloc(2 * ze + 2 * zk + 64);
-    char *host = malloc(ze + 2 * zk + 64);
+    const Scratch scratch = scratch_take(2 * ze + 2 * zk + 64, ze + 2 * zk + 64);
+    char *dev = scratch.dev, *host = scratch.host;
     Qwen4Status st = QW4_OK;
     if (!dev || !host) { st = dev ? report(err, QW4_OOM, "route scratch") : cuda_failure(err, "route scratch"); goto done; }
     float *d_logits = (float *)dev, *d_probs = (float *)(dev + ze), *d_w = (float *)(dev + 2 * ze + zk);
@@ -691,7 +727,7 @@ Qwen4Status qwen4_moe_route(const Qwen4MoeConfig *c, Qwen4F32 logits, Qwen4MoeRo
     }
     st = report(err, QW4_OK, "");
 done:
-    qw4sh_free(dev); free(host);
+    scratch_give(scratch);
     return st;
 }
 
@@ -726,8 +762,9 @@ Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *c, Qwen4U32Mut ids, QW4Moe
     }
     if (pairs > UINT32_MAX / 2) return report(err, QW4_OVERFLOW, "too many pairs");
     const size_t zp = pairs * 4, ze = (e + 1) * 4;
-    char *dev = qw4sh_malloc(3 * zp + 2 * ze + 64 + 16);
-    uint32_t *host = malloc(3 * zp + ze + 64);
+    const Scratch scratch = scratch_take(3 * zp + 2 * ze + 64 + 16, 3 * zp + ze + 64);
+    char *dev = scratch.dev;
+    uint32_t *host = (uint32_t *)scratch.host;
     Qwen4Status st = QW4_OK;
     if (!dev || !host) { st = dev ? report(err, QW4_OOM, "group scratch") : cuda_failure(err, "group scratch"); goto done; }
     uint32_t *d_ids = (uint32_t *)dev, *d_p2r = (uint32_t *)(dev + zp), *d_r2p = (uint32_t *)(dev + 2 * zp);
@@ -747,7 +784,7 @@ Qwen4Status qw4_moe_group_pairs(const Qwen4MoeConfig *c, Qwen4U32Mut ids, QW4Moe
     for (size_t j = 0; j < pairs; j++) { g.pair_to_row[j] = h_p2r[j]; g.row_to_pair[j] = h_r2p[j]; }
     st = report(err, QW4_OK, "");
 done:
-    qw4sh_free(dev); free(host);
+    scratch_give(scratch);
     return st;
 }
 
