@@ -50,7 +50,7 @@ from picoforge_b200.layer import MoeLayer  # noqa: E402
 # benchmark, so the figure comes from the capture summarised in the named file (same command, same workload) and
 # is reported with that source; a workload without a capture of its current kernel reports null.
 TRAFFIC = {
-    "c1:fused_decode_kernel": {"bytes": 32.07e6 + 0.02e6, "source": "profiles/decode_c1_fused_decode_kernel.md"},
+    "c1:fused_decode_kernel": {"bytes": 32.90e6 + 0.05e6, "source": "profiles/decode_c1_fused_decode_kernel.md"},
 }
 
 STAGES = ("router_logits", "route", "group", "gate_up_routed", "gate_up_shared", "down_routed", "down_shared", "combine")
@@ -603,6 +603,30 @@ def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind
 
     clocks16 = (C.c_uint64 * 16)()
     lib.qw4cu_decode_phase_clocks(layers[(args.steps - 1) % len(layers)].work, clocks16)
+
+    # ---- the batch's real caller: speculative verify of 1 + 3 rows through a 48-layer stack (host buffers, one wait) ----
+    stack = None
+    if tokens <= 4 and world == 1 and not args.profile:
+        depth = 48
+        handles = (C.c_void_p * depth)(*[layers[i % len(layers)].moe for i in range(depth)])
+        cfg = specs[0].config()
+        verify = C.c_void_p()
+        if lib.qw4cu_verify_create(handles, depth, C.byref(cfg), C.byref(verify), C.byref(err)) == 0:
+            xs, ys = np.ascontiguousarray(x[:tokens]), np.empty_like(x[:tokens])
+            appends = 12
+            for i in range(3 + appends):
+                if i == 3:
+                    start = time.perf_counter()
+                # every layer's output feeds the next: keep the chain finite by restarting from x each append
+                if lib.qw4cu_verify_append(verify, xs.ctypes.data, tokens, ys.ctypes.data, None, C.byref(err)) != 0:
+                    raise abi.MoeError(err.code, err)
+                lib.qw4cu_verify_keep(verify, 1, C.byref(err))
+            seconds = (time.perf_counter() - start) / appends
+            lib.qw4cu_verify_destroy(verify)
+            stack = {"layers": depth, "rows": tokens, "ms_per_append": seconds * 1e3, "us_per_layer": seconds * 1e6 / depth,
+                     "us_per_token_layer": seconds * 1e6 / depth / tokens,
+                     "note": "qw4cu_verify_append: host x in, host y out, 48 layers enqueued back to back, one host wait; "
+                             "the 8 weight sets repeat down the stack"}
     for layer in layers:
         layer.close()
     for pointer in [x_dev] + y_dev:
@@ -674,6 +698,7 @@ def decode_line(args, api, rank, local_rank, world, control, hbm_peak, peak_kind
                   "stage_us_multi_kernel_path": stage_us, "stage_bytes": bytes_by_stage},
         "e2e": {"value": e2e_us_per_token, "unit": "us/token", "h2d_bytes_per_step": int(x.nbytes),   # status words: cleared only after an error
                 "d2h_bytes_per_step": int(x.nbytes) + 16, "steps": e2e_steps},
+        "verify_stack": stack,
         "gpu_launches": int(launches),
         "clocks": clock_summary,
         "cpu_baseline": cpu,
