@@ -122,6 +122,22 @@ def test_decode_one_kernel_path_metric(gpu):
     report_metric("c1 decode, fused_decode_kernel", spec, x, [0, 3], ids, weights, y, want["y"][[0, 3]])
 
 
+def test_tensor_core_prefill_path_metric(gpu):
+    """The same metric on the tcgen05 prefill path (Q4_K, more than 64 tokens): exact integer codes and a 22-bit
+    hi + lo split of the activations, so it lands orders of magnitude under the int8-digit paths."""
+    spec = synth.make_layer(2, routed_type=abi.Q4_K, shared_type=abi.Q4_K, experts=64, top_k=6)
+    x = synth.activations(2, 96)
+    want = oracle.forward(spec, x, threads=synth.threads())
+    with MoeLayer(gpu, spec, 96) as layer:
+        gpu.lib.qw4cu_launch_log_begin()
+        y, ids, weights = layer.forward(x)
+        names = gpu.launch_names()
+    assert "prefill_tc_kernel" in names and "expert_tile_kernel" not in names, names
+    np.testing.assert_array_equal(ids, want["ids"])
+    worst = report_metric("96-token prefill, prefill_tc_kernel", spec, x, [0, 47, 95], ids, weights, y, want["y"][[0, 47, 95]])
+    assert worst <= 2.0 ** -20
+
+
 def test_three_layer_stack_fed_layer_to_layer(gpu):
     """Layer l + 1 reads the GPU's output of layer l, brought back to unit RMS on the host (the
     engine has norms and other blocks in between).  Every layer is checked against the oracle run
