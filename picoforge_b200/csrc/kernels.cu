@@ -459,12 +459,14 @@ __global__ void __launch_bounds__(256) router_fast_kernel(DevTensor router, DevT
 template <bool EXACT, int TI, int TJ>
 __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevTensor srouter, const float *__restrict__ x, uint32_t tokens,
                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
-    constexpr int BM = 16 * TI, BN = 16 * TJ, BK = 16;
+    // columns per stage: the narrower the tile of router rows, the less arithmetic a stage holds, so it covers more
+    // columns to keep the global-memory round trip of the next stage hidden (two stages of shared memory, <= 45 KB)
+    constexpr int BM = 16 * TI, BN = 16 * TJ, BK = TJ >= 4 ? 16 : TJ == 2 ? 32 : 64, PASSES = BK / 16;
     __shared__ __align__(16) float xs[2][BK][BM + 4], ws[2][BK][BN + 4];
     const uint32_t experts = router.n_out, K = router.k_logical;
     const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
     const uint32_t t0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
-    // loader: thread -> (row tid / 4, float4 tid % 4) of each (up to 64) x 16 tile
+    // loader: thread -> (row tid / 4, float4 tid % 4) of each (up to 64) x 16 piece of a stage
     const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4;
     const uint32_t gt = t0 + lr, ge = e0 + lr;
     const bool load_x = lr < BM, load_w = lr < BN;
@@ -476,19 +478,31 @@ __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevT
     for (int i = 0; i < TI; i++)
 #pragma unroll
         for (int j = 0; j < TJ; j++) acc[i][j] = 0.0f;
-    float4 xa = xrow ? *reinterpret_cast<const float4 *>(xrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 wa = wrow ? *reinterpret_cast<const float4 *>(wrow + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 xa[PASSES], wa[PASSES];
+#pragma unroll
+    for (int q = 0; q < PASSES; q++) {
+        xa[q] = xrow ? *reinterpret_cast<const float4 *>(xrow + 16 * q + lc) : zero;
+        wa[q] = wrow ? *reinterpret_cast<const float4 *>(wrow + 16 * q + lc) : zero;
+    }
     const uint32_t steps = K / BK;
     for (uint32_t s = 0; s < steps; s++) {
         const uint32_t b = s & 1u;
-        if (load_x) { xs[b][lc][lr] = xa.x; xs[b][lc + 1][lr] = xa.y; xs[b][lc + 2][lr] = xa.z; xs[b][lc + 3][lr] = xa.w; }
-        if (load_w) { ws[b][lc][lr] = wa.x; ws[b][lc + 1][lr] = wa.y; ws[b][lc + 2][lr] = wa.z; ws[b][lc + 3][lr] = wa.w; }
+#pragma unroll
+        for (int q = 0; q < PASSES; q++) {
+            const uint32_t c = 16 * q + lc;
+            if (load_x) { xs[b][c][lr] = xa[q].x; xs[b][c + 1][lr] = xa[q].y; xs[b][c + 2][lr] = xa[q].z; xs[b][c + 3][lr] = xa[q].w; }
+            if (load_w) { ws[b][c][lr] = wa[q].x; ws[b][c + 1][lr] = wa[q].y; ws[b][c + 2][lr] = wa[q].z; ws[b][c + 3][lr] = wa[q].w; }
+        }
         __syncthreads();
         if (s + 1 < steps) {
-            xa = xrow ? *reinterpret_cast<const float4 *>(xrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-            wa = wrow ? *reinterpret_cast<const float4 *>(wrow + (s + 1) * BK + lc) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
 #pragma unroll
+            for (int q = 0; q < PASSES; q++) {
+                xa[q] = xrow ? *reinterpret_cast<const float4 *>(xrow + (s + 1) * BK + 16 * q + lc) : zero;
+                wa[q] = wrow ? *reinterpret_cast<const float4 *>(wrow + (s + 1) * BK + 16 * q + lc) : zero;
+            }
+        }
+#pragma unroll 16
         for (int kk = 0; kk < BK; kk++) {
             float av[TI], bv[TJ];
 #pragma unroll
@@ -1288,7 +1302,7 @@ static int launch_router(const QW4ShLayer *layer, const float *x, size_t tokens,
         if (allow_smem(router_exact_small_kernel, smem)) return -1;
         router_exact_small_kernel<<<dim3((rows + 31) / 32, (unsigned)tokens), 32, smem, stream>>>(router, srouter, x, logits, shared_logit, status);
         LAUNCHED("router_exact_small_kernel");
-    } else if (tokens > 16 && router.k_logical % 16 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
+    } else if (tokens > 16 && router.k_logical % 64 == 0 && ((uintptr_t)x & 15u) == 0 && router.row_bytes % 16 == 0) {
 #define ROUTER_GEMM(TI, TJ) do { \
         const dim3 grid((unsigned)((tokens + 16 * TI - 1) / (16 * TI)), (rows + 16 * TJ - 1) / (16 * TJ)); \
         if (mode == 0) router_gemm_kernel<true, TI, TJ><<<grid, 256, 0, stream>>>(router, srouter, x, (uint32_t)tokens, logits, shared_logit, status); \
