@@ -277,6 +277,7 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         parity = {"tokens": sample, "max_abs": float(np.abs(y0[:sample] - want["y"]).max()),
                   "ids_equal": bool(np.array_equal(ids0[:sample], want["ids"]))}
         del full
+    barrier()                                                                        # the other ranks wait here while rank 0 runs the oracle
 
     def step():
         for c in range(chunks):
@@ -326,8 +327,11 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         t = torch.tensor([elapsed_ms], dtype=torch.float64)
         control.all_reduce(t, op=control.ReduceOp.MAX)
         elapsed_ms = float(t.item())
+    transport = "this library's kernels over NVLink peer memory (push all-gather, pull reduce-scatter)" if lib.qw4cu_ep_transport(comm.handle) \
+        else ("none (one rank)" if world == 1 else "NCCL (ncclAllGather, ncclReduceScatter)")
     for layer in layers:
         layer.close()
+    barrier()
     comm.close()
     for pointer in x_dev + [y_dev]:
         lib.qw4cu_free(pointer)
@@ -346,7 +350,8 @@ def run_sharded(name, args, api, rank, world, control, hbm_peak, peak_kind):
         "ms_per_step": ms_per_step, "us_per_token_layer": ms_per_step * 1e3 / (tokens * n_layers),
         "us_per_chunk_layer": ms_per_step * 1e3 / passes, "tokens_per_s": tokens / (ms_per_step * 1e-3), "scaling": "strong",
         "parallelism": f"expert parallel over {world} GPU(s): {epr} experts each, router and shared expert replicated, tokens data-parallel; "
-                       "per layer one all-gather of token rows and one reduce-scatter of partial sums, issued by the library (NCCL)",
+                       "per layer one all-gather of token rows and one reduce-scatter of partial sums, issued by the library",
+        "transport": transport,
         "weights": "layer 0: quantised Gaussian masters (checked against the CPU oracle); other layers: fabricated blocks of the same formats",
         "roofline": {"bound": "hbm", "kernel": "whole step, all GPUs", "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s",
                      "frac": achieved / (hbm_peak * world), "peak_kind": peak_kind, "algorithmic_bytes": touched, "traffic": None},

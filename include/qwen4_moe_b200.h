@@ -278,14 +278,23 @@ Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
  * over a token's experts therefore runs per rank and then over ranks, not in slot order: y agrees
  * with the one-device layer within the layer tolerance, ids and route weights bit for bit.
  *
- * qw4cu_moe_ep_forward_device does the whole step, collectives included, through NCCL (taken from
- * the process at run time: libnccl.so.2, or the file named by QW4CU_NCCL_LIBRARY).  A C host makes
- * the communicator itself: rank 0 calls qw4cu_ep_unique_id and hands the 128 bytes to the other
- * ranks by any means, then every rank calls qw4cu_ep_create with its device current (world 1 needs
- * no NCCL and no id).  The workspace must have capacity for (world + 1) * tokens_local tokens.
- * Every rank must make the same sequence of calls; all of them enqueue on the stream in force and
- * return without waiting (the exchange buffers grow on the first call of a size: make that call
- * outside any stream capture).
+ * qw4cu_moe_ep_forward_device does the whole step, both exchanges included.  A C host makes the
+ * communicator itself: rank 0 calls qw4cu_ep_unique_id and hands the 128 bytes to the other ranks by
+ * any means, then every rank calls qw4cu_ep_create with its device current (world 1 needs no NCCL and
+ * no id).  NCCL is taken from the process at run time (libnccl.so.2, or the file named by
+ * QW4CU_NCCL_LIBRARY).  Transport of the two exchanges (qw4cu_ep_transport: 1 peer memory, 0 NCCL):
+ * by default this library's own kernels over NVLink peer memory: the ranks map each other's exchange
+ * buffers (CUDA IPC handles, handed round through the communicator when the buffers are made), the
+ * all-gather is a push of the rank's rows into every rank's buffer with plain peer stores, the
+ * reduce-scatter a pull of the own tokens' partial rows from every rank, added in rank order; ranks meet
+ * at epoch words that they raise in each other's memory, every wait is bounded (about eight seconds, then
+ * QW4_GPU_ERROR "device state error" at the next qw4cu_moe_work_sync).  NCCL's ncclAllGather /
+ * ncclReduceScatter carry the exchanges when a mapping fails on any rank or QW4CU_EP_TRANSPORT=nccl.
+ * The workspace must have capacity for (world + 1) * tokens_local tokens.  Every rank must make the same
+ * sequence of calls with the same token count, qw4cu_ep_destroy included (with the peer transport it waits
+ * for the other ranks, so that no buffer goes away under a peer that still reads it); all calls enqueue on
+ * the stream in force and return without waiting (the exchange buffers are made on the first call of a
+ * size, a collective step with host synchronisation: make that call outside any stream capture).
  *
  * The two compute pieces are also callable on their own, for a caller with an exchange of its
  * own (or one process that plays several ranks):
@@ -302,6 +311,7 @@ Qwen4Status qw4cu_moe_create_sharded(const Qwen4MoeConfig *config, const Qwen4Mo
 int qw4cu_ep_unique_id(unsigned char id[128]);
 Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW4CuEp **out, Qwen4Error *err);
 void qw4cu_ep_destroy(QW4CuEp *ep);
+int qw4cu_ep_transport(const QW4CuEp *ep);
 size_t qw4cu_ep_row_floats(const Qwen4Moe *moe);
 Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *moe, QW4CuEp *ep, const float *x_dev, float *y_dev, size_t tokens_local,
                                         uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work, Qwen4Error *err);

@@ -484,6 +484,7 @@ Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW
 void qw4cu_ep_trace(int on) { qw4sh_ep_trace(on); }
 uint64_t qw4cu_ep_trace_read(double *ms, int n) { return ms ? qw4sh_ep_trace_read(ms, n) : 0; }
 void qw4cu_ep_destroy(QW4CuEp *ep) { if (ep) { qw4sh_ep_destroy(ep->shim); free(ep); } }
+int qw4cu_ep_transport(const QW4CuEp *ep) { return ep ? qw4sh_ep_transport(ep->shim) : 0; }
 size_t qw4cu_ep_row_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_row_floats((uint32_t)m->c.hidden_size, (uint32_t)m->c.top_k) : 0; }
 
 static Qwen4Status ep_shard(const Qwen4Moe *m, size_t world, size_t rank, Qwen4Error *err) {
@@ -532,11 +533,11 @@ Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *m, QW4CuEp *ep, const fl
     if (graph < 0) return cuda_failure(err, "graph replay");
     if (graph == 1) return report(err, QW4_OK, "");
     Qwen4Status st = qw4cu_moe_ep_begin_device(m, x_dev, tokens_local, qw4sh_ep_msg_local(ep->shim), ids_dev, weights_dev, w, err);
-    if (st == QW4_OK && qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.stream)) st = cuda_failure(err, "all-gather");
+    if (st == QW4_OK && qw4sh_ep_all_gather(ep->shim, tokens_local * qw4sh_ep_row_floats(h, k), w->d.status, w->d.stream)) st = cuda_failure(err, "all-gather");
     if (st == QW4_OK)
         st = qw4cu_moe_ep_experts_device(m, qw4sh_ep_msg_all(ep->shim), tokens_local * world, rank * tokens_local,
                                          qw4sh_ep_partial_buffer(ep->shim), w, err);
-    if (st == QW4_OK && qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.stream)) st = cuda_failure(err, "reduce-scatter");
+    if (st == QW4_OK && qw4sh_ep_reduce_scatter(ep->shim, y_dev, tokens_local * h, w->d.status, w->d.stream)) st = cuda_failure(err, "reduce-scatter");
     if (graph == 2 && qw4sh_graph_finish(&w->d, st != QW4_OK) && st == QW4_OK) st = cuda_failure(err, "graph capture");
     if (st != QW4_OK) return st;
     if (qw4sh_ep_trace_mark(10, w->d.stream) || qw4sh_ep_trace_collect()) return cuda_failure(err, "stage trace");
