@@ -62,7 +62,9 @@ constexpr int FNS = 2;                          // ring stages per warp
 constexpr uint32_t FSTAGE = 4608;               // bytes per ring stage (IQ2_XXS: 4096 payload + 512 super-scales)
 constexpr uint32_t F_LUT_GRID = 256 * 128, F_LUT_SIGN = 128 * 128, F_LUT_BYTES = F_LUT_GRID + F_LUT_SIGN;
 constexpr uint32_t FZP = FMAXE + 4;             // pitch of a logit row in shared memory (floats)
-constexpr int CROWS = 32;                       // router rows per chain CTA (lane = row)
+constexpr int CROWS = 32;                       // router rows per chain CTA (lane = row).  64 rows (two chain warps per token, nine
+                                                // chain CTAs) evened out the streaming CTAs' shares but ran the chains at 42 k cycles
+                                                // instead of 25 k, and the step at 44.4 us instead of 42.0
 constexpr int CSTG = 16;                        // chunks in flight in a chain CTA
 constexpr int CCH = 64;                         // columns per chunk: 256 bytes per row
 // words of the sync array
