@@ -312,6 +312,11 @@ int qw4cu_ep_unique_id(unsigned char id[128]);
 Qwen4Status qw4cu_ep_create(const unsigned char id[128], int rank, int world, QW4CuEp **out, Qwen4Error *err);
 void qw4cu_ep_destroy(QW4CuEp *ep);
 int qw4cu_ep_transport(const QW4CuEp *ep);
+/* Test aid for the bounded waits of the peer transport: runs the wait kernel as rank 0 of two on a flag row that
+ * nothing raises (raise_first = 0) or that the "peer" has already raised (1), with a limit of `polls` polls (capped
+ * at 65536, about a tenth of a second).  Returns 1 when the wait ran out and recorded the state error, 0 when it
+ * was satisfied, -1 on a CUDA error.  Needs no second GPU and leaves the context usable. */
+int qw4cu_ep_wait_probe(uint32_t polls, int raise_first);
 size_t qw4cu_ep_row_floats(const Qwen4Moe *moe);
 Qwen4Status qw4cu_moe_ep_forward_device(const Qwen4Moe *moe, QW4CuEp *ep, const float *x_dev, float *y_dev, size_t tokens_local,
                                         uint32_t *ids_dev, float *weights_dev, Qwen4MoeWork *work, Qwen4Error *err);

@@ -178,7 +178,8 @@ float *qw4sh_ep_msg_all(QW4ShEp *ep);
 float *qw4sh_ep_partial_buffer(QW4ShEp *ep);
 int qw4sh_ep_all_gather(QW4ShEp *ep, size_t floats_per_rank, uint32_t *status, void *stream);
 int qw4sh_ep_reduce_scatter(QW4ShEp *ep, float *y, size_t floats_per_rank, uint32_t *status, void *stream);
-int qw4sh_ep_transport(const QW4ShEp *ep);   /* 1: this library's kernels over peer memory; 0: NCCL */
+int qw4sh_ep_transport(const QW4ShEp *ep);
+int qw4sh_ep_wait_probe(uint32_t polls, int raise_first);   /* 1: this library's kernels over peer memory; 0: NCCL */
 int qw4sh_graph_try(const QW4ShWork *work, const void *layer, const void *x, const void *y, const void *ids, const void *weights,
                     size_t tokens, int mode);
 int qw4sh_graph_finish(const QW4ShWork *work, int enqueue_failed);

@@ -168,12 +168,13 @@ __global__ void ep_signal_partial_kernel(PeerTable pt, uint32_t rank, uint32_t w
     for (uint32_t r = 0; r < world; r++) if (r != rank) st_release_sys(pt.flags[r] + EP_FLAG_PARTIAL + rank, epoch);
 }
 // Lane r waits until rank r's epoch in this rank's flag row has reached this rank's own (the ranks step together).
+constexpr uint32_t EP_WAIT_POLLS = 1u << 22;                                  // about eight seconds with the sleeps below
 __global__ void __launch_bounds__(32) ep_wait_kernel(const uint32_t *flags_local, uint32_t base, const uint32_t *own_epoch, uint32_t rank,
-                                                     uint32_t world, uint32_t *status) {
+                                                     uint32_t world, uint32_t limit, uint32_t *status) {
     const uint32_t r = threadIdx.x;
     if (r >= world || r == rank) return;
     const uint32_t want = *own_epoch;
-    for (uint32_t polls = 0; polls < (1u << 22); polls++) {                     // about eight seconds with the sleeps below
+    for (uint32_t polls = 0; polls < limit; polls++) {
         if ((int32_t)(ld_acquire_sys(flags_local + base + r) - want) >= 0) return;
         __nanosleep(polls < 64 ? 20 : polls < 4096 ? 200 : 2000);
     }
@@ -438,7 +439,7 @@ extern "C" int qw4sh_ep_all_gather(QW4ShEp *ep, size_t floats_per_rank, uint32_t
         const uint32_t quads = (uint32_t)(floats_per_rank / 4), blocks = (quads + 255) / 256;
         ep_push_kernel<<<blocks < 296 ? blocks : 296, 256, 0, (cudaStream_t)stream>>>(ep->msg_local, quads, ep->table, (uint32_t)ep->rank, (uint32_t)ep->world, ep->state);
         qw4sh_note_launch("ep_push_kernel");
-        ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->flags, EP_FLAG_ROWS, &ep->state->epoch_rows, (uint32_t)ep->rank, (uint32_t)ep->world, status);
+        ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->flags, EP_FLAG_ROWS, &ep->state->epoch_rows, (uint32_t)ep->rank, (uint32_t)ep->world, EP_WAIT_POLLS, status);
         return qw4sh_note_launch("ep_wait_kernel");
     }
     return nccl_check(g_nccl.all_gather(ep->msg_local, ep->msg_all, floats_per_rank, NCCL_FLOAT, ep->comm, (cudaStream_t)stream), "ncclAllGather");
@@ -450,10 +451,31 @@ extern "C" int qw4sh_ep_reduce_scatter(QW4ShEp *ep, float *y, size_t floats_per_
         const uint32_t quads = (uint32_t)(floats_per_rank / 4), blocks = (quads + 255) / 256;
         ep_signal_partial_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->table, (uint32_t)ep->rank, (uint32_t)ep->world, ep->state);
         qw4sh_note_launch("ep_signal_partial_kernel");
-        ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->flags, EP_FLAG_PARTIAL, &ep->state->epoch_partial, (uint32_t)ep->rank, (uint32_t)ep->world, status);
+        ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->flags, EP_FLAG_PARTIAL, &ep->state->epoch_partial, (uint32_t)ep->rank, (uint32_t)ep->world, EP_WAIT_POLLS, status);
         qw4sh_note_launch("ep_wait_kernel");
         ep_pull_sum_kernel<<<blocks < 592 ? blocks : 592, 256, 0, (cudaStream_t)stream>>>(ep->table, y, quads, (uint32_t)ep->rank, (uint32_t)ep->world);
         return qw4sh_note_launch("ep_pull_sum_kernel");
     }
     return nccl_check(g_nccl.reduce_scatter(ep->partial, y, floats_per_rank, NCCL_FLOAT, NCCL_SUM, ep->comm, (cudaStream_t)stream), "ncclReduceScatter");
+}
+
+// Test aid: the wait kernel on a flag row that nothing raises, as rank 0 of two, with a short poll limit (at most
+// 65536 polls, about a tenth of a second).  Returns the status bits the kernel left (QW4SH_ERR_STATE when the wait
+// ran out, as it must) or a negative value on a CUDA error; the context stays usable either way.
+extern "C" int qw4sh_ep_wait_probe(uint32_t polls, int raise_first) {
+    uint32_t *words = nullptr;                                                  // [0..15] flag row, [16] own epoch, [17] status
+    CU(cudaMalloc(&words, 32 * sizeof(uint32_t)));
+    uint32_t host[32] = {0};
+    host[16] = 1;                                                               // this rank is at epoch 1
+    if (raise_first) host[EP_FLAG_ROWS + 1] = 1;                                // ... and so is the peer (the wait returns at once)
+    cudaError_t e = cudaMemcpy(words, host, sizeof host, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        ep_wait_kernel<<<1, 32>>>(words, EP_FLAG_ROWS, words + 16, 0u, 2u, polls < 65536u ? polls : 65536u, words + 17);
+        qw4sh_note_launch("ep_wait_kernel");
+        e = cudaDeviceSynchronize();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(host, words, sizeof host, cudaMemcpyDeviceToHost);
+    cudaFree(words);
+    if (e != cudaSuccess) { qw4sh_fail_text(cudaGetErrorString(e)); return -1; }
+    return (int)host[17];
 }

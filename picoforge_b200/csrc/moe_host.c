@@ -485,6 +485,10 @@ void qw4cu_ep_trace(int on) { qw4sh_ep_trace(on); }
 uint64_t qw4cu_ep_trace_read(double *ms, int n) { return ms ? qw4sh_ep_trace_read(ms, n) : 0; }
 void qw4cu_ep_destroy(QW4CuEp *ep) { if (ep) { qw4sh_ep_destroy(ep->shim); free(ep); } }
 int qw4cu_ep_transport(const QW4CuEp *ep) { return ep ? qw4sh_ep_transport(ep->shim) : 0; }
+int qw4cu_ep_wait_probe(uint32_t polls, int raise_first) {
+    const int bits = qw4sh_ep_wait_probe(polls, raise_first);
+    return bits < 0 ? -1 : (bits & QW4SH_ERR_STATE) ? 1 : 0;
+}
 size_t qw4cu_ep_row_floats(const Qwen4Moe *m) { return m ? qw4sh_ep_row_floats((uint32_t)m->c.hidden_size, (uint32_t)m->c.top_k) : 0; }
 
 static Qwen4Status ep_shard(const Qwen4Moe *m, size_t world, size_t rank, Qwen4Error *err) {

@@ -138,6 +138,20 @@ def test_sharded_layer_matches_the_oracle_with_the_ranks_played_in_one_process(g
     assert np.abs(y - want["y"]).max() <= 1e-3
 
 
+@pytest.mark.gpu
+def test_a_wait_that_nothing_satisfies_runs_out_and_reports(gpu):
+    """The epoch wait of the peer transport is bounded: on a flag that no peer raises it gives up after its poll
+    limit and records the state error; the context stays usable (the next forward works)."""
+    from picoforge_b200 import abi, synth
+    from picoforge_b200.layer import MoeLayer
+    assert gpu.lib.qw4cu_ep_wait_probe(2000, 1) == 0                            # the peer is already there: satisfied at once
+    assert gpu.lib.qw4cu_ep_wait_probe(2000, 0) == 1                            # nobody raises the flag: the wait runs out
+    spec = synth.make_layer(5, routed_type=abi.Q4_K, shared_type=abi.Q4_K, experts=8, top_k=2, hidden=512, inter=256, shared_inter=256)
+    with MoeLayer(gpu, spec, 2) as layer:
+        y, _, _ = layer.forward(synth.activations(5, 2, 512))
+    assert np.isfinite(y).all()
+
+
 def _nccl_worker(rank, world, port, routed, tokens, results):
     import ctypes as C
     import torch.distributed as dist
