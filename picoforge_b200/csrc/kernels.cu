@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(256) router_gemm_kernel(DevTensor router, DevT
                                                           float *__restrict__ logits, float *__restrict__ shared_logit, uint32_t *status) {
     // columns per stage: the narrower the tile of router rows, the less arithmetic a stage holds, so it covers more
     // columns to keep the global-memory round trip of the next stage hidden (two stages of shared memory, <= 45 KB)
-    constexpr int BM = 16 * TI, BN = 16 * TJ, BK = TJ >= 4 ? 16 : TJ == 2 ? 32 : 64, PASSES = BK / 16;
+    constexpr int BM = 16 * TI, BN = 16 * TJ, BK = TJ >= 2 ? 32 : 64, PASSES = BK / 16;
     __shared__ __align__(16) float xs[2][BK][BM + 4], ws[2][BK][BN + 4];
     const uint32_t experts = router.n_out, K = router.k_logical;
     const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
