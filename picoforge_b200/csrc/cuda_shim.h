@@ -29,6 +29,9 @@ typedef struct {
      * qw4sh_fused_prepare once the images are resident; ready = 0 when the layer does not fit that path */
     unsigned char fused_maps[4][128];
     int fused_maps_ready;
+    /* the same path: expanded images (4-bit codes) of the IQ2_XXS expert tensors, owned by the layer */
+    void *fused_alt[8];
+    size_t fused_alt_bytes;
 } QW4ShLayer;
 
 /* Device scratch of one workspace, sized for `cap` tokens. */
@@ -149,6 +152,7 @@ int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const fl
  * (default), 0 never.  fused_decode launches it; phase_clocks copies CTA 0's SM clock at its
  * phase boundaries of the workspace's last launch (after a synchronise). */
 int qw4sh_fused_prepare(QW4ShLayer *layer);
+void qw4sh_fused_release(QW4ShLayer *layer);
 int qw4sh_fused_supported(const QW4ShLayer *layer, size_t tokens, const float *x, const float *y, int sm_count);
 void qw4sh_set_fused_decode(int mode);
 int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,

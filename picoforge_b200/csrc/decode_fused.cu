@@ -22,8 +22,9 @@
 //
 //   A  x -> shared memory, int8 digit pairs of x, tree-summed logits of rows sc, sc + NS, ...
 //   B  work unit = 8 gate rows + the same 8 up rows of one expert (gate in MMA rows 0-7, up in
-//      8-15); a unit is cut into K slices dealt to the CTA's warps, each warp fetching slices with
-//      TMA bulk copies into its own ring and feeding int8 tensor-core MMAs with the raw codes.
+//      8-15); a unit is cut into slices of 512 columns dealt to the CTA's warps, each warp fetching
+//      slices into its own ring (Q4_K: one 3-D tensor-map request per matrix; IQ2_XXS: one bulk copy
+//      of a contiguous span of its expanded image) and feeding int8 tensor-core MMAs with the codes.
 //      Units come in granules of four (32 activation columns): the warp that sums a granule's
 //      slices applies SwiGLU and writes the activation as int8 digit pairs with ONE SCALE PER
 //      32-COLUMN CHUNK, so that no row maximum has to cross the grid and phase C starts with a
@@ -58,8 +59,9 @@ constexpr int FMAXK = 16;                       // top-k limit
 constexpr int FMAXE = 512;                      // experts limit
 constexpr int FMAXSRC = FTOK * FMAXK + 1;       // shared expert + distinct routed experts
 constexpr int FRMAX = 4;                        // router rows per streaming CTA
-constexpr int FNS = 2;                          // ring stages per warp
-constexpr uint32_t FSTAGE = 4608;               // bytes per ring stage (IQ2_XXS: 4096 payload + 512 super-scales)
+constexpr int FNS = 2;                          // ring stages per warp, gate/up phase (three stages fit and were measured: no faster)
+constexpr int FNC = 2;                          // ring stages per warp, down phase
+constexpr uint32_t FSTAGE = 4608;               // bytes per ring stage: 16 rows x 288 bytes (512 columns of either format)
 constexpr uint32_t F_LUT_GRID = 256 * 128, F_LUT_SIGN = 128 * 128, F_LUT_BYTES = F_LUT_GRID + F_LUT_SIGN;
 constexpr uint32_t FZP = FMAXE + 4;             // pitch of a logit row in shared memory (floats)
 constexpr int CROWS = 32;                       // router rows per chain CTA (lane = row).  64 rows (two chain warps per token, nine
@@ -85,7 +87,7 @@ struct FusedArgs {
     float2 *asc;                                // [T*k + T][imax / 32] per chunk: scale, sum of the chunk's represented values
     uint32_t *ids_out;
     float *weights_out;
-    const uint8_t *lut;                         // IQ2_XXS tables image (F_LUT_BYTES) or nullptr
+    const uint8_t *lut;                         // unused (no format of this path needs tables)
     uint32_t *sync;                             // counters (S_*), then the phase clocks of the first streaming CTA
     uint32_t *status;
     uint32_t partial_slices;                    // capacity of the partial-sum buffer (slices per CTA)
@@ -149,7 +151,7 @@ __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max,
     c = (c + 127) & ~127u;
     p.asc = c; c += rows_c * (inter_max / 32) * 8;
     c = (c + 127) & ~127u;
-    p.tiles = c; c += FW * FNS * FSTAGE;
+    p.tiles = c; c += FW * FNC * FSTAGE;
     p.cpartial = c; c += FW * 32 * 8;
     uint32_t m = a > b ? a : b;
     m = m > c ? m : c;
@@ -372,80 +374,56 @@ template <> struct HalvesS<T_Q4_K> {
     }
 };
 
-// The IQ2_XXS tables in shared memory, built by the CTA itself from the 2-bit level list.
-// Grid: 256 entries of 128 bytes, each holding 8 copies of {magnitudes 0-3, magnitudes 4-7, the same
-// negated byte by byte} (lane L reads copy L % 8 with one 128-bit load).  Signs: 128 entries of 128
-// bytes, each 16 copies of two byte-permute selectors (lane L reads copy L % 16 with a 64-bit load):
-// nibble i of a selector is i for a positive weight and i + 4 for a negative one, so that ONE prmt
-// of (magnitudes, negated magnitudes) yields four signed int8 weights.  The eighth sign of a group
-// is the parity of the seven stored ones.  Neither table has bank conflicts.
-__device__ __forceinline__ void build_iq2_tables(uint8_t *lut) {
-    for (uint32_t entry = threadIdx.x; entry < 256 + 128; entry += blockDim.x) {
-        uint4 *to = reinterpret_cast<uint4 *>(lut + entry * 128u);            // the sign entries follow the grid's
-        if (entry < 256) {
-            const uint32_t levels = c_iq2_levels[entry];
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                lo |= iq2_magnitude((levels >> (2 * j)) & 3u) << (8 * j);
-                hi |= iq2_magnitude((levels >> (2 * j + 8)) & 3u) << (8 * j);
-            }
-            // magnitudes are never zero, so (v ^ 0xff) + 1 = -v stays inside its byte
-            const uint4 v = make_uint4(lo, hi, (lo ^ 0xffffffffu) + 0x01010101u, (hi ^ 0xffffffffu) + 0x01010101u);
-#pragma unroll
-            for (int c = 0; c < 8; c++) to[c] = v;
-        } else {
-            const uint32_t signs = iq2_signs8(entry - 256);
-            uint32_t lo = 0x3210u, hi = 0x3210u;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if ((signs >> j) & 1u) lo += 4u << (4 * j);
-                if ((signs >> (j + 4)) & 1u) hi += 4u << (4 * j);
-            }
-#pragma unroll
-            for (int c = 0; c < 8; c++) to[c] = make_uint4(lo, hi, lo, hi);
-        }
-    }
+// IQ2_XXS on this path is read from a second resident image, made at create (iq2_expand_kernel below): every
+// weight as a 4-bit code (level | sign << 2), laid out for this kernel.  2.06 bits per weight become 4.5, and in
+// exchange a lane turns eight weights into MMA operands with one shift and two byte permutes against an 8-byte
+// table held in two registers (the codebook and sign look-ups of the packed form cost four shared-memory reads per
+// eight weights and bound the whole kernel).  Decoded values are the same bits.
+//
+// Block of 512 columns, 288 bytes (the geometry of two Q4_K blocks, so slices, stages and tensor-map boxes are
+// shared with that format):
+//   [0, 256)    codes: the 32-bit word of lane t for 32-column chunk j of half h (columns 128 h + 32 j + 8 t .. + 7,
+//               nibble i = column + i) sits at 64 h + 16 t + 4 j, so a lane reads its four chunks of a half with
+//               one 128-bit load;
+//   [256, 272)  2 * scale + 1 of the sixteen 32-column chunks, one byte each;
+//   [272, 276)  the fp16 super-scales of the two 256-column source blocks;  [276, 288) zero.
+constexpr uint32_t T_IQ2N = 116;                        // not a GGUF type: the expanded image of an IQ2_XXS tensor
+constexpr uint32_t IQ2N_LO = 8u | 25u << 8 | 43u << 16 | 60u << 24;                                  // iq2_magnitude(0..3)
+constexpr uint32_t IQ2N_HI = (256u - 8u) | (256u - 25u) << 8 | (256u - 43u) << 16 | (256u - 60u) << 24;   // the same, negated
+
+__device__ __forceinline__ uint4 lds_ring4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
 }
-// Signed int8 weights of the lane's eight columns of one group: g.x holds the four grid indices
-// (byte t is the lane's), g.y the four 7-bit sign fields and the scale.  `rg` / `rs` are the
-// lane's rotate counts that bring its index byte / sign field to bit 7, where the tables' 128-byte
-// entry pitch wants them.
-__device__ __forceinline__ void iq2_weights(const uint2 g, uint32_t grid, uint32_t sign, uint32_t rg, uint32_t rs, uint32_t &lo, uint32_t &hi) {
-    const uint4 v = lds_table4(grid + (__funnelshift_r(g.x, g.x, rg) & 0x7f80u));
-    const uint2 sel = lds_table2(sign + (__funnelshift_r(g.y, g.y, rs) & 0x3f80u));
-    lo = __byte_perm(v.x, v.z, sel.x);
-    hi = __byte_perm(v.y, v.w, sel.y);
+__device__ __forceinline__ uint32_t lds_ring1(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
 }
 
-// IQ2_XXS: r0 / r1 point at the two rows' first 8-byte group of the span (a multiple of 16
-// groups from the row start, so the in-row swizzle `swz` applies to the local index); d0p / d1p
-// at the fp16 super-scales of the span's first block.
-template <> struct Halves<T_IQ2_XXS> {
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
-                                            const uint16_t *d1p, const uint8_t *lut, uint32_t t, const uint8_t *xq, const int2 *,
+template <> struct Halves<T_IQ2N> {
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t, const uint16_t *,
+                                            const uint16_t *, const uint8_t *, uint32_t t, const uint8_t *xq, const int2 *,
                                             float &f0, float &f1) {
-        const uint32_t grid = fs_u32(lut) + (threadIdx.x & 7u) * 16u, sign = fs_u32(lut) + F_LUT_GRID + (threadIdx.x & 15u) * 8u;
-        const uint32_t rg = (8u * t + 25u) & 31u, rs = (7u * t + 25u) & 31u;
-        const uint32_t a0s = fs_u32(r0), a1s = fs_u32(r1), d0s = fs_u32(d0p), d1s = fs_u32(d1p);
+        const uint32_t a0s = fs_u32(r0) + 16u * t, a1s = fs_u32(r1) + 16u * t;
         uint32_t xs = fs_u32(xq);
 #pragma unroll 1
         for (uint32_t h = 0; h < halves; h++, xs += 128) {
-            const uint32_t at = ((h * 4u) ^ swz) * 8u;
-            uint2 g0[4], g1[4], bq[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) { g0[j] = lds_ring2(a0s + at + 8 * j); g1[j] = lds_ring2(a1s + at + 8 * j); bq[j] = lds_ring2(xs + j * 32); }
-            const uint32_t dh0 = lds_ring_u16(d0s + (h >> 1) * 2u), dh1 = lds_ring_u16(d1s + (h >> 1) * 2u);
+            const uint32_t at = (h >> 2) * 288u, hh = h & 3u;
+            const uint4 w0 = lds_ring4(a0s + at + 64u * hh), w1 = lds_ring4(a1s + at + 64u * hh);
+            const uint32_t s0 = lds_ring1(a0s - 16u * t + at + 256u + 4u * hh), s1 = lds_ring1(a1s - 16u * t + at + 256u + 4u * hh);
+            const uint32_t dh0 = lds_ring_u16(a0s - 16u * t + at + 272u + (hh >> 1) * 2u), dh1 = lds_ring_u16(a1s - 16u * t + at + 272u + (hh >> 1) * 2u);
+            const uint32_t c0[4] = {w0.x, w0.y, w0.z, w0.w}, c1[4] = {w1.x, w1.y, w1.z, w1.w};
             int iacc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                uint32_t a0, a1, a2, a3;
-                iq2_weights(g0[j], grid, sign, rg, rs, a0, a2);
-                iq2_weights(g1[j], grid, sign, rg, rs, a1, a3);
+                const uint2 bq = lds_ring2(xs + j * 32);
                 int c[4];
-                fmma_zero(c, a0, a1, a2, a3, bq[j].x, bq[j].y);
-                const int w0 = (int)((g0[j].y >> 27) | 1u), w1 = (int)((g1[j].y >> 27) | 1u);         // 2 * scale + 1
-                iacc[0] += c[0] * w0; iacc[1] += c[1] * w0; iacc[2] += c[2] * w1; iacc[3] += c[3] * w1;
+                fmma_zero(c, __byte_perm(IQ2N_LO, IQ2N_HI, c0[j]), __byte_perm(IQ2N_LO, IQ2N_HI, c1[j]),
+                          __byte_perm(IQ2N_LO, IQ2N_HI, c0[j] >> 16), __byte_perm(IQ2N_LO, IQ2N_HI, c1[j] >> 16), bq.x, bq.y);
+                const int k0 = (int)((s0 >> (8 * j)) & 0xffu), k1 = (int)((s1 >> (8 * j)) & 0xffu);               // 2 * scale + 1
+                iacc[0] += c[0] * k0; iacc[1] += c[1] * k0; iacc[2] += c[2] * k1; iacc[3] += c[3] * k1;
             }
             const float lo = 1.0f / 254.0f;
             const float d0 = __half2float(__ushort_as_half((uint16_t)dh0)) * 0.125f, d1 = __half2float(__ushort_as_half((uint16_t)dh1)) * 0.125f;
@@ -454,37 +432,31 @@ template <> struct Halves<T_IQ2_XXS> {
         }
     }
 };
-template <> struct HalvesS<T_IQ2_XXS> {
-    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t swz, const uint16_t *d0p,
-                                            const uint16_t *d1p, const uint8_t *lut, uint32_t t, const uint8_t *aq, const float2 *asc,
+template <> struct HalvesS<T_IQ2N> {
+    static __device__ __forceinline__ void run(const uint8_t *r0, const uint8_t *r1, uint32_t halves, uint32_t, const uint16_t *,
+                                            const uint16_t *, const uint8_t *, uint32_t t, const uint8_t *aq, const float2 *asc,
                                             float &f0, float &f1) {
-        const uint32_t grid = fs_u32(lut) + (threadIdx.x & 7u) * 16u, sign = fs_u32(lut) + F_LUT_GRID + (threadIdx.x & 15u) * 8u;
-        const uint32_t rg = (8u * t + 25u) & 31u, rs = (7u * t + 25u) & 31u;
-        const uint32_t a0s = fs_u32(r0), a1s = fs_u32(r1), d0s = fs_u32(d0p), d1s = fs_u32(d1p);
+        const uint32_t a0s = fs_u32(r0) + 16u * t, a1s = fs_u32(r1) + 16u * t;
         uint32_t xs = fs_u32(aq), ss = fs_u32(asc);
 #pragma unroll 1
         for (uint32_t h = 0; h < halves; h++, xs += 128, ss += 32) {
-            const uint32_t at = ((h * 4u) ^ swz) * 8u;
-            uint2 g0[4], g1[4], bq[4], sc[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                g0[j] = lds_ring2(a0s + at + 8 * j); g1[j] = lds_ring2(a1s + at + 8 * j);
-                bq[j] = lds_ring2(xs + j * 32); sc[j] = lds_ring2(ss + j * 8);
-            }
-            const uint32_t dh0 = lds_ring_u16(d0s + (h >> 1) * 2u), dh1 = lds_ring_u16(d1s + (h >> 1) * 2u);
+            const uint32_t at = (h >> 2) * 288u, hh = h & 3u;
+            const uint4 w0 = lds_ring4(a0s + at + 64u * hh), w1 = lds_ring4(a1s + at + 64u * hh);
+            const uint32_t s0 = lds_ring1(a0s - 16u * t + at + 256u + 4u * hh), s1 = lds_ring1(a1s - 16u * t + at + 256u + 4u * hh);
+            const uint32_t dh0 = lds_ring_u16(a0s - 16u * t + at + 272u + (hh >> 1) * 2u), dh1 = lds_ring_u16(a1s - 16u * t + at + 272u + (hh >> 1) * 2u);
+            const uint32_t c0[4] = {w0.x, w0.y, w0.z, w0.w}, c1[4] = {w1.x, w1.y, w1.z, w1.w};
             float fa0 = 0.0f, fa1 = 0.0f;
             const float lo = 1.0f / 254.0f;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                uint32_t a0, a1, a2, a3;
-                iq2_weights(g0[j], grid, sign, rg, rs, a0, a2);
-                iq2_weights(g1[j], grid, sign, rg, rs, a1, a3);
+                const uint2 bq = lds_ring2(xs + j * 32), sc = lds_ring2(ss + j * 8);
                 int c[4];
-                fmma_zero(c, a0, a1, a2, a3, bq[j].x, bq[j].y);
-                const float w0 = (float)((g0[j].y >> 27) | 1u), w1 = (float)((g1[j].y >> 27) | 1u);   // 2 * scale + 1
-                const float a = __uint_as_float(sc[j].x);
-                fa0 = fmaf(w0 * a, fmaf((float)c[1], lo, (float)c[0]), fa0);
-                fa1 = fmaf(w1 * a, fmaf((float)c[3], lo, (float)c[2]), fa1);
+                fmma_zero(c, __byte_perm(IQ2N_LO, IQ2N_HI, c0[j]), __byte_perm(IQ2N_LO, IQ2N_HI, c1[j]),
+                          __byte_perm(IQ2N_LO, IQ2N_HI, c0[j] >> 16), __byte_perm(IQ2N_LO, IQ2N_HI, c1[j] >> 16), bq.x, bq.y);
+                const float k0 = (float)((s0 >> (8 * j)) & 0xffu), k1 = (float)((s1 >> (8 * j)) & 0xffu);       // 2 * scale + 1
+                const float a = __uint_as_float(sc.x);
+                fa0 = fmaf(k0 * a, fmaf((float)c[1], lo, (float)c[0]), fa0);
+                fa1 = fmaf(k1 * a, fmaf((float)c[3], lo, (float)c[2]), fa1);
             }
             const float d0 = __half2float(__ushort_as_half((uint16_t)dh0)) * 0.125f, d1 = __half2float(__ushort_as_half((uint16_t)dh1)) * 0.125f;
             f0 = fmaf(d0, fa0, f0);
@@ -493,26 +465,63 @@ template <> struct HalvesS<T_IQ2_XXS> {
     }
 };
 
+// One thread per 32-column chunk of a row: the chunk's 32 codes, its scale byte, and (first chunk of a 256-column
+// source block) the block's super-scale, from the resident IQ2_XXS image into the expanded one.
+// which < 0: rows in order, [expert][row][blocks] (down tiles: sixteen rows are one contiguous span).  which = 0 / 1
+// (gate / up): unit slices, [expert][unit of 8 rows][block][gate rows | up rows][288 bytes], so that the sixteen row
+// pieces of one ring stage are ONE contiguous span of 4608 bytes.
+__global__ void __launch_bounds__(256) iq2_expand_kernel(DevTensor t, uint8_t *__restrict__ out, int which) {
+    const uint32_t nb = t.k_storage >> 8, chunks = t.k_storage >> 5;
+    const uint64_t rows = (uint64_t)t.n_out * t.n_experts, total = rows * chunks;
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const uint64_t grow = i / chunks;                                          // expert * n_out + row
+    const uint32_t q = (uint32_t)(i % chunks), expert = (uint32_t)(grow / t.n_out), row = (uint32_t)(grow % t.n_out);
+    const uint8_t *mat = t.data + (uint64_t)expert * t.expert_bytes;
+    const uint32_t blk = q >> 3, ch = q & 7u;
+    const uint8_t *group = mat + ((uint64_t)row * nb * 8u + ((blk * 8u + ch) ^ iq2_swizzle(row, nb))) * 8u;
+    const uint32_t bits = load_u32(group + 4);
+    const uint32_t nb5 = t.k_storage >> 9;                                      // 512-column blocks per row
+    uint8_t *block = which < 0 ? out + (grow * nb5 + (q >> 4)) * 288u           // the 512-column block of this chunk
+                               : out + ((((uint64_t)expert * (t.n_out >> 3) + (row >> 3)) * nb5 + (q >> 4)) * 2u + (uint32_t)which) * 2304u + (row & 7u) * 288u;
+    const uint32_t h = (q >> 2) & 3u, j = q & 3u;
+    for (uint32_t slot = 0; slot < 4; slot++) {                                 // slot = lane t of the consumer: columns 8 t .. 8 t + 7
+        const uint32_t levels = c_iq2_levels[group[slot]], signs = iq2_signs8((bits >> (7 * slot)) & 127u);
+        uint32_t word = 0;
+        for (uint32_t c = 0; c < 8; c++) word |= (((levels >> (2 * c)) & 3u) | (((signs >> c) & 1u) << 2)) << (4 * c);
+        *reinterpret_cast<uint32_t *>(block + 64u * h + 16u * slot + 4u * j) = word;
+    }
+    block[256u + 4u * h + j] = (uint8_t)(2u * (bits >> 28) + 1u);
+    if (ch == 0) {
+        const uint64_t blocks = (uint64_t)t.n_out * nb;
+        *reinterpret_cast<uint16_t *>(block + 272u + (blk & 1u) * 2u) = (uint16_t)load_u16(mat + blocks * 64u + ((uint64_t)row * nb + blk) * 2u);
+    }
+}
+
 // Geometry of one format inside the rings.
 template <uint32_t TYPE> struct FGeo;
 template <> struct FGeo<T_Q4_K> { static constexpr uint32_t SLICE_BLOCKS = 2, BLOCK_BYTES = 144; };      // 512 columns, 288 B per row
-template <> struct FGeo<T_IQ2_XXS> { static constexpr uint32_t SLICE_BLOCKS = 4, BLOCK_BYTES = 64; };    // 1024 columns, 256 B per row
+template <> struct FGeo<T_IQ2N> { static constexpr uint32_t SLICE_BLOCKS = 2, BLOCK_BYTES = 144; };      // the same: one 288-byte block of 512 columns
 
 // Copies of slice `s` of a gate/up unit (8 gate rows + 8 up rows from row `row0` of expert `expert`) into `stage`:
-// row r at r * slice bytes; IQ2_XXS also gets the unit's super-scales behind the rows.  The eight row pieces of a
+// row r at r * slice bytes.  The eight row pieces of a
 // matrix are ONE tensor-map request (issuing a request costs the warp about a hundred cycles whatever its size).
 template <uint32_t TYPE>
 __device__ __forceinline__ void issue_unit_slice(const CUtensorMap *gate_map, const CUtensorMap *up_map, const uint8_t *gate_mat,
                                               const uint8_t *up_mat, uint32_t expert, uint32_t n_out, uint32_t nb, uint32_t row0, uint32_t s,
                                               uint8_t *stage, uint64_t *bar, uint32_t lane) {
     constexpr uint32_t slice_bytes = FGeo<TYPE>::SLICE_BLOCKS * FGeo<TYPE>::BLOCK_BYTES;
-    if (lane == 0) fbar_expect(bar, 16 * slice_bytes + (TYPE == T_IQ2_XXS ? 2 * 8 * nb * 2 : 0));
+    if (TYPE == T_IQ2N) {
+        // the expanded image keeps a unit slice (gate rows, then up rows) as one span: gate_mat is the image's base
+        if (lane == 0) {
+            fbar_expect(bar, 16 * slice_bytes);
+            fbulk(stage, gate_mat + ((((uint64_t)expert * (n_out >> 3) + (row0 >> 3)) * (nb >> 1) + s) * 16u) * slice_bytes, 16 * slice_bytes, bar);
+        }
+        return;
+    }
+    if (lane == 0) fbar_expect(bar, 16 * slice_bytes);
     __syncwarp();
     if (lane < 2) ftma_rows(stage + lane * 8 * slice_bytes, lane ? up_map : gate_map, s * (slice_bytes / 4), row0, expert, bar);
-    else if (TYPE == T_IQ2_XXS && lane < 4) {
-        const uint8_t *mat = lane == 2 ? gate_mat : up_mat;                 // the matrix of this expert
-        fbulk(stage + 16 * slice_bytes + (lane - 2) * 8 * nb * 2, mat + n_out * nb * 64u + row0 * nb * 2u, 8 * nb * 2, bar);
-    }
 }
 template <uint32_t TYPE>
 __device__ __forceinline__ void consume_unit_slice(const uint8_t *stage, uint32_t nb, uint32_t s, const uint8_t *lut, const uint8_t *xq_lane,
@@ -523,16 +532,14 @@ __device__ __forceinline__ void consume_unit_slice(const uint8_t *stage, uint32_
                       d + (8 + g) * nb + s * SB, lut, t, xq_lane + s * SB * 256u, xsum_tok + s * SB * 8u, f0, f1);
 }
 
-// Down tile: 16 rows x K (K <= 512 for Q4_K, <= 1024 for IQ2_XXS), fetched whole; IQ2_XXS
-// super-scales at +4096.
+// Down tile: 16 rows x K (K <= 512), fetched whole.
 template <uint32_t TYPE>
 __device__ __forceinline__ void issue_down_tile(const uint8_t *mat, uint32_t n_out, uint32_t nb, uint32_t row0, uint8_t *stage, uint64_t *bar,
                                              uint32_t lane) {
     const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
     if (lane == 0) {
-        fbar_expect(bar, 16 * row_bytes + (TYPE == T_IQ2_XXS ? 16 * nb * 2 : 0));
+        fbar_expect(bar, 16 * row_bytes);
         fbulk(stage, mat + row0 * row_bytes, 16 * row_bytes, bar);
-        if (TYPE == T_IQ2_XXS) fbulk(stage + 4096, mat + n_out * nb * 64u + row0 * nb * 2u, 16 * nb * 2, bar);
     }
 }
 template <uint32_t TYPE>
@@ -989,12 +996,14 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
 
     const uint32_t T = a.tokens, H = a.hidden, E = a.experts, k = a.top_k, I = a.inter, IS = a.shared_inter;
     const uint32_t pairs = T * k, rows_c = pairs + T, imax = I > IS ? I : IS;
-    constexpr bool LUT = RT == T_IQ2_XXS || ST == T_IQ2_XXS;
+    constexpr bool LUT = false;                                                // no format on this path needs tables in shared memory
     const FPlan p = make_fplan(H, imax, rows_c, a.partial_slices, LUT);
     const uint32_t warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t sc = blockIdx.x - NC, NS = gridDim.x - NC;
-    uint64_t *ringbar = reinterpret_cast<uint64_t *>(smem + p.bars);           // [FW][FNS]
+    uint64_t *ringbar = reinterpret_cast<uint64_t *>(smem + p.bars);           // [FW][FNS], four single ones, then [FW][FNC]
     uint64_t *rowbar = ringbar + FW * FNS;
+    uint64_t *tilebar = ringbar + FW * FNS + 4 + (threadIdx.x >> 5) * FNC;     // this warp's barriers of the down phase
+    static_assert((FW * FNS + 4 + FW * FNC) * 8 <= 512, "the barrier block is 512 bytes");
     uint64_t *lutbar = rowbar + 1;
     uint64_t *xbar = lutbar + 1;                                               // x rows (phase A), then the fast logits (phase B)
     uint64_t *abar = xbar + 1;                                                 // activation digits (phase C)
@@ -1013,12 +1022,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     unsigned long long *clocks = reinterpret_cast<unsigned long long *>(a.sync + S_CLOCKS);
     const bool clocked = sc == 0 && tid == 0;
 
-    if (tid < FW * FNS + 4) {                                                  // the barriers lie one after the other: one thread each
+    if (tid < FW * FNS + 4 + FW * FNC) {                                       // the barriers lie one after the other: one thread each
         fbar_init(&ringbar[tid], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 8) misc_f[tid] = 0.0f;
-    if (LUT) build_iq2_tables(smem + p.lut);
     float4 *xconsts = reinterpret_cast<float4 *>(smem + p.misc + 512);
     __syncthreads();
 
@@ -1221,8 +1229,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 if (sh) issue_unit_slice<ST>(&map_sg, &map_su, a.w[4].data, a.w[5].data, 0, IS, nbh, u * 8, s, stage, &bar[at % FNS], lane);
                 else {
                     const uint32_t v = u - gs * 4, ur = gr * 4, e = srcs[1 + v / ur].expert;
-                    issue_unit_slice<RT>(&map_g, &map_u, a.w[1].data + (uint64_t)e * a.w[1].expert_bytes,
-                                         a.w[2].data + (uint64_t)e * a.w[2].expert_bytes, e, I, nbh, (v % ur) * 8, s, stage, &bar[at % FNS], lane);
+                    issue_unit_slice<RT>(&map_g, &map_u, a.w[1].data, a.w[2].data, e, I, nbh, (v % ur) * 8, s, stage, &bar[at % FNS], lane);
                 }
             };
             __syncthreads();                                                       // the keys in zs are dead: the ring may be written
@@ -1233,7 +1240,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             for (uint32_t tile = sc; tile < (H >> 4); tile += NS)
                 for (uint32_t j = warp * 4 + lane; lane < 4 && j < n_src; j += FW * 4) {      // a few requests per warp: none of them falls behind
                     const Src s = srcs[j];
-                    const uint32_t rb = s.shared ? (IS >> 8) * (ST == T_Q4_K ? 144u : 64u) : (I >> 8) * (RT == T_Q4_K ? 144u : 64u);
+                    const uint32_t rb = (s.shared ? IS >> 8 : I >> 8) * 144u;
                     const uint8_t *mat = s.shared ? a.w[6].data : a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes;
                     fprefetch_l2(mat + tile * 16 * rb, 16 * rb);
                 }
@@ -1338,18 +1345,17 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     if (sc < (H >> 4) && lists_ok) {
         uint8_t *aq = region + p.aq;
         float2 *asc = reinterpret_cast<float2 *>(region + p.asc);
-        uint8_t *tiles = region + p.tiles + warp * FNS * FSTAGE;
+        uint8_t *tiles = region + p.tiles + warp * FNC * FSTAGE;
         float2 *cpartial = reinterpret_cast<float2 *>(region + p.cpartial);
         const uint32_t my_src = n_src > warp ? (n_src - 1 - warp) / FW + 1 : 0;
         const uint32_t n_tiles = ((H >> 4) - sc + NS - 1) / NS;
         const uint32_t steps = my_src * n_tiles;
-        auto issue = [&](uint32_t n) {                                         // the ring barriers go on counting where phase B left them
+        auto issue = [&](uint32_t n) {                                         // this phase has ring barriers of its own, counted from zero
             const uint32_t tile = sc + (n / my_src) * NS, j = warp + (n % my_src) * FW;
             const Src s = srcs[j];
-            const uint32_t at = ring_count + n;
-            uint8_t *stage = tiles + (at % FNS) * FSTAGE;
-            if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &bar[at % FNS], lane);
-            else issue_down_tile<RT>(a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes, H, I >> 8, tile * 16, stage, &bar[at % FNS], lane);
+            uint8_t *stage = tiles + (n % FNC) * FSTAGE;
+            if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &tilebar[n % FNC], lane);
+            else issue_down_tile<RT>(a.w[3].data + (uint64_t)s.expert * a.w[3].expert_bytes, H, I >> 8, tile * 16, stage, &tilebar[n % FNC], lane);
         };
         bool ok = __syncthreads_and(alive);                                    // also: phase B's use of the region is over
         if (ok) {
@@ -1361,7 +1367,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 fbulk(aq, a.aq, aq_bytes, abar);
                 fbulk(asc, a.asc, asc_bytes, abar);
             }
-            for (uint32_t n = 0; n < FNS && n < steps; n++) issue(n);
+            for (uint32_t n = 0; n < FNC && n < steps; n++) issue(n);
             ok = __syncthreads_and(fbar_wait(abar, 0, a.status));
         }
         alive = ok;
@@ -1380,10 +1386,9 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 const uint32_t row_t = s.shared ? pairs + (t < T ? t : 0) : (live_t ? t * k + s.slot(t) : 0);
                 const uint8_t *aq_lane = aq + (2 * row_g + (g & 1u)) * p.ap + 8 * t;
                 const float2 *asc_tok = asc + row_t * (imax >> 5);
-                const uint32_t at = ring_count + n;
-                if (alive) alive = fbar_wait(&bar[at % FNS], (at / FNS) & 1u, a.status);
+                if (alive) alive = fbar_wait(&tilebar[n % FNC], (n / FNC) & 1u, a.status);
                 alive = __all_sync(0xffffffffu, alive);
-                const uint8_t *stage = tiles + (at % FNS) * FSTAGE;
+                const uint8_t *stage = tiles + (n % FNC) * FSTAGE;
                 float f0 = 0.0f, f1 = 0.0f;
                 if (alive) {
                     if (s.shared) consume_down_tile<ST>(stage, IS >> 8, lut, aq_lane, asc_tok, g, t, f0, f1);
@@ -1391,7 +1396,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 }
                 __syncwarp();
                 fproxy_fence();
-                if (alive && n + FNS < steps) issue(n + FNS);
+                if (alive && n + FNC < steps) issue(n + FNC);
                 if (live_t) {
                     const float coef = s.shared ? fast_sigmoid(misc_f[4 + t]) : wts_s[t * k + s.slot(t)];
                     acc0 = fmaf(coef, f0, acc0); acc1 = fmaf(coef, f1, acc1);
@@ -1443,7 +1448,7 @@ static int g_wrong_speculation = 0;
 extern "C" void qw4sh_set_wrong_speculation(int on) { g_wrong_speculation = on ? 1 : 0; }
 
 static bool fused_type(uint32_t type) { return type == T_Q4_K || type == T_IQ2_XXS; }
-static uint32_t slice_blocks(uint32_t type) { return type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS; }
+static uint32_t slice_blocks(uint32_t) { return FGeo<T_Q4_K>::SLICE_BLOCKS; }          // both formats of this path: 512 columns per slice
 
 // Chain CTAs: one per 32 rows of the router (the shared expert's router is row E), and at least
 // one per token (chain CTA t routes token t).  The fast mode keeps only the routing CTAs.
@@ -1463,8 +1468,7 @@ static uint32_t partial_capacity(const QW4ShLayer *l, size_t tokens, uint32_t st
 
 static FPlan plan_for(const QW4ShLayer *l, size_t tokens, uint32_t streaming) {
     const uint32_t imax = l->inter > l->shared_inter ? l->inter : l->shared_inter;
-    const bool lut = l->w[1].type == T_IQ2_XXS || l->w[4].type == T_IQ2_XXS;
-    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, streaming), lut);
+    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, streaming), false);
 }
 
 // Bytes of the workspace arrays the kernel needs beyond the common ones (for `cap` tokens, at most FTOK used).
@@ -1480,8 +1484,21 @@ extern "C" void qw4sh_fused_scratch_sizes(const QW4ShLayer *l, size_t *aq_bytes,
 typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-// {32-bit words of a row's packed payload, rows of an expert, experts}; box = one slice of eight rows.
-static int rows_map(const QW4ShTensor *t, CUtensorMap *map) {
+// The tensor this path streams for resident tensor i: the tensor itself (Q4_K) or its expanded image (IQ2_XXS), whose
+// rows have the geometry of Q4_K rows (144 bytes per 256 columns).
+static DevTensor fused_view(const QW4ShLayer *l, int i) {
+    DevTensor t = fdev(l->w[i]);
+    const int holder = (i == 2 || i == 5) ? i - 1 : i;                     // gate and up share the gate's image
+    if (t.type == T_IQ2_XXS && l->fused_alt[holder]) {
+        t.data = (const uint8_t *)l->fused_alt[holder];
+        t.type = T_IQ2N;
+        t.row_bytes = (t.k_storage >> 8) * 144u;
+        t.expert_bytes = (uint64_t)t.row_bytes * t.n_out;
+    }
+    return t;
+}
+// {32-bit words of a row's packed payload, rows of an expert, experts}; box = one slice (288 bytes) of eight rows.
+static int rows_map(const DevTensor &t, CUtensorMap *map) {
     static EncodeTiled encode = nullptr;
     if (!encode) {
         void *fn = nullptr;
@@ -1489,31 +1506,55 @@ static int rows_map(const QW4ShTensor *t, CUtensorMap *map) {
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess || !fn) return -1;
         encode = (EncodeTiled)fn;
     }
-    const uint32_t nb = t->k_storage >> 8;
-    const uint32_t block = t->type == T_Q4_K ? FGeo<T_Q4_K>::BLOCK_BYTES : FGeo<T_IQ2_XXS>::BLOCK_BYTES;
-    const uint32_t slice = (t->type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS) * block;
-    const cuuint64_t dims[3] = {(cuuint64_t)nb * block / 4, t->n_out, t->n_experts};
-    const cuuint64_t strides[2] = {(cuuint64_t)nb * block, t->expert_bytes};
+    constexpr uint32_t slice = FGeo<T_Q4_K>::SLICE_BLOCKS * FGeo<T_Q4_K>::BLOCK_BYTES;
+    const cuuint64_t dims[3] = {(cuuint64_t)t.row_bytes / 4, t.n_out, t.n_experts};
+    const cuuint64_t strides[2] = {(cuuint64_t)t.row_bytes, t.expert_bytes};
     const cuuint32_t box[3] = {slice / 4, 8, 1}, elem[3] = {1, 1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void *)t->data, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void *)t.data, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -2;
 }
 static bool fused_type(uint32_t type);
-// Called once the images are resident.  A layer the path cannot take simply gets no maps; 0 unless encoding failed.
+extern "C" void qw4sh_fused_release(QW4ShLayer *l) {
+    for (int i = 0; i < 8; i++) { if (l->fused_alt[i]) cudaFree(l->fused_alt[i]); l->fused_alt[i] = nullptr; }
+    l->fused_alt_bytes = 0;
+    l->fused_maps_ready = 0;
+}
+// Called once the images are resident.  A layer the path cannot take simply gets no maps and no expanded images; 0
+// unless a CUDA call failed.
 extern "C" int qw4sh_fused_prepare(QW4ShLayer *l) {
     l->fused_maps_ready = 0;
+    l->fused_alt_bytes = 0;
+    for (int i = 0; i < 8; i++) l->fused_alt[i] = nullptr;
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    if (l->w[2].type != l->w[1].type || l->w[3].type != l->w[1].type || l->w[5].type != l->w[4].type || l->w[6].type != l->w[4].type) return 0;
+    for (int i = 1; i <= 6; i++) {
+        const QW4ShTensor *t = &l->w[i];
+        if (!fused_type(t->type) || t->k_storage % 512 || t->k_logical != t->k_storage || t->n_out % 32 || ((uintptr_t)t->data & 15u) ||
+            t->expert_bytes % 16) return 0;
+    }
+    // expanded images: gate and up of a group share one (unit slices interleaved, held by the gate's slot), down has its own
+    for (int i = 1; i <= 6; i++) {
+        if (l->w[i].type != T_IQ2_XXS || i == 2 || i == 5) continue;
+        const bool pair = i == 1 || i == 4;
+        const DevTensor src = fdev(l->w[i]);
+        if (pair && (l->w[i + 1].n_out != src.n_out || l->w[i + 1].k_storage != src.k_storage || l->w[i + 1].n_experts != src.n_experts)) return 0;
+        const size_t bytes = (size_t)src.n_experts * src.n_out * (src.k_storage >> 9) * 288u * (pair ? 2 : 1);
+        cudaError_t e = cudaMalloc(&l->fused_alt[i], bytes);
+        if (e == cudaSuccess) e = cudaMemset(l->fused_alt[i], 0, bytes);
+        if (e == cudaSuccess) {
+            const uint64_t chunks = (uint64_t)src.n_experts * src.n_out * (src.k_storage >> 5);
+            iq2_expand_kernel<<<(unsigned)((chunks + 255) / 256), 256>>>(src, (uint8_t *)l->fused_alt[i], pair ? 0 : -1);
+            if (pair) iq2_expand_kernel<<<(unsigned)((chunks + 255) / 256), 256>>>(fdev(l->w[i + 1]), (uint8_t *)l->fused_alt[i], 1);
+            e = cudaDeviceSynchronize();
+        }
+        if (e != cudaSuccess) { qw4sh_fused_release(l); return -1; }
+        l->fused_alt_bytes += bytes;
+    }
     const int which[4] = {1, 2, 4, 5};
     for (int i = 0; i < 4; i++) {
-        const QW4ShTensor *t = &l->w[which[i]];
-        const uint32_t slice_blocks = t->type == T_Q4_K ? FGeo<T_Q4_K>::SLICE_BLOCKS : FGeo<T_IQ2_XXS>::SLICE_BLOCKS;
-        if (!fused_type(t->type) || t->k_storage % (256 * slice_blocks) || t->k_logical != t->k_storage || t->n_out % 32 ||
-            ((uintptr_t)t->data & 15u) || t->expert_bytes % 16) return 0;
-    }
-    for (int i = 0; i < 4; i++) {
         alignas(64) CUtensorMap map;
-        if (rows_map(&l->w[which[i]], &map)) return -1;
+        if (rows_map(fused_view(l, which[i]), &map)) { qw4sh_fused_release(l); return -1; }
         memcpy(l->fused_maps[i], &map, sizeof map);
     }
     l->fused_maps_ready = 1;
@@ -1533,8 +1574,7 @@ extern "C" int qw4sh_fused_supported(const QW4ShLayer *l, size_t tokens, const f
     if (l->w[2].type != rt || l->w[3].type != rt || l->w[5].type != st || l->w[6].type != st) return 0;
     for (int i = 1; i <= 6; i++) if (l->w[i].k_logical != l->w[i].k_storage) return 0;
     // a down tile (16 rows) must fit one ring stage
-    if (rt == T_Q4_K ? I > 512 : I > 1024) return 0;
-    if (st == T_Q4_K ? IS > 512 : IS > 1024) return 0;
+    if (I > 512 || IS > 512 || I % 512 || IS % 512) return 0;
     const uint32_t nc = chain_ctas(l, tokens, 0);
     if (grid < 1 || (uint32_t)grid <= nc) return 0;
     const uint32_t streaming = (uint32_t)grid - nc;
@@ -1575,7 +1615,7 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
                                   uint32_t *ids_out, float *weights_out, int router_mode, int sm_count) {
     if (!work->fused_aq || !work->fused_asc || !work->logits_fast) return -5;
     FusedArgs a;
-    for (int i = 0; i < 8; i++) a.w[i] = fdev(layer->w[i]);
+    for (int i = 0; i < 8; i++) a.w[i] = fused_view(layer, i);
     a.x = x; a.y = y;
     a.hc = HcAdd{work->hc_residual, work->hc_inject, work->hc_streams};
     a.tokens = (uint32_t)tokens; a.hidden = layer->hidden; a.experts = layer->experts; a.top_k = layer->top_k;
@@ -1595,6 +1635,6 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
     const uint32_t smem = p.total > c.total ? p.total : c.total;
     if (smem > 227u * 1024u - 1024u) return -4;
     cudaStream_t s = (cudaStream_t)work->stream;
-    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_Q4_K, T_IQ2_XXS>(a, layer, smem, sm_count, s);
-    return st == T_Q4_K ? launch_fused<T_IQ2_XXS, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_IQ2_XXS, T_IQ2_XXS>(a, layer, smem, sm_count, s);
+    if (rt == T_Q4_K) return st == T_Q4_K ? launch_fused<T_Q4_K, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_Q4_K, T_IQ2N>(a, layer, smem, sm_count, s);
+    return st == T_Q4_K ? launch_fused<T_IQ2N, T_Q4_K>(a, layer, smem, sm_count, s) : launch_fused<T_IQ2N, T_IQ2N>(a, layer, smem, sm_count, s);
 }

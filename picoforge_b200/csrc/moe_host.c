@@ -174,6 +174,7 @@ static Qwen4Status check_packed(const QW4PackedCpuView *v, Qwen4Error *err) {
 static void release(Qwen4Moe *m) {
     if (m && --m->refs == 0) {
         for (int a = 0; a < 8; a++) qw4sh_free(m->image[a]);
+        qw4sh_fused_release(&m->layer);
         free(m);
     }
 }
@@ -217,7 +218,8 @@ static Qwen4Status create_shard(const Qwen4MoeConfig *c, const Qwen4MoeWeights *
             .k_logical = (uint32_t)l->k_logical, .n_out = (uint32_t)l->n_out, .n_experts = (uint32_t)l->n_experts,
             .row_bytes = (uint32_t)l->row_bytes, .expert_bytes = l->expert_bytes};
     }
-    if (qw4sh_fused_prepare(&m->layer)) { release(m); return cuda_failure(err, "tensor maps"); }
+    if (qw4sh_fused_prepare(&m->layer)) { release(m); return cuda_failure(err, "decode path images"); }
+    m->device_bytes += m->layer.fused_alt_bytes;
     *out = m;
     return report(err, QW4_OK, "");
 }
