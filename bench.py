@@ -50,7 +50,7 @@ from picoforge_b200.layer import MoeLayer  # noqa: E402
 # benchmark, so the figure comes from the capture summarised in the named file (same command, same workload) and
 # is reported with that source; a workload without a capture of its current kernel reports null.
 TRAFFIC = {
-    "c1:fused_decode_kernel": {"bytes": 32.90e6 + 0.05e6, "source": "profiles/decode_c1_fused_decode_kernel.md"},
+    "c1:fused_decode_kernel": {"bytes": 64.77e6 + 1.68e6, "source": "profiles/decode_c1_fused_decode_kernel.md"},
 }
 
 STAGES = ("router_logits", "route", "group", "gate_up_routed", "gate_up_shared", "down_routed", "down_shared", "combine")
