@@ -363,7 +363,9 @@ void qw4cu_set_expert_path(int path);
  * exact routes are compared with that speculation before the down projection, and the experts
  * are run again with the exact ids in the rare launch where the expert sets differ, so ids and
  * route weights are always the exact mode's.  -1 (default): used whenever the layer fits it; 0:
- * never (the multi-kernel sequence runs instead).
+ * never (the multi-kernel sequence runs instead).  A layer that fits this path holds, for each of
+ * its IQ2_XXS expert tensors, a second resident image made at create (4-bit codes, 4.5 bits per
+ * weight: the kernel streams that one; same decoded values); qw4cu_moe_device_bytes counts it.
  * qw4cu_decode_phase_clocks copies the SM clock that the first streaming CTA of the workspace's
  * last one-kernel launch read at its phase boundaries into clocks[0..12] (start, x staged, fast
  * logits written, x digitised, barrier 1 passed, expert sets speculated, sources listed, gate/up
