@@ -1216,9 +1216,14 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
             uint8_t *ring = region + p.ring + warp * FNS * FSTAGE;
             float2 *partial = reinterpret_cast<float2 *>(region + p.partial);
             alive = __all_sync(0xffffffffu, alive);
-            auto locate = [&](uint32_t n, uint32_t &ul, uint32_t &s, bool &sh) {   // CTA slice n -> local unit, slice, kind
-                if (n < n_shu * spu_s) { ul = n / spu_s; s = n % spu_s; sh = true; }
-                else { const uint32_t m = n - n_shu * spu_s; ul = n_shu + m / spu_r; s = m % spu_r; sh = false; }
+            // CTA slice n -> local unit, slice, kind.  Both formats cut a unit into the same number of slices; the
+            // divisors are powers of two for every shape met so far, and a runtime division costs a lone lane as
+            // much as a quarter of a slice's arithmetic.
+            const uint32_t spu = spu_r, spu_sh = (spu & (spu - 1u)) ? 32u : 31u - (uint32_t)__clz(spu);
+            const uint32_t ur = gr * 4, ur_sh = (ur & (ur - 1u)) ? 32u : 31u - (uint32_t)__clz(ur);
+            auto locate = [&](uint32_t n, uint32_t &ul, uint32_t &s, bool &sh) {
+                if (spu_sh < 32u) { ul = n >> spu_sh; s = n & (spu - 1u); } else { ul = n / spu; s = n - ul * spu; }
+                sh = ul < n_shu;
             };
             auto issue = [&](uint32_t i) {
                 uint32_t ul, s; bool sh;
@@ -1228,8 +1233,8 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 uint8_t *stage = ring + (at % FNS) * FSTAGE;
                 if (sh) issue_unit_slice<ST>(&map_sg, &map_su, a.w[4].data, a.w[5].data, 0, IS, nbh, u * 8, s, stage, &bar[at % FNS], lane);
                 else {
-                    const uint32_t v = u - gs * 4, ur = gr * 4, e = srcs[1 + v / ur].expert;
-                    issue_unit_slice<RT>(&map_g, &map_u, a.w[1].data, a.w[2].data, e, I, nbh, (v % ur) * 8, s, stage, &bar[at % FNS], lane);
+                    const uint32_t v = u - gs * 4, vq = ur_sh < 32u ? v >> ur_sh : v / ur, e = srcs[1 + vq].expert;
+                    issue_unit_slice<RT>(&map_g, &map_u, a.w[1].data, a.w[2].data, e, I, nbh, (v - vq * ur) * 8, s, stage, &bar[at % FNS], lane);
                 }
             };
             __syncthreads();                                                       // the keys in zs are dead: the ring may be written
@@ -1350,8 +1355,11 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         const uint32_t my_src = n_src > warp ? (n_src - 1 - warp) / FW + 1 : 0;
         const uint32_t n_tiles = ((H >> 4) - sc + NS - 1) / NS;
         const uint32_t steps = my_src * n_tiles;
+        uint32_t next_tile = sc, next_src = warp;                              // issues come in step order: the next step's tile and source
         auto issue = [&](uint32_t n) {                                         // this phase has ring barriers of its own, counted from zero
-            const uint32_t tile = sc + (n / my_src) * NS, j = warp + (n % my_src) * FW;
+            const uint32_t tile = next_tile, j = next_src;
+            next_src += FW;
+            if (next_src >= n_src) { next_src = warp; next_tile += NS; }
             const Src s = srcs[j];
             uint8_t *stage = tiles + (n % FNC) * FSTAGE;
             if (s.shared) issue_down_tile<ST>(a.w[6].data, H, IS >> 8, tile * 16, stage, &tilebar[n % FNC], lane);
