@@ -421,6 +421,12 @@ size_t qw4cu_launch_log(char *out, size_t cap);
 Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *moe, uint32_t tensor, size_t expert,
                                   size_t row0, size_t rows, float *out, size_t out_elements,
                                   Qwen4Error *err);
+/* The same from the EXPANDED image that the one-kernel decode path streams for an IQ2_XXS expert tensor
+ * (tensor 1-6); QW4_UNSUPPORTED when the tensor has none (another format, or a layer that does not fit
+ * that path). */
+Qwen4Status qw4cu_moe_decode_rows_expanded(const Qwen4Moe *moe, uint32_t tensor, size_t expert,
+                                           size_t row0, size_t rows, float *out, size_t out_elements,
+                                           Qwen4Error *err);
 
 /* Dispatch lists for ids that are already in device memory, computed WITHOUT allocating
  * anything.  This entry point has no counterpart in the reference.  It is for callers that

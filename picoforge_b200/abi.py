@@ -239,6 +239,7 @@ class MoeApi:
             "qw4cu_set_decode_wrong_speculation": ([C.c_int], None),
             "qw4cu_stage_times": ([C.POINTER(C.c_double), C.POINTER(C.c_uint64)], C.c_int),
             "qw4cu_moe_decode_rows": ([P, C.c_uint32, C.c_size_t, C.c_size_t, C.c_size_t, P, C.c_size_t, E], C.c_int),
+            "qw4cu_moe_decode_rows_expanded": ([P, C.c_uint32, C.c_size_t, C.c_size_t, C.c_size_t, P, C.c_size_t, E], C.c_int),
             "qw4cu_group_pairs_device_noalloc": ([C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P, E], C.c_int),
             "qw4cu_malloc": ([C.c_size_t], P),
             "qw4cu_free": ([P], None),

@@ -153,6 +153,7 @@ int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const fl
  * phase boundaries of the workspace's last launch (after a synchronise). */
 int qw4sh_fused_prepare(QW4ShLayer *layer);
 void qw4sh_fused_release(QW4ShLayer *layer);
+int qw4sh_fused_decode_rows_expanded(const QW4ShLayer *layer, int tensor, size_t expert, size_t row0, size_t rows, float *out, void *stream);
 int qw4sh_fused_supported(const QW4ShLayer *layer, size_t tokens, const float *x, const float *y, int sm_count);
 void qw4sh_set_fused_decode(int mode);
 int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, float *y, size_t tokens,

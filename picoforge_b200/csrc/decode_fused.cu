@@ -498,6 +498,25 @@ __global__ void __launch_bounds__(256) iq2_expand_kernel(DevTensor t, uint8_t *_
     }
 }
 
+// Probe: rows [row0, row0 + rows) of one expert decoded FROM THE EXPANDED IMAGE into floats [rows, k], with the
+// arithmetic of the reference's decoder (src/qwen4_packed.c:102-120: d * (2 s + 1) * 0.125 * magnitude, signed), so
+// that the image can be compared bit for bit with a CPU decode of the GGUF bytes.  which as above.
+__global__ void __launch_bounds__(256) iq2n_decode_rows_kernel(const uint8_t *__restrict__ image, uint32_t k, uint32_t n_out, uint32_t expert,
+                                                               uint32_t row0, uint32_t rows, int which, float *__restrict__ out) {
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (uint64_t)rows * k) return;
+    const uint32_t row = row0 + (uint32_t)(i / k), col = (uint32_t)(i % k), nb5 = k >> 9;
+    const uint8_t *block = which < 0 ? image + (((uint64_t)expert * n_out + row) * nb5 + (col >> 9)) * 288u
+                                     : image + ((((uint64_t)expert * (n_out >> 3) + (row >> 3)) * nb5 + (col >> 9)) * 2u + (uint32_t)which) * 2304u + (row & 7u) * 288u;
+    const uint32_t c = col & 511u, h = c >> 7, j = (c >> 5) & 3u, t = (c >> 3) & 3u, n = c & 7u;
+    const uint32_t word = *reinterpret_cast<const uint32_t *>(block + 64u * h + 16u * t + 4u * j), code = (word >> (4 * n)) & 15u;
+    const uint32_t twice_plus_one = block[256u + 4u * h + j];
+    const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block + 272u + (h >> 1) * 2u));
+    const float scale = __fmul_rn(__fmul_rn(d, (float)twice_plus_one), 0.125f);
+    const float value = __fmul_rn(scale, (float)iq2_magnitude(code & 3u));
+    out[i] = (code & 4u) ? -value : value;
+}
+
 // Geometry of one format inside the rings.
 template <uint32_t TYPE> struct FGeo;
 template <> struct FGeo<T_Q4_K> { static constexpr uint32_t SLICE_BLOCKS = 2, BLOCK_BYTES = 144; };      // 512 columns, 288 B per row
@@ -1567,6 +1586,20 @@ extern "C" int qw4sh_fused_prepare(QW4ShLayer *l) {
     }
     l->fused_maps_ready = 1;
     return 0;
+}
+
+// Probe entry: decode rows of tensor i (1-6) from its expanded image; -3 when the tensor has none.
+extern "C" int qw4sh_fused_decode_rows_expanded(const QW4ShLayer *l, int i, size_t expert, size_t row0, size_t rows, float *out, void *stream) {
+    if (i < 1 || i > 6 || l->w[i].type != T_IQ2_XXS) return -3;
+    const int holder = (i == 2 || i == 5) ? i - 1 : i;
+    if (!l->fused_alt[holder]) return -3;
+    const int which = i == 3 || i == 6 ? -1 : (i == holder ? 0 : 1);
+    const uint64_t total = (uint64_t)rows * l->w[i].k_storage;
+    if (!total) return 0;
+    iq2n_decode_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t *)l->fused_alt[holder], l->w[i].k_storage,
+                                                                                          l->w[i].n_out, (uint32_t)expert, (uint32_t)row0, (uint32_t)rows,
+                                                                                          which, out);
+    return qw4sh_note_launch("iq2n_decode_rows_kernel");
 }
 
 // Whether the one-kernel decode path covers this layer and batch.

@@ -796,8 +796,18 @@ done:
 }
 
 /* ---- probes and plumbing ---------------------------------------------------------------- */
+static Qwen4Status decode_rows_from(const Qwen4Moe *m, uint32_t tensor, size_t expert, size_t row0, size_t rows, float *out,
+                                    size_t out_elements, bool expanded, Qwen4Error *err);
 Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *m, uint32_t tensor, size_t expert, size_t row0, size_t rows, float *out,
                                   size_t out_elements, Qwen4Error *err) {
+    return decode_rows_from(m, tensor, expert, row0, rows, out, out_elements, false, err);
+}
+Qwen4Status qw4cu_moe_decode_rows_expanded(const Qwen4Moe *m, uint32_t tensor, size_t expert, size_t row0, size_t rows, float *out,
+                                           size_t out_elements, Qwen4Error *err) {
+    return decode_rows_from(m, tensor, expert, row0, rows, out, out_elements, true, err);
+}
+static Qwen4Status decode_rows_from(const Qwen4Moe *m, uint32_t tensor, size_t expert, size_t row0, size_t rows, float *out,
+                                    size_t out_elements, bool expanded, Qwen4Error *err) {
     if (!m || !m->alive) return report(err, QW4_BAD_STATE, "inactive MoE");
     if (tensor >= 8 || !out) return report(err, QW4_INVALID_ARGUMENT, "bad tensor index or output");
     const QW4ShTensor *t = &m->layer.w[tensor];
@@ -807,7 +817,9 @@ Qwen4Status qw4cu_moe_decode_rows(const Qwen4Moe *m, uint32_t tensor, size_t exp
     const size_t bytes = rows * (size_t)t->k_storage * 4;
     float *dev = qw4sh_malloc(bytes);
     if (!dev) return cuda_failure(err, "decode scratch");
-    int rc = qw4sh_decode_rows(t, expert, row0, rows, dev, NULL);
+    int rc = expanded ? qw4sh_fused_decode_rows_expanded(&m->layer, (int)tensor, expert, row0, rows, dev, NULL)
+                      : qw4sh_decode_rows(t, expert, row0, rows, dev, NULL);
+    if (rc == -3) { qw4sh_free(dev); return report(err, QW4_UNSUPPORTED, "this tensor has no expanded image"); }
     if (!rc) rc = qw4sh_stream_sync(NULL);
     if (!rc) rc = qw4sh_memcpy(out, dev, bytes, 0);
     qw4sh_free(dev);

@@ -81,6 +81,29 @@ def test_decode_at_layer_shapes(gpu, routed):
                 np.testing.assert_array_equal(bits(got), bits(oracle.decode_rows(spec.types[tensor], raw, 16, k)))
 
 
+def test_expanded_image_decodes_to_the_oracle_bits(gpu):
+    """The second resident image of IQ2_XXS expert tensors (4-bit codes, read by the one-kernel decode path): whole
+    rows of every expert tensor, routed and shared, against the oracle's decode of the GGUF bytes, bit for bit."""
+    import ctypes as C
+    spec = synth.make_layer(22, routed_type=abi.IQ2_XXS, shared_type=abi.IQ2_XXS, experts=4, top_k=2)
+    with MoeLayer(gpu, spec, 1) as layer:
+        for tensor in (1, 2, 3, 4, 5, 6):
+            k, _, n_out, n_experts = spec.shapes()[tensor]
+            rb = abi.row_bytes(spec.types[tensor], k)
+            for expert, row0, rows in ((0, 0, 24), (n_experts - 1, n_out - 40, 40)):
+                got = np.empty((rows, k), np.float32)
+                err = abi.Qwen4Error()
+                st = gpu.lib.qw4cu_moe_decode_rows_expanded(layer.moe, tensor, expert, row0, rows, got.ctypes.data, got.size, C.byref(err))
+                assert st == 0, err.detail
+                raw = spec.tensors[tensor][(expert * n_out + row0) * rb:(expert * n_out + row0 + rows) * rb]
+                np.testing.assert_array_equal(bits(got), bits(oracle.decode_rows(spec.types[tensor], raw, rows, k)))
+    other = synth.make_layer(23, routed_type=abi.Q4_K, shared_type=abi.Q4_K, experts=4, top_k=2)
+    with MoeLayer(gpu, other, 1) as layer:                                      # no IQ2_XXS tensor: no expanded image
+        got = np.empty((1, other.hidden), np.float32)
+        err = abi.Qwen4Error()
+        assert gpu.lib.qw4cu_moe_decode_rows_expanded(layer.moe, 1, 0, 0, 1, got.ctypes.data, got.size, C.byref(err)) == abi.UNSUPPORTED
+
+
 # ---- routing -------------------------------------------------------------------------------
 def test_route_known_answers(gpu):
     z = np.array([[0.0, 1e-9, 0.0, -1e-9], [0.0, 2.0, 2.0, -1000.0]], np.float32)
