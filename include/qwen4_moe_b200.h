@@ -263,6 +263,9 @@ Qwen4Status qw4cu_moe_forward_hc_add_device(const Qwen4Moe *moe, const float *x_
 /* Waits for the workspace's stream, converts the device error word (bit 1 nonfinite, bit 2
  * bounds, bit 4 state) into a status and latches the workspace on failure. */
 Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *work, Qwen4Error *err);
+/* The same for n workspaces on the stream in force (e.g. the layers of a stack enqueued back to back): all status
+ * words are fetched, then one wait; the first failing workspace's status is returned, every failing one is latched. */
+Qwen4Status qw4cu_moe_work_sync_many(Qwen4MoeWork *const *works, size_t n, Qwen4Error *err);
 
 /* Expert parallelism (no counterpart in the reference, which is a single-device engine).
  * Experts are cut into equal contiguous blocks, one per rank; the router and the shared expert

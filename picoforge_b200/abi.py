@@ -256,6 +256,7 @@ class MoeApi:
             "qw4cu_verify_keep": ([P, C.c_size_t, C.POINTER(Qwen4Error)], C.c_int),
             "qw4cu_verify_position": ([P], C.c_uint64),
             "qw4cu_verify_pending": ([P], C.c_size_t),
+            "qw4cu_moe_work_sync_many": ([C.POINTER(P), C.c_size_t, C.POINTER(Qwen4Error)], C.c_int),
             "qw4cu_ep_transport": ([P], C.c_int),
             "qw4cu_ep_wait_probe": ([C.c_uint32, C.c_int], C.c_int),
             "qw4cu_mem_info": ([C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)], C.c_int),

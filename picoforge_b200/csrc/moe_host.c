@@ -563,6 +563,40 @@ Qwen4Status qw4cu_moe_work_sync(Qwen4MoeWork *w, Qwen4Error *err) {
     return report(err, QW4_OK, "");
 }
 
+/* The same for several workspaces that share the stream in force (layers enqueued back to back): every status
+ * word is fetched first, then ONE wait, then each workspace is judged in order; the first failure is returned and
+ * its workspace latched (the later ones are judged too, so that none stays unexamined). */
+Qwen4Status qw4cu_moe_work_sync_many(Qwen4MoeWork *const *works, size_t n, Qwen4Error *err) {
+    if (!works && n) return report(err, QW4_INVALID_ARGUMENT, "null workspace list");
+    void *stream = NULL;
+    for (size_t i = 0; i < n; i++) {
+        if (!works[i]) return report(err, QW4_INVALID_ARGUMENT, "null workspace");
+        use_current_stream(works[i]);
+        stream = works[i]->d.stream;
+        if (qw4sh_memcpy2d_async(works[i]->status_host, 16, works[i]->d.status, 16, 16, 1, 0, stream)) {
+            works[i]->failed = true;
+            return cuda_failure(err, "status copy");
+        }
+    }
+    if (n && qw4sh_stream_sync(stream)) {
+        for (size_t i = 0; i < n; i++) works[i]->failed = true;
+        return cuda_failure(err, "stream synchronize");
+    }
+    Qwen4Status first = QW4_OK;
+    Qwen4Error local;
+    bool cleared = false;
+    for (size_t i = 0; i < n; i++) {
+        const Qwen4Status st = status_result(works[i], first == QW4_OK ? err : &local);
+        if (st == QW4_OK) continue;
+        works[i]->failed = true;
+        status_clear(works[i]);
+        cleared = true;
+        if (first == QW4_OK) first = st;
+    }
+    if (cleared) qw4sh_stream_sync(stream);
+    return first == QW4_OK ? report(err, QW4_OK, "") : first;
+}
+
 Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen4MoeRoutes *routes,
                               Qwen4MoeWork *w, Qwen4Error *err) {
     if (!m || !w) return report(err, QW4_INVALID_ARGUMENT, "null forward handle");

@@ -112,9 +112,9 @@ Qwen4Status qw4cu_verify_append(QW4CuVerify *v, const float *x_host, size_t coun
     if (qw4sh_memcpy2d_async(pin_y, count * row, v->act[v->layers & 1], count * row, count * row, 1, 0, stream) ||
         qw4sh_memcpy2d_async(pin_ids, ids_bytes, v->ids_dev, ids_bytes, ids_bytes, 1, 0, stream))
         return verify_fail(err, QW4_GPU_ERROR, "output copy");
-    /* every workspace reports its own kernels' error words; the last wait also covers the copies */
-    for (size_t l = 0; l < v->layers; l++) {
-        const Qwen4Status st = qw4cu_moe_work_sync(v->work[l], err);
+    /* every workspace reports its own kernels' error words: all fetched behind the copies, one wait for everything */
+    {
+        const Qwen4Status st = qw4cu_moe_work_sync_many(v->work, v->layers, err);
         if (st != QW4_OK) return st;
     }
     memcpy(y_host, pin_y, count * row);
