@@ -151,6 +151,7 @@ int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const fl
  * supported: 1 when the layer, batch and pointers fit it.  set_fused_decode: -1 automatic
  * (default), 0 never.  fused_decode launches it; phase_clocks copies CTA 0's SM clock at its
  * phase boundaries of the workspace's last launch (after a synchronise). */
+int qw4sh_takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, const float *y, size_t tokens);
 int qw4sh_fused_prepare(QW4ShLayer *layer);
 void qw4sh_fused_release(QW4ShLayer *layer);
 int qw4sh_fused_decode_rows_expanded(const QW4ShLayer *layer, int tensor, size_t expert, size_t row0, size_t rows, float *out, void *stream);

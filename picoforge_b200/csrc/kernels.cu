@@ -1566,6 +1566,12 @@ static bool takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const fl
     return g_only_step < 0 && g_expert_path != 0 && !work->routed && qw4sh_fused_supported(layer, tokens, x, y, sm_count());
 }
 
+// Whether a forward of this batch would run as the one-kernel decode path (which writes every y element exactly once
+// and never reads y, so y may lie in pinned host memory).
+extern "C" int qw4sh_takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, const float *y, size_t tokens) {
+    return !g_stage_timing && takes_fused(layer, work, x, y, tokens) ? 1 : 0;
+}
+
 __global__ void __launch_bounds__(256) hc_add_kernel(const float *__restrict__ y, uint32_t hidden, HcAdd hc, uint32_t *status) {
     const uint32_t t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
     if (c < hidden && !hc_add(hc, t, c, hidden, y[(uint64_t)t * hidden + c])) atomicOr(status, QW4SH_ERR_NONFINITE);

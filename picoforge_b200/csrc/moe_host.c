@@ -648,12 +648,15 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
             for (size_t row = 0; row < n; row++) memcpy(pin_x + row * h, xs + row * (x.stride_bytes[0] / 4), h * 4);
             rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, pin_x, h * 4, h * 4, n, 1, w->d.stream);
         } else rc |= qw4sh_memcpy2d_async(w->d.x, h * 4, xs, x.stride_bytes[0], h * 4, n, 1, w->d.stream);
+        /* the one-kernel decode path writes each y element once and reads none: it stores straight into the pinned
+         * staging (device-addressable), and the copy of y back drops out of the call */
+        const bool direct_y = small && !observe && qw4sh_takes_fused(&m->layer, &w->d, w->d.x, pin_y, n);
         if (!rc && observe)                    /* stage by stage in the reference's order, every stage shown to the observer */
             rc = qw4sh_observed_forward(&m->layer, &w->d, w->d.x, w->d.y, n, xs, x.stride_bytes[0] / 4, start, w->observer, w->observer_ctx);
-        else if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, w->d.y, n, NULL, NULL, current_router_mode());
+        else if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, direct_y ? pin_y : w->d.y, n, NULL, NULL, current_router_mode());
         if (!rc) rc = qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream);
         if (!rc && small) {
-            rc = qw4sh_memcpy2d_async(pin_y, h * 4, w->d.y, h * 4, h * 4, n, 0, w->d.stream);
+            if (!direct_y) rc = qw4sh_memcpy2d_async(pin_y, h * 4, w->d.y, h * 4, h * 4, n, 0, w->d.stream);
             if (routes) {
                 rc |= qw4sh_memcpy2d_async(pin_ids, k * 4, w->d.ids, k * 4, k * 4, n, 0, w->d.stream);
                 rc |= qw4sh_memcpy2d_async(pin_w, k * 4, w->d.weights, k * 4, k * 4, n, 0, w->d.stream);
