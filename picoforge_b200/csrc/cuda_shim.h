@@ -74,6 +74,9 @@ typedef struct {
     float *hc_residual;
     const float *hc_inject;
     uint32_t hc_streams;
+    /* set per call, NULL otherwise: pinned host words [4] into which the one-kernel decode path copies the status
+     * words when its last CTA leaves (the host forward then needs no copy of them) */
+    uint32_t *status_mirror;
 } QW4ShWork;
 
 enum { QW4SH_ERR_NONFINITE = 1u, QW4SH_ERR_BOUNDS = 2u, QW4SH_ERR_STATE = 4u };

@@ -94,6 +94,7 @@ struct FusedArgs {
     uint32_t chain_ctas;                        // NC
     long long t0;                               // (device side) this CTA's clock at its start
     HcAdd hc;                                   // hyper-connection add applied where y is written (residual nullptr: none)
+    uint32_t *status_mirror;                    // pinned host words [4] that receive the status words at the end, or nullptr
 };
 
 // One distinct source of phase C / one expert of phase B.
@@ -1010,6 +1011,8 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
         }
         __syncthreads();
         if (leaving_last && tid < 8) { a.sync[tid] = 0; __threadfence(); }
+        // every CTA's error bits are in before its exit count: the last one hands the words to the host
+        if (leaving_last && tid < 4 && a.status_mirror) a.status_mirror[tid] = *reinterpret_cast<volatile uint32_t *>(a.status + tid);
     };
     if (blockIdx.x < NC) { chain_cta(a, smem); leave(); return; }
 
@@ -1659,6 +1662,7 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
     for (int i = 0; i < 8; i++) a.w[i] = fused_view(layer, i);
     a.x = x; a.y = y;
     a.hc = HcAdd{work->hc_residual, work->hc_inject, work->hc_streams};
+    a.status_mirror = work->status_mirror;
     a.tokens = (uint32_t)tokens; a.hidden = layer->hidden; a.experts = layer->experts; a.top_k = layer->top_k;
     a.inter = layer->inter; a.shared_inter = layer->shared_inter; a.norm = layer->norm; a.router_mode = router_mode == 0 && g_wrong_speculation ? 2 : router_mode;
     a.logits = work->logits; a.shared_logit = work->shared_logit; a.ids = work->ids; a.weights = work->weights;

@@ -653,8 +653,15 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
         const bool direct_y = small && !observe && qw4sh_takes_fused(&m->layer, &w->d, w->d.x, pin_y, n);
         if (!rc && observe)                    /* stage by stage in the reference's order, every stage shown to the observer */
             rc = qw4sh_observed_forward(&m->layer, &w->d, w->d.x, w->d.y, n, xs, x.stride_bytes[0] / 4, start, w->observer, w->observer_ctx);
-        else if (!rc) rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, direct_y ? pin_y : w->d.y, n, NULL, NULL, current_router_mode());
-        if (!rc) rc = qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream);
+        else if (!rc) {
+            if (direct_y) {                   /* the kernel also hands over the status words itself */
+                w->status_host[0] = UINT32_MAX; w->status_host[1] = UINT32_MAX;
+                w->d.status_mirror = w->status_host;
+            }
+            rc = qw4sh_layer_forward(&m->layer, &w->d, w->d.x, direct_y ? pin_y : w->d.y, n, NULL, NULL, current_router_mode());
+            w->d.status_mirror = NULL;
+        }
+        if (!rc && !direct_y) rc = qw4sh_memcpy2d_async(w->status_host, 16, w->d.status, 16, 16, 1, 0, w->d.stream);
         if (!rc && small) {
             if (!direct_y) rc = qw4sh_memcpy2d_async(pin_y, h * 4, w->d.y, h * 4, h * 4, n, 0, w->d.stream);
             if (routes) {
@@ -663,6 +670,8 @@ Qwen4Status qwen4_moe_forward(const Qwen4Moe *m, Qwen4F32 x, Qwen4F32Mut y, Qwen
             }
         }
         if (!rc) rc = qw4sh_stream_sync(w->d.stream);
+        if (!rc && direct_y && w->status_host[0] == UINT32_MAX)        /* the launch fell back to the multi-kernel sequence: fetch the words */
+            rc = qw4sh_memcpy(w->status_host, w->d.status, 16, 0);
         if (rc) { st = cuda_failure(err, "layer execution"); break; }
         if ((st = status_result(w, err)) != QW4_OK) break;
         w->status_clean = true;
