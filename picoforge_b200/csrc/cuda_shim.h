@@ -19,6 +19,11 @@ typedef struct {
     uint32_t k_storage, k_logical, n_out, n_experts;
     uint32_t row_bytes;
     uint64_t expert_bytes;
+    /* tile kernels, gate / up tensors: tensor maps (CUtensorMap, 128 bytes each) of the sections of the resident image
+     * (Q4_K and IQ2_XXS: the packed rows; Q2_K: codes, scale bytes, super-scales), made by qw4sh_tile_prepare; with them
+     * the eight row pieces of a section come as one request.  0 sections: the kernel copies row by row. */
+    unsigned char tile_maps[3][128];
+    int tile_sections;
 } QW4ShTensor;
 
 typedef struct {
@@ -154,6 +159,7 @@ int qw4sh_layer_forward(const QW4ShLayer *layer, const QW4ShWork *work, const fl
  * supported: 1 when the layer, batch and pointers fit it.  set_fused_decode: -1 automatic
  * (default), 0 never.  fused_decode launches it; phase_clocks copies CTA 0's SM clock at its
  * phase boundaries of the workspace's last launch (after a synchronise). */
+int qw4sh_tile_prepare(QW4ShLayer *layer);
 int qw4sh_takes_fused(const QW4ShLayer *layer, const QW4ShWork *work, const float *x, const float *y, size_t tokens);
 int qw4sh_fused_prepare(QW4ShLayer *layer);
 void qw4sh_fused_release(QW4ShLayer *layer);

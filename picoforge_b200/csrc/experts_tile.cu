@@ -15,8 +15,10 @@
 // chunk step waiting for an L2 round trip.)
 //
 // Every mbarrier wait is bounded (about a second) and then records QW4SH_ERR_STATE.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "cuda_shim.h"
 #include "formats.cuh"
@@ -46,7 +48,9 @@ struct TileArgs {
     const uint8_t *lut;                         // IQ2_XXS tables image
     float *out;                                 // gate/up: act [pairs][n_out]; down: out [pairs][n_out]
     uint32_t *status;
+    uint32_t use_maps;                          // gate/up: the section maps passed beside this struct are valid
 };
+struct TileMaps { CUtensorMap m[2][3]; };       // [gate, up][section]
 
 __device__ __forceinline__ uint32_t ts_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tbar_init(uint64_t *bar, uint32_t count) {
@@ -72,6 +76,12 @@ __device__ __forceinline__ bool tbar_wait(uint64_t *bar, uint32_t parity, uint32
 __device__ __forceinline__ void tbulk(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(ts_u32(dst_smem)), "l"(src), "r"(bytes), "r"(ts_u32(bar)) : "memory");
+}
+// Rows [y, y + 8) of expert z, 32-bit words [x, x + box) of each, through a 3-D tensor map {words of a row's
+// section, rows of an expert, experts}: eight row pieces that lie a row apart in memory as ONE request.
+__device__ __forceinline__ void ttma_rows(void *dst_smem, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t z, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(ts_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(ts_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tproxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmma_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -274,7 +284,7 @@ __host__ __device__ inline uint32_t tile_smem_bytes(uint32_t k) {
 
 // MODE 0: gate + up + SwiGLU -> act; MODE 1: down -> out.
 template <uint32_t TYPE, int MODE>
-__global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
+__global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a, const __grid_constant__ TileMaps maps) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool LUT = TYPE == T_IQ2_XXS;
     constexpr uint32_t SB = TGeo<TYPE>::SLICE_BLOCKS, BB = TGeo<TYPE>::BLOCK_BYTES, STAGE = TStage<TYPE>::BYTES;
@@ -342,7 +352,15 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
             if (TYPE == T_Q2_K) {
                 // three sections per matrix: codes, scale bytes, {d, dmin}; in the stage at 0, 4096 and 5120
                 const uint64_t blocks = (uint64_t)n_out * nb;
-                if (MODE == 0) {
+                if (MODE == 0 && a.use_maps) {
+                    if (lane == 0) tbar_expect(full, 16 * (SB * 84u));
+                    __syncwarp();
+                    if (lane < 6) {                                             // lane = 3 * matrix + section
+                        const uint32_t mx = lane / 3, sec = lane % 3;
+                        const uint32_t piece = sec == 0 ? SB * 64u : sec == 1 ? SB * 16u : SB * 4u, base = sec == 0 ? 0u : sec == 1 ? 4096u : 5120u;
+                        ttma_rows(stage + base + mx * 8 * piece, &maps.m[mx][sec], s * (piece / 4), row0, grp.expert, full);
+                    }
+                } else if (MODE == 0) {
                     if (lane == 0) tbar_expect(full, 16 * (SB * 84u));
                     __syncwarp();
                     if (lane < 16) {
@@ -360,6 +378,16 @@ __global__ void __launch_bounds__(TT, 1) expert_tile_kernel(const TileArgs a) {
                     tbulk(stage, mat + b0 * 64u, 16 * nb * 64u, full);
                     tbulk(stage + 4096, mat + blocks * 64u + b0 * 16u, 16 * nb * 16u, full);
                     tbulk(stage + 5120, mat + blocks * 80u + b0 * 4u, 16 * nb * 4u, full);
+                }
+            } else if (MODE == 0 && a.use_maps) {
+                constexpr uint32_t slice_bytes = SB * BB;
+                if (lane == 0) tbar_expect(full, 16 * slice_bytes + (LUT ? 2 * 8 * nb * 2 : 0));
+                __syncwarp();
+                if (lane < 2) ttma_rows(stage + lane * 8 * slice_bytes, &maps.m[lane][0], s * (slice_bytes / 4), row0, grp.expert, full);
+                else if (LUT && lane < 4) {
+                    const DevTensor &w = lane == 2 ? a.w0 : a.w1;
+                    const uint8_t *mat = w.data + (uint64_t)grp.expert * w.expert_bytes;
+                    tbulk(stage + 16 * slice_bytes + (lane - 2) * 8 * nb * 2, mat + (uint64_t)n_out * nb * 64u + (uint64_t)row0 * nb * 2u, 8 * nb * 2, full);
                 }
             } else if (MODE == 0) {
                 constexpr uint32_t slice_bytes = SB * BB;
@@ -534,12 +562,60 @@ extern "C" int qw4sh_build_dense_tile_groups(uint32_t tokens, void *groups, uint
 }
 
 template <uint32_t TYPE, int MODE>
-static int launch_tile(const TileArgs &a, int ctas, cudaStream_t stream) {
+static int launch_tile(const TileArgs &a, const TileMaps &maps, int ctas, cudaStream_t stream) {
     const size_t smem = tile_smem_bytes<TYPE>(a.w0.k_storage);
     cudaError_t e = cudaFuncSetAttribute(expert_tile_kernel<TYPE, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    expert_tile_kernel<TYPE, MODE><<<ctas, TT, smem, stream>>>(a);
+    expert_tile_kernel<TYPE, MODE><<<ctas, TT, smem, stream>>>(a, maps);
     return qw4sh_note_launch("expert_tile_kernel");
+}
+
+// ---- section maps of the gate / up tensors -------------------------------------------------------------------------
+typedef CUresult (*TileEncode)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int section_map(const QW4ShTensor *t, uint64_t offset, uint32_t row_stride, uint32_t piece, CUtensorMap *map) {
+    static TileEncode encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess || !fn) return -1;
+        encode = (TileEncode)fn;
+    }
+    if (row_stride % 16 || piece % 16 || t->expert_bytes % 16 || ((uintptr_t)(t->data + offset) & 15u)) return -2;
+    const cuuint64_t dims[3] = {row_stride / 4, t->n_out, t->n_experts};
+    const cuuint64_t strides[2] = {row_stride, t->expert_bytes};
+    const cuuint32_t box[3] = {piece / 4, 8, 1}, elem[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void *)(t->data + offset), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -3;
+}
+// Called once the images are resident: the gate / up tensors (routed and shared) that the tile kernels can take get
+// their section maps; a tensor without them is copied row by row.  Never fails the create.
+extern "C" int qw4sh_tile_prepare(QW4ShLayer *l) {
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    const int which[4] = {1, 2, 4, 5};
+    for (int i = 0; i < 4; i++) {
+        QW4ShTensor *t = &l->w[which[i]];
+        t->tile_sections = 0;
+        if (!qw4sh_tile_supported(t, 0)) continue;
+        const uint32_t nb = t->k_storage >> 8;
+        const uint64_t blocks = (uint64_t)t->n_out * nb;
+        alignas(64) CUtensorMap maps[3];
+        int rc = 0, sections = 1;
+        if (t->type == T_Q4_K) rc = section_map(t, 0, nb * 144u, TGeo<T_Q4_K>::SLICE_BLOCKS * 144u, &maps[0]);
+        else if (t->type == T_IQ2_XXS) rc = section_map(t, 0, nb * 64u, TGeo<T_IQ2_XXS>::SLICE_BLOCKS * 64u, &maps[0]);
+        else {
+            constexpr uint32_t SB = TGeo<T_Q2_K>::SLICE_BLOCKS;
+            sections = 3;
+            rc = section_map(t, 0, nb * 64u, SB * 64u, &maps[0]);
+            if (!rc) rc = section_map(t, blocks * 64u, nb * 16u, SB * 16u, &maps[1]);
+            if (!rc) rc = section_map(t, blocks * 80u, nb * 4u, SB * 4u, &maps[2]);
+        }
+        if (rc) continue;
+        memcpy(t->tile_maps, maps, sizeof(CUtensorMap) * sections);
+        t->tile_sections = sections;
+    }
+    return 0;
 }
 
 // mode 0: gate (w0) + up (w1) -> act [pairs][n_out]; mode 1: down (w0) -> out [pairs][n_out].  Input rows are
@@ -553,8 +629,13 @@ extern "C" int qw4sh_expert_tiles(int mode, const QW4ShTensor *w0, const QW4ShTe
     a.groups = (const TGroup *)groups; a.n_groups = n_groups; a.row_to_pair = row_to_pair; a.k_div = k_div;
     a.digits = digits; a.sums = sums; a.scale = scale; a.lut = nullptr; a.out = out; a.status = status;
     if (w0->type == T_IQ2_XXS && !(a.lut = qw4sh_lut_image())) return -3;
+    alignas(64) TileMaps maps;
+    memset(&maps, 0, sizeof maps);
+    const int want = w0->type == T_Q2_K ? 3 : 1;
+    a.use_maps = mode == 0 && w1 && w0->tile_sections == want && w1->tile_sections == want ? 1u : 0u;
+    if (a.use_maps) { memcpy(maps.m[0], w0->tile_maps, sizeof(CUtensorMap) * want); memcpy(maps.m[1], w1->tile_maps, sizeof(CUtensorMap) * want); }
     cudaStream_t s = (cudaStream_t)stream;
-    if (w0->type == T_Q4_K) return mode == 0 ? launch_tile<T_Q4_K, 0>(a, ctas, s) : launch_tile<T_Q4_K, 1>(a, ctas, s);
-    if (w0->type == T_Q2_K) return mode == 0 ? launch_tile<T_Q2_K, 0>(a, ctas, s) : launch_tile<T_Q2_K, 1>(a, ctas, s);
-    return mode == 0 ? launch_tile<T_IQ2_XXS, 0>(a, ctas, s) : launch_tile<T_IQ2_XXS, 1>(a, ctas, s);
+    if (w0->type == T_Q4_K) return mode == 0 ? launch_tile<T_Q4_K, 0>(a, maps, ctas, s) : launch_tile<T_Q4_K, 1>(a, maps, ctas, s);
+    if (w0->type == T_Q2_K) return mode == 0 ? launch_tile<T_Q2_K, 0>(a, maps, ctas, s) : launch_tile<T_Q2_K, 1>(a, maps, ctas, s);
+    return mode == 0 ? launch_tile<T_IQ2_XXS, 0>(a, maps, ctas, s) : launch_tile<T_IQ2_XXS, 1>(a, maps, ctas, s);
 }

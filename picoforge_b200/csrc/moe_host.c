@@ -218,6 +218,7 @@ static Qwen4Status create_shard(const Qwen4MoeConfig *c, const Qwen4MoeWeights *
             .k_logical = (uint32_t)l->k_logical, .n_out = (uint32_t)l->n_out, .n_experts = (uint32_t)l->n_experts,
             .row_bytes = (uint32_t)l->row_bytes, .expert_bytes = l->expert_bytes};
     }
+    (void)qw4sh_tile_prepare(&m->layer);
     if (qw4sh_fused_prepare(&m->layer)) { release(m); return cuda_failure(err, "decode path images"); }
     m->device_bytes += m->layer.fused_alt_bytes;
     *out = m;
