@@ -1557,6 +1557,7 @@ extern "C" int qw4sh_fused_prepare(QW4ShLayer *l) {
     l->fused_alt_bytes = 0;
     for (int i = 0; i < 8; i++) l->fused_alt[i] = nullptr;
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    if (g_fused_mode == 0) return 0;                                            // switched off before create: no maps, no expanded images
     if (l->w[2].type != l->w[1].type || l->w[3].type != l->w[1].type || l->w[5].type != l->w[4].type || l->w[6].type != l->w[4].type) return 0;
     for (int i = 1; i <= 6; i++) {
         const QW4ShTensor *t = &l->w[i];
