@@ -369,6 +369,7 @@ void qw4cu_set_expert_path(int path);
  * never (the multi-kernel sequence runs instead).  A layer that fits this path holds, for each of
  * its IQ2_XXS expert tensors, a second resident image made at create (4-bit codes, 4.5 bits per
  * weight: the kernel streams that one; same decoded values); qw4cu_moe_device_bytes counts it.
+ * A layer created while mode 0 is in force gets neither the image nor the path, whatever the mode later.
  * qw4cu_decode_phase_clocks copies the SM clock that the first streaming CTA of the workspace's
  * last one-kernel launch read at its phase boundaries into clocks[0..12] (start, x staged, fast
  * logits written, x digitised, barrier 1 passed, expert sets speculated, sources listed, gate/up
