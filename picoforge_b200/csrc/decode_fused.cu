@@ -62,7 +62,6 @@ constexpr int FRMAX = 4;                        // router rows per streaming CTA
 constexpr int FNS = 2;                          // ring stages per warp, gate/up phase (three stages fit and were measured: no faster)
 constexpr int FNC = 2;                          // ring stages per warp, down phase
 constexpr uint32_t FSTAGE = 4608;               // bytes per ring stage: 16 rows x 288 bytes (512 columns of either format)
-constexpr uint32_t F_LUT_GRID = 256 * 128, F_LUT_SIGN = 128 * 128, F_LUT_BYTES = F_LUT_GRID + F_LUT_SIGN;
 constexpr uint32_t FZP = FMAXE + 4;             // pitch of a logit row in shared memory (floats)
 constexpr int CROWS = 32;                       // router rows per chain CTA (lane = row).  64 rows (two chain warps per token, nine
                                                 // chain CTAs) evened out the streaming CTAs' shares but ran the chains at 42 k cycles
@@ -87,7 +86,6 @@ struct FusedArgs {
     float2 *asc;                                // [T*k + T][imax / 32] per chunk: scale, sum of the chunk's represented values
     uint32_t *ids_out;
     float *weights_out;
-    const uint8_t *lut;                         // unused (no format of this path needs tables)
     uint32_t *sync;                             // counters (S_*), then the phase clocks of the first streaming CTA
     uint32_t *status;
     uint32_t partial_slices;                    // capacity of the partial-sum buffer (slices per CTA)
@@ -107,14 +105,14 @@ struct Src {
 // Shared-memory plan of a streaming CTA (byte offsets), the same on host and device.  `region` is
 // reused by the three phases; the digit image of x lives at its start through phases A and B.
 struct FPlan {
-    uint32_t bars, ids, wts, idx, wtx, misc, tokmask, slotmap, src, lut, region, total;
+    uint32_t bars, ids, wts, idx, wtx, misc, tokmask, slotmap, src, region, total;
     uint32_t kp;                                // pitch of one digit row of x
     uint32_t xq, xsum;                          // phases A and B (inside region)
     uint32_t xf, xf_pitch, rows, row_pitch;     // phase A
     uint32_t zs, ring, partial;                 // phase B
     uint32_t aq, ap, asc, tiles, cpartial;      // phase C
 };
-__host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max, uint32_t rows_c, uint32_t partial_slices, bool lut) {
+__host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max, uint32_t rows_c, uint32_t partial_slices) {
     FPlan p;
     uint32_t at = 0;
     p.bars = at; at += 512;
@@ -126,7 +124,6 @@ __host__ __device__ inline FPlan make_fplan(uint32_t hidden, uint32_t inter_max,
     p.tokmask = at; at += FMAXE;
     p.slotmap = at; at += FMAXE * 4;
     p.src = at; at += ((FMAXSRC * 8 + 127) & ~127u);
-    p.lut = at; if (lut) at += F_LUT_BYTES;
     p.region = at;
     p.kp = hidden + 32;
     uint32_t head = 0;
@@ -230,9 +227,8 @@ __device__ __forceinline__ void fmma_zero(int (&c)[4], uint32_t a0, uint32_t a1,
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// Shared-memory loads by 32-bit shared address.  The `ring` forms are volatile: they read memory that bulk
-// copies rewrite between uses and must stay behind the mbarrier wait that precedes them in program order; the
-// `table` forms read tables that never change after the CTA built them, so the compiler may move them freely.
+// Shared-memory loads by 32-bit shared address, volatile: they read memory that bulk copies rewrite between uses
+// and must stay behind the mbarrier wait that precedes them in program order.
 __device__ __forceinline__ uint2 lds_ring2(uint32_t a) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
@@ -243,17 +239,6 @@ __device__ __forceinline__ uint32_t lds_ring_u16(uint32_t a) {
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
 }
-__device__ __forceinline__ uint2 lds_table2(uint32_t a) {
-    uint2 v;
-    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint4 lds_table4(uint32_t a) {
-    uint4 v;
-    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-
 // Thread 0 waits until *counter >= expected (bounded); the verdict reaches every thread.
 // False (CTA-uniform) when the wait ran out.
 __device__ __forceinline__ bool wait_counter(const uint32_t *counter, uint32_t expected, uint32_t *status, uint32_t *flag_smem) {
@@ -544,12 +529,12 @@ __device__ __forceinline__ void issue_unit_slice(const CUtensorMap *gate_map, co
     if (lane < 2) ftma_rows(stage + lane * 8 * slice_bytes, lane ? up_map : gate_map, s * (slice_bytes / 4), row0, expert, bar);
 }
 template <uint32_t TYPE>
-__device__ __forceinline__ void consume_unit_slice(const uint8_t *stage, uint32_t nb, uint32_t s, const uint8_t *lut, const uint8_t *xq_lane,
+__device__ __forceinline__ void consume_unit_slice(const uint8_t *stage, uint32_t nb, uint32_t s, const uint8_t *xq_lane,
                                                    const int2 *xsum_tok, uint32_t g, uint32_t t, float &f0, float &f1) {
     constexpr uint32_t SB = FGeo<TYPE>::SLICE_BLOCKS, slice_bytes = SB * FGeo<TYPE>::BLOCK_BYTES;
     const uint16_t *d = reinterpret_cast<const uint16_t *>(stage + 16 * slice_bytes);
     Halves<TYPE>::run(stage + g * slice_bytes, stage + (8 + g) * slice_bytes, SB * 2, iq2_swizzle(g, nb), d + g * nb + s * SB,
-                      d + (8 + g) * nb + s * SB, lut, t, xq_lane + s * SB * 256u, xsum_tok + s * SB * 8u, f0, f1);
+                      d + (8 + g) * nb + s * SB, nullptr, t, xq_lane + s * SB * 256u, xsum_tok + s * SB * 8u, f0, f1);
 }
 
 // Down tile: 16 rows x K (K <= 512), fetched whole.
@@ -563,11 +548,11 @@ __device__ __forceinline__ void issue_down_tile(const uint8_t *mat, uint32_t n_o
     }
 }
 template <uint32_t TYPE>
-__device__ __forceinline__ void consume_down_tile(const uint8_t *stage, uint32_t nb, const uint8_t *lut, const uint8_t *aq_lane,
+__device__ __forceinline__ void consume_down_tile(const uint8_t *stage, uint32_t nb, const uint8_t *aq_lane,
                                                   const float2 *asc_tok, uint32_t g, uint32_t t, float &f0, float &f1) {
     const uint32_t row_bytes = nb * FGeo<TYPE>::BLOCK_BYTES;
     const uint16_t *d = reinterpret_cast<const uint16_t *>(stage + 4096);
-    HalvesS<TYPE>::run(stage + g * row_bytes, stage + (8 + g) * row_bytes, nb * 2, iq2_swizzle(g, nb), d + g * nb, d + (8 + g) * nb, lut, t,
+    HalvesS<TYPE>::run(stage + g * row_bytes, stage + (8 + g) * row_bytes, nb * 2, iq2_swizzle(g, nb), d + g * nb, d + (8 + g) * nb, nullptr, t,
                        aq_lane, asc_tok, f0, f1);
 }
 
@@ -1018,8 +1003,7 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
 
     const uint32_t T = a.tokens, H = a.hidden, E = a.experts, k = a.top_k, I = a.inter, IS = a.shared_inter;
     const uint32_t pairs = T * k, rows_c = pairs + T, imax = I > IS ? I : IS;
-    constexpr bool LUT = false;                                                // no format on this path needs tables in shared memory
-    const FPlan p = make_fplan(H, imax, rows_c, a.partial_slices, LUT);
+    const FPlan p = make_fplan(H, imax, rows_c, a.partial_slices);
     const uint32_t warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t sc = blockIdx.x - NC, NS = gridDim.x - NC;
     uint64_t *ringbar = reinterpret_cast<uint64_t *>(smem + p.bars);           // [FW][FNS], four single ones, then [FW][FNC]
@@ -1037,7 +1021,6 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
     uint32_t *misc_u = reinterpret_cast<uint32_t *>(smem + p.misc) + 16;       // [0] wait flag, [1] spec ok, [2] sources, [3] verify, [4..19] chunk counts
     uint8_t *tokmask = smem + p.tokmask, *slotmap = smem + p.slotmap;
     Src *srcs = reinterpret_cast<Src *>(smem + p.src);
-    const uint8_t *lut = smem + p.lut;
     uint8_t *region = smem + p.region;
     uint8_t *xq = region + p.xq;
     int2 *xsum = reinterpret_cast<int2 *>(region + p.xsum);
@@ -1283,8 +1266,8 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 const uint8_t *stage = ring + (at % FNS) * FSTAGE;
                 float f0 = 0.0f, f1 = 0.0f;
                 if (alive) {
-                    if (sh) consume_unit_slice<ST>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
-                    else consume_unit_slice<RT>(stage, nbh, s, lut, xq_lane, xsum_tok, g, t, f0, f1);
+                    if (sh) consume_unit_slice<ST>(stage, nbh, s, xq_lane, xsum_tok, g, t, f0, f1);
+                    else consume_unit_slice<RT>(stage, nbh, s, xq_lane, xsum_tok, g, t, f0, f1);
                 }
                 partial[(warp + i * FW) * 32 + lane] = make_float2(f0, f1);
                 __syncwarp();
@@ -1421,8 +1404,8 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
                 const uint8_t *stage = tiles + (n % FNC) * FSTAGE;
                 float f0 = 0.0f, f1 = 0.0f;
                 if (alive) {
-                    if (s.shared) consume_down_tile<ST>(stage, IS >> 8, lut, aq_lane, asc_tok, g, t, f0, f1);
-                    else consume_down_tile<RT>(stage, I >> 8, lut, aq_lane, asc_tok, g, t, f0, f1);
+                    if (s.shared) consume_down_tile<ST>(stage, IS >> 8, aq_lane, asc_tok, g, t, f0, f1);
+                    else consume_down_tile<RT>(stage, I >> 8, aq_lane, asc_tok, g, t, f0, f1);
                 }
                 __syncwarp();
                 fproxy_fence();
@@ -1463,7 +1446,6 @@ __global__ void __launch_bounds__(FT, 1) fused_decode_kernel(const __grid_consta
 using namespace qw4;
 
 extern "C" int qw4sh_note_launch(const char *name);
-extern "C" const uint8_t *qw4sh_lut_image(void);
 
 static DevTensor fdev(const QW4ShTensor &s) {
     DevTensor t;
@@ -1498,7 +1480,7 @@ static uint32_t partial_capacity(const QW4ShLayer *l, size_t tokens, uint32_t st
 
 static FPlan plan_for(const QW4ShLayer *l, size_t tokens, uint32_t streaming) {
     const uint32_t imax = l->inter > l->shared_inter ? l->inter : l->shared_inter;
-    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, streaming), false);
+    return make_fplan(l->hidden, imax, (uint32_t)tokens * l->top_k + (uint32_t)tokens, partial_capacity(l, tokens, streaming));
 }
 
 // Bytes of the workspace arrays the kernel needs beyond the common ones (for `cap` tokens, at most FTOK used).
@@ -1672,7 +1654,6 @@ extern "C" int qw4sh_fused_decode(const QW4ShLayer *layer, const QW4ShWork *work
     a.ids_out = ids_out; a.weights_out = weights_out;
     a.sync = work->sync; a.status = work->status;
     const uint32_t rt = layer->w[1].type, st = layer->w[4].type;
-    a.lut = nullptr;
     const uint32_t streaming = (uint32_t)sm_count - chain_ctas(layer, tokens, 0);     // the same split in every mode (plans, capacity)
     a.chain_ctas = (uint32_t)sm_count - streaming;
     a.partial_slices = partial_capacity(layer, tokens, streaming);
