@@ -1553,6 +1553,22 @@ static int side_stream(cudaStream_t *stream, cudaEvent_t **events) {
     return 0;
 }
 
+// A third stream, for work of the expert-parallel step that may run beside both the main stream and the shared
+// expert's branch (the digits of the gathered rows, beside the lists): stream and two events, [0] fork, [1] done.
+static cudaStream_t g_aux_stream[64] = {nullptr};
+static cudaEvent_t g_aux_event[64][2] = {{nullptr}};
+static int aux_stream(cudaStream_t *stream, cudaEvent_t **events) {
+    int device = 0;
+    CU(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(cudaErrorInvalidDevice, "device index");
+    if (!g_aux_stream[device]) {
+        CU(cudaStreamCreateWithFlags(&g_aux_stream[device], cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++) CU(cudaEventCreateWithFlags(&g_aux_event[device][i], cudaEventDisableTiming));
+    }
+    *stream = g_aux_stream[device]; *events = g_aux_event[device];
+    return 0;
+}
+
 static int launch_route_group_small(const QW4ShLayer *layer, const QW4ShWork *work, uint32_t T, cudaStream_t stream) {
     const uint32_t E = layer->experts, k = layer->top_k;
     route_group_small_kernel<<<T, 512, (size_t)T * k * 4, stream>>>(E, k, layer->norm, work->logits, T, work->probs, work->ids,
@@ -1864,6 +1880,18 @@ extern "C" int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, 
     uint32_t *local = work->ids + own * k;                                  // behind this rank's own routes
     int rc;
     if ((rc = qw4sh_ep_trace_mark(3, stream))) return rc;                   // stage 2 was the all-gather
+    // the digits of the gathered rows depend on the rows alone: they are made on a stream of their own beside the lists
+    // (in one stream, as before, while stages are being timed)
+    cudaStream_t aux = stream;
+    cudaEvent_t *aux_ev = nullptr;
+    const bool beside = !qw4sh_ep_trace_on();
+    if (beside) {
+        if ((rc = aux_stream(&aux, &aux_ev))) return rc;
+        CU(cudaEventRecord(aux_ev[0], stream));
+        CU(cudaStreamWaitEvent(aux, aux_ev[0], 0));
+        if ((rc = qw4sh_quantize_rows_pitched(msg_all, pitch, T, H, work->xq, work->xneg, work->xsum, work->xscale, aux))) return rc;
+        CU(cudaEventRecord(aux_ev[1], aux));
+    }
     // Lists.  Small batches: the foreign ids are masked out and one CTA sorts the rest.  Large batches: the bitmap
     // dispatch sorts ALL pairs by global expert (a token meets an expert at most once), and this rank's experts are a
     // contiguous slice of that order: its offsets start at offsets[first_expert], its rows at row_to_pair[that].
@@ -1889,7 +1917,8 @@ extern "C" int qw4sh_ep_experts(const QW4ShLayer *layer, const QW4ShWork *work, 
     const int ctas = sm_count();
     const uint32_t *row_end = offsets + local_experts;                      // rows of this rank's experts: [*row_begin (or 0), *row_end)
     if ((rc = qw4sh_ep_trace_mark(4, stream))) return rc;
-    if ((rc = qw4sh_quantize_rows_pitched(msg_all, pitch, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
+    if (beside) CU(cudaStreamWaitEvent(stream, aux_ev[1], 0));
+    else if ((rc = qw4sh_quantize_rows_pitched(msg_all, pitch, T, H, work->xq, work->xneg, work->xsum, work->xscale, stream))) return rc;
     if ((rc = qw4sh_ep_trace_mark(5, stream))) return rc;
     if (tiles) {
         if ((rc = qw4sh_build_tile_groups(offsets, active, work->groups, work->n_groups, stream))) return rc;
