@@ -377,8 +377,9 @@ extern "C" void qw4sh_ep_destroy(QW4ShEp *ep) {
         cudaDeviceSynchronize();
         unsigned char zero = 0;
         cudaMemcpy(ep->handles + ep->rank, &zero, 1, cudaMemcpyHostToDevice);
-        tiny_all_gather(ep, 1);                                                  // nobody frees before everybody has finished its last step
+        tiny_all_gather(ep, 1);                                                  // nobody lets go before everybody has finished its last step
         peer_close(ep);
+        tiny_all_gather(ep, 1);                                                  // nobody frees what a peer still has mapped
     }
     if (ep->comm) g_nccl.comm_destroy(ep->comm);
     cudaFree(ep->msg_local); cudaFree(ep->pool);
@@ -413,6 +414,7 @@ extern "C" int qw4sh_ep_reserve(QW4ShEp *ep, uint32_t hidden, uint32_t k, size_t
             CU(cudaMemcpy(ep->handles + ep->rank, &zero, 1, cudaMemcpyHostToDevice));
             if (tiny_all_gather(ep, 1)) return -1;
             peer_close(ep);
+            if (tiny_all_gather(ep, 1)) return -1;                             // nobody frees what a peer still has mapped
         }
     }
     cudaFree(ep->pool);
