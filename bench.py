@@ -22,10 +22,13 @@ decode stays on one GPU: independent replicas, no collective on the data path, w
 
 The two sharded configurations are measured beside it at every N, N = 1 included, through the
 library's expert-parallel step (`qw4cu_moe_ep_forward_device`: experts in N contiguous blocks, one
-all-gather and one reduce-scatter per layer over NCCL), and reported under "sharded": c4 (64
+all-gather and one reduce-scatter per layer, by the library's push / pull kernels over NVLink peer memory
+or through NCCL), and reported under "sharded": c4 (64
 streams x 1 token through 48 Q4_K layers, Zipf expert popularity) and c3 (8 chunks of 1024 tokens
 through 48 layers, Q2_K routed + Q4_K shared), each with the parity of its first layer against the
-CPU oracle.  `--workload c3|c4` runs one of them alone; `--sharded ""` leaves them out.
+CPU oracle.  `--workload c3|c4` runs one of them alone; `--sharded ""` leaves them out.  At N = 1 the
+line also carries the single-token step ("c0"), the 1024-token prefill chunk ("c2") and the 1 + 3-row
+verify append through a 48-layer stack ("verify_stack").
 """
 from __future__ import annotations
 
@@ -448,6 +451,13 @@ def main():
             c0 = decode_line(side, api, rank, local_rank, world, control, hbm_peak, peak_kind)
             headline["c0"] = {"workload": c0["config"]["workload"], "us_per_layer": c0["ms_per_step"] * 1e3, "roofline": c0["roofline"],
                               "e2e": c0["e2e"], "timing": c0["timing"], "gpu_launches": c0["gpu_launches"]}
+            # ... and so does the 1024-token prefill chunk (two weight sets, three regions of at most five steps)
+            side = copy.copy(args)
+            side.workload, side.repeats, side.cpu_seconds, side.layers, side.steps = "c2", 3, 0.0, 2, min(args.steps, 5)
+            c2 = decode_line(side, api, rank, local_rank, world, control, hbm_peak, peak_kind)
+            headline["c2"] = {"workload": c2["config"]["workload"], "us_per_chunk": c2["ms_per_step"] * 1e3, "us_per_token": c2["value"],
+                              "roofline": c2["roofline"], "roofline_tensor": c2["roofline_tensor"], "timing": c2["timing"],
+                              "stage_us": c2["layer"]["stage_us_multi_kernel_path"], "gpu_launches": c2["gpu_launches"]}
     if args.profile:
         return
     sharded = {}
